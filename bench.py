@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Benchmark of the Zoph_RNN inference forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2]
+
+One "step" = one pass of the hot path over one synthetic minibatch of the workload (teacher-forced
+scoring: gather -> LSTM stack -> attention -> softmax log-probs; for c4: one batched beam decode).
+Prints ONE JSON line (rank 0).  `value` is whole-job throughput with inputs resident in HBM; `e2e` is the
+same metric through the host-buffer C-ABI call (H2D of the ids and D2H of the results inside the timed
+region).  `--impl reference` times the CPU restatement of the reference's math (the oracle) on the host
+cores on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from zoph_rnn_b200 import synth  # noqa: E402
+
+WORKLOADS = {
+    # BASELINE.json configs[0..4]
+    "c1": dict(desc="LM 1x100 V=10k B=8 T=35 fp32", kind="lm", L=1, H=100, Vs=0, Vt=10000, B=8, S=0, T=35,
+               att=0, feed=0, scale=0.08, dist="uniform", zipf=None),
+    "c2": dict(desc="seq2seq 4x1000 V=50k/50k B=128 S=50 T=50 global-dot attention + feed-input fp32", kind="s2s",
+               L=4, H=1000, Vs=50000, Vt=50000, B=128, S=(50, 50), T=(50, 50), att=2, feed=1, scale=0.1,
+               dist="uniform", zipf=1.1),
+    "c3": dict(desc="seq2seq 2x1000 V=40k/40k B=64 S~U[10,80] T=60 local-p D=10 + feed-input fp32", kind="s2s",
+               L=2, H=1000, Vs=40000, Vt=40000, B=64, S=(10, 80), T=(60, 60), att=1, feed=1, scale=0.1,
+               dist="uniform", zipf=1.1),
+    "c4": dict(desc="beam decode 2x1000 V=50k global-dot attention beam 12, 64 sentences S~U[10,50]", kind="decode",
+               L=2, H=1000, Vs=50000, Vt=50000, B=64, S=(10, 50), T=None, att=2, feed=1, scale=0.1,
+               dist="uniform", zipf=1.1, beam=12, max_ratio=2.0, min_ratio=0.5, longest_sent=100),
+    "c5": dict(desc="LM 2x2048 V=200k B=256 T=64", kind="lm", L=2, H=2048, Vs=0, Vt=200000, B=256, S=0, T=64,
+               att=0, feed=0, scale=0.02, dist="normal", zipf=1.05),
+}
+
+
+def make_cfg(w):
+    return synth.make_cfg(w["L"], w["H"], w["Vs"], w["Vt"], lm=int(w["kind"] == "lm"), attention=w["att"],
+                          feed_input=w["feed"], D=10)
+
+
+def make_inputs(w, seed, B=None):
+    B = B or w["B"]
+    if w["kind"] == "lm":
+        tin, tout = synth.make_lm_batch(w["Vt"], B, w["T"], seed=seed, zipf_s=w["zipf"])
+        return dict(src=None, tin=tin, tout=tout, tokens=int((tout != -1).sum()))
+    if w["kind"] == "s2s":
+        src, tin, tout = synth.make_s2s_batch(w["Vs"], w["Vt"], B, w["S"][0], w["S"][1], w["T"][0], w["T"][1],
+                                              seed=seed, zipf_s=w["zipf"])
+        return dict(src=src, tin=tin, tout=tout, tokens=int((tout != -1).sum()))
+    srcs = synth.make_decode_sources(w["Vs"], B, w["S"][0], w["S"][1], seed=seed, zipf_s=w["zipf"])
+    return dict(srcs=srcs)
+
+
+def sample_clocks_start(path):
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+    try:
+        f = open(path, "w")
+        return subprocess.Popen(["nvidia-smi", "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "200"],
+                                stdout=f, stderr=subprocess.DEVNULL), f
+    except OSError:
+        return None, None
+
+
+def sample_clocks_stop(proc, f, path, gpu_index):
+    out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
+    if proc is None:
+        return out
+    proc.terminate()
+    try:
+        proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+        proc.kill()
+    f.close()
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in open(path):
+        p = [x.strip() for x in line.split(",")]
+        if len(p) < 9 or not p[0].isdigit() or int(p[0]) != gpu_index:
+            continue
+        try:
+            sm.append(float(p[1])); mx.append(float(p[2]))
+        except ValueError:
+            continue
+        for nm, v in zip(names, p[5:9]):
+            if v.lower().startswith("active"):
+                reasons.add(nm)
+    if sm:
+        out = dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+    return out
+
+
+def run_reference(args, w, rank):
+    """CPU arm: the oracle (a port of the reference's kernel math; the reference itself cannot be built
+    for this machine) on a bounded sample of the workload, all host threads."""
+    if rank != 0:
+        return
+    from oracle import oracle_lib as ol
+    ol.build()
+    cfg = make_cfg(w)
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    om = ol.OracleModel(cfg, weights)
+    ol.set_acc_float(True)  # float accumulation = the reference's SGEMM arithmetic
+    cores = ol.num_threads()
+    if w["kind"] == "decode":
+        Bs = 1
+        inp = make_inputs(w, 1234, B=Bs)
+        sample = f"{Bs} of {w['B']} sentences, full beam {w['beam']}"
+
+        def step():
+            ids, ln, sc = om.beam_decode(inp["srcs"], w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
+            return int(np.maximum(ln[:, 0] - 1, 0).sum())
+    else:
+        Bs = max(1, min(w["B"], 8 if w["H"] >= 1000 else w["B"]))
+        inp = make_inputs(w, 1234, B=Bs)
+        Tn = inp["tin"].shape[0]
+        if w["H"] >= 2048:  # c5: bound the sample further
+            Tn = 4
+        sample = f"{Bs} of {w['B']} sentences x {Tn} of {inp['tin'].shape[0]} target steps, full model"
+
+        def step():
+            om.score_batch(inp["src"], inp["tin"][:Tn], inp["tout"][:Tn])
+            return int((inp["tout"][:Tn] != -1).sum())
+    for _ in range(min(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    toks = 0
+    for _ in range(args.steps):
+        toks += step()
+    dt = time.perf_counter() - t0
+    val = toks / dt
+    unit = "tokens/s"
+    line = dict(impl="reference", metric=metric_name(w), value=val, unit=unit, n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1e3 * dt / args.steps, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload + ": " + w["desc"]),
+                cpu_baseline=dict(value=val, unit=unit, cores=cores, kind="port", sample=sample),
+                e2e=dict(value=val, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def metric_name(w):
+    return "beam-decode tokens/sec" if w["kind"] == "decode" else "scored tokens/sec"
+
+
+def cpu_baseline(w):
+    """Bounded CPU sample (rank 0, N=1 only), reported next to the GPU number."""
+    from oracle import oracle_lib as ol
+    ol.build()
+    cfg = make_cfg(w)
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    om = ol.OracleModel(cfg, weights)
+    ol.set_acc_float(True)
+    if w["kind"] == "decode":
+        inp = make_inputs(w, 1234, B=1)
+        t0 = time.perf_counter()
+        ids, ln, sc = om.beam_decode(inp["srcs"], w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
+        dt = time.perf_counter() - t0
+        toks = int(np.maximum(ln[:, 0] - 1, 0).sum())
+        sample = f"1 of {w['B']} sentences, full beam {w['beam']}"
+    else:
+        Bs = max(1, min(w["B"], 8 if w["H"] >= 1000 else w["B"]))
+        inp = make_inputs(w, 1234, B=Bs)
+        Tn = 4 if w["H"] >= 2048 else inp["tin"].shape[0]
+        t0 = time.perf_counter()
+        om.score_batch(inp["src"], inp["tin"][:Tn], inp["tout"][:Tn])
+        dt = time.perf_counter() - t0
+        toks = int((inp["tout"][:Tn] != -1).sum())
+        sample = f"{Bs} of {w['B']} sentences x {Tn} of {inp['tin'].shape[0]} target steps, full model, 1 pass"
+    ol.set_acc_float(False)
+    return dict(value=toks / dt, unit="tokens/s", cores=ol.num_threads(), kind="port", sample=sample)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from zoph_rnn_b200 import api
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    cfg = make_cfg(w)
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    model = api.neuralMT_model(cfg)
+    model.load_weights(weights)
+    del weights
+    # sentences are sharded by rank (weak scaling: every rank scores/decodes its own minibatch, no collective)
+    inp = make_inputs(w, 1234 + rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    if w["kind"] == "decode":
+        srcs = inp["srcs"]
+        lens = np.array([len(s) for s in srcs], dtype=np.int32)
+        S_max, n = int(lens.max()), len(srcs)
+        padded = np.full((S_max, n), -1, dtype=np.int32)
+        for i, s in enumerate(srcs):
+            padded[S_max - len(s):, i] = s
+        d_src = torch.as_tensor(padded).cuda()
+        Lmax = w["longest_sent"] + 4
+        d_ids = torch.empty(n * Lmax, dtype=torch.int32, device="cuda")
+        d_len = torch.empty(n, dtype=torch.int32, device="cuda")
+        d_sc = torch.empty(n, dtype=torch.float32, device="cuda")
+
+        def step_device():
+            model.decode_device(d_src, lens, S_max, w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0,
+                                w["longest_sent"], d_ids, d_len, d_sc)
+
+        def step_host():
+            ids, ln, sc = model.decode(srcs, w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
+            return int(np.maximum(ln[:, 0] - 1, 0).sum())
+        h2d = int(lens.sum()) * 4
+        d2h = n * (Lmax + 2) * 4
+        step_device()
+        torch.cuda.synchronize()
+        tokens_per_step = int(np.maximum(d_len.cpu().numpy() - 1, 0).sum())  # emitted 1-best tokens incl. <EOF>
+    else:
+        src, tin, tout = inp["src"], inp["tin"], inp["tout"]
+        T, B = tin.shape
+        S = src.shape[0] if src is not None else 0
+        d_src = torch.as_tensor(src).cuda() if src is not None else None
+        d_tin, d_tout = torch.as_tensor(tin).cuda(), torch.as_tensor(tout).cuda()
+        d_lp = torch.empty(T * B, dtype=torch.float32, device="cuda")
+        p_src = torch.as_tensor(src).pin_memory() if src is not None else None
+        p_tin, p_tout = torch.as_tensor(tin).pin_memory(), torch.as_tensor(tout).pin_memory()
+
+        def step_device():
+            model.get_error_device(d_src, S, d_tin, d_tout, T, B, d_lp)
+
+        def step_host():
+            model.get_error(p_src, p_tin, p_tout)
+            return inp["tokens"]
+        h2d = (S * B + 2 * T * B) * 4
+        d2h = T * B * 4
+        tokens_per_step = inp["tokens"]
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    barrier()
+    clk_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
+    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    proc, f = sample_clocks_start(clk_path)
+    api.lib().zrnn_kernel_timing(1)
+    api.reset_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_device()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = api.launch_count()
+    ktime = api.kernel_timing_report()
+    api.lib().zrnn_kernel_timing(0)
+    # end-to-end through the host-buffer entry point
+    step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sample_clocks_stop(proc, f, clk_path, torch.cuda.current_device())
+    if world > 1:
+        t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1]) / 1e3
+        tk = torch.tensor([tokens_per_step], dtype=torch.int64, device="cuda")
+        dist.all_reduce(tk, op=dist.ReduceOp.SUM)
+        tokens_all = int(tk[0])
+    else:
+        tokens_all = tokens_per_step
+    if rank == 0:
+        peaks = {}
+        pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak_src = "fallback"
+        if os.path.exists(pk_path):
+            peaks = json.load(open(pk_path))
+            peak_src = "measured"
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        ncols = n * w["beam"] if w["kind"] == "decode" else T * B
+        roof = roofline(w, cfg, ktime, hbm_peak, peak_src, ncols, args.steps)
+        line = dict(metric=metric_name(w), value=tokens_all * args.steps / (ms / 1e3), unit="tokens/s",
+                    n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms / args.steps,
+                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                    config=dict(workload=args.workload + ": " + w["desc"], sharding="sentences by rank, no collective",
+                                l2="weights and embeddings (>1 GB) exceed the 126 MB L2 every step"),
+                    clocks=clocks, gpu_launches=int(launches),
+                    e2e=dict(value=tokens_all * args.steps / e2e_s, unit="tokens/s", h2d_bytes_per_step=h2d,
+                             d2h_bytes_per_step=d2h),
+                    roofline=roof, kernels=ktime)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def roofline(w, cfg, ktime, hbm_peak, peak_src, softmax_cols, steps):
+    """Roofline of the dominant kernel class, from CUDA-event durations recorded around every launch of that
+    class inside the timed region.  Algorithmic bytes per launch follow the per-unit figures of DESIGN.md."""
+    if not ktime:
+        return None
+    top = max(ktime, key=lambda k: ktime[k]["ms"])
+    H, B = cfg["H"], w["B"] * (w.get("beam", 1) if w["kind"] == "decode" else 1)
+    n = ktime[top]["launches"]
+    avg_s = ktime[top]["ms"] / 1e3 / max(n, 1)
+    if top == "lstm_cell":
+        # weights once per step (8 HxH matrices; 12 on target layer 0 with feed-input) + biases + x,h,c in / h,c out
+        L = cfg["num_layers"]
+        mats = 8.0
+        if cfg["feed_input"] and not cfg["lm"]:
+            mats = (8.0 * (2 * L - 1) + 12.0) / (2 * L) if w["kind"] != "decode" else (8.0 * (L - 1) + 12.0) / L
+        alg = (mats * H * H + 4 * H + 5.0 * H * B) * 4
+        unit_note = f"avg {mats:.2f} HxH fp32 matrices + 5 HxB activations per launch"
+    elif top == "softmax_gemm":
+        N = softmax_cols
+        alg = (cfg["V_tgt"] * H + H * N + 2 * N) * 4
+        unit_note = "D once + h columns + 2 floats per column"
+    else:
+        alg = None
+        unit_note = "no algorithmic-bytes model for this class"
+    out = dict(kernel=top, bound="hbm", unit="GB/s", peak=hbm_peak, peak_source=peak_src, launches=n,
+               avg_launch_us=avg_s * 1e6, traffic=None, note=unit_note)
+    if alg:
+        out["achieved"] = alg / avg_s / 1e9
+        out["frac"] = out["achieved"] / hbm_peak
+        out["algorithmic_bytes_per_launch"] = alg
+    return out
+
+
+if __name__ == "__main__":
+    main()

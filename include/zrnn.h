@@ -1,0 +1,212 @@
+/*
+ * zrnn.h - C ABI of the B200-native inference forward path for Zoph_RNN models
+ * (embedding column gather -> stacked LSTM step -> attention -> vocabulary softmax, for
+ * teacher-forced scoring and beam decoding).
+ *
+ * The reference exposes this path only as C++ template classes inside one translation unit;
+ * each entry point below names the reference member it stands in for (paths are relative to
+ * the reference project).  Conventions:
+ *   - every function returns a zrnn_status; nothing exits the process; zrnn_last_error() gives
+ *     the message of the last failure on the calling thread;
+ *   - matrices are column-major exactly as in the reference (IDX2C(i,j,ld)=j*ld+i,
+ *     src/BZ_CUDA_UTIL.h:26): activations H x B (one column per sentence), embeddings H x V,
+ *     softmax weights V x H; token ids are int32, time-major idx[b + t*B], -1 = padding;
+ *   - pointers named d_* are device pointers on the current CUDA device, pointers named h_* (or
+ *     unprefixed in the model-level calls) are host pointers; `stream` is a cudaStream_t passed
+ *     as void* (NULL = the legacy default stream);
+ *   - handles own their device memory and free it in *_destroy; a handle is not thread-safe,
+ *     distinct handles may be used from distinct host threads;
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails with
+ *     ZRNN_E_CUDA.
+ */
+#ifndef ZRNN_H
+#define ZRNN_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  ZRNN_OK = 0,
+  ZRNN_E_ARG = 1,     /* bad shape, null pointer, unsupported combination */
+  ZRNN_E_CUDA = 2,    /* CUDA runtime error or no device */
+  ZRNN_E_NCCL = 3,    /* reserved for the collective layer */
+  ZRNN_E_TIMEOUT = 4, /* a bounded device-side wait gave up */
+  ZRNN_E_IO = 5,      /* weight file missing, truncated or malformed */
+  ZRNN_E_STATE = 6    /* call order violated (e.g. forward before load) */
+} zrnn_status;
+
+typedef enum { ZRNN_F32 = 0, ZRNN_BF16 = 1 } zrnn_dtype;
+typedef enum { ZRNN_ATT_NONE = 0, ZRNN_ATT_LOCAL_P = 1, ZRNN_ATT_GLOBAL_DOT = 2 } zrnn_attention_type;
+
+const char* zrnn_status_string(int status);
+const char* zrnn_last_error(void);
+/* library version, and the compute capability the kernels were built for (100 = sm_100a) */
+int zrnn_version(void);
+int zrnn_built_for_sm(void);
+/* number of kernels this library has launched on the calling thread since the last reset */
+long long zrnn_launch_count(void);
+void zrnn_reset_launch_count(void);
+/* Optional per-class kernel timing for the benchmark's roofline report (no reference counterpart; the
+ * reference only has wall-clock Timer blocks, src/memory_util.h:83-124).  While on, the library records a CUDA
+ * event pair around every launch group of each class on the launching stream (at most 16384 pairs per thread).
+ * Classes: 0 embedding gather, 1 LSTM cell, 2 attention, 3 softmax GEMM, 4 softmax reduce / top-k, 5 beam step,
+ * 6 state reorder.  zrnn_kernel_timing_read waits for the recorded events. */
+int zrnn_kernel_timing(int on);
+int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total_ms);
+
+/* ------------------------------------------------------------------------------------------
+ * Input preparation.  Replaces vocab_to_01 / vocab_to_nonM1 (src/custom_kernels.h:9-32), called
+ * from Input_To_Hidden_Layer::prep_GPU_vocab_indices (src/Input_To_Hidden_Layer.hpp:1178-1225):
+ * ids with -1 padding -> (id or 0, mask 0/1).
+ * ---------------------------------------------------------------------------------------- */
+int zrnn_prep_vocab_indices(const int* d_ids_raw, int n, int* d_ids_nonm1, int* d_mask01, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * LSTM layers.  zrnn_lstm_layer stands for both Input_To_Hidden_Layer (layer 0: embedding
+ * gather + LSTM, src/Input_To_Hidden_Layer.h:146-203) and Hidden_To_Hidden_Layer (layers >= 1,
+ * src/Hidden_To_Hidden_Layer.h:138-177).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zrnn_lstm_layer zrnn_lstm_layer;
+
+/* Input_To_Hidden_Layer::init_Input_To_Hidden_Layer (src/Input_To_Hidden_Layer.hpp:171) and
+ * init_feed_input (:235).  V = input vocabulary size. */
+int zrnn_ih_create(int H, int V, int feed_input, int dtype, zrnn_lstm_layer** out);
+/* Hidden_To_Hidden_Layer::init_Hidden_To_Hidden_Layer (src/Hidden_To_Hidden_Layer.hpp:125). */
+int zrnn_hh_create(int H, int dtype, zrnn_lstm_layer** out);
+/* load_weights (src/Input_To_Hidden_Layer.hpp:1104-1171, src/Hidden_To_Hidden_Layer.hpp:704-742).
+ * h_tensors: host pointers to column-major fp32 matrices in the reference's file order:
+ *   W_hi b_i W_hf b_f W_hc b_c W_ho b_o [W (H x V), ih only] M_i M_f M_o M_c [Q_i Q_f Q_o Q_c, feed-input only]
+ * n_tensors must equal 12 (+1 for ih) (+4 with feed-input). */
+int zrnn_lstm_load(zrnn_lstm_layer* layer, const float* const* h_tensors, int n_tensors);
+/* sparse_lookup_kernel (src/custom_kernels.h:340-348): d_x[:,n] = W[:,ids[n]], n_cols columns. */
+int zrnn_ih_gather(zrnn_lstm_layer* layer, const int* d_ids_nonm1, int n_cols, float* d_x, void* stream);
+/* LSTM_IH_Node::forward_prop_GPU (src/LSTM.hpp:76-421): gather + one LSTM step for B columns.
+ * d_htild_prev non-NULL adds the feed-input term Q*htild (the reference skips it at node index 0,
+ * src/LSTM.hpp:154,175).  h/c buffers are H x B; outputs may not alias inputs. */
+int zrnn_ih_forward(zrnn_lstm_layer* layer, const int* d_ids_nonm1, const int* d_mask01, const float* d_h_prev,
+                    const float* d_c_prev, const float* d_htild_prev, int B, float* d_h_out, float* d_c_out,
+                    void* stream);
+/* LSTM_HH_Node::forward_prop_GPU (src/LSTM_HH.hpp:103-333): one LSTM step on the h of the layer below. */
+int zrnn_hh_forward(zrnn_lstm_layer* layer, const float* d_h_below, const int* d_mask01, const float* d_h_prev,
+                    const float* d_c_prev, int B, float* d_h_out, float* d_c_out, void* stream);
+int zrnn_lstm_destroy(zrnn_lstm_layer* layer);
+
+/* ------------------------------------------------------------------------------------------
+ * Attention (src/attention_layer.h:28-33, ctor src/attention_layer.hpp:3-173, decoder init
+ * :176-259).  ZRNN_ATT_LOCAL_P is the reference's local-p model with the "general" score;
+ * ZRNN_ATT_GLOBAL_DOT is an extension (dot score over every valid source position) that shares
+ * the reference's tanh combiner and feed-input wiring.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zrnn_attention zrnn_attention;
+int zrnn_att_create(int H, int D, int att_type, int dtype, zrnn_attention** out);
+/* attention_layer::load_weights (src/attention_layer.hpp:485-491): W_a W_p v_p(1xH) output_bias W_c_p1 W_c_p2 */
+int zrnn_att_load(zrnn_attention* att, const float* const* h_tensors, int n_tensors);
+/* prep_minibatch_info (src/attention_layer.hpp:580-583) plus the d_total_hs_mat pointer table:
+ * d_hs = S_max slots of H x B_src (slot t = top-layer source state at encoder step t); d_len/d_offset =
+ * the reference's batch_info halves [S_b...][S_max-S_b...] (src/fileHelper.h:480-496).  Each source
+ * column serves cols_per_sentence consecutive target columns (1 for scoring, beam for decoding, which
+ * replaces the per-beam replication of src/model.hpp:2434-2445). */
+int zrnn_att_set_source(zrnn_attention* att, const float* d_hs, int S_max, int B_src, const int* d_len,
+                        const int* d_offset, int cols_per_sentence);
+/* attention_node::forward_prop (src/attention_node.hpp:73-394).  d_align_out (optional): local-p
+ * (2D+1) x B weights stored [j*B+b]; global S_max x B stored [s*B+b] in source-position order. */
+int zrnn_att_forward(zrnn_attention* att, const float* d_h_t, const int* d_mask01, int B, float* d_htild_out,
+                     float* d_align_out, void* stream);
+int zrnn_att_destroy(zrnn_attention* att);
+
+/* ------------------------------------------------------------------------------------------
+ * Softmax loss layer (base_loss_layer virtuals src/base_loss.h:17-63, softmax_layer
+ * src/softmax.hpp).  A layer may hold only rows [shard_lo, shard_hi) of D for vocabulary sharding.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zrnn_softmax zrnn_softmax;
+int zrnn_softmax_create(int V, int H, int dtype, int shard_lo, int shard_hi, zrnn_softmax** out);
+/* softmax_layer::load_weights (src/softmax.hpp:337-355): D (V x H), b_d (V x 1), full matrices. */
+int zrnn_softmax_load(zrnn_softmax* sm, const float* h_D, const float* h_b_d);
+/* get_perplexity_GPU + compute_loss_GPU (src/softmax.hpp:636-692,867-900): natural-log probability of
+ * d_targets[n] for each of N columns of d_h (H x N); 0 where d_mask01[n]==0.  The V x N logits are never
+ * materialised.  Unsharded layers only. */
+int zrnn_softmax_score(zrnn_softmax* sm, const float* d_h, const int* d_targets, const int* d_mask01, int N,
+                       float* d_logp_out, void* stream);
+/* Sharded scoring, step 1: per-column (max, sum exp(z-max), target logit or 0) over this shard's rows. */
+int zrnn_softmax_partials(zrnn_softmax* sm, const float* d_h, const int* d_targets, int N, float* d_max,
+                          float* d_sum, float* d_tgt, void* stream);
+/* Sharded scoring, step 2: combine G shards' partials (each array G x N, shard-major) into log-probs. */
+int zrnn_softmax_combine(const float* d_max, const float* d_sum, const float* d_tgt, int G, int N,
+                         const int* d_mask01, float* d_logp_out, void* stream);
+/* get_distribution_GPU (src/softmax.hpp:514-632) fused with the per-column pre-selection of
+ * decoder::expand_hypothesis_without_fsa (src/decoder.h:1197-1219): the k largest log-probabilities of
+ * each of N columns, sorted descending (k <= 16), their word ids, and the log-probability of <EOF> (id 1). */
+int zrnn_softmax_topk(zrnn_softmax* sm, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
+                      float* d_logp_eos, void* stream);
+int zrnn_softmax_destroy(zrnn_softmax* sm);
+
+/* ------------------------------------------------------------------------------------------
+ * Whole model (neuralMT_model, src/model.h / src/model.hpp).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zrnn_model zrnn_model;
+typedef struct {
+  int num_layers;   /* -N */
+  int H;            /* -H, LSTM_size */
+  int V_src;        /* -v (ignored for language models) */
+  int V_tgt;        /* -V */
+  int lm;           /* 1 = sequence model (-s): no source side */
+  int attention;    /* zrnn_attention_type; the reference's --attention-model means ZRNN_ATT_LOCAL_P */
+  int feed_input;   /* --feed-input */
+  int D;            /* --attention-width */
+  int dtype;        /* zrnn_dtype of the arithmetic */
+} zrnn_model_config;
+
+/* neuralMT_model::initModel / initModel_decoding (src/model.hpp:3-435, 476-698). */
+int zrnn_model_create(const zrnn_model_config* cfg, zrnn_model** out);
+/* Tensor list in weight-file order (src/model.hpp:2172-2241). name buffer >= 32 bytes. */
+int zrnn_model_num_tensors(zrnn_model* m);
+int zrnn_model_tensor_info(zrnn_model* m, int i, char* name, int* rows, int* cols);
+/* Copy one fp32 column-major host tensor into the model; zrnn_model_finalize after the last one. */
+int zrnn_model_set_tensor(zrnn_model* m, int i, const float* h_data);
+int zrnn_model_finalize(zrnn_model* m);
+/* neuralMT_model::load_weights (src/model.hpp:2172-2241) with read_matrix_GPU (src/Eigen_Util.h:83-112):
+ * parse a text model.nn.  The architecture comes from the file's 9-int header
+ * (src/add_model_info.h:7-9); att_type_override picks local-p or global-dot when the header says the model
+ * has attention (the reference has no flag for the type), D is --attention-width. */
+int zrnn_model_load_file(const char* path, int att_type_override, int D, int dtype, zrnn_model** out);
+int zrnn_model_get_config(zrnn_model* m, zrnn_model_config* cfg);
+
+/* neuralMT_model::getError / get_perplexity (src/model.hpp:1463-1802, 2281-2355) for one minibatch.
+ * Host buffers: src_ids [S_max*B] reversed + left-padded with -1 (NULL for a language model),
+ * tgt_in / tgt_out [T*B] right-padded with -1.  logp_out [T*B] receives the natural-log probability of
+ * every target token (0 under padding); *total_logp their sum (what the reference prints per minibatch). */
+int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tgt_in, const int* tgt_out, int T,
+                     int B, float* logp_out, double* total_logp);
+/* Same, with ids already on the device and results left on the device; asynchronous on `stream`. */
+int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in,
+                            const int* d_tgt_out, int T, int B, float* d_logp_out, void* stream);
+/* Copies the top-layer vectors the last scoring call handed to the softmax (H x (T*B)) into d_out, which holds
+ * capacity_cols columns; *n_cols receives the number of columns available.  For layer-level checks. */
+int zrnn_model_copy_top_states(zrnn_model* m, float* d_out, int capacity_cols, int* n_cols, void* stream);
+/* The model's softmax layer (owned by the model). */
+zrnn_softmax* zrnn_model_softmax(zrnn_model* m);
+
+/* Beam decoding of n_sent sentences at once: ensemble_factory::decode_file_batch
+ * (src/ensemble_factory.hpp:583-765) with forward_prop_source / forward_prop_target /
+ * swap_decoding_states (src/model.hpp:2367-2452, 2573-2726) and decoder::expand_hypothesis_without_fsa,
+ * finish_current_hypotheses, output_k_best_hypotheses (src/decoder.h:1157-1315, 672-688, 1386-1463).
+ * The reference decodes one sentence at a time; results equal n_sent independent decodes.
+ * src_ids: concatenated reversed source ids; src_len[n_sent]; beam (-b) is capped at floor(sqrt(V_tgt));
+ * k_best (-k n-best count); min_ratio/max_ratio (--dec-ratio); penalty (--penalty); longest_sent (-L).
+ * Outputs (host): out_ids [n_sent*k_best*(longest_sent+4)] padded with -1, out_len [n_sent*k_best]
+ * (0 = fewer than k hypotheses passed the length filter), out_score [n_sent*k_best]. */
+int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best,
+                           float min_ratio, float max_ratio, float penalty, int longest_sent, int* out_ids,
+                           int* out_len, float* out_score);
+/* Same with the source ids already resident on the device (padded [S_max*n_sent], reversed, left-padded
+ * with -1) and results left in device buffers; asynchronous on `stream`. */
+int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src_ids_padded, const int* h_src_len, int S_max,
+                                  int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                                  int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score, void* stream);
+int zrnn_model_destroy(zrnn_model* m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZRNN_H */

@@ -1,0 +1,142 @@
+"""GPU parity tests of the whole path (scoring and beam decoding) through the C ABI."""
+import numpy as np
+import pytest
+
+from tests import helpers
+from zoph_rnn_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from zoph_rnn_b200 import api as a
+    return a
+
+
+def build_model(api, cfg, w):
+    m = api.neuralMT_model(cfg)
+    assert [(r, c) for _, r, c in m.tensor_spec()] == [(r, c) for _, r, c in synth.tensor_spec(cfg)]
+    m.load_weights(w)
+    return m
+
+
+@pytest.mark.parametrize("name", helpers.golden_cases())
+def test_scoring_matches_golden(api, name):
+    cfg, w, g = helpers.load_golden(name)
+    m = build_model(api, cfg, w)
+    src = g["src"] if "src" in g else None
+    lp, tot = m.get_error(src, g["tgt_in"], g["tgt_out"])
+    helpers.assert_logp_close(lp, g["logp"])
+    assert abs(tot - g["logp"].sum()) < 1e-4 * max(1.0, abs(g["logp"].sum()))
+    assert np.all(lp[g["tgt_out"] == -1] == 0.0)
+
+
+@pytest.mark.parametrize("name", [n for n in helpers.golden_cases() if n.startswith("s2s")])
+def test_decoding_matches_golden(api, name):
+    from tests.golden.make_golden import DECODE as d
+    cfg, w, g = helpers.load_golden(name)
+    m = build_model(api, cfg, w)
+    srcs = helpers.split_sources(g["dec_src"], g["dec_len"])
+    ids, ln, sc = m.decode(srcs, d["beam"], d["k_best"], d["min_ratio"], d["max_ratio"], d["penalty"], d["longest_sent"])
+    assert np.array_equal(ln, g["dec_hyp_len"])
+    assert np.array_equal(ids, g["dec_ids"])
+    np.testing.assert_allclose(sc, g["dec_score"], rtol=1e-5, atol=1e-4)
+
+
+def test_config1_lm_full_size(api, oracle):
+    """BASELINE config 1 at full size: LM, 1 layer, H=100, V=10,000, B=8, T=35, U[-0.08,0.08] weights."""
+    cfg = synth.make_cfg(1, 100, 0, 10000, lm=1)
+    w = synth.make_weights(cfg, seed=1234, scale=0.08)
+    tin, tout = synth.make_lm_batch(10000, 8, 35, seed=1234)
+    want = oracle.OracleModel(cfg, w).score_batch(None, tin, tout)
+    m = build_model(api, cfg, w)
+    lp, tot = m.get_error(None, tin, tout)
+    helpers.assert_logp_close(lp, want)
+    ppl_got = np.exp(-lp.sum() / lp.size)
+    ppl_want = np.exp(-want.sum() / want.size)
+    assert abs(ppl_got - ppl_want) / ppl_want < 1e-5
+
+
+@pytest.mark.parametrize("att,L,H,B,S,T", [(2, 4, 96, 16, (12, 12), (11, 11)),     # config 2 shape, scaled down
+                                            (1, 2, 128, 16, (5, 40), (4, 20)),      # config 3 shape: ragged + masks
+                                            (2, 2, 200, 130, (3, 9), (3, 9))])      # more columns than one tile
+def test_scoring_matches_oracle_scaled_configs(api, oracle, att, L, H, B, S, T):
+    cfg = synth.make_cfg(L, H, 500, 700, attention=att, feed_input=1, D=10)
+    w = synth.make_weights(cfg, seed=42, scale=0.1)
+    src, tin, tout = synth.make_s2s_batch(500, 700, B, S[0], S[1], T[0], T[1], seed=7)
+    om = oracle.OracleModel(cfg, w)
+    want, want_top = om.score_batch(src, tin, tout, want_top=True)
+    m = build_model(api, cfg, w)
+    lp, _ = m.get_error(src, tin, tout)
+    helpers.assert_logp_close(lp, want)
+    top = m.last_top_states().cpu().numpy().reshape(tin.shape[0], B, H)
+    np.testing.assert_allclose(top, want_top, rtol=1e-4, atol=2e-6)
+
+
+def test_scoring_batch_independence(api):
+    """Size-independent property: a sentence scores the same alone and inside a padded batch."""
+    cfg = synth.make_cfg(2, 64, 300, 400, attention=1, feed_input=1, D=4)
+    w = synth.make_weights(cfg, seed=8, scale=0.15)
+    m = build_model(api, cfg, w)
+    src, tin, tout = synth.make_s2s_batch(300, 400, 9, 3, 20, 3, 15, seed=3)
+    full, _ = m.get_error(src, tin, tout)
+    for b in (0, 4, 8):
+        s = src[:, b][src[:, b] != -1].reshape(-1, 1)
+        n = int((tin[:, b] != -1).sum())
+        one, _ = m.get_error(np.ascontiguousarray(s), np.ascontiguousarray(tin[:n, b:b + 1]),
+                             np.ascontiguousarray(tout[:n, b:b + 1]))
+        helpers.assert_logp_close(one[:, 0], full[:n, b], rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("att,feed", [(0, 0), (1, 1), (2, 1), (2, 0)])
+def test_decoding_matches_oracle(api, oracle, att, feed):
+    cfg = synth.make_cfg(2, 48, 200, 300, attention=att, feed_input=feed, D=3)
+    w = synth.make_weights(cfg, seed=21 + att, scale=0.25)
+    srcs = synth.make_decode_sources(200, 9, 3, 14, seed=4)
+    om = oracle.OracleModel(cfg, w)
+    kw = dict(beam=6, k_best=2, min_ratio=0.5, max_ratio=2.0, penalty=0.1, longest_sent=40)
+    ids, ln, sc = om.beam_decode(srcs, **kw)
+    m = build_model(api, cfg, w)
+    gi, gl, gs = m.decode(srcs, **kw)
+    agree = (gl == ln) & np.all(gi == ids, axis=2)
+    assert agree.mean() >= 0.995, f"hypothesis agreement {agree.mean():.3f}"
+    np.testing.assert_allclose(gs[agree], sc[agree], rtol=1e-5, atol=1e-4)
+    # batched decoding equals one-sentence-at-a-time decoding
+    one_i, one_l, one_s = m.decode(srcs[3:4], **kw)
+    assert np.array_equal(one_i[0], gi[3]) and np.array_equal(one_l[0], gl[3])
+
+
+def test_model_file_round_trip(api, tmp_path):
+    from zoph_rnn_b200.model_file import write_model_nn
+    cfg = synth.make_cfg(2, 24, 40, 50, attention=1, feed_input=1, D=3)
+    w = synth.make_weights(cfg, seed=2, scale=0.3)
+    p = tmp_path / "model.nn"
+    write_model_nn(p, cfg, w)
+    m_file = api.neuralMT_model.from_file(p, att_type=1, D=3)
+    assert m_file.cfg["num_layers"] == 2 and m_file.cfg["H"] == 24 and m_file.cfg["feed_input"] == 1
+    m_mem = build_model(api, cfg, w)
+    src, tin, tout = synth.make_s2s_batch(40, 50, 5, 3, 9, 3, 8, seed=1)
+    a, _ = m_file.get_error(src, tin, tout)
+    b, _ = m_mem.get_error(src, tin, tout)
+    np.testing.assert_allclose(a, b, rtol=1e-6, atol=1e-6)
+    # truncated file -> IO status, not a crash
+    text = p.read_text()
+    (tmp_path / "cut.nn").write_text(text[: len(text) // 2])
+    with pytest.raises(api.ZrnnError) as e:
+        api.neuralMT_model.from_file(tmp_path / "cut.nn", att_type=1, D=3)
+    assert e.value.status == 5
+
+
+def test_error_statuses(api):
+    import torch
+    cfg = synth.make_cfg(1, 8, 10, 12)
+    m = api.neuralMT_model(cfg)
+    with pytest.raises(api.ZrnnError) as e:  # weights never loaded
+        m.get_error(np.zeros((2, 1), np.int32), np.zeros((2, 1), np.int32), np.zeros((2, 1), np.int32))
+    assert e.value.status == 6
+    sm = api.softmax_layer(10, 4, shard_lo=0, shard_hi=5)
+    with pytest.raises(api.ZrnnError):
+        sm.compute_loss(torch.zeros(4, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"), None)

@@ -1,0 +1,315 @@
+"""Host-side mirror of the reference's layer API over the C ABI (include/zrnn.h).
+
+Class and method names follow the reference's C++ classes (Input_To_Hidden_Layer,
+Hidden_To_Hidden_Layer, attention_layer, softmax_layer, neuralMT_model) so that tests read like
+calls into the reference.  PyTorch is used only to own device memory and streams; every bit of
+arithmetic happens inside libzrnn.so.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import ATT_GLOBAL_DOT, ATT_LOCAL_P, ATT_NONE, BF16, F32, ModelConfig, ZrnnError, check, lib  # noqa: F401
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
+
+
+def _host_list(tensors):
+    keep = [_f32(t) for t in tensors]
+    arr = (_lib.c_float_p * len(keep))(*[k.ctypes.data_as(_lib.c_float_p) for k in keep])
+    return keep, arr
+
+
+def _dev_i32(a):
+    return torch.as_tensor(np.ascontiguousarray(a, dtype=np.int32)).cuda()
+
+
+def prep_vocab_indices(ids_raw):
+    """ids with -1 padding (int32 CUDA tensor) -> (ids with -1 replaced by 0, 0/1 mask).
+    Mirrors Input_To_Hidden_Layer::prep_GPU_vocab_indices (src/Input_To_Hidden_Layer.hpp:1178-1225)."""
+    ids = torch.empty_like(ids_raw)
+    mask = torch.empty_like(ids_raw)
+    check(lib().zrnn_prep_vocab_indices(_ptr(ids_raw), ids_raw.numel(), _ptr(ids), _ptr(mask), _stream()))
+    return ids, mask
+
+
+class _LstmLayer:
+    def __init__(self):
+        self._h = ctypes.c_void_p()
+
+    def load_weights(self, tensors):
+        """tensors in the reference's file order (see zrnn_lstm_load in include/zrnn.h)."""
+        keep, arr = _host_list(tensors)
+        check(lib().zrnn_lstm_load(self._h, arr, len(keep)))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().zrnn_lstm_destroy(self._h)
+            self._h = None
+
+
+class Input_To_Hidden_Layer(_LstmLayer):
+    """Layer 0: embedding gather + LSTM (src/Input_To_Hidden_Layer.h:146-203)."""
+
+    def __init__(self, LSTM_size, input_vocab_size, feed_input=False, dtype=F32):
+        super().__init__()
+        self.H, self.V, self.feed_input = LSTM_size, input_vocab_size, bool(feed_input)
+        check(lib().zrnn_ih_create(LSTM_size, input_vocab_size, int(feed_input), dtype, ctypes.byref(self._h)))
+
+    def gather(self, ids_nonm1):
+        x = torch.empty(ids_nonm1.numel() * self.H, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_ih_gather(self._h, _ptr(ids_nonm1), ids_nonm1.numel(), _ptr(x), _stream()))
+        return x
+
+    def forward_prop(self, ids_nonm1, mask01, h_prev, c_prev, h_tild_prev=None):
+        """LSTM_IH_Node::forward_prop (src/LSTM.hpp:76-421). Tensors are flat column-major H x B."""
+        B = ids_nonm1.numel()
+        h, c = torch.empty_like(h_prev), torch.empty_like(c_prev)
+        check(lib().zrnn_ih_forward(self._h, _ptr(ids_nonm1), _ptr(mask01), _ptr(h_prev), _ptr(c_prev),
+                                    _ptr(h_tild_prev), B, _ptr(h), _ptr(c), _stream()))
+        return h, c
+
+
+class Hidden_To_Hidden_Layer(_LstmLayer):
+    """Layers >= 1 (src/Hidden_To_Hidden_Layer.h:138-177)."""
+
+    def __init__(self, LSTM_size, dtype=F32):
+        super().__init__()
+        self.H = LSTM_size
+        check(lib().zrnn_hh_create(LSTM_size, dtype, ctypes.byref(self._h)))
+
+    def forward_prop(self, h_below, mask01, h_prev, c_prev):
+        """LSTM_HH_Node::forward_prop (src/LSTM_HH.hpp:103-333)."""
+        B = h_prev.numel() // self.H
+        h, c = torch.empty_like(h_prev), torch.empty_like(c_prev)
+        check(lib().zrnn_hh_forward(self._h, _ptr(h_below), _ptr(mask01), _ptr(h_prev), _ptr(c_prev), B, _ptr(h),
+                                    _ptr(c), _stream()))
+        return h, c
+
+
+class attention_layer:
+    """src/attention_layer.h:28-33; att_type ATT_LOCAL_P (the reference's model) or ATT_GLOBAL_DOT."""
+
+    def __init__(self, LSTM_size, D, att_type=ATT_LOCAL_P, dtype=F32):
+        self._h = ctypes.c_void_p()
+        self.H, self.D, self.att_type = LSTM_size, D, att_type
+        self._keep = None
+        check(lib().zrnn_att_create(LSTM_size, D, att_type, dtype, ctypes.byref(self._h)))
+
+    def load_weights(self, tensors):
+        keep, arr = _host_list(tensors)
+        check(lib().zrnn_att_load(self._h, arr, len(keep)))
+
+    def prep_minibatch_info(self, hs, S_max, B_src, lens, offsets, cols_per_sentence=1):
+        """attention_layer::prep_minibatch_info (src/attention_layer.hpp:580-583) + the source-state table."""
+        self._keep = (hs, lens, offsets)
+        self.S_max = S_max
+        check(lib().zrnn_att_set_source(self._h, _ptr(hs), S_max, B_src, _ptr(lens), _ptr(offsets), cols_per_sentence))
+
+    def forward_prop(self, h_t, mask01, want_alignments=False):
+        """attention_node::forward_prop (src/attention_node.hpp:73-394)."""
+        B = h_t.numel() // self.H
+        out = torch.empty_like(h_t)
+        al = None
+        if want_alignments:
+            n = (2 * self.D + 1) * B if self.att_type == ATT_LOCAL_P else self.S_max * B
+            al = torch.zeros(n, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_att_forward(self._h, _ptr(h_t), _ptr(mask01), B, _ptr(out), _ptr(al), _stream()))
+        return (out, al) if want_alignments else out
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().zrnn_att_destroy(self._h)
+            self._h = None
+
+
+class softmax_layer:
+    """src/softmax.hpp; rows [shard_lo, shard_hi) of D for vocabulary sharding."""
+
+    def __init__(self, output_vocab_size, LSTM_size, dtype=F32, shard_lo=0, shard_hi=None, _borrowed=None):
+        self.V, self.H = output_vocab_size, LSTM_size
+        self.lo, self.hi = shard_lo, output_vocab_size if shard_hi is None else shard_hi
+        self._owned = _borrowed is None
+        if _borrowed is not None:
+            self._h = ctypes.c_void_p(_borrowed)
+        else:
+            self._h = ctypes.c_void_p()
+            check(lib().zrnn_softmax_create(self.V, self.H, dtype, self.lo, self.hi, ctypes.byref(self._h)))
+
+    def load_weights(self, D, b_d):
+        D, b_d = _f32(D), _f32(b_d)
+        check(lib().zrnn_softmax_load(self._h, D.ctypes.data_as(_lib.c_float_p), b_d.ctypes.data_as(_lib.c_float_p)))
+
+    def compute_loss(self, h, targets, mask01):
+        """get_perplexity_GPU + compute_loss_GPU (src/softmax.hpp:636-692, 867-900): ln p(target) per column."""
+        N = targets.numel()
+        out = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_softmax_score(self._h, _ptr(h), _ptr(targets), _ptr(mask01), N, _ptr(out), _stream()))
+        return out
+
+    def partials(self, h, targets):
+        N = targets.numel()
+        mx, sm, tg = (torch.empty(N, dtype=torch.float32, device="cuda") for _ in range(3))
+        check(lib().zrnn_softmax_partials(self._h, _ptr(h), _ptr(targets), N, _ptr(mx), _ptr(sm), _ptr(tg), _stream()))
+        return mx, sm, tg
+
+    @staticmethod
+    def combine(mx, sm, tg, mask01):
+        """mx/sm/tg: [G, N] shard-major CUDA tensors."""
+        G, N = mx.shape
+        out = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_softmax_combine(_ptr(mx.contiguous()), _ptr(sm.contiguous()), _ptr(tg.contiguous()), G, N,
+                                         _ptr(mask01), _ptr(out), _stream()))
+        return out
+
+    def topk(self, h, k):
+        """get_distribution_GPU + per-column pre-selection (src/softmax.hpp:514-632, src/decoder.h:1197-1219)."""
+        N = h.numel() // self.H
+        val = torch.empty(N * k, dtype=torch.float32, device="cuda")
+        idx = torch.empty(N * k, dtype=torch.int32, device="cuda")
+        eos = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_softmax_topk(self._h, _ptr(h), N, k, _ptr(val), _ptr(idx), _ptr(eos), _stream()))
+        return val.view(N, k), idx.view(N, k), eos
+
+    def __del__(self):
+        if getattr(self, "_h", None) and self._owned:
+            lib().zrnn_softmax_destroy(self._h)
+        self._h = None
+
+
+class neuralMT_model:
+    """src/model.h: the whole model.  cfg is a dict with keys num_layers, H, V_src, V_tgt, lm, attention,
+    feed_input, D (zoph_rnn_b200.synth.make_cfg builds one)."""
+
+    def __init__(self, cfg=None, dtype=F32, _handle=None):
+        self._h = ctypes.c_void_p()
+        if _handle is not None:
+            self._h = _handle
+            c = ModelConfig()
+            check(lib().zrnn_model_get_config(self._h, ctypes.byref(c)))
+            self.cfg = {k: getattr(c, k) for k, _ in ModelConfig._fields_}
+        else:
+            c = ModelConfig(cfg["num_layers"], cfg["H"], cfg["V_src"], cfg["V_tgt"], cfg["lm"], cfg["attention"],
+                            cfg["feed_input"], cfg["D"], dtype)
+            check(lib().zrnn_model_create(ctypes.byref(c), ctypes.byref(self._h)))
+            self.cfg = dict(cfg, dtype=dtype)
+
+    @classmethod
+    def from_file(cls, path, att_type=ATT_LOCAL_P, D=10, dtype=F32):
+        """neuralMT_model::load_weights (src/model.hpp:2172-2241) from a text model.nn."""
+        h = ctypes.c_void_p()
+        check(lib().zrnn_model_load_file(str(path).encode(), att_type, D, dtype, ctypes.byref(h)))
+        return cls(_handle=h)
+
+    def tensor_spec(self):
+        out = []
+        for i in range(lib().zrnn_model_num_tensors(self._h)):
+            name = ctypes.create_string_buffer(32)
+            r, c = ctypes.c_int(), ctypes.c_int()
+            check(lib().zrnn_model_tensor_info(self._h, i, name, ctypes.byref(r), ctypes.byref(c)))
+            out.append((name.value.decode(), r.value, c.value))
+        return out
+
+    def load_weights(self, tensors):
+        for i, t in enumerate(tensors):
+            t = _f32(t)
+            check(lib().zrnn_model_set_tensor(self._h, i, t.ctypes.data_as(_lib.c_float_p)))
+        check(lib().zrnn_model_finalize(self._h))
+
+    def get_error(self, src_ids, tgt_in, tgt_out):
+        """neuralMT_model::getError (src/model.hpp:1463-1802) through the host-buffer entry point.
+        Arrays are [S,B] / [T,B] int32 (NumPy, or pinned CPU torch tensors).  Returns (logp [T,B], total)."""
+        def host(a):
+            if a is None:
+                return None, None
+            if isinstance(a, torch.Tensor):
+                return a, ctypes.c_void_p(a.data_ptr())
+            a = np.ascontiguousarray(a, dtype=np.int32)
+            return a, ctypes.c_void_p(a.ctypes.data)
+        ks, ps = host(src_ids)
+        ki, pi = host(tgt_in)
+        ko, po = host(tgt_out)
+        T, B = ki.shape
+        S = ks.shape[0] if ks is not None else 0
+        out = np.empty((T, B), dtype=np.float32)
+        tot = ctypes.c_double()
+        check(lib().zrnn_score_batch(self._h, ps, S, pi, po, T, B, ctypes.c_void_p(out.ctypes.data), ctypes.byref(tot)))
+        return out, tot.value
+
+    def get_error_device(self, d_src, S, d_tin, d_tout, T, B, d_logp):
+        """Device-resident variant: int32 CUDA tensors in, float32 CUDA tensor out, asynchronous."""
+        check(lib().zrnn_score_batch_device(self._h, _ptr(d_src), S, _ptr(d_tin), _ptr(d_tout), T, B, _ptr(d_logp),
+                                            _stream()))
+
+    def last_top_states(self):
+        """The vectors the last scoring call handed to the softmax, flat column-major H x (T*B)."""
+        n = ctypes.c_int()
+        check(lib().zrnn_model_copy_top_states(self._h, None, 0, ctypes.byref(n), None))
+        out = torch.empty(n.value * self.cfg["H"], dtype=torch.float32, device="cuda")
+        check(lib().zrnn_model_copy_top_states(self._h, _ptr(out), n.value, ctypes.byref(n), _stream()))
+        return out
+
+    def softmax(self):
+        return softmax_layer(self.cfg["V_tgt"], self.cfg["H"], _borrowed=lib().zrnn_model_softmax(self._h))
+
+    def decode(self, sources, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100):
+        """ensemble_factory::decode_file_batch (src/ensemble_factory.hpp:583-765) for a list of reversed source
+        id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k])."""
+        n = len(sources)
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]), dtype=np.int32)
+        lens = np.ascontiguousarray([len(s) for s in sources], dtype=np.int32)
+        Lmax = longest_sent + 4
+        ids = np.empty((n, k_best, Lmax), dtype=np.int32)
+        ln = np.empty((n, k_best), dtype=np.int32)
+        sc = np.empty((n, k_best), dtype=np.float32)
+        check(lib().zrnn_beam_decode_batch(self._h, ctypes.c_void_p(flat.ctypes.data), ctypes.c_void_p(lens.ctypes.data),
+                                           n, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
+                                           ctypes.c_void_p(ids.ctypes.data), ctypes.c_void_p(ln.ctypes.data),
+                                           ctypes.c_void_p(sc.ctypes.data)))
+        return ids, ln, sc
+
+    def decode_device(self, d_src_padded, src_lens, S_max, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
+                      d_ids, d_len, d_score):
+        lens = np.ascontiguousarray(src_lens, dtype=np.int32)
+        check(lib().zrnn_beam_decode_batch_device(self._h, _ptr(d_src_padded), ctypes.c_void_p(lens.ctypes.data), S_max,
+                                                  len(lens), beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
+                                                  _ptr(d_ids), _ptr(d_len), _ptr(d_score), _stream()))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().zrnn_model_destroy(self._h)
+            self._h = None
+
+
+def launch_count():
+    return lib().zrnn_launch_count()
+
+
+def reset_launch_count():
+    lib().zrnn_reset_launch_count()
+
+
+KERNEL_CLASSES = ("gather", "lstm_cell", "attention", "softmax_gemm", "softmax_reduce", "beam_step", "state_reorder")
+
+
+def kernel_timing_report():
+    """{class name: {"launches": n, "ms": total}} for the classes that ran while zrnn_kernel_timing was on."""
+    out = {}
+    for i, name in enumerate(KERNEL_CLASSES):
+        n, ms = ctypes.c_longlong(), ctypes.c_double()
+        check(lib().zrnn_kernel_timing_read(i, ctypes.byref(n), ctypes.byref(ms)))
+        if n.value:
+            out[name] = dict(launches=n.value, ms=ms.value)
+    return out

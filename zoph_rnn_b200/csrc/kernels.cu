@@ -1,0 +1,774 @@
+// Hand-written sm_100a kernels (exact-fp32 SIMT family) for the Zoph_RNN inference forward path.
+// Layouts follow the reference: column-major, activations H x B, ids time-major int32.
+#include "kernels.cuh"
+
+#include <cfloat>
+#include <cstdint>
+
+namespace zrnn {
+
+static thread_local long long g_launches = 0;
+void count_launch(int n) { g_launches += n; }
+long long launch_count_value() { return g_launches; }
+void launch_count_reset() { g_launches = 0; }
+
+// ------------------------------------------------------------------------------------------
+// small helpers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// block-wide sum; result valid in every thread. `red` needs 32 floats.
+__device__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// ------------------------------------------------------------------------------------------
+// ids: -1 padding -> (id or 0, mask)
+// ------------------------------------------------------------------------------------------
+__global__ void prep_ids_kernel(const int* __restrict__ raw, int n, int* __restrict__ nonm1, int* __restrict__ mask01) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int v = raw[i];
+    if (nonm1) nonm1[i] = (v == -1) ? 0 : v;
+    if (mask01) mask01[i] = (v == -1) ? 0 : 1;
+  }
+}
+cudaError_t launch_prep_ids(const int* raw, int n, int* nonm1, int* mask01, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const int blocks = (n + 255) / 256;
+  prep_ids_kernel<<<blocks > 1184 ? 1184 : blocks, 256, 0, st>>>(raw, n, nonm1, mask01);
+  count_launch();
+  return cudaGetLastError();
+}
+
+__global__ void fill_int_kernel(int* p, int v, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
+}
+__global__ void src_len_kernel(const int* __restrict__ mask01, int T, int B, int* len, int* offset) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int n = 0;
+  for (int t = 0; t < T; ++t) n += mask01[(size_t)t * B + b];
+  len[b] = n;
+  offset[b] = T - n;
+}
+cudaError_t launch_src_len(const int* mask01, int T, int B, int* len, int* offset, cudaStream_t st) {
+  if (B <= 0) return cudaSuccess;
+  src_len_kernel<<<(B + 127) / 128, 128, 0, st>>>(mask01, T, B, len, offset);
+  count_launch();
+  return cudaGetLastError();
+}
+__global__ void div_map_kernel(int* map, int n, int div) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) map[i] = i / div;
+}
+cudaError_t launch_div_map(int* map, int n, int div, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  div_map_kernel<<<(n + 127) / 128, 128, 0, st>>>(map, n, div);
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_fill_int(int* p, int v, size_t n, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  size_t blocks = (n + 255) / 256;
+  fill_int_kernel<<<(unsigned)(blocks > 1184 ? 1184 : blocks), 256, 0, st>>>(p, v, n);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// embedding column gather: x[:,n] = W[:,ids[n]] -- a bit copy, 16-byte vectorised when H % 4 == 0.
+// One CTA of 128 threads per 4 columns keeps every load/store a full 128-byte line.
+// ------------------------------------------------------------------------------------------
+__global__ void gather_columns_kernel(const float* __restrict__ W, int H, const int* __restrict__ ids, int n_cols,
+                                      float* __restrict__ x) {
+  const int vec = ((H & 3) == 0);
+  for (int col = blockIdx.x; col < n_cols; col += gridDim.x) {
+    int id = ids[col];
+    if (id < 0) id = 0;  // an invalid beam slot; its column is never consumed
+    const float* src = W + (size_t)id * H;
+    float* dst = x + (size_t)col * H;
+    if (vec) {
+      const float4* s4 = reinterpret_cast<const float4*>(src);
+      float4* d4 = reinterpret_cast<float4*>(dst);
+      for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) d4[i] = __ldg(s4 + i);
+    } else {
+      for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+  }
+}
+cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_cols, float* x, cudaStream_t st) {
+  if (n_cols <= 0) return cudaSuccess;
+  const int threads = H >= 512 ? 128 : 64;
+  gather_columns_kernel<<<n_cols > 148 * 16 ? 148 * 16 : n_cols, threads, 0, st>>>(W, H, ids, n_cols, x);
+  count_launch();
+  return cudaGetLastError();
+}
+
+__global__ void col_gather_kernel(ColGatherArgs a) {
+  const int arr = blockIdx.y;
+  const float* src = a.src[arr];
+  float* dst = a.dst[arr];
+  const int H = a.H;
+  for (int col = blockIdx.x; col < a.n_cols; col += gridDim.x) {
+    const int sc = a.map[col];
+    const float* s = src + (size_t)sc * H;
+    float* d = dst + (size_t)col * H;
+    if ((H & 3) == 0) {
+      for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x)
+        reinterpret_cast<float4*>(d)[i] = reinterpret_cast<const float4*>(s)[i];
+    } else {
+      for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = s[i];
+    }
+  }
+}
+cudaError_t launch_col_gather(const ColGatherArgs& a, cudaStream_t st) {
+  if (a.n_cols <= 0 || a.n_arrays <= 0) return cudaSuccess;
+  dim3 grid(a.n_cols > 1184 ? 1184 : a.n_cols, a.n_arrays);
+  col_gather_kernel<<<grid, 128, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// fused multi-source fp32 GEMM with LSTM / store / log-sum-exp epilogues
+// ------------------------------------------------------------------------------------------
+template <int GATES, int EPI, int TM, int TN>
+__global__ void __launch_bounds__(256) fused_gemm_kernel(const GemmArgs p) {
+  constexpr int BM = 16 * TM, BN = 16 * TN, BK = 16;
+  constexpr int TH = BM / GATES;  // rows of each gate block covered by this CTA
+  __shared__ __align__(16) float As[2][BK][BM + 4];
+  __shared__ __align__(16) float Bs[2][BK][BN + 4];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.x * TH;
+  const int n0 = blockIdx.y * BN;
+  const int M = p.M, N = p.N;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+  int ntiles = 0;
+  for (int s = 0; s < p.nsrc; ++s) ntiles += (p.src[s].K + BK - 1) / BK;
+
+  float ra[TM], rb[TN];
+  int fs = 0, fk0 = 0;  // fetch cursor: source index, k offset
+  auto fetch = [&]() {
+    const GemmSrc& S = p.src[fs];
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int e = tid + 256 * i;
+      const int m = e % BM, k = e / BM;
+      const int g = m / TH, row = m0 + (m % TH);
+      const int kk = fk0 + k;
+      ra[i] = (row < M && kk < S.K) ? __ldg(S.A[g] + (size_t)kk * S.lda + row) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < TN; ++i) {
+      const int e = tid + 256 * i;
+      const int k = e % BK, n = e / BK;
+      const int kk = fk0 + k, col = n0 + n;
+      rb[i] = (col < N && kk < S.K) ? S.B[(size_t)col * S.ldb + kk] : 0.f;
+    }
+    fk0 += BK;
+    if (fk0 >= S.K) { fk0 = 0; ++fs; }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int e = tid + 256 * i;
+      As[buf][e / BM][e % BM] = ra[i];
+    }
+#pragma unroll
+    for (int i = 0; i < TN; ++i) {
+      const int e = tid + 256 * i;
+      Bs[buf][e % BK][e / BK] = rb[i];
+    }
+  };
+
+  if (ntiles > 0) {
+    fetch();
+    stage(0);
+  }
+  __syncthreads();
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) fetch();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[buf][k][tx + 16 * i];
+#pragma unroll
+      for (int j4 = 0; j4 < TN / 4; ++j4) {
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][k][j4 * 64 + ty * 4]);
+        b[4 * j4 + 0] = v.x; b[4 * j4 + 1] = v.y; b[4 * j4 + 2] = v.z; b[4 * j4 + 3] = v.w;
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (t + 1 < ntiles) stage(buf ^ 1);
+    __syncthreads();
+  }
+
+  // ---------------- epilogues ----------------
+  if (EPI == EPI_STORE) {
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int r = tx + 16 * i;
+      const int g = r / TH, row = m0 + (r % TH);
+      if (row >= M) continue;
+      const float bv = p.bias[g] ? p.bias[g][row] : 0.f;
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int col = n0 + (j / 4) * 64 + ty * 4 + (j % 4);
+        if (col >= N) continue;
+        float v = acc[i][j] + bv;
+        if (p.act == 1 && (p.act_rows == 0 || row < p.act_rows)) v = tanhf(v);
+        if (p.mask) v *= (float)p.mask[col];
+        p.C[(size_t)col * p.ldc + (size_t)g * M + row] = v;
+      }
+    }
+  } else if (EPI == EPI_LSTM) {
+    constexpr int U = TM / 4;  // hidden units per thread
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int row = m0 + tx + 16 * u;
+      if (row >= M) continue;
+      const float b_i = p.bias[0][row], b_f = p.bias[1][row], b_g = p.bias[2][row], b_o = p.bias[3][row];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int col = n0 + (j / 4) * 64 + ty * 4 + (j % 4);
+        if (col >= N) continue;
+        const float gi = sigmoidf_acc(acc[0 * U + u][j] + b_i);
+        const float gf = sigmoidf_acc(acc[1 * U + u][j] + b_f);
+        const float gg = tanhf(acc[2 * U + u][j] + b_g);
+        const float go = sigmoidf_acc(acc[3 * U + u][j] + b_o);
+        const size_t idx = (size_t)col * M + row;
+        float c = gf * p.c_prev[idx] + gi * gg;
+        float h = go * tanhf(c);
+        if (p.mask) {
+          const float mk = (float)p.mask[col];
+          h *= mk;
+          c *= mk;
+        }
+        p.h_out[idx] = h;
+        p.c_out[idx] = c;
+        if (p.h_out2) p.h_out2[idx] = h;
+      }
+    }
+  } else {  // EPI_LSE
+    float (&z)[TM][TN] = acc;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int row = m0 + tx + 16 * i;
+      const float bv = (row < M && p.bias[0]) ? p.bias[0][row] : 0.f;
+#pragma unroll
+      for (int j = 0; j < TN; ++j) z[i][j] = (row < M) ? acc[i][j] + bv : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int col = n0 + (j / 4) * 64 + ty * 4 + (j % 4);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < TM; ++i) mx = fmaxf(mx, z[i][j]);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sm = 0.f;
+#pragma unroll
+      for (int i = 0; i < TM; ++i) sm += (z[i][j] == -INFINITY) ? 0.f : expf(z[i][j] - mx);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      if (col < N) {
+        if (tx == 0) {
+          p.part_max[(size_t)blockIdx.x * N + col] = mx;
+          p.part_sum[(size_t)blockIdx.x * N + col] = sm;
+        }
+        if (p.target) {
+          const int tg = p.target[col] - p.target_offset;
+#pragma unroll
+          for (int i = 0; i < TM; ++i)
+            if (m0 + tx + 16 * i == tg && tg >= 0 && tg < M) p.tgt_logit[col] = z[i][j];
+        }
+      }
+    }
+  }
+}
+
+int gemm_rows_per_tile(int gates, int tile) { return (tile ? 128 : 64) / gates; }
+
+template <int GATES, int EPI>
+static cudaError_t launch_fused_gemm_t(const GemmArgs& a, int tile, cudaStream_t st) {
+  const int TH = gemm_rows_per_tile(GATES, tile);
+  const int BN = tile ? 128 : 64;
+  dim3 grid((a.M + TH - 1) / TH, (a.N + BN - 1) / BN);
+  if (grid.x == 0 || grid.y == 0) return cudaSuccess;
+  if (tile) fused_gemm_kernel<GATES, EPI, 8, 8><<<grid, 256, 0, st>>>(a);
+  else fused_gemm_kernel<GATES, EPI, 4, 4><<<grid, 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, cudaStream_t st) {
+  if (gates == 4 && epi == EPI_LSTM) return launch_fused_gemm_t<4, EPI_LSTM>(a, tile, st);
+  if (gates == 4 && epi == EPI_STORE) return launch_fused_gemm_t<4, EPI_STORE>(a, tile, st);
+  if (gates == 1 && epi == EPI_STORE) return launch_fused_gemm_t<1, EPI_STORE>(a, tile, st);
+  if (gates == 1 && epi == EPI_LSE) return launch_fused_gemm_t<1, EPI_LSE>(a, tile, st);
+  return cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------------------------------
+// combine per-tile softmax partials: one thread per column
+// ------------------------------------------------------------------------------------------
+__global__ void lse_combine_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
+                                   const float* __restrict__ tgt, int n_parts, int n_tgt, int N,
+                                   const int* __restrict__ mask, float* __restrict__ logp) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  if (mask && mask[n] != 1) { logp[n] = 0.f; return; }
+  float mx = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, pm[(size_t)i * N + n]);
+  double sum = 0.0;
+  for (int i = 0; i < n_parts; ++i) {
+    const float m = pm[(size_t)i * N + n];
+    if (m != -INFINITY) sum += (double)ps[(size_t)i * N + n] * exp((double)m - (double)mx);
+  }
+  double tg = 0.0;
+  for (int i = 0; i < n_tgt; ++i) tg += (double)tgt[(size_t)i * N + n];
+  logp[n] = (float)((tg - (double)mx) - log(sum));
+}
+__global__ void lse_reduce_kernel(const float* __restrict__ pm, const float* __restrict__ ps, int n_parts, int N,
+                                  float* __restrict__ out_max, float* __restrict__ out_sum) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float mx = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, pm[(size_t)i * N + n]);
+  double sum = 0.0;
+  for (int i = 0; i < n_parts; ++i) {
+    const float m = pm[(size_t)i * N + n];
+    if (m != -INFINITY) sum += (double)ps[(size_t)i * N + n] * exp((double)m - (double)mx);
+  }
+  out_max[n] = mx;
+  out_sum[n] = (float)sum;
+}
+cudaError_t launch_lse_reduce(const float* pm, const float* ps, int n_parts, int N, float* out_max, float* out_sum,
+                              cudaStream_t st) {
+  if (N <= 0) return cudaSuccess;
+  lse_reduce_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, n_parts, N, out_max, out_sum);
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_lse_combine_shards(const float* pm, const float* ps, const float* tgt, int G, int N, const int* mask,
+                                      float* logp, cudaStream_t st) {
+  if (N <= 0) return cudaSuccess;
+  lse_combine_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, tgt, G, G, N, mask, logp);
+  count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tgt, int n_parts, int N, const int* mask,
+                               float* logp, cudaStream_t st) {
+  if (N <= 0) return cudaSuccess;
+  lse_combine_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, tgt, n_parts, 1, N, mask, logp);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// per-column top-k of log-softmax(z): one CTA per column
+// ------------------------------------------------------------------------------------------
+#define ZR_TOPK_MAX 16
+__global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict__ z, int V, int N, int k,
+                                                         float* __restrict__ val_out, int* __restrict__ idx_out,
+                                                         float* __restrict__ logp_eos) {
+  __shared__ float lv[ZR_TOPK_MAX][256];
+  __shared__ int li[ZR_TOPK_MAX][256];
+  __shared__ float red_m[8], red_s[8];
+  __shared__ float win_v[8];
+  __shared__ int win_t[8];
+  __shared__ float s_M, s_logS;
+  __shared__ int s_winner;
+  const int col = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const float* zc = z + (size_t)col * V;
+  int cnt = 0;
+  float thr = -INFINITY;  // value of the last kept element once the list is full
+  float m = -INFINITY, s = 0.f;
+  for (int i = tid; i < V; i += 256) {
+    const float v = zc[i];
+    if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
+    else s += expf(v - m);
+    if (cnt < k || v > thr) {
+      int pos = (cnt < k) ? cnt : k - 1;
+      while (pos > 0 && lv[pos - 1][tid] < v) {
+        lv[pos][tid] = lv[pos - 1][tid];
+        li[pos][tid] = li[pos - 1][tid];
+        --pos;
+      }
+      lv[pos][tid] = v;
+      li[pos][tid] = i;
+      if (cnt < k) ++cnt;
+      if (cnt == k) thr = lv[k - 1][tid];
+    }
+  }
+  // block (max, sum)
+  float wm = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+  float ws = (m == -INFINITY) ? 0.f : s * expf(m - wm);
+  ws = warp_sum(ws);
+  if (lane == 0) { red_m[w] = wm; red_s[w] = ws; }
+  __syncthreads();
+  if (tid == 0) {
+    float M = -INFINITY;
+    for (int i = 0; i < 8; ++i) M = fmaxf(M, red_m[i]);
+    double S = 0.0;
+    for (int i = 0; i < 8; ++i)
+      if (red_m[i] != -INFINITY) S += (double)red_s[i] * exp((double)red_m[i] - (double)M);
+    s_M = M;
+    s_logS = (float)log(S);
+    if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - M) - s_logS : -INFINITY;
+  }
+  __syncthreads();
+  int head = 0;
+  for (int r = 0; r < k; ++r) {
+    float v = (head < cnt) ? lv[head][tid] : -INFINITY;
+    int id = (head < cnt) ? li[head][tid] : 0x7fffffff;
+    int t = tid;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, id, o);
+      const int ot = __shfl_xor_sync(0xffffffffu, t, o);
+      if (ov > v || (ov == v && oi < id)) { v = ov; id = oi; t = ot; }
+    }
+    if (lane == 0) { win_v[w] = v; win_t[w] = t; red_m[w] = __int_as_float(id); }
+    __syncthreads();
+    if (tid == 0) {
+      float bv = win_v[0];
+      int bt = win_t[0], bi = __float_as_int(red_m[0]);
+      for (int i = 1; i < 8; ++i) {
+        const int oi = __float_as_int(red_m[i]);
+        if (win_v[i] > bv || (win_v[i] == bv && oi < bi)) { bv = win_v[i]; bt = win_t[i]; bi = oi; }
+      }
+      s_winner = bt;
+      const bool ok = bv != -INFINITY;
+      val_out[(size_t)col * k + r] = ok ? (bv - s_M) - s_logS : -INFINITY;
+      idx_out[(size_t)col * k + r] = ok ? bi : -1;
+    }
+    __syncthreads();
+    if (tid == s_winner) ++head;
+    __syncthreads();
+  }
+}
+cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
+                             cudaStream_t st) {
+  if (N <= 0) return cudaSuccess;
+  if (k < 1 || k > ZR_TOPK_MAX) return cudaErrorInvalidValue;
+  topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, val_out, idx_out, logp_eos);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// attention: window / global scores, masked softmax, context.  One CTA per target column.
+// ------------------------------------------------------------------------------------------
+#define ZR_ATT_MAXW 64
+__global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
+  __shared__ float red[32];
+  __shared__ float s_al[ZR_ATT_MAXW];
+  __shared__ int s_slot[ZR_ATT_MAXW];
+  __shared__ float s_p;
+  __shared__ int s_lo, s_hi;
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
+  const int H = a.H, Wn = 2 * a.D + 1, sb = b / a.cols_per_sent;
+  float* c = a.c_t + (size_t)b * H;
+  if (a.mask && a.mask[b] != 1) {  // create_indicies_kernel: every window slot is -1 -> context 0
+    for (int i = tid; i < H; i += blockDim.x) c[i] = 0.f;
+    if (a.align_out)
+      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    return;
+  }
+  float part = 0.f;
+  for (int i = tid; i < H; i += blockDim.x) part += a.v_p[i] * a.tanh1[(size_t)b * a.ld_tq + i];
+  const float tot = block_sum(part, red);
+  const int len = a.len[sb], off = a.offset[sb];
+  if (tid == 0) {
+    const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)tot)));
+    const float pt = len * sg;
+    const int ip = (int)pt;
+    s_p = pt;
+    s_lo = (0 > ip - a.D) ? 0 : (ip - a.D);
+    s_hi = ((len - 1) < ip + a.D) ? (len - 1) : (ip + a.D);
+  }
+  __syncthreads();
+  const int lo = s_lo, hi = s_hi;
+  const float* q = a.q + (size_t)b * a.ld_tq;
+  for (int j = w; j < Wn; j += nw) {
+    const int pos = lo + j;
+    int slot = -1;
+    float sc = 0.f;
+    if (pos <= hi) {
+      slot = len - 1 - pos + off;
+      const float* hv = a.hs + ((size_t)slot * a.B_src + sb) * H;
+      for (int i = lane; i < H; i += 32) sc += hv[i] * q[i];
+      sc = warp_sum(sc);
+    }
+    if (lane == 0) { s_al[j] = sc; s_slot[j] = slot; }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float sum = 0.f, mx = 0.f;  // the reference starts the max at 0
+    for (int j = 0; j < Wn; ++j)
+      if (s_slot[j] != -1 && s_al[j] > mx) mx = s_al[j];
+    for (int j = 0; j < Wn; ++j) {
+      if (s_slot[j] != -1) { s_al[j] = expf(s_al[j] - mx); sum += s_al[j]; }
+      else s_al[j] = 0.f;
+    }
+    const float sigma_sq = (float)((a.D * a.D) / 4.0);
+    for (int j = 0; j < Wn; ++j) {
+      if (s_slot[j] != -1) {
+        const float d = s_p - (float)(lo + j);
+        const float gs = expf((-1.f * d * d) / (2.f * sigma_sq));
+        if (sum != 0.f) s_al[j] = (s_al[j] / sum) * gs;
+      }
+    }
+  }
+  __syncthreads();
+  if (a.align_out)
+    for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+  for (int i = tid; i < H; i += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < Wn; ++j) {
+      const int slot = s_slot[j];
+      if (slot != -1) acc += s_al[j] * a.hs[((size_t)slot * a.B_src + sb) * H + i];
+    }
+    c[i] = acc;
+  }
+}
+cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st) {
+  if (a.B <= 0) return cudaSuccess;
+  if (2 * a.D + 1 > ZR_ATT_MAXW) return cudaErrorInvalidValue;
+  att_local_kernel<<<a.B, 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+__global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
+  extern __shared__ float s_sc[];  // S_max scores
+  __shared__ float red[32];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
+  const int H = a.H, sb = b / a.cols_per_sent;
+  float* c = a.c_t + (size_t)b * H;
+  if (a.align_out)
+    for (int s = tid; s < a.S_max; s += blockDim.x) a.align_out[(size_t)s * a.B + b] = 0.f;
+  if (a.mask && a.mask[b] != 1) {
+    for (int i = tid; i < H; i += blockDim.x) c[i] = 0.f;
+    return;
+  }
+  const int len = a.len[sb], off = a.offset[sb];
+  const float* h = a.h_t + (size_t)b * H;
+  for (int pos = w; pos < len; pos += nw) {
+    const float* hv = a.hs + ((size_t)(len - 1 - pos + off) * a.B_src + sb) * H;
+    float sc = 0.f;
+    for (int i = lane; i < H; i += 32) sc += hv[i] * h[i];
+    sc = warp_sum(sc);
+    if (lane == 0) s_sc[pos] = sc;
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int pos = tid; pos < len; pos += blockDim.x) mx = fmaxf(mx, s_sc[pos]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[w] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < nw; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float part = 0.f;
+  for (int pos = tid; pos < len; pos += blockDim.x) {
+    const float e = expf(s_sc[pos] - mx);
+    s_sc[pos] = e;
+    part += e;
+  }
+  const float sum = block_sum(part, red);
+  const float inv = 1.0f / sum;
+  if (a.align_out)
+    for (int pos = tid; pos < len; pos += blockDim.x) a.align_out[(size_t)pos * a.B + b] = s_sc[pos] * inv;
+  for (int i = tid; i < H; i += blockDim.x) {
+    float acc = 0.f;
+    for (int pos = 0; pos < len; ++pos)
+      acc += (s_sc[pos] * inv) * a.hs[((size_t)(len - 1 - pos + off) * a.B_src + sb) * H + i];
+    c[i] = acc;
+  }
+}
+cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
+  if (a.B <= 0) return cudaSuccess;
+  const size_t smem = sizeof(float) * (size_t)(a.S_max > 0 ? a.S_max : 1);
+  if (smem > 40 * 1024) return cudaErrorInvalidValue;
+  att_global_kernel<<<a.B, 256, smem, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// beam bookkeeping, one CTA per sentence
+// ------------------------------------------------------------------------------------------
+__global__ void beam_init_kernel(const BeamArgs a) {
+  const int s = blockIdx.x, tid = threadIdx.x;
+  const size_t rowbase = (size_t)s * a.beam * a.Lmax;
+  for (int i = tid; i < a.beam * a.Lmax; i += blockDim.x) { a.top_sent[rowbase + i] = 0; a.top_tmp[rowbase + i] = 0; }
+  for (int i = tid; i < a.beam; i += blockDim.x) {
+    a.scores[s * a.beam + i] = 0.f;
+    a.cur_ids[s * a.beam + i] = 0;
+    a.col_map[s * a.beam + i] = s * a.beam + i;
+  }
+  for (int i = tid; i < a.k_best * a.Lmax; i += blockDim.x) a.best_ids[(size_t)s * a.k_best * a.Lmax + i] = -1;
+  for (int i = tid; i < a.k_best; i += blockDim.x) { a.best_len[s * a.k_best + i] = 0; a.best_score[s * a.k_best + i] = 0.f; }
+}
+cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st) {
+  if (a.n_sent <= 0) return cudaSuccess;
+  beam_init_kernel<<<a.n_sent, 128, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// insert (prefix of `row` up to position last_pos, then <EOF>) with `score` into the sentence's k-best list
+__device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int last_pos, float score) {
+  const int len = last_pos + 2;
+  const float ratio = ((float)len) / (float)a.src_len[s];
+  if (!(ratio > a.min_ratio)) return;
+  int* ids = a.best_ids + (size_t)s * a.k_best * a.Lmax;
+  int* lens = a.best_len + s * a.k_best;
+  float* sc = a.best_score + s * a.k_best;
+  int pos = 0;
+  while (pos < a.k_best && lens[pos] != 0 && !(score > sc[pos])) ++pos;
+  if (pos >= a.k_best) return;
+  for (int j = a.k_best - 1; j > pos; --j) {
+    if (lens[j - 1] == 0) continue;
+    for (int i = 0; i < a.Lmax; ++i) ids[(size_t)j * a.Lmax + i] = ids[(size_t)(j - 1) * a.Lmax + i];
+    lens[j] = lens[j - 1];
+    sc[j] = sc[j - 1];
+  }
+  for (int i = 0; i < a.Lmax; ++i) ids[(size_t)pos * a.Lmax + i] = (i <= last_pos) ? row[i] : (i == last_pos + 1 ? 1 : -1);
+  lens[pos] = len;
+  sc[pos] = score;
+}
+
+__global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
+  __shared__ float cv[256];
+  __shared__ int cp[256];  // payload: beam column * 32 + candidate rank
+  __shared__ int n_chg[16], n_cur[16];
+  __shared__ float n_sc[16];
+  const int s = blockIdx.x, tid = threadIdx.x, beam = a.beam, kc = a.k_cand, t = a.step;
+  const int base = s * beam;
+  const int max_steps = a.max_steps[s];
+  int* rows = a.top_sent + (size_t)base * a.Lmax;
+  int* tmp = a.top_tmp + (size_t)base * a.Lmax;
+  if (t > max_steps) {
+    if (tid < beam) a.col_map[base + tid] = base + tid;
+    return;
+  }
+  if (t == max_steps) {  // finish_current_hypotheses
+    if (tid == 0)
+      for (int i = 0; i < beam; ++i) {
+        if (a.cur_ids[base + i] == -1) continue;
+        const float sc = a.scores[base + i] + (a.logp_eos[base + i] + a.penalty);
+        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, sc);
+      }
+    if (tid < beam) a.col_map[base + tid] = base + tid;
+    return;
+  }
+  // ---- expand
+  int ncols = (t == 0) ? 1 : beam;
+  {
+    int v = 0;
+    while (v < ncols && a.cur_ids[base + v] != -1) ++v;
+    ncols = v;
+  }
+  {
+    const int i = tid / kc, r = tid % kc;
+    float v = -INFINITY;
+    if (i < ncols) {
+      const float lp = a.cand_val[(size_t)(base + i) * kc + r];
+      if (a.cand_idx[(size_t)(base + i) * kc + r] >= 0 && lp != -INFINITY) v = lp + a.scores[base + i];
+    }
+    cv[tid] = v;
+    cp[tid] = i * 32 + r;
+  }
+  __syncthreads();
+  for (int ksz = 2; ksz <= 256; ksz <<= 1)
+    for (int j = ksz >> 1; j > 0; j >>= 1) {
+      const int ixj = tid ^ j;
+      if (ixj > tid) {
+        const bool desc = ((tid & ksz) == 0);
+        const float x = cv[tid], y = cv[ixj];
+        if (desc ? (x < y) : (x > y)) {
+          cv[tid] = y; cv[ixj] = x;
+          const int tp = cp[tid]; cp[tid] = cp[ixj]; cp[ixj] = tp;
+        }
+      }
+      __syncthreads();
+    }
+  if (tid == 0) {
+    int filled = 0, pidx = 0;
+    while (filled < beam) {
+      if (pidx >= 256 || cv[pidx] == -INFINITY) {
+        n_cur[filled] = -1; n_chg[filled] = 0; n_sc[filled] = 0.f;
+        ++filled;
+        continue;
+      }
+      const float val = cv[pidx];
+      const int i = cp[pidx] / 32, r = cp[pidx] % 32;
+      ++pidx;
+      const int wd = a.cand_idx[(size_t)(base + i) * kc + r];
+      if (wd == 0) continue;  // <START> is never extended
+      if (wd == 1) {          // <EOF>: finished hypothesis, does not take a slot
+        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, val + a.penalty);
+      } else {
+        n_cur[filled] = wd; n_chg[filled] = i; n_sc[filled] = val + a.penalty;
+        ++filled;
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < beam * a.Lmax; e += blockDim.x) {
+    const int f = e / a.Lmax, i = e % a.Lmax;
+    int v = rows[(size_t)n_chg[f] * a.Lmax + i];
+    if (i == t + 1) v = (n_cur[f] == -1) ? 0 : n_cur[f];
+    tmp[e] = v;
+  }
+  __syncthreads();
+  for (int e = tid; e < beam * a.Lmax; e += blockDim.x) rows[e] = tmp[e];
+  if (tid < beam) {
+    a.cur_ids[base + tid] = n_cur[tid];
+    a.col_map[base + tid] = base + n_chg[tid];
+    a.scores[base + tid] = n_sc[tid];
+  }
+}
+cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st) {
+  if (a.n_sent <= 0) return cudaSuccess;
+  if (a.beam < 1 || a.beam > 15 || a.k_cand > 16 || a.beam * a.k_cand > 256) return cudaErrorInvalidValue;
+  beam_step_kernel<<<a.n_sent, 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace zrnn

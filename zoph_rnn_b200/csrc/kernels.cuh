@@ -1,0 +1,135 @@
+// Launch interfaces of the hand-written sm_100a kernels for the Zoph_RNN inference forward path.
+// Everything is column-major fp32 as in the reference (activations H x B, one column per sentence).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace zrnn {
+
+// thread-local launch counter (each launcher increments it once per kernel launch)
+void count_launch(int n = 1);
+
+// ---- input preparation (replaces vocab_to_01 / vocab_to_nonM1, src/custom_kernels.h:9-32)
+cudaError_t launch_prep_ids(const int* raw, int n, int* nonm1, int* mask01, cudaStream_t st);
+
+// ---- embedding column gather (replaces sparse_lookup_kernel, src/custom_kernels.h:340-348)
+cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_cols, float* x, cudaStream_t st);
+
+// ---- generic column gather over several H x ncols arrays at once: dst[a][:,c] = src[a][:,map[c]]
+// (replaces the per-column cudaMemcpy loops of swap_states_decoding / transfer_decoding_states_GPU,
+// src/Input_To_Hidden_Layer.hpp:1231-1260, src/model.hpp:2715-2719)
+struct ColGatherArgs {
+  enum { MAX_ARRAYS = 24 };
+  const float* src[MAX_ARRAYS];
+  float* dst[MAX_ARRAYS];
+  int n_arrays;
+  int H, n_cols;
+  const int* map;  // n_cols source column indices
+};
+cudaError_t launch_col_gather(const ColGatherArgs& a, cudaStream_t st);
+
+// ---- fused multi-source GEMM:  acc[M x N] = sum_s A_s[M x K_s] * B_s[K_s x N]
+// With gates == 4 the M rows are 4 interleaved H-row blocks (one per LSTM gate i,f,g,o) and each
+// thread owns all four gates of its hidden units, so the cell update happens in registers and the
+// gate pre-activations never reach HBM.
+struct GemmSrc {
+  const float* A[4];  // one base pointer per gate block (A[0] only when gates == 1); column-major, ld = lda
+  int lda;
+  const float* B;  // K x N column-major
+  int ldb;
+  int K;
+};
+enum { EPI_STORE = 0, EPI_LSTM = 1, EPI_LSE = 2 };
+struct GemmArgs {
+  GemmSrc src[3];
+  int nsrc;
+  int M;  // rows per gate block
+  int N;
+  // EPI_STORE: C = act(acc + bias[row]) * mask[col]
+  float* C;
+  int ldc;
+  const float* bias[4];  // per gate block; may be null
+  const int* mask;       // per column; may be null
+  int act;               // 0 none, 1 tanh
+  int act_rows;          // act applies to rows < act_rows only (0 = all rows)
+  // EPI_LSTM (gates i,f,g,o): c = f*c_prev + i*g ; h = o*tanh(c) ; (h,c) *= mask
+  const float* c_prev;
+  float* h_out;
+  float* c_out;
+  float* h_out2;  // optional second copy of h (e.g. the attention memory slot)
+  // EPI_LSE: per (row tile, column) max and sum exp(z - max) of z = acc + bias, plus the logit of target[col]
+  const int* target;  // global row index; target - target_offset outside [0,M) is ignored
+  int target_offset;  // first global row held by this matrix (vocabulary sharding)
+  float* part_max;    // [n_row_tiles x N]
+  float* part_sum;
+  float* tgt_logit;  // [N], must be zero-filled by the caller when targets may fall outside [0,M)
+};
+// tile = 0: 64 x 64 CTA tile (4x4 per thread); tile = 1: 128 x 128 (8x8 per thread)
+cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, cudaStream_t st);
+int gemm_rows_per_tile(int gates, int tile);
+
+// ---- softmax partial combine: logp[n] = (tgt - M) - log(sum_i s_i exp(m_i - M)); 0 where mask==0
+cudaError_t launch_lse_combine(const float* part_max, const float* part_sum, const float* tgt_logit, int n_parts,
+                               int N, const int* mask, float* logp, cudaStream_t st);
+// same with the target logit summed over G shard rows of tgt_logit[G x N] (exactly one shard holds it, the others 0)
+cudaError_t launch_lse_combine_shards(const float* part_max, const float* part_sum, const float* tgt_logit, int G,
+                                      int N, const int* mask, float* logp, cudaStream_t st);
+// reduce n_parts row-tile partials to one (max, sum exp(z-max)) per column
+cudaError_t launch_lse_reduce(const float* part_max, const float* part_sum, int n_parts, int N, float* out_max,
+                              float* out_sum, cudaStream_t st);
+
+// ---- decode: per column the k largest log-probabilities (sorted) from logits z[V x N] + normaliser
+cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
+                             cudaStream_t st);
+
+// ---- attention
+struct AttArgs {
+  int H, B, D, S_max, B_src, cols_per_sent;
+  const float* hs;  // S_max slots of H x B_src
+  const int* len;   // per source column
+  const int* offset;
+  const int* mask;   // per target column
+  const float* h_t;  // H x B
+  // local-p only
+  const float* tanh1;  // tanh(W_p h), column b at tanh1 + b*ld_tq
+  const float* v_p;    // H
+  const float* q;      // W_a^T h, column b at q + b*ld_tq
+  int ld_tq;
+  float* c_t;          // context out, H x B
+  float* align_out;    // optional
+};
+cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st);
+cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);
+
+// ---- beam bookkeeping (replaces decoder::expand_hypothesis_without_fsa / finish_current_hypotheses /
+// output_k_best_hypotheses, src/decoder.h:1157-1315, 672-688, 1386-1463, run on the host there)
+struct BeamArgs {
+  int n_sent, beam, k_cand, Lmax, k_best, step;
+  float min_ratio, penalty;
+  const float* cand_val;   // [n_sent*beam][k_cand] log-probs, sorted descending
+  const int* cand_idx;     // [n_sent*beam][k_cand]
+  const float* logp_eos;   // [n_sent*beam]
+  const int* src_len;      // [n_sent]
+  const int* max_steps;    // [n_sent]
+  int* top_sent;           // [n_sent][beam][Lmax]
+  int* top_tmp;            // same size
+  float* scores;           // [n_sent][beam]
+  int* cur_ids;            // [n_sent*beam] current word per column (-1 invalid)
+  int* col_map;            // [n_sent*beam] source column for the state reorder
+  int* best_ids;           // [n_sent][k_best][Lmax]
+  int* best_len;           // [n_sent][k_best]
+  float* best_score;       // [n_sent][k_best]
+};
+cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st);
+cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st);
+
+// misc
+cudaError_t launch_fill_int(int* p, int v, size_t n, cudaStream_t st);
+// len[b] = number of unmasked steps of column b in mask[T x B]; offset[b] = T - len[b]
+// (the reference's batch_info, src/fileHelper.h:480-496)
+cudaError_t launch_src_len(const int* mask01, int T, int B, int* len, int* offset, cudaStream_t st);
+// map[c] = c / div
+cudaError_t launch_div_map(int* map, int n, int div, cudaStream_t st);
+long long launch_count_value();
+void launch_count_reset();
+
+}  // namespace zrnn

@@ -1,0 +1,1039 @@
+// C ABI (include/zrnn.h) and the C++ host side above it: layer objects mirroring the reference's
+// Input_To_Hidden_Layer / Hidden_To_Hidden_Layer / attention_layer / softmax_layer, and the
+// neuralMT_model drivers for teacher-forced scoring and batched beam decoding.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/zrnn.h"
+#include "kernels.cuh"
+#include "model_file.hpp"
+
+namespace {
+
+thread_local std::string g_err;
+int fail(int code, const std::string& msg) {
+  g_err = msg;
+  return code;
+}
+#define ZR_CUDA(expr)                                                                 \
+  do {                                                                                \
+    cudaError_t _e = (expr);                                                          \
+    if (_e != cudaSuccess)                                                            \
+      return fail(ZRNN_E_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));   \
+  } while (0)
+#define ZR_CHECK(cond, msg)                    \
+  do {                                         \
+    if (!(cond)) return fail(ZRNN_E_ARG, msg); \
+  } while (0)
+#define ZR_TRY(expr)                \
+  do {                              \
+    int _s = (expr);                \
+    if (_s != ZRNN_OK) return _s;   \
+  } while (0)
+
+// device buffer that only grows
+struct DevBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+  cudaError_t reserve(size_t bytes) {
+    if (bytes <= cap) return cudaSuccess;
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) cap = bytes;
+    return e;
+  }
+  void release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+  }
+  template <class T> T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+// carve 256-byte aligned pieces out of one DevBuf
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* b) : base((char*)b) {}
+  template <class T> T* take(size_t n) {
+    T* r = reinterpret_cast<T*>(base + off);
+    off += (n * sizeof(T) + 255) / 256 * 256;
+    return r;
+  }
+};
+size_t aligned(size_t bytes) { return (bytes + 255) / 256 * 256; }
+
+cudaError_t upload(float** dst, const float* src, size_t n) {
+  cudaError_t e = cudaMalloc((void**)dst, n * sizeof(float));
+  if (e != cudaSuccess) return e;
+  return cudaMemcpy(*dst, src, n * sizeof(float), cudaMemcpyHostToDevice);
+}
+
+// Optional CUDA-event timing of kernel classes (used by the benchmark's roofline report).
+enum { KC_GATHER = 0, KC_LSTM = 1, KC_ATT = 2, KC_SOFTMAX_GEMM = 3, KC_SOFTMAX_REDUCE = 4, KC_BEAM = 5, KC_REORDER = 6, KC_COUNT = 7 };
+struct KTiming {
+  bool on = false;
+  std::vector<cudaEvent_t> ev;  // pairs
+  std::vector<int> cls;
+  size_t used = 0;  // pairs in use
+};
+thread_local KTiming g_kt;
+const size_t KT_CAP = 16384;
+struct KScope {
+  long idx = -1;
+  cudaStream_t s;
+  KScope(int c, cudaStream_t st) : s(st) {
+    if (!g_kt.on || g_kt.used >= KT_CAP) return;
+    if (g_kt.ev.size() < 2 * (g_kt.used + 1)) {
+      cudaEvent_t a, b;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+      g_kt.ev.push_back(a);
+      g_kt.ev.push_back(b);
+      g_kt.cls.push_back(c);
+    }
+    idx = (long)g_kt.used++;
+    g_kt.cls[idx] = c;
+    cudaEventRecord(g_kt.ev[2 * idx], s);
+  }
+  ~KScope() {
+    if (idx >= 0) cudaEventRecord(g_kt.ev[2 * idx + 1], s);
+  }
+};
+
+int check_device() {
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0)
+    return fail(ZRNN_E_CUDA, std::string("no CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "count 0"));
+  return ZRNN_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// layer objects
+// ------------------------------------------------------------------------------------------
+struct zrnn_lstm_layer {
+  int H = 0, V = 0, feed = 0, dtype = 0, is_ih = 0;
+  bool loaded = false;
+  float* W = nullptr;   // embedding H x V
+  float* Wh = nullptr;  // 4 x (H x H): gates i,f,g,o
+  float* Mx = nullptr;  // 4 x (H x H)
+  float* Q = nullptr;   // 4 x (H x H), feed-input only
+  float* b = nullptr;   // 4 x H
+  DevBuf x;             // gather scratch for zrnn_ih_forward
+  ~zrnn_lstm_layer() {
+    cudaFree(W); cudaFree(Wh); cudaFree(Mx); cudaFree(Q); cudaFree(b);
+    x.release();
+  }
+};
+
+struct zrnn_attention {
+  int H = 0, D = 0, type = 0, dtype = 0;
+  bool loaded = false;
+  float* WpWaT = nullptr;  // stacked [W_p ; W_a^T], 2H x H column-major (local-p only)
+  float* v_p = nullptr;
+  float* bias = nullptr;
+  float* Wc1 = nullptr;
+  float* Wc2 = nullptr;
+  const float* hs = nullptr;
+  int S_max = 0, B_src = 0, cols_per_sent = 1;
+  const int* len = nullptr;
+  const int* off = nullptr;
+  DevBuf tq, ctx;
+  ~zrnn_attention() {
+    cudaFree(WpWaT); cudaFree(v_p); cudaFree(bias); cudaFree(Wc1); cudaFree(Wc2);
+    tq.release(); ctx.release();
+  }
+};
+
+struct zrnn_softmax {
+  int V = 0, H = 0, dtype = 0, lo = 0, hi = 0;
+  bool loaded = false;
+  float* D = nullptr;  // (hi-lo) x H
+  float* b = nullptr;  // hi-lo
+  DevBuf parts, tgt, logits;
+  ~zrnn_softmax() {
+    cudaFree(D); cudaFree(b);
+    parts.release(); tgt.release(); logits.release();
+  }
+};
+
+namespace {
+
+int lstm_cell_launch(zrnn_lstm_layer* L, const float* x, const int* mask, const float* h_prev, const float* c_prev,
+                     const float* htild, int B, float* h_out, float* c_out, float* h_out2, cudaStream_t st) {
+  const int H = L->H;
+  const size_t HH = (size_t)H * H;
+  zrnn::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  int n = 0;
+  auto add = [&](const float* A, const float* Bm) {
+    for (int k = 0; k < 4; ++k) g.src[n].A[k] = A + k * HH;
+    g.src[n].lda = H; g.src[n].B = Bm; g.src[n].ldb = H; g.src[n].K = H;
+    ++n;
+  };
+  add(L->Mx, x);
+  add(L->Wh, h_prev);
+  if (htild) add(L->Q, htild);
+  g.nsrc = n;
+  g.M = H; g.N = B;
+  for (int k = 0; k < 4; ++k) g.bias[k] = L->b + (size_t)k * H;
+  g.mask = mask;
+  g.c_prev = c_prev; g.h_out = h_out; g.c_out = c_out; g.h_out2 = h_out2;
+  KScope ks(KC_LSTM, st);
+  ZR_CUDA(zrnn::launch_fused_gemm(g, 4, zrnn::EPI_LSTM, 0, st));
+  return ZRNN_OK;
+}
+
+int att_forward_launch(zrnn_attention* A, const float* h_t, const int* mask, int B, float* htild, float* align,
+                       cudaStream_t st) {
+  const int H = A->H;
+  ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
+  KScope ks(KC_ATT, st);
+  zrnn::AttArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.H = H; a.B = B; a.D = A->D; a.S_max = A->S_max; a.B_src = A->B_src; a.cols_per_sent = A->cols_per_sent;
+  a.hs = A->hs; a.len = A->len; a.offset = A->off; a.mask = mask; a.h_t = h_t;
+  a.c_t = A->ctx.as<float>(); a.align_out = align;
+  if (A->type == ZRNN_ATT_LOCAL_P) {
+    ZR_CUDA(A->tq.reserve(sizeof(float) * (size_t)2 * H * B));
+    zrnn::GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.nsrc = 1;
+    g.src[0].A[0] = A->WpWaT; g.src[0].lda = 2 * H; g.src[0].B = h_t; g.src[0].ldb = H; g.src[0].K = H;
+    g.M = 2 * H; g.N = B; g.C = A->tq.as<float>(); g.ldc = 2 * H; g.act = 1; g.act_rows = H;
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+    a.tanh1 = A->tq.as<float>(); a.q = A->tq.as<float>() + H; a.ld_tq = 2 * H; a.v_p = A->v_p;
+    ZR_CUDA(zrnn::launch_att_local(a, st));
+  } else {
+    ZR_CUDA(zrnn::launch_att_global(a, st));
+  }
+  zrnn::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.nsrc = 2;
+  g.src[0].A[0] = A->Wc1; g.src[0].lda = H; g.src[0].B = A->ctx.as<float>(); g.src[0].ldb = H; g.src[0].K = H;
+  g.src[1].A[0] = A->Wc2; g.src[1].lda = H; g.src[1].B = h_t; g.src[1].ldb = H; g.src[1].K = H;
+  g.M = H; g.N = B; g.C = htild; g.ldc = H; g.bias[0] = A->bias; g.mask = mask; g.act = 1;
+  ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+  return ZRNN_OK;
+}
+
+// per-column (max, sum exp) partials over this layer's rows + target logit into S->parts / tgt
+int softmax_partials_launch(zrnn_softmax* S, const float* h, const int* targets, int N, int* n_parts, float** pm,
+                            float** ps, float* tgt, cudaStream_t st) {
+  const int Vs = S->hi - S->lo, H = S->H;
+  const int tile = (N >= 96 && Vs >= 512) ? 1 : 0;
+  const int rows = zrnn::gemm_rows_per_tile(1, tile);
+  const int np = (Vs + rows - 1) / rows;
+  ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
+  ZR_CUDA(cudaMemsetAsync(tgt, 0, sizeof(float) * (size_t)N, st));
+  zrnn::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.nsrc = 1;
+  g.src[0].A[0] = S->D; g.src[0].lda = Vs; g.src[0].B = h; g.src[0].ldb = H; g.src[0].K = H;
+  g.M = Vs; g.N = N; g.bias[0] = S->b;
+  g.target = targets; g.target_offset = S->lo;
+  g.part_max = S->parts.as<float>(); g.part_sum = S->parts.as<float>() + (size_t)np * N;
+  g.tgt_logit = tgt;
+  *n_parts = np; *pm = g.part_max; *ps = g.part_sum;
+  KScope ks(KC_SOFTMAX_GEMM, st);
+  ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
+  return ZRNN_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// model
+// ------------------------------------------------------------------------------------------
+struct TensorSlot {
+  std::string name;
+  int rows, cols;
+  int owner;  // 0 = src layer, 1 = tgt layer, 2 = attention, 3 = softmax
+  int layer;
+  int index;  // position in the owner's load list
+};
+
+struct zrnn_model {
+  zrnn_model_config cfg;
+  std::vector<zrnn_lstm_layer*> src, tgt;
+  zrnn_attention* att = nullptr;
+  zrnn_softmax* sm = nullptr;
+  std::vector<TensorSlot> slots;
+  std::vector<std::vector<float>> staged;
+  bool finalized = false;
+  cudaStream_t stream = nullptr;
+  DevBuf ws, io;
+  const float* last_top = nullptr;
+  int last_top_cols = 0;
+  std::vector<int> h_tmp;
+  ~zrnn_model() {
+    for (auto* l : src) delete l;
+    for (auto* l : tgt) delete l;
+    delete att;
+    delete sm;
+    ws.release(); io.release();
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+extern "C" {
+
+const char* zrnn_status_string(int s) {
+  switch (s) {
+    case ZRNN_OK: return "ok";
+    case ZRNN_E_ARG: return "invalid argument";
+    case ZRNN_E_CUDA: return "CUDA error";
+    case ZRNN_E_NCCL: return "NCCL error";
+    case ZRNN_E_TIMEOUT: return "device wait timed out";
+    case ZRNN_E_IO: return "weight file error";
+    case ZRNN_E_STATE: return "invalid call order";
+  }
+  return "unknown status";
+}
+const char* zrnn_last_error(void) { return g_err.c_str(); }
+int zrnn_version(void) { return 100; }
+int zrnn_built_for_sm(void) { return 100; }
+long long zrnn_launch_count(void) { return zrnn::launch_count_value(); }
+void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
+
+int zrnn_kernel_timing(int on) {
+  g_kt.on = on != 0;
+  if (on) g_kt.used = 0;
+  return ZRNN_OK;
+}
+int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total_ms) {
+  ZR_CHECK(kernel_class >= 0 && kernel_class < KC_COUNT && launches && total_ms, "kernel_timing_read: bad arguments");
+  *launches = 0;
+  *total_ms = 0.0;
+  for (size_t i = 0; i < g_kt.used; ++i) {
+    if (g_kt.cls[i] != kernel_class) continue;
+    ZR_CUDA(cudaEventSynchronize(g_kt.ev[2 * i + 1]));
+    float ms = 0.f;
+    ZR_CUDA(cudaEventElapsedTime(&ms, g_kt.ev[2 * i], g_kt.ev[2 * i + 1]));
+    *launches += 1;
+    *total_ms += ms;
+  }
+  return ZRNN_OK;
+}
+
+int zrnn_prep_vocab_indices(const int* d_ids_raw, int n, int* d_ids_nonm1, int* d_mask01, void* stream) {
+  ZR_CHECK(d_ids_raw && n >= 0, "prep_vocab_indices: null ids or negative n");
+  ZR_CUDA(zrnn::launch_prep_ids(d_ids_raw, n, d_ids_nonm1, d_mask01, (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- LSTM layers
+static int lstm_create(int H, int V, int feed, int dtype, int is_ih, zrnn_lstm_layer** out) {
+  ZR_CHECK(out, "lstm_create: null out");
+  ZR_CHECK(H > 0, "lstm_create: H must be positive");
+  ZR_CHECK(!is_ih || V > 0, "ih_create: V must be positive");
+  ZR_CHECK(dtype == ZRNN_F32, "lstm_create: only ZRNN_F32 arithmetic is available in this layer");
+  ZR_TRY(check_device());
+  auto* L = new zrnn_lstm_layer();
+  L->H = H; L->V = V; L->feed = feed ? 1 : 0; L->dtype = dtype; L->is_ih = is_ih;
+  *out = L;
+  return ZRNN_OK;
+}
+int zrnn_ih_create(int H, int V, int feed_input, int dtype, zrnn_lstm_layer** out) {
+  return lstm_create(H, V, feed_input, dtype, 1, out);
+}
+int zrnn_hh_create(int H, int dtype, zrnn_lstm_layer** out) { return lstm_create(H, 0, 0, dtype, 0, out); }
+
+int zrnn_lstm_load(zrnn_lstm_layer* L, const float* const* t, int n) {
+  ZR_CHECK(L && t, "lstm_load: null argument");
+  const int expect = 12 + (L->is_ih ? 1 : 0) + (L->feed ? 4 : 0);
+  ZR_CHECK(n == expect, "lstm_load: expected " + std::to_string(expect) + " tensors, got " + std::to_string(n));
+  for (int i = 0; i < n; ++i) ZR_CHECK(t[i], "lstm_load: null tensor " + std::to_string(i));
+  const int H = L->H;
+  const size_t HH = (size_t)H * H;
+  cudaFree(L->W); cudaFree(L->Wh); cudaFree(L->Mx); cudaFree(L->Q); cudaFree(L->b);
+  L->W = L->Wh = L->Mx = L->Q = L->b = nullptr;
+  L->loaded = false;
+  // file order: W_hi b_i W_hf b_f W_hc b_c W_ho b_o [W] M_i M_f M_o M_c [Q_i Q_f Q_o Q_c]; device gate order i,f,g,o
+  std::vector<float> pack(4 * HH);
+  for (int g = 0; g < 4; ++g) std::memcpy(pack.data() + g * HH, t[2 * g], sizeof(float) * HH);
+  ZR_CUDA(upload(&L->Wh, pack.data(), 4 * HH));
+  std::vector<float> bias(4 * (size_t)H);
+  for (int g = 0; g < 4; ++g) std::memcpy(bias.data() + (size_t)g * H, t[2 * g + 1], sizeof(float) * H);
+  ZR_CUDA(upload(&L->b, bias.data(), 4 * (size_t)H));
+  int p = 8;
+  if (L->is_ih) { ZR_CUDA(upload(&L->W, t[p], (size_t)H * L->V)); ++p; }
+  const int order[4] = {0, 1, 3, 2};  // file i,f,o,c -> gate slots i,f,o(3),g(2)
+  for (int k = 0; k < 4; ++k) std::memcpy(pack.data() + order[k] * HH, t[p + k], sizeof(float) * HH);
+  ZR_CUDA(upload(&L->Mx, pack.data(), 4 * HH));
+  p += 4;
+  if (L->feed) {
+    for (int k = 0; k < 4; ++k) std::memcpy(pack.data() + order[k] * HH, t[p + k], sizeof(float) * HH);
+    ZR_CUDA(upload(&L->Q, pack.data(), 4 * HH));
+  }
+  L->loaded = true;
+  return ZRNN_OK;
+}
+
+int zrnn_ih_gather(zrnn_lstm_layer* L, const int* d_ids, int n_cols, float* d_x, void* stream) {
+  ZR_CHECK(L && L->is_ih, "ih_gather: not an input layer");
+  if (!L->loaded) return fail(ZRNN_E_STATE, "ih_gather: weights not loaded");
+  ZR_CHECK(d_ids && d_x && n_cols >= 0, "ih_gather: bad arguments");
+  ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, d_ids, n_cols, d_x, (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+
+int zrnn_ih_forward(zrnn_lstm_layer* L, const int* d_ids, const int* d_mask, const float* d_h_prev,
+                    const float* d_c_prev, const float* d_htild_prev, int B, float* d_h_out, float* d_c_out,
+                    void* stream) {
+  ZR_CHECK(L && L->is_ih, "ih_forward: not an input layer");
+  if (!L->loaded) return fail(ZRNN_E_STATE, "ih_forward: weights not loaded");
+  ZR_CHECK(d_ids && d_h_prev && d_c_prev && d_h_out && d_c_out && B >= 0, "ih_forward: bad arguments");
+  ZR_CHECK(!d_htild_prev || L->feed, "ih_forward: htild given but the layer has no feed-input weights");
+  ZR_CHECK(d_h_out != d_h_prev && d_c_out != d_c_prev, "ih_forward: outputs may not alias inputs");
+  if (B == 0) return ZRNN_OK;
+  ZR_CUDA(L->x.reserve(sizeof(float) * (size_t)L->H * B));
+  ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, d_ids, B, L->x.as<float>(), (cudaStream_t)stream));
+  return lstm_cell_launch(L, L->x.as<float>(), d_mask, d_h_prev, d_c_prev, d_htild_prev, B, d_h_out, d_c_out, nullptr,
+                          (cudaStream_t)stream);
+}
+
+int zrnn_hh_forward(zrnn_lstm_layer* L, const float* d_h_below, const int* d_mask, const float* d_h_prev,
+                    const float* d_c_prev, int B, float* d_h_out, float* d_c_out, void* stream) {
+  ZR_CHECK(L, "hh_forward: null layer");
+  if (!L->loaded) return fail(ZRNN_E_STATE, "hh_forward: weights not loaded");
+  ZR_CHECK(d_h_below && d_h_prev && d_c_prev && d_h_out && d_c_out && B >= 0, "hh_forward: bad arguments");
+  ZR_CHECK(d_h_out != d_h_prev && d_c_out != d_c_prev, "hh_forward: outputs may not alias inputs");
+  if (B == 0) return ZRNN_OK;
+  return lstm_cell_launch(L, d_h_below, d_mask, d_h_prev, d_c_prev, nullptr, B, d_h_out, d_c_out, nullptr,
+                          (cudaStream_t)stream);
+}
+int zrnn_lstm_destroy(zrnn_lstm_layer* L) {
+  delete L;
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- attention
+int zrnn_att_create(int H, int D, int att_type, int dtype, zrnn_attention** out) {
+  ZR_CHECK(out, "att_create: null out");
+  ZR_CHECK(H > 0, "att_create: H must be positive");
+  ZR_CHECK(att_type == ZRNN_ATT_LOCAL_P || att_type == ZRNN_ATT_GLOBAL_DOT, "att_create: unknown attention type");
+  ZR_CHECK(att_type != ZRNN_ATT_LOCAL_P || (D >= 1 && 2 * D + 1 <= 64), "att_create: D must be in [1,31]");
+  ZR_CHECK(dtype == ZRNN_F32, "att_create: only ZRNN_F32 arithmetic is available in this layer");
+  ZR_TRY(check_device());
+  auto* A = new zrnn_attention();
+  A->H = H; A->D = D; A->type = att_type; A->dtype = dtype;
+  *out = A;
+  return ZRNN_OK;
+}
+int zrnn_att_load(zrnn_attention* A, const float* const* t, int n) {
+  ZR_CHECK(A && t, "att_load: null argument");
+  ZR_CHECK(n == 6, "att_load: expected 6 tensors (W_a W_p v_p output_bias W_c_p1 W_c_p2)");
+  for (int i = 0; i < n; ++i) ZR_CHECK(t[i], "att_load: null tensor");
+  const int H = A->H;
+  const size_t HH = (size_t)H * H;
+  cudaFree(A->WpWaT); cudaFree(A->v_p); cudaFree(A->bias); cudaFree(A->Wc1); cudaFree(A->Wc2);
+  A->WpWaT = A->v_p = A->bias = A->Wc1 = A->Wc2 = nullptr;
+  A->loaded = false;
+  if (A->type == ZRNN_ATT_LOCAL_P) {
+    // rows 0..H-1 = W_p, rows H..2H-1 = W_a^T, so one GEMM gives tanh(W_p h) and q = W_a^T h
+    std::vector<float> st(2 * HH);
+    const float* Wa = t[0];
+    const float* Wp = t[1];
+    for (int k = 0; k < H; ++k)
+      for (int r = 0; r < H; ++r) {
+        st[(size_t)k * 2 * H + r] = Wp[(size_t)k * H + r];
+        st[(size_t)k * 2 * H + H + r] = Wa[(size_t)r * H + k];
+      }
+    ZR_CUDA(upload(&A->WpWaT, st.data(), 2 * HH));
+    ZR_CUDA(upload(&A->v_p, t[2], H));
+  }
+  ZR_CUDA(upload(&A->bias, t[3], H));
+  ZR_CUDA(upload(&A->Wc1, t[4], HH));
+  ZR_CUDA(upload(&A->Wc2, t[5], HH));
+  A->loaded = true;
+  return ZRNN_OK;
+}
+int zrnn_att_set_source(zrnn_attention* A, const float* d_hs, int S_max, int B_src, const int* d_len,
+                        const int* d_offset, int cols_per_sentence) {
+  ZR_CHECK(A && d_hs && d_len && d_offset, "att_set_source: null argument");
+  ZR_CHECK(S_max > 0 && B_src > 0 && cols_per_sentence > 0, "att_set_source: sizes must be positive");
+  ZR_CHECK(S_max <= 10000, "att_set_source: S_max too large");
+  A->hs = d_hs; A->S_max = S_max; A->B_src = B_src; A->len = d_len; A->off = d_offset;
+  A->cols_per_sent = cols_per_sentence;
+  return ZRNN_OK;
+}
+int zrnn_att_forward(zrnn_attention* A, const float* d_h_t, const int* d_mask, int B, float* d_htild_out,
+                     float* d_align_out, void* stream) {
+  ZR_CHECK(A && d_h_t && d_htild_out && B >= 0, "att_forward: bad arguments");
+  if (!A->loaded) return fail(ZRNN_E_STATE, "att_forward: weights not loaded");
+  if (!A->hs) return fail(ZRNN_E_STATE, "att_forward: zrnn_att_set_source has not been called");
+  ZR_CHECK(B <= A->B_src * A->cols_per_sent, "att_forward: more target columns than source columns provide");
+  if (B == 0) return ZRNN_OK;
+  return att_forward_launch(A, d_h_t, d_mask, B, d_htild_out, d_align_out, (cudaStream_t)stream);
+}
+int zrnn_att_destroy(zrnn_attention* A) {
+  delete A;
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- softmax
+int zrnn_softmax_create(int V, int H, int dtype, int shard_lo, int shard_hi, zrnn_softmax** out) {
+  ZR_CHECK(out, "softmax_create: null out");
+  ZR_CHECK(V > 0 && H > 0, "softmax_create: V and H must be positive");
+  ZR_CHECK(0 <= shard_lo && shard_lo < shard_hi && shard_hi <= V, "softmax_create: bad shard range");
+  ZR_CHECK(dtype == ZRNN_F32, "softmax_create: only ZRNN_F32 arithmetic is available in this layer");
+  ZR_TRY(check_device());
+  auto* S = new zrnn_softmax();
+  S->V = V; S->H = H; S->dtype = dtype; S->lo = shard_lo; S->hi = shard_hi;
+  *out = S;
+  return ZRNN_OK;
+}
+int zrnn_softmax_load(zrnn_softmax* S, const float* h_D, const float* h_b_d) {
+  ZR_CHECK(S && h_D && h_b_d, "softmax_load: null argument");
+  cudaFree(S->D); cudaFree(S->b);
+  S->D = S->b = nullptr;
+  S->loaded = false;
+  const int Vs = S->hi - S->lo;
+  ZR_CUDA(cudaMalloc((void**)&S->D, sizeof(float) * (size_t)Vs * S->H));
+  ZR_CUDA(cudaMemcpy2D(S->D, sizeof(float) * (size_t)Vs, h_D + S->lo, sizeof(float) * (size_t)S->V,
+                       sizeof(float) * (size_t)Vs, S->H, cudaMemcpyHostToDevice));
+  ZR_CUDA(upload(&S->b, h_b_d + S->lo, Vs));
+  S->loaded = true;
+  return ZRNN_OK;
+}
+int zrnn_softmax_partials(zrnn_softmax* S, const float* d_h, const int* d_targets, int N, float* d_max, float* d_sum,
+                          float* d_tgt, void* stream) {
+  ZR_CHECK(S && d_h && d_targets && d_max && d_sum && d_tgt && N >= 0, "softmax_partials: bad arguments");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_partials: weights not loaded");
+  if (N == 0) return ZRNN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int np = 0;
+  float *pm, *ps;
+  ZR_TRY(softmax_partials_launch(S, d_h, d_targets, N, &np, &pm, &ps, d_tgt, st));
+  // reduce this shard's row tiles to one (max, sum) per column
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_lse_reduce(pm, ps, np, N, d_max, d_sum, st));
+  return ZRNN_OK;
+}
+int zrnn_softmax_combine(const float* d_max, const float* d_sum, const float* d_tgt, int G, int N,
+                         const int* d_mask, float* d_logp_out, void* stream) {
+  ZR_CHECK(d_max && d_sum && d_tgt && d_logp_out && G >= 1 && N >= 0, "softmax_combine: bad arguments");
+  if (N == 0) return ZRNN_OK;
+  ZR_CUDA(zrnn::launch_lse_combine_shards(d_max, d_sum, d_tgt, G, N, d_mask, d_logp_out, (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+int zrnn_softmax_score(zrnn_softmax* S, const float* d_h, const int* d_targets, const int* d_mask, int N,
+                       float* d_logp_out, void* stream) {
+  ZR_CHECK(S && d_h && d_targets && d_logp_out && N >= 0, "softmax_score: bad arguments");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_score: weights not loaded");
+  ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_score: layer is vocabulary-sharded; use partials + combine");
+  if (N == 0) return ZRNN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  ZR_CUDA(S->tgt.reserve(sizeof(float) * (size_t)N));
+  int np = 0;
+  float *pm, *ps;
+  ZR_TRY(softmax_partials_launch(S, d_h, d_targets, N, &np, &pm, &ps, S->tgt.as<float>(), st));
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_lse_combine(pm, ps, S->tgt.as<float>(), np, N, d_mask, d_logp_out, st));
+  return ZRNN_OK;
+}
+int zrnn_softmax_topk(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
+                      float* d_logp_eos, void* stream) {
+  ZR_CHECK(S && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk: bad arguments");
+  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk: k must be in [1,16]");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk: weights not loaded");
+  ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_topk: layer is vocabulary-sharded");
+  if (N == 0) return ZRNN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
+  zrnn::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.nsrc = 1;
+  g.src[0].A[0] = S->D; g.src[0].lda = S->V; g.src[0].B = d_h; g.src[0].ldb = S->H; g.src[0].K = S->H;
+  g.M = S->V; g.N = N; g.C = S->logits.as<float>(); g.ldc = S->V; g.bias[0] = S->b;
+  {
+    KScope ks(KC_SOFTMAX_GEMM, st);
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
+  }
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, d_logp_out, d_idx_out, d_logp_eos, st));
+  return ZRNN_OK;
+}
+int zrnn_softmax_destroy(zrnn_softmax* S) {
+  delete S;
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- model
+static void add_lstm_slots(zrnn_model* m, const std::string& pre, int owner, int layer, int H, int V_emb, bool feed) {
+  int idx = 0;
+  auto add = [&](const std::string& n, int r, int c) { m->slots.push_back({pre + "." + n, r, c, owner, layer, idx++}); };
+  const char* g1[4] = {"i", "f", "c", "o"};
+  for (int g = 0; g < 4; ++g) { add(std::string("W_h") + g1[g], H, H); add(std::string("b_") + g1[g], H, 1); }
+  if (V_emb > 0) add("W", H, V_emb);
+  const char* g2[4] = {"i", "f", "o", "c"};
+  for (int g = 0; g < 4; ++g) add(std::string("M_") + g2[g], H, H);
+  if (feed) for (int g = 0; g < 4; ++g) add(std::string("Q_") + g2[g], H, H);
+}
+
+int zrnn_model_create(const zrnn_model_config* c, zrnn_model** out) {
+  ZR_CHECK(c && out, "model_create: null argument");
+  ZR_CHECK(c->num_layers >= 1 && c->num_layers <= 8, "model_create: num_layers must be in [1,8]");
+  ZR_CHECK(c->H > 0 && c->V_tgt > 1, "model_create: H and V_tgt must be positive");
+  ZR_CHECK(c->lm || c->V_src > 0, "model_create: V_src must be positive for a sequence-to-sequence model");
+  ZR_CHECK(c->attention >= 0 && c->attention <= 2, "model_create: unknown attention type");
+  ZR_CHECK(!(c->lm && c->attention), "model_create: a language model has no source to attend to");
+  ZR_CHECK(!c->feed_input || c->attention, "model_create: feed-input needs an attention model");
+  ZR_CHECK(c->dtype == ZRNN_F32, "model_create: only ZRNN_F32 arithmetic is available");
+  ZR_TRY(check_device());
+  auto* m = new zrnn_model();
+  m->cfg = *c;
+  const int H = c->H, L = c->num_layers;
+  int st = ZRNN_OK;
+  if (!c->lm)
+    for (int l = 0; l < L && st == ZRNN_OK; ++l) {
+      zrnn_lstm_layer* ly = nullptr;
+      st = l == 0 ? zrnn_ih_create(H, c->V_src, 0, c->dtype, &ly) : zrnn_hh_create(H, c->dtype, &ly);
+      if (st == ZRNN_OK) {
+        m->src.push_back(ly);
+        add_lstm_slots(m, "src" + std::to_string(l), 0, l, H, l == 0 ? c->V_src : 0, false);
+      }
+    }
+  for (int l = 0; l < L && st == ZRNN_OK; ++l) {
+    zrnn_lstm_layer* ly = nullptr;
+    st = l == 0 ? zrnn_ih_create(H, c->V_tgt, c->feed_input, c->dtype, &ly) : zrnn_hh_create(H, c->dtype, &ly);
+    if (st != ZRNN_OK) break;
+    m->tgt.push_back(ly);
+    add_lstm_slots(m, "tgt" + std::to_string(l), 1, l, H, l == 0 ? c->V_tgt : 0, l == 0 && c->feed_input);
+    if (c->attention && l == L - 1) {
+      st = zrnn_att_create(H, c->D, c->attention, c->dtype, &m->att);
+      const char* names[6] = {"att.W_a", "att.W_p", "att.v_p", "att.output_bias", "att.W_c_p1", "att.W_c_p2"};
+      const int rows[6] = {H, H, 1, H, H, H}, cols[6] = {H, H, H, 1, H, H};
+      for (int i = 0; i < 6; ++i) m->slots.push_back({names[i], rows[i], cols[i], 2, 0, i});
+    }
+  }
+  if (st == ZRNN_OK) st = zrnn_softmax_create(c->V_tgt, H, c->dtype, 0, c->V_tgt, &m->sm);
+  if (st == ZRNN_OK) {
+    m->slots.push_back({"softmax.D", c->V_tgt, H, 3, 0, 0});
+    m->slots.push_back({"softmax.b_d", c->V_tgt, 1, 3, 0, 1});
+    m->staged.resize(m->slots.size());
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess)
+      st = fail(ZRNN_E_CUDA, "model_create: cannot create stream");
+  }
+  if (st != ZRNN_OK) {
+    delete m;
+    return st;
+  }
+  *out = m;
+  return ZRNN_OK;
+}
+
+int zrnn_model_num_tensors(zrnn_model* m) { return m ? (int)m->slots.size() : 0; }
+int zrnn_model_tensor_info(zrnn_model* m, int i, char* name, int* rows, int* cols) {
+  ZR_CHECK(m && i >= 0 && i < (int)m->slots.size(), "tensor_info: bad index");
+  if (name) { std::strncpy(name, m->slots[i].name.c_str(), 31); name[31] = 0; }
+  if (rows) *rows = m->slots[i].rows;
+  if (cols) *cols = m->slots[i].cols;
+  return ZRNN_OK;
+}
+int zrnn_model_set_tensor(zrnn_model* m, int i, const float* h_data) {
+  ZR_CHECK(m && h_data && i >= 0 && i < (int)m->slots.size(), "set_tensor: bad arguments");
+  const size_t n = (size_t)m->slots[i].rows * m->slots[i].cols;
+  m->staged[i].assign(h_data, h_data + n);
+  m->finalized = false;
+  return ZRNN_OK;
+}
+int zrnn_model_finalize(zrnn_model* m) {
+  ZR_CHECK(m, "finalize: null model");
+  for (size_t i = 0; i < m->slots.size(); ++i)
+    if (m->staged[i].empty()) return fail(ZRNN_E_STATE, "finalize: tensor " + m->slots[i].name + " was never set");
+  size_t i = 0;
+  auto load_lstm = [&](zrnn_lstm_layer* L, int owner, int layer) -> int {
+    std::vector<const float*> ptrs;
+    while (i < m->slots.size() && m->slots[i].owner == owner && m->slots[i].layer == layer) ptrs.push_back(m->staged[i++].data());
+    return zrnn_lstm_load(L, ptrs.data(), (int)ptrs.size());
+  };
+  for (size_t l = 0; l < m->src.size(); ++l) ZR_TRY(load_lstm(m->src[l], 0, (int)l));
+  for (size_t l = 0; l < m->tgt.size(); ++l) {
+    ZR_TRY(load_lstm(m->tgt[l], 1, (int)l));
+    if (m->att && l + 1 == m->tgt.size()) {
+      const float* p[6];
+      for (int k = 0; k < 6; ++k) p[k] = m->staged[i++].data();
+      ZR_TRY(zrnn_att_load(m->att, p, 6));
+    }
+  }
+  ZR_TRY(zrnn_softmax_load(m->sm, m->staged[i].data(), m->staged[i + 1].data()));
+  for (auto& v : m->staged) std::vector<float>().swap(v);
+  m->staged.assign(m->slots.size(), std::vector<float>(1, 0.f));  // mark as "set"; data now lives on the device
+  m->finalized = true;
+  return ZRNN_OK;
+}
+
+int zrnn_model_load_file(const char* path, int att_type_override, int D, int dtype, zrnn_model** out) {
+  ZR_CHECK(path && out, "load_file: null argument");
+  zrnn::ModelFileReader rd;
+  zrnn::ModelFileHeader h;
+  std::string err;
+  if (!rd.open(path, &h, &err)) return fail(ZRNN_E_IO, "load_file: " + err);
+  if (h.multi_source || h.char_cnn) return fail(ZRNN_E_ARG, "load_file: multi-source / char-CNN models are not supported");
+  zrnn_model_config c;
+  std::memset(&c, 0, sizeof(c));
+  c.num_layers = h.num_layers; c.H = h.H; c.V_src = h.lm ? 0 : h.V_src; c.V_tgt = h.V_tgt; c.lm = h.lm ? 1 : 0;
+  c.attention = h.attention ? (att_type_override ? att_type_override : ZRNN_ATT_LOCAL_P) : ZRNN_ATT_NONE;
+  c.feed_input = (h.attention && h.feed_input) ? 1 : 0;
+  c.D = D > 0 ? D : 10;
+  c.dtype = dtype;
+  zrnn_model* m = nullptr;
+  ZR_TRY(zrnn_model_create(&c, &m));
+  std::vector<float> buf;
+  for (size_t i = 0; i < m->slots.size(); ++i) {
+    buf.resize((size_t)m->slots[i].rows * m->slots[i].cols);
+    if (!rd.read_matrix(m->slots[i].rows, m->slots[i].cols, buf.data(), &err)) {
+      const std::string nm = m->slots[i].name;
+      delete m;
+      return fail(ZRNN_E_IO, "load_file: " + nm + ": " + err);
+    }
+    zrnn_model_set_tensor(m, (int)i, buf.data());
+  }
+  const int st = zrnn_model_finalize(m);
+  if (st != ZRNN_OK) { delete m; return st; }
+  *out = m;
+  return ZRNN_OK;
+}
+
+int zrnn_model_get_config(zrnn_model* m, zrnn_model_config* cfg) {
+  ZR_CHECK(m && cfg, "get_config: null argument");
+  *cfg = m->cfg;
+  return ZRNN_OK;
+}
+zrnn_softmax* zrnn_model_softmax(zrnn_model* m) { return m ? m->sm : nullptr; }
+int zrnn_model_copy_top_states(zrnn_model* m, float* d_out, int capacity_cols, int* n_cols, void* stream) {
+  ZR_CHECK(m && n_cols, "copy_top_states: null argument");
+  *n_cols = m->last_top_cols;
+  if (!d_out || !m->last_top) return ZRNN_OK;
+  const int n = std::min(capacity_cols, m->last_top_cols);
+  ZR_CUDA(cudaMemcpyAsync(d_out, m->last_top, sizeof(float) * (size_t)n * m->cfg.H, cudaMemcpyDeviceToDevice,
+                          (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+int zrnn_model_destroy(zrnn_model* m) {
+  delete m;
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- scoring driver
+// Runs the encoder over S_max steps for B columns. On return hstate[l][cur[l]] / cstate hold the final states and
+// hs_all (if non-null) the top-layer state of every step.
+struct StateSet {
+  std::vector<float*> h[2], c[2];
+  std::vector<int> cur;
+};
+
+static int run_encoder(zrnn_model* m, const int* ids_nonm1, const int* mask, int S_max, int B, float* X0,
+                       float* hs_all, StateSet& st, cudaStream_t s) {
+  const int H = m->cfg.H, L = m->cfg.num_layers;
+  const size_t HB = (size_t)H * B;
+  {
+    KScope ks(KC_GATHER, s);
+    ZR_CUDA(zrnn::launch_gather_columns(m->src[0]->W, H, ids_nonm1, S_max * B, X0, s));
+  }
+  for (int t = 0; t < S_max; ++t) {
+    const float* x = X0 + (size_t)t * HB;
+    for (int l = 0; l < L; ++l) {
+      const int cu = st.cur[l];
+      float* h2 = (l == L - 1 && hs_all) ? hs_all + (size_t)t * HB : nullptr;
+      ZR_TRY(lstm_cell_launch(m->src[l], x, mask + (size_t)t * B, st.h[cu][l], st.c[cu][l], nullptr, B, st.h[cu ^ 1][l],
+                              st.c[cu ^ 1][l], h2, s));
+      st.cur[l] = cu ^ 1;
+      x = st.h[cu ^ 1][l];
+    }
+  }
+  return ZRNN_OK;
+}
+
+int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in,
+                            const int* d_tgt_out, int T, int B, float* d_logp_out, void* stream) {
+  ZR_CHECK(m && d_tgt_in && d_tgt_out && d_logp_out, "score_batch: null argument");
+  if (!m->finalized) return fail(ZRNN_E_STATE, "score_batch: model weights not finalized");
+  ZR_CHECK(T >= 0 && B >= 0, "score_batch: negative size");
+  ZR_CHECK(m->cfg.lm || (d_src_ids && S_max > 0), "score_batch: a sequence-to-sequence model needs source ids");
+  if (T == 0 || B == 0) return ZRNN_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const zrnn_model_config& c = m->cfg;
+  const int H = c.H, L = c.num_layers;
+  const size_t HB = (size_t)H * B;
+  const int S = c.lm ? 0 : S_max;
+  const size_t nS = (size_t)S * B, nT = (size_t)T * B;
+  size_t bytes = 0;
+  bytes += 2 * aligned(sizeof(int) * (nS + 1)) + 4 * aligned(sizeof(int) * nT) + 2 * aligned(sizeof(int) * B);
+  bytes += 2 * aligned(sizeof(float) * (HB * S + 1)) + 2 * aligned(sizeof(float) * HB * T);
+  bytes += 4 * (size_t)L * aligned(sizeof(float) * HB);
+  ZR_CUDA(m->ws.reserve(bytes));
+  Carver cv(m->ws.p);
+  int* src_id = cv.take<int>(nS + 1);
+  int* src_mk = cv.take<int>(nS + 1);
+  int* tin_id = cv.take<int>(nT);
+  int* tin_mk = cv.take<int>(nT);
+  int* tout_id = cv.take<int>(nT);
+  int* tout_mk = cv.take<int>(nT);
+  int* len = cv.take<int>(B);
+  int* off = cv.take<int>(B);
+  float* X0 = cv.take<float>(HB * S + 1);
+  float* hs_all = cv.take<float>(HB * S + 1);
+  float* Xt = cv.take<float>(HB * T);
+  float* Hseq = cv.take<float>(HB * T);
+  StateSet st;
+  st.cur.assign(L, 0);
+  for (int k = 0; k < 2; ++k) {
+    st.h[k].resize(L); st.c[k].resize(L);
+    for (int l = 0; l < L; ++l) { st.h[k][l] = cv.take<float>(HB); st.c[k][l] = cv.take<float>(HB); }
+  }
+  for (int l = 0; l < L; ++l) {
+    ZR_CUDA(cudaMemsetAsync(st.h[0][l], 0, sizeof(float) * HB, s));
+    ZR_CUDA(cudaMemsetAsync(st.c[0][l], 0, sizeof(float) * HB, s));
+  }
+  ZR_CUDA(zrnn::launch_prep_ids(d_tgt_in, (int)nT, tin_id, tin_mk, s));
+  ZR_CUDA(zrnn::launch_prep_ids(d_tgt_out, (int)nT, tout_id, tout_mk, s));
+  if (!c.lm) {
+    ZR_CUDA(zrnn::launch_prep_ids(d_src_ids, (int)nS, src_id, src_mk, s));
+    ZR_CUDA(zrnn::launch_src_len(src_mk, S, B, len, off, s));
+    ZR_TRY(run_encoder(m, src_id, src_mk, S, B, X0, c.attention ? hs_all : nullptr, st, s));
+    if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, hs_all, S, B, len, off, 1));
+  }
+  // target side: layer l starts from the encoder's final (h,c) of layer l (src/model.hpp:1714-1724)
+  {
+    KScope ks(KC_GATHER, s);
+    ZR_CUDA(zrnn::launch_gather_columns(m->tgt[0]->W, H, tin_id, (int)nT, Xt, s));
+  }
+  for (int t = 0; t < T; ++t) {
+    const float* x = Xt + (size_t)t * HB;
+    const int* mk = tin_mk + (size_t)t * B;
+    float* top_slot = Hseq + (size_t)t * HB;
+    for (int l = 0; l < L; ++l) {
+      const int cu = st.cur[l];
+      const float* feed = (l == 0 && c.feed_input && t > 0) ? Hseq + (size_t)(t - 1) * HB : nullptr;
+      float* h2 = (l == L - 1 && !c.attention) ? top_slot : nullptr;
+      ZR_TRY(lstm_cell_launch(m->tgt[l], x, mk, st.h[cu][l], st.c[cu][l], feed, B, st.h[cu ^ 1][l], st.c[cu ^ 1][l], h2, s));
+      st.cur[l] = cu ^ 1;
+      x = st.h[cu ^ 1][l];
+    }
+    if (c.attention) ZR_TRY(att_forward_launch(m->att, x, mk, B, top_slot, nullptr, s));
+  }
+  m->last_top = Hseq;
+  m->last_top_cols = (int)nT;
+  return zrnn_softmax_score(m->sm, Hseq, tout_id, tout_mk, (int)nT, d_logp_out, s);
+}
+
+int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tgt_in, const int* tgt_out, int T,
+                     int B, float* logp_out, double* total_logp) {
+  ZR_CHECK(m && tgt_in && tgt_out && logp_out, "score_batch: null argument");
+  ZR_CHECK(T >= 0 && B >= 0 && S_max >= 0, "score_batch: negative size");
+  if (total_logp) *total_logp = 0.0;
+  if (T == 0 || B == 0) return ZRNN_OK;
+  const size_t nS = m->cfg.lm ? 0 : (size_t)S_max * B, nT = (size_t)T * B;
+  ZR_CHECK(m->cfg.lm || src_ids, "score_batch: a sequence-to-sequence model needs source ids");
+  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * (nS + 1)) + 2 * aligned(sizeof(int) * nT) + aligned(sizeof(float) * nT)));
+  Carver cv(m->io.p);
+  int* d_src = cv.take<int>(nS + 1);
+  int* d_tin = cv.take<int>(nT);
+  int* d_tout = cv.take<int>(nT);
+  float* d_lp = cv.take<float>(nT);
+  cudaStream_t s = m->stream;
+  if (nS) ZR_CUDA(cudaMemcpyAsync(d_src, src_ids, sizeof(int) * nS, cudaMemcpyHostToDevice, s));
+  ZR_CUDA(cudaMemcpyAsync(d_tin, tgt_in, sizeof(int) * nT, cudaMemcpyHostToDevice, s));
+  ZR_CUDA(cudaMemcpyAsync(d_tout, tgt_out, sizeof(int) * nT, cudaMemcpyHostToDevice, s));
+  ZR_TRY(zrnn_score_batch_device(m, nS ? d_src : nullptr, S_max, d_tin, d_tout, T, B, d_lp, s));
+  ZR_CUDA(cudaMemcpyAsync(logp_out, d_lp, sizeof(float) * nT, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaStreamSynchronize(s));
+  if (total_logp) {
+    double tot = 0;
+    for (size_t i = 0; i < nT; ++i) tot += logp_out[i];
+    *total_logp = tot;
+  }
+  return ZRNN_OK;
+}
+
+// ---------------------------------------------------------------- beam decoding driver
+int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_src_len, int S_max, int n_sent,
+                                  int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                                  int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score,
+                                  void* stream) {
+  ZR_CHECK(m && d_src && h_src_len && d_out_ids && d_out_len && d_out_score, "beam_decode: null argument");
+  if (!m->finalized) return fail(ZRNN_E_STATE, "beam_decode: model weights not finalized");
+  const zrnn_model_config& c = m->cfg;
+  ZR_CHECK(!c.lm, "beam_decode: needs a sequence-to-sequence model");
+  ZR_CHECK(n_sent >= 0 && S_max > 0 && beam >= 1 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
+  if (n_sent == 0) return ZRNN_OK;
+  const int cap = (int)std::sqrt((double)c.V_tgt);  // src/ensemble_factory.hpp:19-21
+  if (beam > cap) beam = cap;
+  ZR_CHECK(beam >= 1 && beam <= 15, "beam_decode: beam must be in [1,15] after the sqrt(V) cap");
+  const int kc = beam + 1;
+  ZR_CHECK(kc <= c.V_tgt, "beam_decode: vocabulary smaller than beam+1");
+  const int Lmax = longest_sent + 4;  // src/main.cu:408
+  cudaStream_t s = (cudaStream_t)stream;
+  const int H = c.H, L = c.num_layers, n = n_sent, NB = n_sent * beam;
+  const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
+
+  // per-sentence step limits (src/ensemble_factory.hpp:637)
+  m->h_tmp.resize(2 * (size_t)n);
+  int Tmax = 0;
+  for (int i = 0; i < n; ++i) {
+    ZR_CHECK(h_src_len[i] >= 1 && h_src_len[i] <= S_max, "beam_decode: source length out of range");
+    int ms = std::min((int)(max_ratio * h_src_len[i]), Lmax - 2);
+    ZR_CHECK(ms >= 1, "beam_decode: max_ratio*source_length must allow at least one step");
+    m->h_tmp[i] = h_src_len[i];
+    m->h_tmp[n + i] = ms;
+    Tmax = std::max(Tmax, ms);
+  }
+  size_t bytes = 0;
+  bytes += 2 * aligned(sizeof(int) * nS) + 4 * aligned(sizeof(int) * n);
+  bytes += 3 * aligned(sizeof(int) * NB) + 2 * aligned(sizeof(int) * (size_t)NB * Lmax) + aligned(sizeof(int) * (size_t)NB * kc);
+  bytes += 2 * aligned(sizeof(float) * HBs * S_max) + 4 * (size_t)L * aligned(sizeof(float) * HBs);
+  bytes += (4 * (size_t)L + 3) * aligned(sizeof(float) * HB);
+  bytes += 2 * aligned(sizeof(float) * NB) + aligned(sizeof(float) * (size_t)NB * kc);
+  ZR_CUDA(m->ws.reserve(bytes));
+  Carver cv(m->ws.p);
+  int* src_id = cv.take<int>(nS);
+  int* src_mk = cv.take<int>(nS);
+  int* len = cv.take<int>(n);
+  int* off = cv.take<int>(n);
+  int* d_len_host = cv.take<int>(n);
+  int* max_steps = cv.take<int>(n);
+  int* rep_map = cv.take<int>(NB);
+  int* cur_ids = cv.take<int>(NB);
+  int* col_map = cv.take<int>(NB);
+  int* top_sent = cv.take<int>((size_t)NB * Lmax);
+  int* top_tmp = cv.take<int>((size_t)NB * Lmax);
+  int* cand_idx = cv.take<int>((size_t)NB * kc);
+  float* X0 = cv.take<float>(HBs * S_max);
+  float* hs_all = cv.take<float>(HBs * S_max);
+  StateSet st;
+  st.cur.assign(L, 0);
+  for (int k = 0; k < 2; ++k) {
+    st.h[k].resize(L); st.c[k].resize(L);
+    for (int l = 0; l < L; ++l) { st.h[k][l] = cv.take<float>(HBs); st.c[k][l] = cv.take<float>(HBs); }
+  }
+  std::vector<float*> hp(L), cp(L), hn(L), cn(L);
+  for (int l = 0; l < L; ++l) { hp[l] = cv.take<float>(HB); cp[l] = cv.take<float>(HB); hn[l] = cv.take<float>(HB); cn[l] = cv.take<float>(HB); }
+  float* x = cv.take<float>(HB);
+  float* htild_new = cv.take<float>(HB);
+  float* htild_feed = cv.take<float>(HB);
+  float* scores = cv.take<float>(NB);
+  float* logp_eos = cv.take<float>(NB);
+  float* cand_val = cv.take<float>((size_t)NB * kc);
+
+  ZR_CUDA(cudaMemcpyAsync(d_len_host, m->h_tmp.data(), sizeof(int) * n, cudaMemcpyHostToDevice, s));
+  ZR_CUDA(cudaMemcpyAsync(max_steps, m->h_tmp.data() + n, sizeof(int) * n, cudaMemcpyHostToDevice, s));
+  for (int l = 0; l < L; ++l) {
+    ZR_CUDA(cudaMemsetAsync(st.h[0][l], 0, sizeof(float) * HBs, s));
+    ZR_CUDA(cudaMemsetAsync(st.c[0][l], 0, sizeof(float) * HBs, s));
+  }
+  ZR_CUDA(zrnn::launch_prep_ids(d_src, (int)nS, src_id, src_mk, s));
+  ZR_CUDA(zrnn::launch_src_len(src_mk, S_max, n, len, off, s));
+  ZR_TRY(run_encoder(m, src_id, src_mk, S_max, n, X0, c.attention ? hs_all : nullptr, st, s));
+  if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, hs_all, S_max, n, len, off, beam));
+
+  // replicate the encoder's final (h,c) over the beam (transfer_decoding_states_GPU)
+  ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
+  {
+    zrnn::ColGatherArgs g;
+    std::memset(&g, 0, sizeof(g));
+    for (int l = 0; l < L; ++l) {
+      g.src[g.n_arrays] = st.h[st.cur[l]][l]; g.dst[g.n_arrays++] = hp[l];
+      g.src[g.n_arrays] = st.c[st.cur[l]][l]; g.dst[g.n_arrays++] = cp[l];
+    }
+    g.H = H; g.n_cols = NB; g.map = rep_map;
+    ZR_CUDA(zrnn::launch_col_gather(g, s));
+  }
+  zrnn::BeamArgs ba;
+  std::memset(&ba, 0, sizeof(ba));
+  ba.n_sent = n; ba.beam = beam; ba.k_cand = kc; ba.Lmax = Lmax; ba.k_best = k_best;
+  ba.min_ratio = min_ratio; ba.penalty = penalty;
+  ba.cand_val = cand_val; ba.cand_idx = cand_idx; ba.logp_eos = logp_eos; ba.src_len = d_len_host; ba.max_steps = max_steps;
+  ba.top_sent = top_sent; ba.top_tmp = top_tmp; ba.scores = scores; ba.cur_ids = cur_ids; ba.col_map = col_map;
+  ba.best_ids = d_out_ids; ba.best_len = d_out_len; ba.best_score = d_out_score;
+  ZR_CUDA(zrnn::launch_beam_init(ba, s));
+
+  for (int t = 0; t <= Tmax; ++t) {
+    {
+      KScope ks(KC_GATHER, s);
+      ZR_CUDA(zrnn::launch_gather_columns(m->tgt[0]->W, H, cur_ids, NB, x, s));
+    }
+    const float* xin = x;
+    for (int l = 0; l < L; ++l) {
+      const float* feed = (l == 0 && c.feed_input && t > 0) ? htild_feed : nullptr;
+      ZR_TRY(lstm_cell_launch(m->tgt[l], xin, nullptr, hp[l], cp[l], feed, NB, hn[l], cn[l], nullptr, s));
+      xin = hn[l];
+    }
+    const float* top = xin;
+    if (c.attention) {
+      ZR_TRY(att_forward_launch(m->att, xin, nullptr, NB, htild_new, nullptr, s));
+      top = htild_new;
+    }
+    ZR_TRY(zrnn_softmax_topk(m->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
+    ba.step = t;
+    {
+      KScope ks(KC_BEAM, s);
+      ZR_CUDA(zrnn::launch_beam_step(ba, s));
+    }
+    if (t < Tmax) {  // swap_decoding_states + target_copy_prev_states
+      zrnn::ColGatherArgs g;
+      std::memset(&g, 0, sizeof(g));
+      for (int l = 0; l < L; ++l) {
+        g.src[g.n_arrays] = hn[l]; g.dst[g.n_arrays++] = hp[l];
+        g.src[g.n_arrays] = cn[l]; g.dst[g.n_arrays++] = cp[l];
+      }
+      if (c.feed_input) { g.src[g.n_arrays] = htild_new; g.dst[g.n_arrays++] = htild_feed; }
+      g.H = H; g.n_cols = NB; g.map = col_map;
+      KScope ks(KC_REORDER, s);
+      ZR_CUDA(zrnn::launch_col_gather(g, s));
+    }
+  }
+  return ZRNN_OK;
+}
+
+int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best,
+                           float min_ratio, float max_ratio, float penalty, int longest_sent, int* out_ids,
+                           int* out_len, float* out_score) {
+  ZR_CHECK(m && src_ids && src_len && out_ids && out_len && out_score, "beam_decode: null argument");
+  ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
+  if (n_sent == 0) return ZRNN_OK;
+  int S_max = 0;
+  for (int i = 0; i < n_sent; ++i) {
+    ZR_CHECK(src_len[i] >= 1, "beam_decode: empty source sentence");
+    S_max = std::max(S_max, src_len[i]);
+  }
+  const int Lmax = longest_sent + 4;
+  // pad on the host into the reference's minibatch layout: time-major, left-padded with -1
+  std::vector<int> padded((size_t)S_max * n_sent, -1);
+  size_t pos = 0;
+  for (int i = 0; i < n_sent; ++i) {
+    for (int t = 0; t < src_len[i]; ++t) padded[(size_t)(S_max - src_len[i] + t) * n_sent + i] = src_ids[pos + t];
+    pos += src_len[i];
+  }
+  const size_t nO = (size_t)n_sent * k_best;
+  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * padded.size()) + aligned(sizeof(int) * nO * Lmax) +
+                        aligned(sizeof(int) * nO) + aligned(sizeof(float) * nO)));
+  Carver cv(m->io.p);
+  int* d_src = cv.take<int>(padded.size());
+  int* d_ids = cv.take<int>(nO * Lmax);
+  int* d_len = cv.take<int>(nO);
+  float* d_sc = cv.take<float>(nO);
+  cudaStream_t s = m->stream;
+  ZR_CUDA(cudaMemcpyAsync(d_src, padded.data(), sizeof(int) * padded.size(), cudaMemcpyHostToDevice, s));
+  ZR_TRY(zrnn_beam_decode_batch_device(m, d_src, src_len, S_max, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
+                                       longest_sent, d_ids, d_len, d_sc, s));
+  ZR_CUDA(cudaMemcpyAsync(out_ids, d_ids, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaStreamSynchronize(s));
+  return ZRNN_OK;
+}
+
+}  // extern "C"
