@@ -32,6 +32,10 @@ WORKLOADS = {
     "c2": dict(desc="seq2seq 4x1000 V=50k/50k B=128 S=50 T=50 global-dot attention + feed-input fp32", kind="s2s",
                L=4, H=1000, Vs=50000, Vt=50000, B=128, S=(50, 50), T=(50, 50), att=2, feed=1, scale=0.1,
                dist="uniform", zipf=1.1),
+    # small stand-in with config 2's layer shapes (H=1000, B=128, feed-input, global attention) for profiler captures
+    "c2s": dict(desc="profiling stand-in: 1x1000 V=8k/8k B=128 S=4 T=4 global-dot attention + feed-input fp32", kind="s2s",
+                L=1, H=1000, Vs=8000, Vt=8000, B=128, S=(4, 4), T=(4, 4), att=2, feed=1, scale=0.1,
+                dist="uniform", zipf=1.1),
     "c3": dict(desc="seq2seq 2x1000 V=40k/40k B=64 S~U[10,80] T=60 local-p D=10 + feed-input fp32", kind="s2s",
                L=2, H=1000, Vs=40000, Vt=40000, B=64, S=(10, 80), T=(60, 60), att=1, feed=1, scale=0.1,
                dist="uniform", zipf=1.1),
