@@ -128,6 +128,20 @@ int zrnn_softmax_load(zrnn_softmax* sm, const float* h_D, const float* h_b_d);
  * materialised.  Unsharded layers only. */
 int zrnn_softmax_score(zrnn_softmax* sm, const float* d_h, const int* d_targets, const int* d_mask01, int N,
                        float* d_logp_out, void* stream);
+/* Allocation-free variant of zrnn_softmax_score.  No counterpart in the reference: it exists for hosts that
+ * cannot allocate device memory once they are running - a server whose own arena already owns the whole GPU,
+ * or a latency-bound loop that cannot afford the device-wide stall of cudaMalloc/cudaFree.  Same arguments and
+ * results as zrnn_softmax_score, but the per-tile scratch lives in a fixed 16 MiB array inside the library
+ * (zrnn_softmax_score_noalloc_max_floats() floats, present on every GPU that loads the library until the process
+ * exits) and the call performs no cudaMalloc, cudaFree or other allocating call.
+ * Limit: (2*ceil(V/rows)+1)*N floats must fit, rows = 128 when N >= 96 and V >= 512, else 64; beyond it the call
+ * returns ZRNN_E_ARG with the numbers in zrnn_last_error().  The first call on each device looks up the array's
+ * device address (that device must be current); make that first call before starting any stream capture.
+ * All calls on a device share the one array and it keeps the previous call's contents (the call clears what it
+ * needs cleared); two calls that overlap on the GPU - different streams, or different threads - race. */
+int zrnn_softmax_score_noalloc(zrnn_softmax* sm, const float* d_h, const int* d_targets, const int* d_mask01, int N,
+                               float* d_logp_out, void* stream);
+int zrnn_softmax_score_noalloc_max_floats(void);
 /* Sharded scoring, step 1: per-column (max, sum exp(z-max), target logit or 0) over this shard's rows. */
 int zrnn_softmax_partials(zrnn_softmax* sm, const float* d_h, const int* d_targets, int N, float* d_max,
                           float* d_sum, float* d_tgt, void* stream);

@@ -60,6 +60,9 @@ SIGNATURES = {
                                            ctypes.POINTER(c_void_p)]),
     "zrnn_softmax_load": (ctypes.c_int, [c_void_p, c_float_p, c_float_p]),
     "zrnn_softmax_score": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p]),
+    "zrnn_softmax_score_noalloc": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p,
+                                                  c_void_p]),
+    "zrnn_softmax_score_noalloc_max_floats": (ctypes.c_int, []),
     "zrnn_softmax_partials": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p]),
     "zrnn_softmax_combine": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, c_void_p,

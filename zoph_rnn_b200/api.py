@@ -159,6 +159,13 @@ class softmax_layer:
         check(lib().zrnn_softmax_score(self._h, _ptr(h), _ptr(targets), _ptr(mask01), N, _ptr(out), _stream()))
         return out
 
+    def compute_loss_noalloc(self, h, targets, mask01, out):
+        """compute_loss for callers that may not allocate: scratch comes from the library's built-in array and
+        the result goes into the caller's `out` tensor (see zrnn_softmax_score_noalloc in include/zrnn.h)."""
+        check(lib().zrnn_softmax_score_noalloc(self._h, _ptr(h), _ptr(targets), _ptr(mask01), targets.numel(),
+                                               _ptr(out), _stream()))
+        return out
+
     def partials(self, h, targets):
         N = targets.numel()
         mx, sm, tg = (torch.empty(N, dtype=torch.float32, device="cuda") for _ in range(3))

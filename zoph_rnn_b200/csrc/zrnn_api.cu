@@ -1037,3 +1037,77 @@ int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len
 }
 
 }  // extern "C"
+
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free scoring softmax
+// ------------------------------------------------------------------------------------------
+// Some hosts of this library must not allocate device memory while they run: a serving process that handed the
+// whole GPU to its own arena at start-up (a later cudaMalloc fails or fragments it), and a latency-bound decode
+// loop where cudaMalloc / cudaFree would stall every stream of the device.  zrnn_softmax_score grows its
+// scratch buffers on demand, so it is off limits for them.  The variant below takes its scratch from a fixed
+// array that is part of the library image instead; nothing is allocated, the price is a hard size limit.
+#define ZRNN_NOALLOC_SCRATCH_FLOATS (4u * 1024u * 1024u) /* 16 MiB, held by every GPU that loads the library */
+static __device__ __align__(256) float g_noalloc_scratch[ZRNN_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+// Device address of g_noalloc_scratch per device.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel can use, so the address is looked up once per device (with that device
+// current) and passed to the kernels as an ordinary pointer.
+const int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  ZR_CUDA(cudaGetDevice(&dev));
+  ZR_CHECK(dev >= 0 && dev < kMaxDevices, "softmax_score_noalloc: device index out of range");
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    ZR_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return ZRNN_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int zrnn_softmax_score_noalloc_max_floats(void) { return (int)ZRNN_NOALLOC_SCRATCH_FLOATS; }
+
+int zrnn_softmax_score_noalloc(zrnn_softmax* S, const float* d_h, const int* d_targets, const int* d_mask, int N,
+                               float* d_logp_out, void* stream) {
+  ZR_CHECK(S && d_h && d_targets && d_logp_out && N >= 0, "softmax_score_noalloc: bad arguments");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_score_noalloc: weights not loaded");
+  ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_score_noalloc: layer is vocabulary-sharded");
+  if (N == 0) return ZRNN_OK;
+  const int tile = (N >= 96 && S->V >= 512) ? 1 : 0;  // same tiling rule as zrnn_softmax_score
+  const int rows = zrnn::gemm_rows_per_tile(1, tile);
+  const int np = (S->V + rows - 1) / rows;
+  const size_t need = (2 * (size_t)np + 1) * (size_t)N;  // per-tile (max, sum) pairs + one target logit per column
+  if (need > ZRNN_NOALLOC_SCRATCH_FLOATS)
+    return fail(ZRNN_E_ARG, "softmax_score_noalloc: needs " + std::to_string(need) + " scratch floats for V=" +
+                                std::to_string(S->V) + ", N=" + std::to_string(N) + " but the built-in scratch holds " +
+                                std::to_string(ZRNN_NOALLOC_SCRATCH_FLOATS) + "; split the columns or use zrnn_softmax_score");
+  float* scratch = nullptr;
+  ZR_TRY(noalloc_scratch(&scratch));
+  cudaStream_t st = (cudaStream_t)stream;
+  float* pm = scratch;
+  float* ps = scratch + (size_t)np * N;
+  float* tgt = scratch + 2 * (size_t)np * N;
+  // the array still holds the previous call's numbers: the target logits must start from zero, the partials are
+  // fully overwritten by the GEMM epilogue
+  ZR_CUDA(cudaMemsetAsync(tgt, 0, sizeof(float) * (size_t)N, st));
+  zrnn::GemmArgs g;
+  std::memset(&g, 0, sizeof(g));
+  g.nsrc = 1;
+  g.src[0].A[0] = S->D; g.src[0].lda = S->V; g.src[0].B = d_h; g.src[0].ldb = S->H; g.src[0].K = S->H;
+  g.M = S->V; g.N = N; g.bias[0] = S->b;
+  g.target = d_targets; g.target_offset = 0;
+  g.part_max = pm; g.part_sum = ps; g.tgt_logit = tgt;
+  ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
+  ZR_CUDA(zrnn::launch_lse_combine(pm, ps, tgt, np, N, d_mask, d_logp_out, st));
+  return ZRNN_OK;
+}
+
+}  // extern "C"
