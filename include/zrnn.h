@@ -55,6 +55,16 @@ void zrnn_reset_launch_count(void);
 int zrnn_kernel_timing(int on);
 int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total_ms);
 
+/* The GEMM building block: C[n_rows x m_cols] = W[n_rows x K] * X[K x m_cols], all column-major fp32, as the
+ * reference's cublas_gemm_wrapper (src/BZ_CUDA_UTIL.h:691-696) called with CUBLAS_OP_N, CUBLAS_OP_N.
+ * mode 0 = exact fp32 FMA kernel; 1 = tcgen05 tensor cores on bf16-rounded operands; 2 = tcgen05 tf32;
+ * 3 = tcgen05 3xTF32 (operands split into tf32 hi + lo parts, fp32-level accuracy).  Synchronous; allocates
+ * scratch for the packed operands.  Returns ZRNN_E_TIMEOUT if a bounded device-side wait gave up. */
+int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw, const float* d_X, int ldx,
+              float* d_C, int ldc, void* stream);
+/* Reads and clears the device-side error word of the tensor-core kernels (0 = none). */
+int zrnn_tc_error(void);
+
 /* ------------------------------------------------------------------------------------------
  * Input preparation.  Replaces vocab_to_01 / vocab_to_nonM1 (src/custom_kernels.h:9-32), called
  * from Input_To_Hidden_Layer::prep_GPU_vocab_indices (src/Input_To_Hidden_Layer.hpp:1178-1225):

@@ -40,6 +40,9 @@ SIGNATURES = {
     "zrnn_kernel_timing": (ctypes.c_int, [ctypes.c_int]),
     "zrnn_kernel_timing_read": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_longlong),
                                                ctypes.POINTER(ctypes.c_double)]),
+    "zrnn_gemm": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_void_p, ctypes.c_int,
+                                 c_void_p, ctypes.c_int, c_void_p, ctypes.c_int, c_void_p]),
+    "zrnn_tc_error": (ctypes.c_int, []),
     "zrnn_prep_vocab_indices": (ctypes.c_int, [c_void_p, ctypes.c_int, c_void_p, c_void_p, c_void_p]),
     "zrnn_ih_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_void_p)]),
     "zrnn_hh_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_void_p)]),

@@ -45,6 +45,14 @@ def prep_vocab_indices(ids_raw):
     return ids, mask
 
 
+def gemm(W, X, n_rows, m_cols, K, mode=0):
+    """C = W * X (column-major flat CUDA tensors), the reference's cublas_gemm_wrapper N/N case.
+    mode 0 fp32 FMA, 1 bf16 tensor cores, 2 tf32, 3 3xTF32."""
+    C = torch.empty(n_rows * m_cols, dtype=torch.float32, device="cuda")
+    check(lib().zrnn_gemm(mode, n_rows, m_cols, K, _ptr(W), n_rows, _ptr(X), K, _ptr(C), n_rows, _stream()))
+    return C
+
+
 class _LstmLayer:
     def __init__(self):
         self._h = ctypes.c_void_p()

@@ -2,6 +2,8 @@
 // Layouts follow the reference: column-major, activations H x B, ids time-major int32.
 #include "kernels.cuh"
 
+#include <cuda_bf16.h>
+
 #include <cfloat>
 #include <cstdint>
 
@@ -87,6 +89,70 @@ cudaError_t launch_fill_int(int* p, int v, size_t n, cudaStream_t st) {
   if (n == 0) return cudaSuccess;
   size_t blocks = (n + 255) / 256;
   fill_int_kernel<<<(unsigned)(blocks > 1184 ? 1184 : blocks), 256, 0, st>>>(p, v, n);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
+// operand preparation for the tensor-core GEMMs
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tf32_round_prep(float x) {
+  unsigned u = __float_as_uint(x);
+  if ((u & 0x7f800000u) == 0x7f800000u) return x;
+  return __uint_as_float((u + 0x1000u) & 0xffffe000u);
+}
+__device__ __forceinline__ void store_op(void* hi, float* lo, int mode, size_t idx, float v) {
+  if (mode == 0) {
+    reinterpret_cast<__nv_bfloat16*>(hi)[idx] = __float2bfloat16(v);
+  } else if (mode == 1) {
+    reinterpret_cast<float*>(hi)[idx] = v;
+  } else {
+    const float h = tf32_round_prep(v);
+    reinterpret_cast<float*>(hi)[idx] = h;
+    lo[idx] = v - h;
+  }
+}
+__global__ void pack_weights_kernel(const PackArgs a) {
+  const int rows_per_tile = a.G * a.TH;
+  const long long total = (long long)a.n_tiles * rows_per_tile * a.K;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    // hid fastest so the column-major source is read contiguously
+    const int j = (int)(e % a.TH);
+    long long r = e / a.TH;
+    const int tile = (int)(r % a.n_tiles);
+    r /= a.n_tiles;
+    const int g = (int)(r % a.G);
+    const int k = (int)(r / a.G);
+    const int hid = tile * a.TH + j;
+    const float v = hid < a.H ? a.src[g][(size_t)k * a.lda + hid] : 0.f;
+    const size_t prow = (size_t)tile * rows_per_tile + (size_t)g * a.TH + j;
+    store_op(a.dst_hi, a.dst_lo, a.op_mode, prow * a.ld_dst + a.koff + k, v);
+  }
+}
+cudaError_t launch_pack_weights(const PackArgs& a, cudaStream_t st) {
+  const long long total = (long long)a.n_tiles * a.G * a.TH * a.K;
+  if (total <= 0) return cudaSuccess;
+  long long blocks = (total + 255) / 256;
+  pack_weights_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+__global__ void convert_rows_kernel(const float* __restrict__ src, long long rows, int K, long long ld_src, int mode,
+                                    void* dst_hi, float* dst_lo, long long ld_dst) {
+  const long long total = rows * K;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const long long r = e / K;
+    const int k = (int)(e % K);
+    store_op(dst_hi, dst_lo, mode, (size_t)(r * ld_dst + k), src[r * ld_src + k]);
+  }
+}
+cudaError_t launch_convert_rows(const float* src, long long rows, int K, long long ld_src, int op_mode, void* dst_hi,
+                                float* dst_lo, long long ld_dst, cudaStream_t st) {
+  const long long total = rows * K;
+  if (total <= 0) return cudaSuccess;
+  long long blocks = (total + 255) / 256;
+  convert_rows_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, st>>>(src, rows, K, ld_src, op_mode,
+                                                                                        dst_hi, dst_lo, ld_dst);
   count_launch();
   return cudaGetLastError();
 }

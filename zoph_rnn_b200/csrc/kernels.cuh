@@ -122,6 +122,23 @@ struct BeamArgs {
 cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st);
 cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st);
 
+// ---- operand preparation for the tensor-core GEMMs (K-major rows; see tc_gemm.cuh)
+// op_mode: 0 = bf16, 1 = fp32 as is, 2 = fp32 split into hi (tf32-representable) + lo (residual)
+// Packs G column-major (H x K, leading dimension lda) matrices into K-major rows: packed row
+// r = tile*(G*TH) + g*TH + j holds row hid = tile*TH + j of matrix g (zero when hid >= H), written at
+// dst[r*ld_dst + koff + k].  n_tiles = ceil(H / TH).
+struct PackArgs {
+  const float* src[4];
+  int G, H, K, lda, TH, n_tiles;
+  void* dst_hi;
+  float* dst_lo;
+  int op_mode, ld_dst, koff;
+};
+cudaError_t launch_pack_weights(const PackArgs& a, cudaStream_t st);
+// Converts `rows` K-major rows (fp32, stride ld_src) into operand form at dst[r*ld_dst + k].
+cudaError_t launch_convert_rows(const float* src, long long rows, int K, long long ld_src, int op_mode, void* dst_hi,
+                                float* dst_lo, long long ld_dst, cudaStream_t st);
+
 // misc
 cudaError_t launch_fill_int(int* p, int v, size_t n, cudaStream_t st);
 // len[b] = number of unmasked steps of column b in mask[T x B]; offset[b] = T - len[b]

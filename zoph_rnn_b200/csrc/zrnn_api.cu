@@ -13,6 +13,7 @@
 #include "../../include/zrnn.h"
 #include "kernels.cuh"
 #include "model_file.hpp"
+#include "tc_gemm.cuh"
 
 namespace {
 
@@ -1107,6 +1108,98 @@ int zrnn_softmax_score_noalloc(zrnn_softmax* S, const float* d_h, const int* d_t
   g.part_max = pm; g.part_sum = ps; g.tgt_logit = tgt;
   ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
   ZR_CUDA(zrnn::launch_lse_combine(pm, ps, tgt, np, N, d_mask, d_logp_out, st));
+  return ZRNN_OK;
+}
+
+}  // extern "C"
+
+
+// ------------------------------------------------------------------------------------------
+// Stand-alone GEMM (the reference's cublas_gemm_wrapper, src/BZ_CUDA_UTIL.h:691-696, N/N case):
+//   C[n_rows x m_cols] = W[n_rows x K] * X[K x m_cols], all column-major.
+// ------------------------------------------------------------------------------------------
+namespace {
+int* tc_error_word() {
+  static int* p = nullptr;
+  if (!p) {
+    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+  }
+  return p;
+}
+}  // namespace
+
+extern "C" {
+
+int zrnn_tc_error(void) {
+  int* d = tc_error_word();
+  int v = 0;
+  if (!d) return -1;
+  if (cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(d, 0, sizeof(int));
+  return v;
+}
+
+int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw, const float* d_X, int ldx,
+              float* d_C, int ldc, void* stream) {
+  ZR_CHECK(d_W && d_X && d_C && n_rows > 0 && m_cols > 0 && K > 0, "gemm: bad arguments");
+  ZR_CHECK(ldw >= n_rows && ldx >= K && ldc >= n_rows, "gemm: leading dimension too small");
+  ZR_CHECK(mode >= 0 && mode <= 3, "gemm: mode must be 0 (fp32 SIMT), 1 (bf16), 2 (tf32) or 3 (3xtf32)");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode == 0) {
+    zrnn::GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.nsrc = 1;
+    g.src[0].A[0] = d_W; g.src[0].lda = ldw; g.src[0].B = d_X; g.src[0].ldb = ldx; g.src[0].K = K;
+    g.M = n_rows; g.N = m_cols; g.C = d_C; g.ldc = ldc;
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (n_rows >= 256 && m_cols >= 96) ? 1 : 0, st));
+    return ZRNN_OK;
+  }
+  const int tcm = mode == 1 ? zrnn::TC_BF16 : (mode == 2 ? zrnn::TC_TF32 : zrnn::TC_TF32X3);
+  const int op_mode = mode == 1 ? 0 : (mode == 2 ? 1 : 2);
+  const int eb = mode == 1 ? 2 : 4;
+  const int kb_elems = 128 / eb;
+  const int Kpad = (K + 63) / 64 * 64;
+  const int BN = n_rows >= 256 ? 256 : (n_rows >= 128 ? 128 : (n_rows >= 64 ? 64 : 32));
+  const int n_tiles = (n_rows + BN - 1) / BN;
+  const size_t a_elems = (size_t)m_cols * Kpad, b_elems = (size_t)n_tiles * BN * Kpad;
+  DevBuf a_hi, a_lo, b_hi, b_lo;
+  ZR_CUDA(a_hi.reserve(a_elems * eb));
+  ZR_CUDA(b_hi.reserve(b_elems * eb));
+  ZR_CUDA(cudaMemsetAsync(a_hi.p, 0, a_elems * eb, st));
+  ZR_CUDA(cudaMemsetAsync(b_hi.p, 0, b_elems * eb, st));
+  if (mode == 3) {
+    ZR_CUDA(a_lo.reserve(a_elems * 4));
+    ZR_CUDA(b_lo.reserve(b_elems * 4));
+    ZR_CUDA(cudaMemsetAsync(a_lo.p, 0, a_elems * 4, st));
+    ZR_CUDA(cudaMemsetAsync(b_lo.p, 0, b_elems * 4, st));
+  }
+  ZR_CUDA(zrnn::launch_convert_rows(d_X, m_cols, K, ldx, op_mode, a_hi.p, a_lo.as<float>(), Kpad, st));
+  zrnn::PackArgs pk;
+  std::memset(&pk, 0, sizeof(pk));
+  pk.src[0] = d_W; pk.G = 1; pk.H = n_rows; pk.K = K; pk.lda = ldw; pk.TH = BN; pk.n_tiles = n_tiles;
+  pk.dst_hi = b_hi.p; pk.dst_lo = b_lo.as<float>(); pk.op_mode = op_mode; pk.ld_dst = Kpad; pk.koff = 0;
+  ZR_CUDA(zrnn::launch_pack_weights(pk, st));
+  zrnn::TcParams tp;
+  std::memset(&tp, 0, sizeof(tp));
+  bool ok = zrnn::make_kmajor_map(&tp.a[0], a_hi.p, eb, Kpad, m_cols, Kpad, 128) &&
+            zrnn::make_kmajor_map(&tp.b, b_hi.p, eb, Kpad, (long long)n_tiles * BN, Kpad, BN);
+  if (mode == 3)
+    ok = ok && zrnn::make_kmajor_map(&tp.a_lo[0], a_lo.p, 4, Kpad, m_cols, Kpad, 128) &&
+         zrnn::make_kmajor_map(&tp.b_lo, b_lo.p, 4, Kpad, (long long)n_tiles * BN, Kpad, BN);
+  if (!ok) {
+    a_hi.release(); a_lo.release(); b_hi.release(); b_lo.release();
+    return fail(ZRNN_E_CUDA, "gemm: cannot encode TMA tensor maps");
+  }
+  tp.nsrc = 1; tp.kblocks[0] = (K + kb_elems - 1) / kb_elems; tp.b_koff[0] = 0;
+  tp.M = m_cols; tp.N = n_rows; tp.C = d_C; tp.ldc = ldc; tp.err = tc_error_word();
+  cudaError_t e = zrnn::launch_tc_gemm(tp, BN, tcm, zrnn::TC_EPI_STORE, st);
+  cudaError_t e2 = cudaStreamSynchronize(st);
+  a_hi.release(); a_lo.release(); b_hi.release(); b_lo.release();
+  ZR_CUDA(e);
+  ZR_CUDA(e2);
+  const int code = zrnn_tc_error();
+  if (code != 0) return fail(ZRNN_E_TIMEOUT, "gemm: a bounded device wait gave up (role " + std::to_string(code) + ")");
   return ZRNN_OK;
 }
 
