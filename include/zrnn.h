@@ -36,7 +36,15 @@ typedef enum {
   ZRNN_E_STATE = 6    /* call order violated (e.g. forward before load) */
 } zrnn_status;
 
-typedef enum { ZRNN_F32 = 0, ZRNN_BF16 = 1 } zrnn_dtype;
+/* Arithmetic of the GEMM-shaped work (state, biases, activations functions and softmax reductions are fp32 in
+ * every mode):
+ *   ZRNN_F32        fp32-accurate: tcgen05 3xTF32 tensor-core kernels when H >= 128 and H % 4 == 0, else the
+ *                   exact fp32 FMA kernels (environment ZRNN_FP32_ENGINE=simt forces the latter)
+ *   ZRNN_BF16       tcgen05 tensor cores on bf16-rounded weights and activations (H % 8 == 0)
+ *   ZRNN_TF32       tcgen05 tensor cores, single-pass tf32 (H % 4 == 0)
+ *   ZRNN_F32_SIMT   always the exact fp32 FMA kernels
+ *   ZRNN_F32_3XTF32 always the 3xTF32 tensor-core kernels (H % 4 == 0) */
+typedef enum { ZRNN_F32 = 0, ZRNN_BF16 = 1, ZRNN_TF32 = 2, ZRNN_F32_SIMT = 3, ZRNN_F32_3XTF32 = 4 } zrnn_dtype;
 typedef enum { ZRNN_ATT_NONE = 0, ZRNN_ATT_LOCAL_P = 1, ZRNN_ATT_GLOBAL_DOT = 2 } zrnn_attention_type;
 
 const char* zrnn_status_string(int status);

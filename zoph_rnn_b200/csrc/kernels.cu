@@ -23,6 +23,16 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 __device__ __forceinline__ float sigmoidf_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ void att_store_op(const AttArgs& a, int b, int i, float v) {
+  const size_t idx = (size_t)b * a.ld_op + i;
+  if (a.op_b16) reinterpret_cast<__nv_bfloat16*>(a.op_b16)[idx] = __float2bfloat16(v);
+  if (a.op_hi) {
+    unsigned u = __float_as_uint(v);
+    const float hi = ((u & 0x7f800000u) == 0x7f800000u) ? v : __uint_as_float((u + 0x1000u) & 0xffffe000u);
+    a.op_hi[idx] = hi;
+    if (a.op_lo) a.op_lo[idx] = v - hi;
+  }
+}
 
 // block-wide sum; result valid in every thread. `red` needs 32 floats.
 __device__ float block_sum(float v, float* red) {
@@ -182,6 +192,26 @@ cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_c
   if (n_cols <= 0) return cudaSuccess;
   const int threads = H >= 512 ? 128 : 64;
   gather_columns_kernel<<<n_cols > 148 * 16 ? 148 * 16 : n_cols, threads, 0, st>>>(W, H, ids, n_cols, x);
+  count_launch();
+  return cudaGetLastError();
+}
+
+__global__ void gather_rows16_kernel(const uint4* __restrict__ src, int vec_per_row, const int* __restrict__ ids,
+                                     int n_rows, uint4* __restrict__ dst) {
+  for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
+    int id = ids[r];
+    if (id < 0) id = 0;
+    const uint4* s = src + (size_t)id * vec_per_row;
+    uint4* d = dst + (size_t)r * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) d[i] = __ldg(s + i);
+  }
+}
+cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, const int* ids, int n_rows, void* dst,
+                                 cudaStream_t st) {
+  if (n_rows <= 0) return cudaSuccess;
+  if (row_bytes % 16 != 0) return cudaErrorInvalidValue;
+  gather_rows16_kernel<<<n_rows > 148 * 16 ? 148 * 16 : n_rows, 128, 0, st>>>(
+      reinterpret_cast<const uint4*>(src), (int)(row_bytes / 16), ids, n_rows, reinterpret_cast<uint4*>(dst));
   count_launch();
   return cudaGetLastError();
 }
@@ -567,7 +597,7 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
   const int H = a.H, Wn = 2 * a.D + 1, sb = b / a.cols_per_sent;
   float* c = a.c_t + (size_t)b * H;
   if (a.mask && a.mask[b] != 1) {  // create_indicies_kernel: every window slot is -1 -> context 0
-    for (int i = tid; i < H; i += blockDim.x) c[i] = 0.f;
+    for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
     if (a.align_out)
       for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
     return;
@@ -627,6 +657,7 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
       if (slot != -1) acc += s_al[j] * a.hs[((size_t)slot * a.B_src + sb) * H + i];
     }
     c[i] = acc;
+    att_store_op(a, b, i, acc);
   }
 }
 cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st) {
@@ -646,7 +677,7 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
   if (a.align_out)
     for (int s = tid; s < a.S_max; s += blockDim.x) a.align_out[(size_t)s * a.B + b] = 0.f;
   if (a.mask && a.mask[b] != 1) {
-    for (int i = tid; i < H; i += blockDim.x) c[i] = 0.f;
+    for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
     return;
   }
   const int len = a.len[sb], off = a.offset[sb];
@@ -683,6 +714,7 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
     for (int pos = 0; pos < len; ++pos)
       acc += (s_sc[pos] * inv) * a.hs[((size_t)(len - 1 - pos + off) * a.B_src + sb) * H + i];
     c[i] = acc;
+    att_store_op(a, b, i, acc);
   }
 }
 cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {

@@ -13,6 +13,9 @@ cudaError_t launch_prep_ids(const int* raw, int n, int* nonm1, int* mask01, cuda
 
 // ---- embedding column gather (replaces sparse_lookup_kernel, src/custom_kernels.h:340-348)
 cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_cols, float* x, cudaStream_t st);
+// same for rows of `row_bytes` bytes (a multiple of 16) of any element type: dst row n = src row ids[n]
+cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, const int* ids, int n_rows, void* dst,
+                                 cudaStream_t st);
 
 // ---- generic column gather over several H x ncols arrays at once: dst[a][:,c] = src[a][:,map[c]]
 // (replaces the per-column cudaMemcpy loops of swap_states_decoding / transfer_decoding_states_GPU,
@@ -96,6 +99,11 @@ struct AttArgs {
   int ld_tq;
   float* c_t;          // context out, H x B
   float* align_out;    // optional
+  // optional copies of the context in tensor-core operand form (row b at + b*ld_op)
+  void* op_b16;
+  float* op_hi;
+  float* op_lo;
+  int ld_op;
 };
 cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st);
 cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);

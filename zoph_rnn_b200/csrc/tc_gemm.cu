@@ -118,7 +118,7 @@ __device__ __forceinline__ void store_operand(const TcParams& p, size_t idx, flo
   if (p.op_hi) {
     const float hi = tf32_round_dev(v);
     p.op_hi[idx] = hi;
-    p.op_lo[idx] = v - hi;
+    if (p.op_lo) p.op_lo[idx] = v - hi;
   }
 }
 
@@ -129,13 +129,29 @@ __host__ __device__ constexpr int num_stages(int BN, int mode) {
   return s > 8 ? 8 : s;
 }
 
+// 3xTF32 keeps fp32-level accuracy only if the tensor core's accumulator is not asked to absorb hundreds of
+// additions: its fp32 accumulation truncates toward zero (measured: a relative shrink of ~8e-6 after 375
+// additions).  So in that mode the hi*hi products are spread round-robin over NACC TMEM accumulators (each sees
+// 1/NACC of the additions on a smaller partial sum), the two small cross terms go to an accumulator of their own,
+// and the epilogue adds the partial sums with round-to-nearest fp32.
+__host__ __device__ constexpr int num_acc(int BN, int mode) {
+  return mode != TC_TF32X3 ? 1 : (BN <= 32 ? 8 : (BN <= 64 ? 4 : (BN <= 128 ? 2 : 1)));
+}
+__host__ __device__ constexpr int tmem_cols(int BN, int mode) {
+  int need = (mode == TC_TF32X3 ? num_acc(BN, mode) + 1 : 1) * BN;
+  int c = 32;
+  while (c < need) c *= 2;
+  return c;
+}
+
 template <int BN, int MODE, int EPI>
 __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
   constexpr int ST = num_stages(BN, MODE);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
   constexpr uint32_t IDESC = make_idesc(MODE == TC_BF16 ? 1u : 2u, BN);
-  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr int NACC = num_acc(BN, MODE);
+  constexpr int TMEM_COLS = tmem_cols(BN, MODE);
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[ST];
   __shared__ __align__(8) uint64_t empty_bar[ST];
@@ -211,14 +227,16 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         const uint32_t a_addr = smem_u32(tiles + (size_t)st * STAGE);
         const uint32_t b_addr = a_addr + kABytes;
         const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
+        const uint32_t d_main = tmem_base + (uint32_t)((it % NACC) * BN);  // round-robin over the main accumulators
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte k-block
-          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-          umma<MODE != TC_BF16>(tmem_base, da + 2 * k, db + 2 * k, IDESC, acc);
+          const uint32_t acc = (it >= NACC || k > 0) ? 1u : 0u;
+          umma<MODE != TC_BF16>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
           if (MODE == TC_TF32X3) {
             const uint64_t dal = make_smem_desc(b_addr + BBYTES), dbl = make_smem_desc(b_addr + BBYTES + kABytes);
-            umma<1>(tmem_base, dal + 2 * k, db + 2 * k, IDESC, 1u);
-            umma<1>(tmem_base, da + 2 * k, dbl + 2 * k, IDESC, 1u);
+            const uint32_t d_cross = tmem_base + (uint32_t)(NACC * BN);
+            umma<1>(d_cross, dal + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            umma<1>(d_cross, da + 2 * k, dbl + 2 * k, IDESC, 1u);
           }
         }
         umma_commit(&empty_bar[st]);
@@ -231,6 +249,25 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
     const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
     const bool ready = (total_kb == 0) ? false : mbar_wait(&accum_bar, 0, &abort_s, p.err, 3);
     tc_fence_after();
+    const int n_main = total_kb < NACC ? total_kb : NACC;  // main accumulators that were written
+    // 8 accumulator columns starting at `col`, summed over the partial accumulators
+    auto load8 = [&](int col, float* v) {
+      tmem_ld8(taddr + col, v);
+      if (MODE == TC_TF32X3) {
+        float t[8];
+        for (int a = 1; a < n_main; ++a) {
+          tmem_ld8(taddr + a * BN + col, t);
+          tmem_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] += t[u];
+        }
+        tmem_ld8(taddr + NACC * BN + col, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] += t[u];
+      }
+      tmem_wait_ld();
+    };
     if (ready) {
       const bool row_ok = row < p.M;
       const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
@@ -241,8 +278,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         for (int j0 = 0; j0 < TH; j0 += 8) {
           float g[4][8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) tmem_ld8(taddr + q * TH + j0, g[q]);
-          tmem_wait_ld();
+          for (int q = 0; q < 4; ++q) load8(q * TH + j0, g[q]);
           if (row_ok) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -258,7 +294,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
                 h *= mk;
                 c *= mk;
                 p.c_out[idx] = c;
-                p.C[(size_t)row * p.ldc + hid] = h;
+                if (p.C) p.C[(size_t)row * p.ldc + hid] = h;
                 store_operand(p, (size_t)row * p.ld_op + hid, h);
               }
             }
@@ -268,8 +304,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         const int n0 = n_tile * BN;
         for (int c0 = 0; c0 < BN; c0 += 8) {
           float v[8];
-          tmem_ld8(taddr + c0, v);
-          tmem_wait_ld();
+          load8(c0, v);
           if (row_ok) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -290,15 +325,14 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         float mx = -INFINITY, sm = 0.f;
         for (int c0 = 0; c0 < BN; c0 += 8) {
           float v[8];
-          tmem_ld8(taddr + c0, v);
-          tmem_wait_ld();
+          load8(c0, v);
           float cm = -INFINITY;
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int n = n0 + c0 + u;
             v[u] = (n < p.N) ? v[u] + (p.bias ? p.bias[n] : 0.f) : -INFINITY;
             cm = fmaxf(cm, v[u]);
-            if (n == tg) p.tgt_logit[row] = v[u];
+            if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
           }
           if (cm > mx) {
             sm *= expf(mx - cm);  // expf(-inf) = 0 on the first chunk

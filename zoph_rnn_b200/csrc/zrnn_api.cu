@@ -120,10 +120,92 @@ int check_device() {
 }  // namespace
 
 // ------------------------------------------------------------------------------------------
+// arithmetic engines
+// ------------------------------------------------------------------------------------------
+// ENG_SIMT : exact fp32 FMA kernels (kernels.cu)            - any shape
+// ENG_X3   : tcgen05 3xTF32 (operands split into hi + lo)   - fp32-level accuracy, H % 4 == 0
+// ENG_BF16 : tcgen05 on bf16-rounded weights / activations  - H % 8 == 0
+// ENG_TF32 : tcgen05 single-pass tf32                       - H % 4 == 0
+enum { ENG_SIMT = 0, ENG_BF16 = 1, ENG_TF32 = 2, ENG_X3 = 3 };
+
+namespace {
+
+int eng_eb(int e) { return e == ENG_BF16 ? 2 : 4; }
+int eng_opmode(int e) { return e == ENG_BF16 ? 0 : (e == ENG_TF32 ? 1 : 2); }
+int eng_tcmode(int e) { return e == ENG_BF16 ? zrnn::TC_BF16 : (e == ENG_TF32 ? zrnn::TC_TF32 : zrnn::TC_TF32X3); }
+int round64(int x) { return (x + 63) / 64 * 64; }
+
+int pick_engine(int dtype, int H, int* eng) {
+  switch (dtype) {
+    case ZRNN_F32: {
+      const char* e = std::getenv("ZRNN_FP32_ENGINE");
+      const bool want_simt = e && std::strcmp(e, "simt") == 0;
+      *eng = (!want_simt && H % 4 == 0 && H >= 128) ? ENG_X3 : ENG_SIMT;
+      return ZRNN_OK;
+    }
+    case ZRNN_F32_SIMT: *eng = ENG_SIMT; return ZRNN_OK;
+    case ZRNN_F32_3XTF32:
+      ZR_CHECK(H % 4 == 0, "3xTF32 arithmetic needs H to be a multiple of 4");
+      *eng = ENG_X3;
+      return ZRNN_OK;
+    case ZRNN_BF16:
+      ZR_CHECK(H % 8 == 0, "bf16 arithmetic needs H to be a multiple of 8");
+      *eng = ENG_BF16;
+      return ZRNN_OK;
+    case ZRNN_TF32:
+      ZR_CHECK(H % 4 == 0, "tf32 arithmetic needs H to be a multiple of 4");
+      *eng = ENG_TF32;
+      return ZRNN_OK;
+  }
+  return fail(ZRNN_E_ARG, "unknown dtype");
+}
+
+// weights / tables in tensor-core operand form (K-major rows)
+struct OpMem {
+  void* hi = nullptr;
+  float* lo = nullptr;
+  int alloc(size_t elems, int eng) {
+    release();
+    ZR_CUDA(cudaMalloc(&hi, elems * eng_eb(eng)));
+    ZR_CUDA(cudaMemset(hi, 0, elems * eng_eb(eng)));
+    if (eng == ENG_X3) {
+      ZR_CUDA(cudaMalloc((void**)&lo, elems * 4));
+      ZR_CUDA(cudaMemset(lo, 0, elems * 4));
+    }
+    return ZRNN_OK;
+  }
+  void release() {
+    cudaFree(hi);
+    cudaFree(lo);
+    hi = nullptr;
+    lo = nullptr;
+  }
+};
+
+// An activation matrix: column-major fp32 (H x cols) and/or its operand-form copy (cols rows of Kpad elements)
+struct Act {
+  float* f32 = nullptr;
+  void* hi = nullptr;
+  float* lo = nullptr;
+};
+struct Geom {
+  int H, Kpad, eng;
+};
+Act act_at(const Act& a, size_t col, const Geom& g) {
+  Act r;
+  r.f32 = a.f32 ? a.f32 + col * g.H : nullptr;
+  r.hi = a.hi ? (char*)a.hi + col * g.Kpad * eng_eb(g.eng) : nullptr;
+  r.lo = a.lo ? a.lo + col * g.Kpad : nullptr;
+  return r;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
 // layer objects
 // ------------------------------------------------------------------------------------------
 struct zrnn_lstm_layer {
-  int H = 0, V = 0, feed = 0, dtype = 0, is_ih = 0;
+  int H = 0, V = 0, feed = 0, dtype = 0, is_ih = 0, eng = ENG_SIMT;
   bool loaded = false;
   float* W = nullptr;   // embedding H x V
   float* Wh = nullptr;  // 4 x (H x H): gates i,f,g,o
@@ -131,14 +213,20 @@ struct zrnn_lstm_layer {
   float* Q = nullptr;   // 4 x (H x H), feed-input only
   float* b = nullptr;   // 4 x H
   DevBuf x;             // gather scratch for zrnn_ih_forward
+  // tensor-core form: packed [n_tiles*BN rows] x [nsrc*Kpad] with the K axis = (x | h | htild)
+  int Kpad = 0, BN = 32, n_tiles = 0;
+  OpMem Wcat, emb;
+  CUtensorMap wmap, wmap_lo;
+  DevBuf sc_x, sc_h, sc_q, sc_xl, sc_hl, sc_ql;  // operand scratch for the fp32 layer-level entry points
   ~zrnn_lstm_layer() {
     cudaFree(W); cudaFree(Wh); cudaFree(Mx); cudaFree(Q); cudaFree(b);
-    x.release();
+    x.release(); Wcat.release(); emb.release();
+    sc_x.release(); sc_h.release(); sc_q.release(); sc_xl.release(); sc_hl.release(); sc_ql.release();
   }
 };
 
 struct zrnn_attention {
-  int H = 0, D = 0, type = 0, dtype = 0;
+  int H = 0, D = 0, type = 0, dtype = 0, eng = ENG_SIMT;
   bool loaded = false;
   float* WpWaT = nullptr;  // stacked [W_p ; W_a^T], 2H x H column-major (local-p only)
   float* v_p = nullptr;
@@ -150,28 +238,67 @@ struct zrnn_attention {
   const int* len = nullptr;
   const int* off = nullptr;
   DevBuf tq, ctx;
+  int Kpad = 0, BN = 32;
+  OpMem WpWaT_op, Wc_op;  // [2H rows x Kpad], [H rows x 2*Kpad]
+  CUtensorMap pmap, pmap_lo, cmap, cmap_lo;
+  DevBuf ctx_hi, ctx_lo, sc_h, sc_hl;
   ~zrnn_attention() {
     cudaFree(WpWaT); cudaFree(v_p); cudaFree(bias); cudaFree(Wc1); cudaFree(Wc2);
-    tq.release(); ctx.release();
+    tq.release(); ctx.release(); WpWaT_op.release(); Wc_op.release();
+    ctx_hi.release(); ctx_lo.release(); sc_h.release(); sc_hl.release();
   }
 };
 
 struct zrnn_softmax {
-  int V = 0, H = 0, dtype = 0, lo = 0, hi = 0;
+  int V = 0, H = 0, dtype = 0, lo = 0, hi = 0, eng = ENG_SIMT;
   bool loaded = false;
   float* D = nullptr;  // (hi-lo) x H
   float* b = nullptr;  // hi-lo
   DevBuf parts, tgt, logits;
+  int Kpad = 0, BN = 128, n_tiles = 0;
+  OpMem D_op;  // [n_tiles*BN rows x Kpad]
+  CUtensorMap dmap, dmap_lo;
+  DevBuf sc_h, sc_hl;
   ~zrnn_softmax() {
     cudaFree(D); cudaFree(b);
-    parts.release(); tgt.release(); logits.release();
+    parts.release(); tgt.release(); logits.release(); D_op.release(); sc_h.release(); sc_hl.release();
   }
 };
 
 namespace {
 
-int lstm_cell_launch(zrnn_lstm_layer* L, const float* x, const int* mask, const float* h_prev, const float* c_prev,
-                     const float* htild, int B, float* h_out, float* c_out, float* h_out2, cudaStream_t st) {
+int* tc_error_word() {
+  static int* p = nullptr;
+  if (!p) {
+    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+  }
+  return p;
+}
+
+// tensor maps of an activation operand: `rows` rows of H valid elements, stride Kpad
+int act_maps(const Act& a, int eng, int H, int Kpad, int rows, CUtensorMap* hi, CUtensorMap* lo) {
+  if (!a.hi) return fail(ZRNN_E_STATE, "internal: activation has no operand-form copy");
+  if (!zrnn::make_kmajor_map(hi, a.hi, eng_eb(eng), H, rows, Kpad, 128))
+    return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand");
+  if (eng == ENG_X3 && !zrnn::make_kmajor_map(lo, a.lo, 4, H, rows, Kpad, 128))
+    return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand (lo)");
+  return ZRNN_OK;
+}
+
+// fp32 activation (H x cols, column-major) -> operand form in scratch buffers
+int to_operand(const float* f32, int H, int Kpad, int cols, int eng, DevBuf& hi, DevBuf& lo, Act* out, cudaStream_t st) {
+  ZR_CUDA(hi.reserve((size_t)cols * Kpad * eng_eb(eng)));
+  if (eng == ENG_X3) ZR_CUDA(lo.reserve((size_t)cols * Kpad * 4));
+  ZR_CUDA(zrnn::launch_convert_rows(f32, cols, H, H, eng_opmode(eng), hi.p, lo.as<float>(), Kpad, st));
+  out->f32 = const_cast<float*>(f32);
+  out->hi = hi.p;
+  out->lo = eng == ENG_X3 ? lo.as<float>() : nullptr;
+  return ZRNN_OK;
+}
+
+int lstm_cell_simt(zrnn_lstm_layer* L, const float* x, const int* mask, const float* h_prev, const float* c_prev,
+                   const float* htild, int B, float* h_out, float* c_out, cudaStream_t st) {
   const int H = L->H;
   const size_t HH = (size_t)H * H;
   zrnn::GemmArgs g;
@@ -189,65 +316,208 @@ int lstm_cell_launch(zrnn_lstm_layer* L, const float* x, const int* mask, const 
   g.M = H; g.N = B;
   for (int k = 0; k < 4; ++k) g.bias[k] = L->b + (size_t)k * H;
   g.mask = mask;
-  g.c_prev = c_prev; g.h_out = h_out; g.c_out = c_out; g.h_out2 = h_out2;
+  g.c_prev = c_prev; g.h_out = h_out; g.c_out = c_out;
   KScope ks(KC_LSTM, st);
   ZR_CUDA(zrnn::launch_fused_gemm(g, 4, zrnn::EPI_LSTM, 0, st));
   return ZRNN_OK;
 }
 
-int att_forward_launch(zrnn_attention* A, const float* h_t, const int* mask, int B, float* htild, float* align,
-                       cudaStream_t st) {
-  const int H = A->H;
+// One LSTM cell.  x / h_prev / htild and the output are activations in the form the layer's engine needs.
+int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, const int* mask, const float* c_prev,
+                 int B, const Act& out, float* c_out, cudaStream_t st) {
+  if (L->eng == ENG_SIMT)
+    return lstm_cell_simt(L, x.f32, mask, hp.f32, c_prev, q ? q->f32 : nullptr, B, out.f32, c_out, st);
+  const int H = L->H, Kpad = L->Kpad, eng = L->eng;
+  const int kb = (H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng));
+  zrnn::TcParams tp;
+  std::memset(&tp, 0, sizeof(tp));
+  ZR_TRY(act_maps(x, eng, H, Kpad, B, &tp.a[0], &tp.a_lo[0]));
+  ZR_TRY(act_maps(hp, eng, H, Kpad, B, &tp.a[1], &tp.a_lo[1]));
+  tp.nsrc = 2;
+  if (q) {
+    ZR_TRY(act_maps(*q, eng, H, Kpad, B, &tp.a[2], &tp.a_lo[2]));
+    tp.nsrc = 3;
+  }
+  for (int s = 0; s < 3; ++s) { tp.kblocks[s] = kb; tp.b_koff[s] = s * Kpad; }
+  tp.b = L->wmap; tp.b_lo = L->wmap_lo;
+  tp.M = B; tp.N = H; tp.bias = L->b; tp.mask = mask;
+  tp.C = out.f32; tp.ldc = H;
+  tp.op_b16 = eng == ENG_BF16 ? (__nv_bfloat16*)out.hi : nullptr;
+  tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
+  tp.op_lo = out.lo; tp.ld_op = Kpad;
+  if (eng == ENG_TF32 && tp.op_hi) tp.op_lo = nullptr;
+  tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word();
+  KScope ks(KC_LSTM, st);
+  ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st));
+  return ZRNN_OK;
+}
+
+int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const Act& out, float* align,
+                cudaStream_t st) {
+  const int H = A->H, eng = A->eng, Kpad = A->Kpad;
   ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
   KScope ks(KC_ATT, st);
   zrnn::AttArgs a;
   std::memset(&a, 0, sizeof(a));
   a.H = H; a.B = B; a.D = A->D; a.S_max = A->S_max; a.B_src = A->B_src; a.cols_per_sent = A->cols_per_sent;
-  a.hs = A->hs; a.len = A->len; a.offset = A->off; a.mask = mask; a.h_t = h_t;
+  a.hs = A->hs; a.len = A->len; a.offset = A->off; a.mask = mask; a.h_t = h_t.f32;
   a.c_t = A->ctx.as<float>(); a.align_out = align;
+  Act ctx;
+  ctx.f32 = A->ctx.as<float>();
+  if (eng != ENG_SIMT) {
+    ZR_CUDA(A->ctx_hi.reserve((size_t)B * Kpad * eng_eb(eng)));
+    if (eng == ENG_X3) ZR_CUDA(A->ctx_lo.reserve((size_t)B * Kpad * 4));
+    ctx.hi = A->ctx_hi.p;
+    ctx.lo = eng == ENG_X3 ? A->ctx_lo.as<float>() : nullptr;
+    a.ld_op = Kpad;
+    if (eng == ENG_BF16) a.op_b16 = ctx.hi;
+    else { a.op_hi = (float*)ctx.hi; a.op_lo = ctx.lo; }
+  }
   if (A->type == ZRNN_ATT_LOCAL_P) {
     ZR_CUDA(A->tq.reserve(sizeof(float) * (size_t)2 * H * B));
-    zrnn::GemmArgs g;
-    std::memset(&g, 0, sizeof(g));
-    g.nsrc = 1;
-    g.src[0].A[0] = A->WpWaT; g.src[0].lda = 2 * H; g.src[0].B = h_t; g.src[0].ldb = H; g.src[0].K = H;
-    g.M = 2 * H; g.N = B; g.C = A->tq.as<float>(); g.ldc = 2 * H; g.act = 1; g.act_rows = H;
-    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+    if (eng == ENG_SIMT) {
+      zrnn::GemmArgs g;
+      std::memset(&g, 0, sizeof(g));
+      g.nsrc = 1;
+      g.src[0].A[0] = A->WpWaT; g.src[0].lda = 2 * H; g.src[0].B = h_t.f32; g.src[0].ldb = H; g.src[0].K = H;
+      g.M = 2 * H; g.N = B; g.C = A->tq.as<float>(); g.ldc = 2 * H; g.act = 1; g.act_rows = H;
+      ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+    } else {
+      zrnn::TcParams tp;
+      std::memset(&tp, 0, sizeof(tp));
+      ZR_TRY(act_maps(h_t, eng, H, Kpad, B, &tp.a[0], &tp.a_lo[0]));
+      tp.nsrc = 1; tp.kblocks[0] = (H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
+      tp.b = A->pmap; tp.b_lo = A->pmap_lo;
+      tp.M = B; tp.N = 2 * H; tp.C = A->tq.as<float>(); tp.ldc = 2 * H; tp.act = 1; tp.act_rows = H;
+      tp.err = tc_error_word();
+      ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+    }
     a.tanh1 = A->tq.as<float>(); a.q = A->tq.as<float>() + H; a.ld_tq = 2 * H; a.v_p = A->v_p;
     ZR_CUDA(zrnn::launch_att_local(a, st));
   } else {
     ZR_CUDA(zrnn::launch_att_global(a, st));
   }
-  zrnn::GemmArgs g;
-  std::memset(&g, 0, sizeof(g));
-  g.nsrc = 2;
-  g.src[0].A[0] = A->Wc1; g.src[0].lda = H; g.src[0].B = A->ctx.as<float>(); g.src[0].ldb = H; g.src[0].K = H;
-  g.src[1].A[0] = A->Wc2; g.src[1].lda = H; g.src[1].B = h_t; g.src[1].ldb = H; g.src[1].K = H;
-  g.M = H; g.N = B; g.C = htild; g.ldc = H; g.bias[0] = A->bias; g.mask = mask; g.act = 1;
-  ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+  if (eng == ENG_SIMT) {
+    zrnn::GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.nsrc = 2;
+    g.src[0].A[0] = A->Wc1; g.src[0].lda = H; g.src[0].B = ctx.f32; g.src[0].ldb = H; g.src[0].K = H;
+    g.src[1].A[0] = A->Wc2; g.src[1].lda = H; g.src[1].B = h_t.f32; g.src[1].ldb = H; g.src[1].K = H;
+    g.M = H; g.N = B; g.C = out.f32; g.ldc = H; g.bias[0] = A->bias; g.mask = mask; g.act = 1;
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, 0, st));
+  } else {
+    zrnn::TcParams tp;
+    std::memset(&tp, 0, sizeof(tp));
+    const int kb = (H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng));
+    ZR_TRY(act_maps(ctx, eng, H, Kpad, B, &tp.a[0], &tp.a_lo[0]));
+    ZR_TRY(act_maps(h_t, eng, H, Kpad, B, &tp.a[1], &tp.a_lo[1]));
+    tp.nsrc = 2; tp.kblocks[0] = tp.kblocks[1] = kb; tp.b_koff[0] = 0; tp.b_koff[1] = Kpad;
+    tp.b = A->cmap; tp.b_lo = A->cmap_lo;
+    tp.M = B; tp.N = H; tp.bias = A->bias; tp.mask = mask; tp.act = 1;
+    tp.C = out.f32; tp.ldc = H;
+    tp.op_b16 = eng == ENG_BF16 ? (__nv_bfloat16*)out.hi : nullptr;
+    tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
+    tp.op_lo = out.lo; tp.ld_op = Kpad;
+    tp.err = tc_error_word();
+    ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+  }
   return ZRNN_OK;
 }
 
 // per-column (max, sum exp) partials over this layer's rows + target logit into S->parts / tgt
-int softmax_partials_launch(zrnn_softmax* S, const float* h, const int* targets, int N, int* n_parts, float** pm,
+int softmax_partials_launch(zrnn_softmax* S, const Act& h, const int* targets, int N, int* n_parts, float** pm,
                             float** ps, float* tgt, cudaStream_t st) {
   const int Vs = S->hi - S->lo, H = S->H;
-  const int tile = (N >= 96 && Vs >= 512) ? 1 : 0;
-  const int rows = zrnn::gemm_rows_per_tile(1, tile);
-  const int np = (Vs + rows - 1) / rows;
-  ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
   ZR_CUDA(cudaMemsetAsync(tgt, 0, sizeof(float) * (size_t)N, st));
-  zrnn::GemmArgs g;
-  std::memset(&g, 0, sizeof(g));
-  g.nsrc = 1;
-  g.src[0].A[0] = S->D; g.src[0].lda = Vs; g.src[0].B = h; g.src[0].ldb = H; g.src[0].K = H;
-  g.M = Vs; g.N = N; g.bias[0] = S->b;
-  g.target = targets; g.target_offset = S->lo;
-  g.part_max = S->parts.as<float>(); g.part_sum = S->parts.as<float>() + (size_t)np * N;
-  g.tgt_logit = tgt;
-  *n_parts = np; *pm = g.part_max; *ps = g.part_sum;
+  if (S->eng == ENG_SIMT) {
+    const int tile = (N >= 96 && Vs >= 512) ? 1 : 0;
+    const int rows = zrnn::gemm_rows_per_tile(1, tile);
+    const int np = (Vs + rows - 1) / rows;
+    ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
+    zrnn::GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.nsrc = 1;
+    g.src[0].A[0] = S->D; g.src[0].lda = Vs; g.src[0].B = h.f32; g.src[0].ldb = H; g.src[0].K = H;
+    g.M = Vs; g.N = N; g.bias[0] = S->b;
+    g.target = targets; g.target_offset = S->lo;
+    g.part_max = S->parts.as<float>(); g.part_sum = S->parts.as<float>() + (size_t)np * N;
+    g.tgt_logit = tgt;
+    *n_parts = np; *pm = g.part_max; *ps = g.part_sum;
+    KScope ks(KC_SOFTMAX_GEMM, st);
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
+    return ZRNN_OK;
+  }
+  const int eng = S->eng, np = S->n_tiles;
+  ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
+  zrnn::TcParams tp;
+  std::memset(&tp, 0, sizeof(tp));
+  ZR_TRY(act_maps(h, eng, H, S->Kpad, N, &tp.a[0], &tp.a_lo[0]));
+  tp.nsrc = 1; tp.kblocks[0] = (H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
+  tp.b = S->dmap; tp.b_lo = S->dmap_lo;
+  tp.M = N; tp.N = Vs; tp.bias = S->b;
+  tp.target = targets; tp.target_offset = S->lo;
+  tp.part_max = S->parts.as<float>(); tp.part_sum = S->parts.as<float>() + (size_t)np * N; tp.tgt_logit = tgt;
+  tp.err = tc_error_word();
+  *n_parts = np; *pm = tp.part_max; *ps = tp.part_sum;
   KScope ks(KC_SOFTMAX_GEMM, st);
-  ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
+  ZR_CUDA(zrnn::launch_tc_gemm(tp, S->BN, eng_tcmode(eng), zrnn::TC_EPI_LSE, st));
+  return ZRNN_OK;
+}
+
+int softmax_score_act(zrnn_softmax* S, const Act& h, const int* targets, const int* mask, int N, float* logp,
+                      cudaStream_t st) {
+  ZR_CUDA(S->tgt.reserve(sizeof(float) * (size_t)N));
+  int np = 0;
+  float *pm, *ps;
+  ZR_TRY(softmax_partials_launch(S, h, targets, N, &np, &pm, &ps, S->tgt.as<float>(), st));
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_lse_combine(pm, ps, S->tgt.as<float>(), np, N, mask, logp, st));
+  return ZRNN_OK;
+}
+
+int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
+  ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
+  if (S->eng == ENG_SIMT) {
+    zrnn::GemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.nsrc = 1;
+    g.src[0].A[0] = S->D; g.src[0].lda = S->V; g.src[0].B = h.f32; g.src[0].ldb = S->H; g.src[0].K = S->H;
+    g.M = S->V; g.N = N; g.C = S->logits.as<float>(); g.ldc = S->V; g.bias[0] = S->b;
+    KScope ks(KC_SOFTMAX_GEMM, st);
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
+  } else {
+    const int eng = S->eng;
+    zrnn::TcParams tp;
+    std::memset(&tp, 0, sizeof(tp));
+    ZR_TRY(act_maps(h, eng, S->H, S->Kpad, N, &tp.a[0], &tp.a_lo[0]));
+    tp.nsrc = 1; tp.kblocks[0] = (S->H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
+    tp.b = S->dmap; tp.b_lo = S->dmap_lo;
+    tp.M = N; tp.N = S->V; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = S->V;
+    tp.err = tc_error_word();
+    KScope ks(KC_SOFTMAX_GEMM, st);
+    ZR_CUDA(zrnn::launch_tc_gemm(tp, S->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+  }
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st));
+  return ZRNN_OK;
+}
+
+// pack G column-major (rows x K) matrices into operand form at K offset koff
+int pack_into(OpMem& dst, int eng, const float* const* src, int G, int rows, int K, int lda, int TH, int n_tiles,
+              int ld_dst, int koff) {
+  zrnn::PackArgs pk;
+  std::memset(&pk, 0, sizeof(pk));
+  for (int g = 0; g < G; ++g) pk.src[g] = src[g];
+  pk.G = G; pk.H = rows; pk.K = K; pk.lda = lda; pk.TH = TH; pk.n_tiles = n_tiles;
+  pk.dst_hi = dst.hi; pk.dst_lo = dst.lo; pk.op_mode = eng_opmode(eng); pk.ld_dst = ld_dst; pk.koff = koff;
+  ZR_CUDA(zrnn::launch_pack_weights(pk, nullptr));
+  return ZRNN_OK;
+}
+int weight_maps(const OpMem& w, int eng, long long K, long long rows, int box_rows, CUtensorMap* hi, CUtensorMap* lo) {
+  if (!zrnn::make_kmajor_map(hi, w.hi, eng_eb(eng), K, rows, K, box_rows))
+    return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for a weight operand");
+  if (eng == ENG_X3 && !zrnn::make_kmajor_map(lo, w.lo, 4, K, rows, K, box_rows))
+    return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for a weight operand (lo)");
   return ZRNN_OK;
 }
 
@@ -266,6 +536,7 @@ struct TensorSlot {
 
 struct zrnn_model {
   zrnn_model_config cfg;
+  int eng = ENG_SIMT;
   std::vector<zrnn_lstm_layer*> src, tgt;
   zrnn_attention* att = nullptr;
   zrnn_softmax* sm = nullptr;
@@ -307,6 +578,15 @@ int zrnn_built_for_sm(void) { return 100; }
 long long zrnn_launch_count(void) { return zrnn::launch_count_value(); }
 void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
 
+int zrnn_tc_error(void) {
+  int* d = tc_error_word();
+  int v = 0;
+  if (!d) return -1;
+  if (cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(d, 0, sizeof(int));
+  return v;
+}
+
 int zrnn_kernel_timing(int on) {
   g_kt.on = on != 0;
   if (on) g_kt.used = 0;
@@ -338,10 +618,12 @@ static int lstm_create(int H, int V, int feed, int dtype, int is_ih, zrnn_lstm_l
   ZR_CHECK(out, "lstm_create: null out");
   ZR_CHECK(H > 0, "lstm_create: H must be positive");
   ZR_CHECK(!is_ih || V > 0, "ih_create: V must be positive");
-  ZR_CHECK(dtype == ZRNN_F32, "lstm_create: only ZRNN_F32 arithmetic is available in this layer");
+  int eng = ENG_SIMT;
+  ZR_TRY(pick_engine(dtype, H, &eng));
   ZR_TRY(check_device());
   auto* L = new zrnn_lstm_layer();
-  L->H = H; L->V = V; L->feed = feed ? 1 : 0; L->dtype = dtype; L->is_ih = is_ih;
+  L->H = H; L->V = V; L->feed = feed ? 1 : 0; L->dtype = dtype; L->is_ih = is_ih; L->eng = eng;
+  L->Kpad = round64(H);
   *out = L;
   return ZRNN_OK;
 }
@@ -377,6 +659,24 @@ int zrnn_lstm_load(zrnn_lstm_layer* L, const float* const* t, int n) {
     for (int k = 0; k < 4; ++k) std::memcpy(pack.data() + order[k] * HH, t[p + k], sizeof(float) * HH);
     ZR_CUDA(upload(&L->Q, pack.data(), 4 * HH));
   }
+  if (L->eng != ENG_SIMT) {
+    // operand form: gate-interleaved rows (tile of TH hidden units x 4 gates), K axis = x | h | htild
+    const int TH = L->BN / 4, Kpad = L->Kpad, nsrc = L->feed ? 3 : 2;
+    L->n_tiles = (H + TH - 1) / TH;
+    const long long rows = (long long)L->n_tiles * L->BN, Kcat = (long long)nsrc * Kpad;
+    ZR_TRY(L->Wcat.alloc((size_t)rows * Kcat, L->eng));
+    const float* srcs[3] = {L->Mx, L->Wh, L->Q};
+    for (int s = 0; s < nsrc; ++s) {
+      const float* g4[4] = {srcs[s], srcs[s] + HH, srcs[s] + 2 * HH, srcs[s] + 3 * HH};
+      ZR_TRY(pack_into(L->Wcat, L->eng, g4, 4, H, H, H, TH, L->n_tiles, (int)Kcat, s * Kpad));
+    }
+    ZR_TRY(weight_maps(L->Wcat, L->eng, Kcat, rows, L->BN, &L->wmap, &L->wmap_lo));
+    if (L->is_ih) {
+      ZR_TRY(L->emb.alloc((size_t)L->V * Kpad, L->eng));
+      ZR_CUDA(zrnn::launch_convert_rows(L->W, L->V, H, H, eng_opmode(L->eng), L->emb.hi, L->emb.lo, Kpad, nullptr));
+    }
+    ZR_CUDA(cudaDeviceSynchronize());
+  }
   L->loaded = true;
   return ZRNN_OK;
 }
@@ -389,6 +689,49 @@ int zrnn_ih_gather(zrnn_lstm_layer* L, const int* d_ids, int n_cols, float* d_x,
   return ZRNN_OK;
 }
 
+// gather layer-0 inputs in the form the engine consumes
+static int gather_act(zrnn_lstm_layer* L, const int* ids, int n, const Act& x, cudaStream_t st) {
+  KScope ks(KC_GATHER, st);
+  if (L->eng == ENG_SIMT) {
+    ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, ids, n, x.f32, st));
+    return ZRNN_OK;
+  }
+  const size_t rb = (size_t)L->Kpad * eng_eb(L->eng);
+  ZR_CUDA(zrnn::launch_gather_rows16(L->emb.hi, rb, ids, n, x.hi, st));
+  if (L->eng == ENG_X3) ZR_CUDA(zrnn::launch_gather_rows16(L->emb.lo, (size_t)L->Kpad * 4, ids, n, x.lo, st));
+  return ZRNN_OK;
+}
+
+static int layer_forward_f32(zrnn_lstm_layer* L, const int* d_ids, const float* d_x, const int* d_mask,
+                             const float* d_h_prev, const float* d_c_prev, const float* d_htild, int B, float* d_h_out,
+                             float* d_c_out, cudaStream_t st) {
+  const int H = L->H;
+  Act x, hp, q, out;
+  out.f32 = d_h_out;
+  if (L->eng == ENG_SIMT) {
+    if (d_ids) {
+      ZR_CUDA(L->x.reserve(sizeof(float) * (size_t)H * B));
+      x.f32 = L->x.as<float>();
+      ZR_TRY(gather_act(L, d_ids, B, x, st));
+    } else x.f32 = const_cast<float*>(d_x);
+    hp.f32 = const_cast<float*>(d_h_prev);
+    q.f32 = const_cast<float*>(d_htild);
+  } else {
+    if (d_ids) {
+      ZR_CUDA(L->sc_x.reserve((size_t)B * L->Kpad * eng_eb(L->eng)));
+      if (L->eng == ENG_X3) ZR_CUDA(L->sc_xl.reserve((size_t)B * L->Kpad * 4));
+      x.hi = L->sc_x.p;
+      x.lo = L->eng == ENG_X3 ? L->sc_xl.as<float>() : nullptr;
+      ZR_TRY(gather_act(L, d_ids, B, x, st));
+    } else {
+      ZR_TRY(to_operand(d_x, H, L->Kpad, B, L->eng, L->sc_x, L->sc_xl, &x, st));
+    }
+    ZR_TRY(to_operand(d_h_prev, H, L->Kpad, B, L->eng, L->sc_h, L->sc_hl, &hp, st));
+    if (d_htild) ZR_TRY(to_operand(d_htild, H, L->Kpad, B, L->eng, L->sc_q, L->sc_ql, &q, st));
+  }
+  return cell_forward(L, x, hp, d_htild ? &q : nullptr, d_mask, d_c_prev, B, out, d_c_out, st);
+}
+
 int zrnn_ih_forward(zrnn_lstm_layer* L, const int* d_ids, const int* d_mask, const float* d_h_prev,
                     const float* d_c_prev, const float* d_htild_prev, int B, float* d_h_out, float* d_c_out,
                     void* stream) {
@@ -398,10 +741,8 @@ int zrnn_ih_forward(zrnn_lstm_layer* L, const int* d_ids, const int* d_mask, con
   ZR_CHECK(!d_htild_prev || L->feed, "ih_forward: htild given but the layer has no feed-input weights");
   ZR_CHECK(d_h_out != d_h_prev && d_c_out != d_c_prev, "ih_forward: outputs may not alias inputs");
   if (B == 0) return ZRNN_OK;
-  ZR_CUDA(L->x.reserve(sizeof(float) * (size_t)L->H * B));
-  ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, d_ids, B, L->x.as<float>(), (cudaStream_t)stream));
-  return lstm_cell_launch(L, L->x.as<float>(), d_mask, d_h_prev, d_c_prev, d_htild_prev, B, d_h_out, d_c_out, nullptr,
-                          (cudaStream_t)stream);
+  return layer_forward_f32(L, d_ids, nullptr, d_mask, d_h_prev, d_c_prev, d_htild_prev, B, d_h_out, d_c_out,
+                           (cudaStream_t)stream);
 }
 
 int zrnn_hh_forward(zrnn_lstm_layer* L, const float* d_h_below, const int* d_mask, const float* d_h_prev,
@@ -411,8 +752,8 @@ int zrnn_hh_forward(zrnn_lstm_layer* L, const float* d_h_below, const int* d_mas
   ZR_CHECK(d_h_below && d_h_prev && d_c_prev && d_h_out && d_c_out && B >= 0, "hh_forward: bad arguments");
   ZR_CHECK(d_h_out != d_h_prev && d_c_out != d_c_prev, "hh_forward: outputs may not alias inputs");
   if (B == 0) return ZRNN_OK;
-  return lstm_cell_launch(L, d_h_below, d_mask, d_h_prev, d_c_prev, nullptr, B, d_h_out, d_c_out, nullptr,
-                          (cudaStream_t)stream);
+  return layer_forward_f32(L, nullptr, d_h_below, d_mask, d_h_prev, d_c_prev, nullptr, B, d_h_out, d_c_out,
+                           (cudaStream_t)stream);
 }
 int zrnn_lstm_destroy(zrnn_lstm_layer* L) {
   delete L;
@@ -425,10 +766,11 @@ int zrnn_att_create(int H, int D, int att_type, int dtype, zrnn_attention** out)
   ZR_CHECK(H > 0, "att_create: H must be positive");
   ZR_CHECK(att_type == ZRNN_ATT_LOCAL_P || att_type == ZRNN_ATT_GLOBAL_DOT, "att_create: unknown attention type");
   ZR_CHECK(att_type != ZRNN_ATT_LOCAL_P || (D >= 1 && 2 * D + 1 <= 64), "att_create: D must be in [1,31]");
-  ZR_CHECK(dtype == ZRNN_F32, "att_create: only ZRNN_F32 arithmetic is available in this layer");
+  int eng = ENG_SIMT;
+  ZR_TRY(pick_engine(dtype, H, &eng));
   ZR_TRY(check_device());
   auto* A = new zrnn_attention();
-  A->H = H; A->D = D; A->type = att_type; A->dtype = dtype;
+  A->H = H; A->D = D; A->type = att_type; A->dtype = dtype; A->eng = eng; A->Kpad = round64(H);
   *out = A;
   return ZRNN_OK;
 }
@@ -457,6 +799,24 @@ int zrnn_att_load(zrnn_attention* A, const float* const* t, int n) {
   ZR_CUDA(upload(&A->bias, t[3], H));
   ZR_CUDA(upload(&A->Wc1, t[4], HH));
   ZR_CUDA(upload(&A->Wc2, t[5], HH));
+  if (A->eng != ENG_SIMT) {
+    const int Kpad = A->Kpad, BN = A->BN;
+    if (A->type == ZRNN_ATT_LOCAL_P) {
+      const int nt = (2 * H + BN - 1) / BN;
+      ZR_TRY(A->WpWaT_op.alloc((size_t)nt * BN * Kpad, A->eng));
+      const float* g1[1] = {A->WpWaT};
+      ZR_TRY(pack_into(A->WpWaT_op, A->eng, g1, 1, 2 * H, H, 2 * H, BN, nt, Kpad, 0));
+      ZR_TRY(weight_maps(A->WpWaT_op, A->eng, Kpad, (long long)nt * BN, BN, &A->pmap, &A->pmap_lo));
+    }
+    const int nt = (H + BN - 1) / BN;
+    ZR_TRY(A->Wc_op.alloc((size_t)nt * BN * 2 * Kpad, A->eng));
+    const float* c1[1] = {A->Wc1};
+    const float* c2[1] = {A->Wc2};
+    ZR_TRY(pack_into(A->Wc_op, A->eng, c1, 1, H, H, H, BN, nt, 2 * Kpad, 0));
+    ZR_TRY(pack_into(A->Wc_op, A->eng, c2, 1, H, H, H, BN, nt, 2 * Kpad, Kpad));
+    ZR_TRY(weight_maps(A->Wc_op, A->eng, 2 * Kpad, (long long)nt * BN, BN, &A->cmap, &A->cmap_lo));
+    ZR_CUDA(cudaDeviceSynchronize());
+  }
   A->loaded = true;
   return ZRNN_OK;
 }
@@ -476,7 +836,12 @@ int zrnn_att_forward(zrnn_attention* A, const float* d_h_t, const int* d_mask, i
   if (!A->hs) return fail(ZRNN_E_STATE, "att_forward: zrnn_att_set_source has not been called");
   ZR_CHECK(B <= A->B_src * A->cols_per_sent, "att_forward: more target columns than source columns provide");
   if (B == 0) return ZRNN_OK;
-  return att_forward_launch(A, d_h_t, d_mask, B, d_htild_out, d_align_out, (cudaStream_t)stream);
+  cudaStream_t st = (cudaStream_t)stream;
+  Act h, out;
+  h.f32 = const_cast<float*>(d_h_t);
+  out.f32 = d_htild_out;
+  if (A->eng != ENG_SIMT) ZR_TRY(to_operand(d_h_t, A->H, A->Kpad, B, A->eng, A->sc_h, A->sc_hl, &h, st));
+  return att_forward(A, h, d_mask, B, out, d_align_out, st);
 }
 int zrnn_att_destroy(zrnn_attention* A) {
   delete A;
@@ -488,10 +853,12 @@ int zrnn_softmax_create(int V, int H, int dtype, int shard_lo, int shard_hi, zrn
   ZR_CHECK(out, "softmax_create: null out");
   ZR_CHECK(V > 0 && H > 0, "softmax_create: V and H must be positive");
   ZR_CHECK(0 <= shard_lo && shard_lo < shard_hi && shard_hi <= V, "softmax_create: bad shard range");
-  ZR_CHECK(dtype == ZRNN_F32, "softmax_create: only ZRNN_F32 arithmetic is available in this layer");
+  int eng = ENG_SIMT;
+  ZR_TRY(pick_engine(dtype, H, &eng));
   ZR_TRY(check_device());
   auto* S = new zrnn_softmax();
-  S->V = V; S->H = H; S->dtype = dtype; S->lo = shard_lo; S->hi = shard_hi;
+  S->V = V; S->H = H; S->dtype = dtype; S->lo = shard_lo; S->hi = shard_hi; S->eng = eng; S->Kpad = round64(H);
+  S->BN = eng == ENG_X3 ? 128 : 256;
   *out = S;
   return ZRNN_OK;
 }
@@ -505,7 +872,20 @@ int zrnn_softmax_load(zrnn_softmax* S, const float* h_D, const float* h_b_d) {
   ZR_CUDA(cudaMemcpy2D(S->D, sizeof(float) * (size_t)Vs, h_D + S->lo, sizeof(float) * (size_t)S->V,
                        sizeof(float) * (size_t)Vs, S->H, cudaMemcpyHostToDevice));
   ZR_CUDA(upload(&S->b, h_b_d + S->lo, Vs));
+  if (S->eng != ENG_SIMT) {
+    S->n_tiles = (Vs + S->BN - 1) / S->BN;
+    ZR_TRY(S->D_op.alloc((size_t)S->n_tiles * S->BN * S->Kpad, S->eng));
+    const float* g1[1] = {S->D};
+    ZR_TRY(pack_into(S->D_op, S->eng, g1, 1, Vs, S->H, Vs, S->BN, S->n_tiles, S->Kpad, 0));
+    ZR_TRY(weight_maps(S->D_op, S->eng, S->Kpad, (long long)S->n_tiles * S->BN, S->BN, &S->dmap, &S->dmap_lo));
+    ZR_CUDA(cudaDeviceSynchronize());
+  }
   S->loaded = true;
+  return ZRNN_OK;
+}
+static int softmax_input(zrnn_softmax* S, const float* d_h, int N, Act* h, cudaStream_t st) {
+  h->f32 = const_cast<float*>(d_h);
+  if (S->eng != ENG_SIMT) ZR_TRY(to_operand(d_h, S->H, S->Kpad, N, S->eng, S->sc_h, S->sc_hl, h, st));
   return ZRNN_OK;
 }
 int zrnn_softmax_partials(zrnn_softmax* S, const float* d_h, const int* d_targets, int N, float* d_max, float* d_sum,
@@ -514,9 +894,11 @@ int zrnn_softmax_partials(zrnn_softmax* S, const float* d_h, const int* d_target
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_partials: weights not loaded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  Act h;
+  ZR_TRY(softmax_input(S, d_h, N, &h, st));
   int np = 0;
   float *pm, *ps;
-  ZR_TRY(softmax_partials_launch(S, d_h, d_targets, N, &np, &pm, &ps, d_tgt, st));
+  ZR_TRY(softmax_partials_launch(S, h, d_targets, N, &np, &pm, &ps, d_tgt, st));
   // reduce this shard's row tiles to one (max, sum) per column
   KScope ks(KC_SOFTMAX_REDUCE, st);
   ZR_CUDA(zrnn::launch_lse_reduce(pm, ps, np, N, d_max, d_sum, st));
@@ -536,13 +918,9 @@ int zrnn_softmax_score(zrnn_softmax* S, const float* d_h, const int* d_targets, 
   ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_score: layer is vocabulary-sharded; use partials + combine");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  ZR_CUDA(S->tgt.reserve(sizeof(float) * (size_t)N));
-  int np = 0;
-  float *pm, *ps;
-  ZR_TRY(softmax_partials_launch(S, d_h, d_targets, N, &np, &pm, &ps, S->tgt.as<float>(), st));
-  KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_lse_combine(pm, ps, S->tgt.as<float>(), np, N, d_mask, d_logp_out, st));
-  return ZRNN_OK;
+  Act h;
+  ZR_TRY(softmax_input(S, d_h, N, &h, st));
+  return softmax_score_act(S, h, d_targets, d_mask, N, d_logp_out, st);
 }
 int zrnn_softmax_topk(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                       float* d_logp_eos, void* stream) {
@@ -552,19 +930,9 @@ int zrnn_softmax_topk(zrnn_softmax* S, const float* d_h, int N, int k, float* d_
   ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_topk: layer is vocabulary-sharded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
-  zrnn::GemmArgs g;
-  std::memset(&g, 0, sizeof(g));
-  g.nsrc = 1;
-  g.src[0].A[0] = S->D; g.src[0].lda = S->V; g.src[0].B = d_h; g.src[0].ldb = S->H; g.src[0].K = S->H;
-  g.M = S->V; g.N = N; g.C = S->logits.as<float>(); g.ldc = S->V; g.bias[0] = S->b;
-  {
-    KScope ks(KC_SOFTMAX_GEMM, st);
-    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
-  }
-  KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, d_logp_out, d_idx_out, d_logp_eos, st));
-  return ZRNN_OK;
+  Act h;
+  ZR_TRY(softmax_input(S, d_h, N, &h, st));
+  return softmax_topk_act(S, h, N, k, d_logp_out, d_idx_out, d_logp_eos, st);
 }
 int zrnn_softmax_destroy(zrnn_softmax* S) {
   delete S;
@@ -591,10 +959,12 @@ int zrnn_model_create(const zrnn_model_config* c, zrnn_model** out) {
   ZR_CHECK(c->attention >= 0 && c->attention <= 2, "model_create: unknown attention type");
   ZR_CHECK(!(c->lm && c->attention), "model_create: a language model has no source to attend to");
   ZR_CHECK(!c->feed_input || c->attention, "model_create: feed-input needs an attention model");
-  ZR_CHECK(c->dtype == ZRNN_F32, "model_create: only ZRNN_F32 arithmetic is available");
+  int eng = ENG_SIMT;
+  ZR_TRY(pick_engine(c->dtype, c->H, &eng));
   ZR_TRY(check_device());
   auto* m = new zrnn_model();
   m->cfg = *c;
+  m->eng = eng;
   const int H = c->H, L = c->num_layers;
   int st = ZRNN_OK;
   if (!c->lm)
@@ -728,31 +1098,49 @@ int zrnn_model_destroy(zrnn_model* m) {
   return ZRNN_OK;
 }
 
-// ---------------------------------------------------------------- scoring driver
-// Runs the encoder over S_max steps for B columns. On return hstate[l][cur[l]] / cstate hold the final states and
-// hs_all (if non-null) the top-layer state of every step.
-struct StateSet {
-  std::vector<float*> h[2], c[2];
-  std::vector<int> cur;
-};
-
-static int run_encoder(zrnn_model* m, const int* ids_nonm1, const int* mask, int S_max, int B, float* X0,
-                       float* hs_all, StateSet& st, cudaStream_t s) {
-  const int H = m->cfg.H, L = m->cfg.num_layers;
-  const size_t HB = (size_t)H * B;
-  {
-    KScope ks(KC_GATHER, s);
-    ZR_CUDA(zrnn::launch_gather_columns(m->src[0]->W, H, ids_nonm1, S_max * B, X0, s));
+// ---------------------------------------------------------------- drivers
+// A sequence of activations: `slots` consecutive H x B matrices (fp32) and/or operand-form copies.
+static size_t act_bytes(const Geom& g, size_t cols, bool f32, bool op) {
+  size_t b = 0;
+  if (f32) b += aligned(sizeof(float) * cols * g.H);
+  if (op && g.eng != ENG_SIMT) {
+    b += aligned(cols * g.Kpad * eng_eb(g.eng));
+    if (g.eng == ENG_X3) b += aligned(cols * g.Kpad * 4);
   }
-  for (int t = 0; t < S_max; ++t) {
-    const float* x = X0 + (size_t)t * HB;
+  return b;
+}
+static Act act_take(Carver& cv, const Geom& g, size_t cols, bool f32, bool op) {
+  Act a;
+  if (f32) a.f32 = cv.take<float>(cols * g.H);
+  if (op && g.eng != ENG_SIMT) {
+    a.hi = cv.take<char>(cols * g.Kpad * eng_eb(g.eng));
+    if (g.eng == ENG_X3) a.lo = cv.take<float>(cols * g.Kpad);
+  }
+  return a;
+}
+static int act_zero(const Act& a, const Geom& g, size_t cols, cudaStream_t s) {
+  if (a.f32) ZR_CUDA(cudaMemsetAsync(a.f32, 0, sizeof(float) * cols * g.H, s));
+  if (a.hi) ZR_CUDA(cudaMemsetAsync(a.hi, 0, cols * g.Kpad * eng_eb(g.eng), s));
+  if (a.lo) ZR_CUDA(cudaMemsetAsync(a.lo, 0, cols * g.Kpad * 4, s));
+  return ZRNN_OK;
+}
+
+// Encoder over S steps of B columns.  seq[l] receives every step's h of layer l; c ping-pongs in cst.
+// On return cur[l] indexes the final cell state of layer l.
+static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* mask, int S, int B, const Act& X0,
+                       const Act& zero, std::vector<Act>& seq, std::vector<float*> cst[2], std::vector<int>& cur,
+                       cudaStream_t s) {
+  const int L = m->cfg.num_layers;
+  ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
+  for (int t = 0; t < S; ++t) {
+    Act x = act_at(X0, (size_t)t * B, g);
     for (int l = 0; l < L; ++l) {
-      const int cu = st.cur[l];
-      float* h2 = (l == L - 1 && hs_all) ? hs_all + (size_t)t * HB : nullptr;
-      ZR_TRY(lstm_cell_launch(m->src[l], x, mask + (size_t)t * B, st.h[cu][l], st.c[cu][l], nullptr, B, st.h[cu ^ 1][l],
-                              st.c[cu ^ 1][l], h2, s));
-      st.cur[l] = cu ^ 1;
-      x = st.h[cu ^ 1][l];
+      const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
+      const Act out = act_at(seq[l], (size_t)t * B, g);
+      const int cu = cur[l];
+      ZR_TRY(cell_forward(m->src[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], s));
+      cur[l] = cu ^ 1;
+      x = out;
     }
   }
   return ZRNN_OK;
@@ -768,13 +1156,17 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
   cudaStream_t s = (cudaStream_t)stream;
   const zrnn_model_config& c = m->cfg;
   const int H = c.H, L = c.num_layers;
+  const Geom g{H, round64(H), m->eng};
+  const bool tc = m->eng != ENG_SIMT;
   const size_t HB = (size_t)H * B;
   const int S = c.lm ? 0 : S_max;
   const size_t nS = (size_t)S * B, nT = (size_t)T * B;
-  size_t bytes = 0;
-  bytes += 2 * aligned(sizeof(int) * (nS + 1)) + 4 * aligned(sizeof(int) * nT) + 2 * aligned(sizeof(int) * B);
-  bytes += 2 * aligned(sizeof(float) * (HB * S + 1)) + 2 * aligned(sizeof(float) * HB * T);
-  bytes += 4 * (size_t)L * aligned(sizeof(float) * HB);
+  // ---- workspace
+  size_t bytes = 2 * aligned(sizeof(int) * (nS + 1)) + 4 * aligned(sizeof(int) * nT) + 2 * aligned(sizeof(int) * B);
+  bytes += act_bytes(g, nS + 1, !tc, true) + act_bytes(g, nT, !tc, true);          // gathered inputs
+  bytes += (size_t)L * (act_bytes(g, nS + 1, true, true) + act_bytes(g, nT, true, true));  // per-layer h sequences
+  bytes += act_bytes(g, nT, true, true) + act_bytes(g, B, true, true);            // htild sequence, zero state
+  bytes += 2 * (size_t)L * aligned(sizeof(float) * HB);
   ZR_CUDA(m->ws.reserve(bytes));
   Carver cv(m->ws.p);
   int* src_id = cv.take<int>(nS + 1);
@@ -785,50 +1177,46 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
   int* tout_mk = cv.take<int>(nT);
   int* len = cv.take<int>(B);
   int* off = cv.take<int>(B);
-  float* X0 = cv.take<float>(HB * S + 1);
-  float* hs_all = cv.take<float>(HB * S + 1);
-  float* Xt = cv.take<float>(HB * T);
-  float* Hseq = cv.take<float>(HB * T);
-  StateSet st;
-  st.cur.assign(L, 0);
-  for (int k = 0; k < 2; ++k) {
-    st.h[k].resize(L); st.c[k].resize(L);
-    for (int l = 0; l < L; ++l) { st.h[k][l] = cv.take<float>(HB); st.c[k][l] = cv.take<float>(HB); }
-  }
-  for (int l = 0; l < L; ++l) {
-    ZR_CUDA(cudaMemsetAsync(st.h[0][l], 0, sizeof(float) * HB, s));
-    ZR_CUDA(cudaMemsetAsync(st.c[0][l], 0, sizeof(float) * HB, s));
-  }
+  const Act X0 = act_take(cv, g, nS + 1, !tc, true);
+  const Act Xt = act_take(cv, g, nT, !tc, true);
+  std::vector<Act> sseq(L), tseq(L);
+  for (int l = 0; l < L; ++l) { sseq[l] = act_take(cv, g, nS + 1, true, true); tseq[l] = act_take(cv, g, nT, true, true); }
+  const Act hts = act_take(cv, g, nT, true, true);
+  const Act zero = act_take(cv, g, B, true, true);
+  std::vector<float*> cst[2];
+  for (int k = 0; k < 2; ++k) { cst[k].resize(L); for (int l = 0; l < L; ++l) cst[k][l] = cv.take<float>(HB); }
+  std::vector<int> cur(L, 0);
+  ZR_TRY(act_zero(zero, g, B, s));
+  for (int l = 0; l < L; ++l) ZR_CUDA(cudaMemsetAsync(cst[0][l], 0, sizeof(float) * HB, s));
   ZR_CUDA(zrnn::launch_prep_ids(d_tgt_in, (int)nT, tin_id, tin_mk, s));
   ZR_CUDA(zrnn::launch_prep_ids(d_tgt_out, (int)nT, tout_id, tout_mk, s));
   if (!c.lm) {
     ZR_CUDA(zrnn::launch_prep_ids(d_src_ids, (int)nS, src_id, src_mk, s));
     ZR_CUDA(zrnn::launch_src_len(src_mk, S, B, len, off, s));
-    ZR_TRY(run_encoder(m, src_id, src_mk, S, B, X0, c.attention ? hs_all : nullptr, st, s));
-    if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, hs_all, S, B, len, off, 1));
+    ZR_TRY(run_encoder(m, g, src_id, src_mk, S, B, X0, zero, sseq, cst, cur, s));
+    if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S, B, len, off, 1));
   }
   // target side: layer l starts from the encoder's final (h,c) of layer l (src/model.hpp:1714-1724)
-  {
-    KScope ks(KC_GATHER, s);
-    ZR_CUDA(zrnn::launch_gather_columns(m->tgt[0]->W, H, tin_id, (int)nT, Xt, s));
-  }
+  ZR_TRY(gather_act(m->tgt[0], tin_id, (int)nT, Xt, s));
   for (int t = 0; t < T; ++t) {
-    const float* x = Xt + (size_t)t * HB;
+    Act x = act_at(Xt, (size_t)t * B, g);
     const int* mk = tin_mk + (size_t)t * B;
-    float* top_slot = Hseq + (size_t)t * HB;
     for (int l = 0; l < L; ++l) {
-      const int cu = st.cur[l];
-      const float* feed = (l == 0 && c.feed_input && t > 0) ? Hseq + (size_t)(t - 1) * HB : nullptr;
-      float* h2 = (l == L - 1 && !c.attention) ? top_slot : nullptr;
-      ZR_TRY(lstm_cell_launch(m->tgt[l], x, mk, st.h[cu][l], st.c[cu][l], feed, B, st.h[cu ^ 1][l], st.c[cu ^ 1][l], h2, s));
-      st.cur[l] = cu ^ 1;
-      x = st.h[cu ^ 1][l];
+      Act hp = t > 0 ? act_at(tseq[l], (size_t)(t - 1) * B, g) : (c.lm ? zero : act_at(sseq[l], (size_t)(S - 1) * B, g));
+      const Act out = act_at(tseq[l], (size_t)t * B, g);
+      const Act feed = act_at(hts, (size_t)(t > 0 ? t - 1 : 0) * B, g);
+      const bool use_feed = (l == 0 && c.feed_input && t > 0);
+      const int cu = cur[l];
+      ZR_TRY(cell_forward(m->tgt[l], x, hp, use_feed ? &feed : nullptr, mk, cst[cu][l], B, out, cst[cu ^ 1][l], s));
+      cur[l] = cu ^ 1;
+      x = out;
     }
-    if (c.attention) ZR_TRY(att_forward_launch(m->att, x, mk, B, top_slot, nullptr, s));
+    if (c.attention) ZR_TRY(att_forward(m->att, x, mk, B, act_at(hts, (size_t)t * B, g), nullptr, s));
   }
-  m->last_top = Hseq;
+  const Act& top = c.attention ? hts : tseq[L - 1];
+  m->last_top = top.f32;
   m->last_top_cols = (int)nT;
-  return zrnn_softmax_score(m->sm, Hseq, tout_id, tout_mk, (int)nT, d_logp_out, s);
+  return softmax_score_act(m->sm, top, tout_id, tout_mk, (int)nT, d_logp_out, s);
 }
 
 int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tgt_in, const int* tgt_out, int T,
@@ -852,6 +1240,10 @@ int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tg
   ZR_TRY(zrnn_score_batch_device(m, nS ? d_src : nullptr, S_max, d_tin, d_tout, T, B, d_lp, s));
   ZR_CUDA(cudaMemcpyAsync(logp_out, d_lp, sizeof(float) * nT, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
+  if (m->eng != ENG_SIMT) {
+    const int code = zrnn_tc_error();
+    if (code != 0) return fail(ZRNN_E_TIMEOUT, "score_batch: a bounded device wait gave up (role " + std::to_string(code) + ")");
+  }
   if (total_logp) {
     double tot = 0;
     for (size_t i = 0; i < nT; ++i) tot += logp_out[i];
@@ -879,6 +1271,8 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
   const int Lmax = longest_sent + 4;  // src/main.cu:408
   cudaStream_t s = (cudaStream_t)stream;
   const int H = c.H, L = c.num_layers, n = n_sent, NB = n_sent * beam;
+  const Geom g{H, round64(H), m->eng};
+  const bool tc = m->eng != ENG_SIMT;
   const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
 
   // per-sentence step limits (src/ensemble_factory.hpp:637)
@@ -895,8 +1289,9 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
   size_t bytes = 0;
   bytes += 2 * aligned(sizeof(int) * nS) + 4 * aligned(sizeof(int) * n);
   bytes += 3 * aligned(sizeof(int) * NB) + 2 * aligned(sizeof(int) * (size_t)NB * Lmax) + aligned(sizeof(int) * (size_t)NB * kc);
-  bytes += 2 * aligned(sizeof(float) * HBs * S_max) + 4 * (size_t)L * aligned(sizeof(float) * HBs);
-  bytes += (4 * (size_t)L + 3) * aligned(sizeof(float) * HB);
+  bytes += act_bytes(g, nS, !tc, true) + (size_t)L * act_bytes(g, nS, true, true) + act_bytes(g, n, true, true);
+  bytes += 2 * (size_t)L * aligned(sizeof(float) * HBs);
+  bytes += (2 * (size_t)L + 3) * act_bytes(g, NB, true, true) + 2 * (size_t)L * aligned(sizeof(float) * HB);
   bytes += 2 * aligned(sizeof(float) * NB) + aligned(sizeof(float) * (size_t)NB * kc);
   ZR_CUDA(m->ws.reserve(bytes));
   Carver cv(m->ws.p);
@@ -912,45 +1307,67 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
   int* top_sent = cv.take<int>((size_t)NB * Lmax);
   int* top_tmp = cv.take<int>((size_t)NB * Lmax);
   int* cand_idx = cv.take<int>((size_t)NB * kc);
-  float* X0 = cv.take<float>(HBs * S_max);
-  float* hs_all = cv.take<float>(HBs * S_max);
-  StateSet st;
-  st.cur.assign(L, 0);
-  for (int k = 0; k < 2; ++k) {
-    st.h[k].resize(L); st.c[k].resize(L);
-    for (int l = 0; l < L; ++l) { st.h[k][l] = cv.take<float>(HBs); st.c[k][l] = cv.take<float>(HBs); }
+  const Act X0 = act_take(cv, g, nS, !tc, true);
+  std::vector<Act> sseq(L);
+  for (int l = 0; l < L; ++l) sseq[l] = act_take(cv, g, nS, true, true);
+  const Act zero = act_take(cv, g, n, true, true);
+  std::vector<float*> cst[2];
+  for (int k = 0; k < 2; ++k) { cst[k].resize(L); for (int l = 0; l < L; ++l) cst[k][l] = cv.take<float>(HBs); }
+  std::vector<Act> hp(L), hn(L);
+  std::vector<float*> cp(L), cn(L);
+  for (int l = 0; l < L; ++l) {
+    hp[l] = act_take(cv, g, NB, true, true);
+    hn[l] = act_take(cv, g, NB, true, true);
+    cp[l] = cv.take<float>(HB);
+    cn[l] = cv.take<float>(HB);
   }
-  std::vector<float*> hp(L), cp(L), hn(L), cn(L);
-  for (int l = 0; l < L; ++l) { hp[l] = cv.take<float>(HB); cp[l] = cv.take<float>(HB); hn[l] = cv.take<float>(HB); cn[l] = cv.take<float>(HB); }
-  float* x = cv.take<float>(HB);
-  float* htild_new = cv.take<float>(HB);
-  float* htild_feed = cv.take<float>(HB);
+  const Act x = act_take(cv, g, NB, true, true);
+  const Act htild_new = act_take(cv, g, NB, true, true);
+  const Act htild_feed = act_take(cv, g, NB, true, true);
   float* scores = cv.take<float>(NB);
   float* logp_eos = cv.take<float>(NB);
   float* cand_val = cv.take<float>((size_t)NB * kc);
 
   ZR_CUDA(cudaMemcpyAsync(d_len_host, m->h_tmp.data(), sizeof(int) * n, cudaMemcpyHostToDevice, s));
   ZR_CUDA(cudaMemcpyAsync(max_steps, m->h_tmp.data() + n, sizeof(int) * n, cudaMemcpyHostToDevice, s));
-  for (int l = 0; l < L; ++l) {
-    ZR_CUDA(cudaMemsetAsync(st.h[0][l], 0, sizeof(float) * HBs, s));
-    ZR_CUDA(cudaMemsetAsync(st.c[0][l], 0, sizeof(float) * HBs, s));
-  }
+  std::vector<int> cur(L, 0);
+  ZR_TRY(act_zero(zero, g, n, s));
+  for (int l = 0; l < L; ++l) ZR_CUDA(cudaMemsetAsync(cst[0][l], 0, sizeof(float) * HBs, s));
   ZR_CUDA(zrnn::launch_prep_ids(d_src, (int)nS, src_id, src_mk, s));
   ZR_CUDA(zrnn::launch_src_len(src_mk, S_max, n, len, off, s));
-  ZR_TRY(run_encoder(m, src_id, src_mk, S_max, n, X0, c.attention ? hs_all : nullptr, st, s));
-  if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, hs_all, S_max, n, len, off, beam));
+  ZR_TRY(run_encoder(m, g, src_id, src_mk, S_max, n, X0, zero, sseq, cst, cur, s));
+  if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S_max, n, len, off, beam));
 
+  // column gathers move whole operand rows: express every array as floats-per-column
+  auto add_gather = [&](zrnn::ColGatherArgs* ga, int* n_f32, const Act& srcA, const Act& dstA) {
+    // fp32 part
+    ga[0].src[ga[0].n_arrays] = srcA.f32; ga[0].dst[ga[0].n_arrays++] = dstA.f32;
+    if (tc) {
+      ga[1].src[ga[1].n_arrays] = (const float*)srcA.hi; ga[1].dst[ga[1].n_arrays++] = (float*)dstA.hi;
+      if (g.eng == ENG_X3) { ga[2].src[ga[2].n_arrays] = srcA.lo; ga[2].dst[ga[2].n_arrays++] = dstA.lo; }
+    }
+    (void)n_f32;
+  };
+  auto run_gathers = [&](zrnn::ColGatherArgs* ga, const int* map) -> int {
+    ga[0].H = H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad;
+    for (int k = 0; k < 3; ++k) {
+      if (ga[k].n_arrays == 0) continue;
+      ga[k].n_cols = NB; ga[k].map = map;
+      KScope ks(KC_REORDER, s);
+      ZR_CUDA(zrnn::launch_col_gather(ga[k], s));
+    }
+    return ZRNN_OK;
+  };
   // replicate the encoder's final (h,c) over the beam (transfer_decoding_states_GPU)
   ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
   {
-    zrnn::ColGatherArgs g;
-    std::memset(&g, 0, sizeof(g));
+    zrnn::ColGatherArgs ga[3];
+    std::memset(ga, 0, sizeof(ga));
     for (int l = 0; l < L; ++l) {
-      g.src[g.n_arrays] = st.h[st.cur[l]][l]; g.dst[g.n_arrays++] = hp[l];
-      g.src[g.n_arrays] = st.c[st.cur[l]][l]; g.dst[g.n_arrays++] = cp[l];
+      add_gather(ga, nullptr, act_at(sseq[l], (size_t)(S_max - 1) * n, g), hp[l]);
+      ga[0].src[ga[0].n_arrays] = cst[cur[l]][l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
     }
-    g.H = H; g.n_cols = NB; g.map = rep_map;
-    ZR_CUDA(zrnn::launch_col_gather(g, s));
+    ZR_TRY(run_gathers(ga, rep_map));
   }
   zrnn::BeamArgs ba;
   std::memset(&ba, 0, sizeof(ba));
@@ -962,38 +1379,33 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
   ZR_CUDA(zrnn::launch_beam_init(ba, s));
 
   for (int t = 0; t <= Tmax; ++t) {
-    {
-      KScope ks(KC_GATHER, s);
-      ZR_CUDA(zrnn::launch_gather_columns(m->tgt[0]->W, H, cur_ids, NB, x, s));
-    }
-    const float* xin = x;
+    ZR_TRY(gather_act(m->tgt[0], cur_ids, NB, x, s));
+    Act xin = x;
     for (int l = 0; l < L; ++l) {
-      const float* feed = (l == 0 && c.feed_input && t > 0) ? htild_feed : nullptr;
-      ZR_TRY(lstm_cell_launch(m->tgt[l], xin, nullptr, hp[l], cp[l], feed, NB, hn[l], cn[l], nullptr, s));
+      const bool use_feed = (l == 0 && c.feed_input && t > 0);
+      ZR_TRY(cell_forward(m->tgt[l], xin, hp[l], use_feed ? &htild_feed : nullptr, nullptr, cp[l], NB, hn[l], cn[l], s));
       xin = hn[l];
     }
-    const float* top = xin;
+    Act top = xin;
     if (c.attention) {
-      ZR_TRY(att_forward_launch(m->att, xin, nullptr, NB, htild_new, nullptr, s));
+      ZR_TRY(att_forward(m->att, xin, nullptr, NB, htild_new, nullptr, s));
       top = htild_new;
     }
-    ZR_TRY(zrnn_softmax_topk(m->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
+    ZR_TRY(softmax_topk_act(m->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
     ba.step = t;
     {
       KScope ks(KC_BEAM, s);
       ZR_CUDA(zrnn::launch_beam_step(ba, s));
     }
     if (t < Tmax) {  // swap_decoding_states + target_copy_prev_states
-      zrnn::ColGatherArgs g;
-      std::memset(&g, 0, sizeof(g));
+      zrnn::ColGatherArgs ga[3];
+      std::memset(ga, 0, sizeof(ga));
       for (int l = 0; l < L; ++l) {
-        g.src[g.n_arrays] = hn[l]; g.dst[g.n_arrays++] = hp[l];
-        g.src[g.n_arrays] = cn[l]; g.dst[g.n_arrays++] = cp[l];
+        add_gather(ga, nullptr, hn[l], hp[l]);
+        ga[0].src[ga[0].n_arrays] = cn[l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
       }
-      if (c.feed_input) { g.src[g.n_arrays] = htild_new; g.dst[g.n_arrays++] = htild_feed; }
-      g.H = H; g.n_cols = NB; g.map = col_map;
-      KScope ks(KC_REORDER, s);
-      ZR_CUDA(zrnn::launch_col_gather(g, s));
+      if (c.feed_input) add_gather(ga, nullptr, htild_new, htild_feed);
+      ZR_TRY(run_gathers(ga, col_map));
     }
   }
   return ZRNN_OK;
@@ -1034,11 +1446,14 @@ int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
+  if (m->eng != ENG_SIMT) {
+    const int code = zrnn_tc_error();
+    if (code != 0) return fail(ZRNN_E_TIMEOUT, "beam_decode: a bounded device wait gave up (role " + std::to_string(code) + ")");
+  }
   return ZRNN_OK;
 }
 
 }  // extern "C"
-
 
 // ------------------------------------------------------------------------------------------
 // Allocation-free scoring softmax
@@ -1118,27 +1533,7 @@ int zrnn_softmax_score_noalloc(zrnn_softmax* S, const float* d_h, const int* d_t
 // Stand-alone GEMM (the reference's cublas_gemm_wrapper, src/BZ_CUDA_UTIL.h:691-696, N/N case):
 //   C[n_rows x m_cols] = W[n_rows x K] * X[K x m_cols], all column-major.
 // ------------------------------------------------------------------------------------------
-namespace {
-int* tc_error_word() {
-  static int* p = nullptr;
-  if (!p) {
-    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
-  }
-  return p;
-}
-}  // namespace
-
 extern "C" {
-
-int zrnn_tc_error(void) {
-  int* d = tc_error_word();
-  int v = 0;
-  if (!d) return -1;
-  if (cudaMemcpy(&v, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (v) cudaMemset(d, 0, sizeof(int));
-  return v;
-}
 
 int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw, const float* d_X, int ldx,
               float* d_C, int ldc, void* stream) {
