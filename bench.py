@@ -47,6 +47,15 @@ WORKLOADS = {
 }
 
 
+ARITH = {
+    "f32": "fp32-accurate: tcgen05 3xTF32 (hi/lo split operands, fp32 accumulate) when H >= 128, else fp32 FMA",
+    "f32_3xtf32": "fp32-accurate: tcgen05 3xTF32 (hi/lo split operands, fp32 accumulate)",
+    "f32_simt": "exact fp32 FMA kernels",
+    "bf16": "tcgen05 bf16 operands, fp32 accumulate and state",
+    "tf32": "tcgen05 tf32 operands, fp32 accumulate and state",
+}
+
+
 def make_cfg(w):
     return synth.make_cfg(w["L"], w["H"], w["Vs"], w["Vt"], lm=int(w["kind"] == "lm"), attention=w["att"],
                           feed_input=w["feed"], D=10)
@@ -193,6 +202,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32"],
+                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate, 3xTF32 tensor cores when H >= 128)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -215,7 +226,8 @@ def main():
 
     cfg = make_cfg(w)
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
-    model = api.neuralMT_model(cfg)
+    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[args.dtype]
+    model = api.neuralMT_model(cfg, dtype=dtype_id)
     model.load_weights(weights)
     del weights
     # sentences are sharded by rank (weak scaling: every rank scores/decodes its own minibatch, no collective)
@@ -321,8 +333,9 @@ def main():
         roof = roofline(w, cfg, ktime, hbm_peak, peak_src, ncols, args.steps)
         line = dict(metric=metric_name(w), value=tokens_all * args.steps / (ms / 1e3), unit="tokens/s",
                     n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms / args.steps,
-                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype=args.dtype, data="synthetic",
                     config=dict(workload=args.workload + ": " + w["desc"], sharding="sentences by rank, no collective",
+                                arithmetic=ARITH[args.dtype],
                                 l2="weights and embeddings (>1 GB) exceed the 126 MB L2 every step"),
                     clocks=clocks, gpu_launches=int(launches),
                     e2e=dict(value=tokens_all * args.steps / e2e_s, unit="tokens/s", h2d_bytes_per_step=h2d,

@@ -122,10 +122,60 @@ __device__ __forceinline__ void store_operand(const TcParams& p, size_t idx, flo
   }
 }
 
+// 8 consecutive outputs of one row: vector stores when the group is complete and 16-byte aligned
+__device__ __forceinline__ void store8_f32(float* base, size_t idx, const float* v, int nvalid) {
+  if (nvalid == 8 && (idx & 3) == 0) {
+    float4* d = reinterpret_cast<float4*>(base + idx);
+    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    for (int u = 0; u < nvalid; ++u) base[idx + u] = v[u];
+  }
+}
+__device__ __forceinline__ void store8_operand(const TcParams& p, size_t idx, const float* v, int nvalid) {
+  if (p.op_b16) {
+    if (nvalid == 8 && (idx & 7) == 0) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+      __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+      uint4 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&a); pk.y = *reinterpret_cast<uint32_t*>(&b);
+      pk.z = *reinterpret_cast<uint32_t*>(&c); pk.w = *reinterpret_cast<uint32_t*>(&d);
+      *reinterpret_cast<uint4*>(p.op_b16 + idx) = pk;
+    } else {
+      for (int u = 0; u < nvalid; ++u) p.op_b16[idx + u] = __float2bfloat16(v[u]);
+    }
+  }
+  if (p.op_hi) {
+    float hi[8], lo[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { hi[u] = tf32_round_dev(v[u]); lo[u] = v[u] - hi[u]; }
+    store8_f32(p.op_hi, idx, hi, nvalid);
+    if (p.op_lo) store8_f32(p.op_lo, idx, lo, nvalid);
+  }
+}
+// activations: exact for the fp32-accurate mode, hardware approximations (tanh.approx, ~2^-11) for bf16 / tf32
+template <int MODE>
+__device__ __forceinline__ float act_tanh(float x) {
+  if (MODE == TC_TF32X3) return tanhf(x);
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <int MODE>
+__device__ __forceinline__ float act_sigmoid(float x) {
+  if (MODE == TC_TF32X3) return 1.0f / (1.0f + expf(-x));
+  return fmaf(0.5f, act_tanh<MODE>(0.5f * x), 0.5f);
+}
+
 constexpr int kABytes = 128 * 128;  // A tile: 128 rows x 128-byte k-block
 __host__ __device__ constexpr int stage_bytes(int BN, int mode) { return (mode == TC_TF32X3 ? 2 : 1) * (kABytes + BN * 128); }
-__host__ __device__ constexpr int num_stages(int BN, int mode) {
-  int s = (200 * 1024) / stage_bytes(BN, mode);
+// bytes of the split-K exchange slots: SPLITK slots of 128 rows x (BN/SPLITK + 4) floats.  They must not overlap
+// the stage ring: a peer that finishes its main loop early pushes into them while this CTA may still be loading.
+__host__ __device__ constexpr int slot_bytes(int BN, int splitk) {
+  return splitk > 1 ? splitk * 128 * (BN / splitk + 4) * 4 : 0;
+}
+__host__ __device__ constexpr int num_stages(int BN, int mode, int splitk = 1) {
+  int s = (225 * 1024 - 1024 - slot_bytes(BN, splitk)) / stage_bytes(BN, mode);
   return s > 8 ? 8 : s;
 }
 
@@ -144,14 +194,48 @@ __host__ __device__ constexpr int tmem_cols(int BN, int mode) {
   return c;
 }
 
-template <int BN, int MODE, int EPI>
+__device__ __forceinline__ long long gtime() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define ZR_STAMP(i)                                                                                         \
+  do {                                                                                                      \
+    if (p.prof && (threadIdx.x == 0))                                                                       \
+      p.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = gtime(); \
+  } while (0)
+
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// SPLITK > 1: the CTAs of a (1,1,SPLITK) cluster each accumulate a slice of the K axis for the same output tile.
+// Each CTA then finishes 1/SPLITK of the tile's columns: every CTA pushes the matching columns of its partial tile
+// into a slot of the owner's shared memory with remote stores (distributed shared memory; stores need no round
+// trip, remote loads measured ~1.4 us each), a cluster barrier publishes them, and the owner adds its SPLITK slots
+// in a fixed order.  This keeps the number of CTAs high for skinny problems (one 128-row M tile) without every CTA
+// re-reading the whole A operand.
+template <int BN, int MODE, int EPI, int SPLITK>
 __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
-  constexpr int ST = num_stages(BN, MODE);
+  constexpr int ST = num_stages(BN, MODE, SPLITK);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
+  static_assert(ST >= 2, "need at least a double-buffered ring");
   constexpr uint32_t IDESC = make_idesc(MODE == TC_BF16 ? 1u : 2u, BN);
   constexpr int NACC = num_acc(BN, MODE);
   constexpr int TMEM_COLS = tmem_cols(BN, MODE);
+  constexpr int OWNC = BN / SPLITK;  // columns finished by each CTA of the cluster
+  constexpr int PLD = OWNC + 4;      // padded row stride (floats) of a slot: conflict-free 16-byte accesses
+  static_assert(SPLITK == 1 || SPLITK * PLD * 128 * 4 == slot_bytes(BN, SPLITK), "slot size mismatch");
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[ST];
   __shared__ __align__(8) uint64_t empty_bar[ST];
@@ -163,9 +247,15 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const int m0 = blockIdx.x * 128;
   const int n_tile = blockIdx.y;
-  int total_kb = 0;
-  for (int s = 0; s < p.nsrc; ++s) total_kb += p.kblocks[s];
+  const int rank = SPLITK > 1 ? (int)blockIdx.z : 0;  // cluster dims (1,1,SPLITK): rank in cluster == blockIdx.z
+  int all_kb = 0;
+  for (int s = 0; s < p.nsrc; ++s) all_kb += p.kblocks[s];
+  // this CTA's slice [kb_lo, kb_hi) of the global k-block sequence
+  const int kb_lo = (int)(((long long)all_kb * rank) / SPLITK);
+  const int kb_hi = (int)(((long long)all_kb * (rank + 1)) / SPLITK);
+  const int total_kb = kb_hi - kb_lo;
 
+  ZR_STAMP(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -185,14 +275,16 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  ZR_STAMP(1);
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int it = 0;
+      int it = 0, g = 0;
       bool ok = true;
       for (int s = 0; s < p.nsrc && ok; ++s) {
-        for (int kb = 0; kb < p.kblocks[s]; ++kb, ++it) {
+        for (int kb = 0; kb < p.kblocks[s]; ++kb, ++g) {
+          if (g < kb_lo || g >= kb_hi) continue;
           const int st = it % ST;
           const uint32_t ph = (uint32_t)((it / ST) & 1);
           if (!mbar_wait(&empty_bar[st], ph ^ 1u, &abort_s, p.err, 1)) { ok = false; break; }
@@ -205,14 +297,13 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
             tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
             tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], p.b_koff[s] + kx, n_tile * BN);
           }
+          ++it;
         }
       }
       if (!ok) {
-        // wait (bounded) for copies already in flight before the CTA may retire
-        for (int st = 0; st < ST; ++st) {
-          const long long t0 = clock64();
-          while (clock64() - t0 < 2000000LL) {}
-        }
+        // give copies already in flight time to land before the CTA may retire
+        const long long t0 = clock64();
+        while (clock64() - t0 < 20000000LL) {}
       }
     }
   } else if (warp == 5) {
@@ -243,115 +334,212 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       }
       if (ok) umma_commit(&accum_bar);
     }
-  } else {
-    // ------------------------------------------------------------ epilogue (warps 0-3)
-    const int row = m0 + warp * 32 + lane;
-    const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const bool ready = (total_kb == 0) ? false : mbar_wait(&accum_bar, 0, &abort_s, p.err, 3);
-    tc_fence_after();
-    const int n_main = total_kb < NACC ? total_kb : NACC;  // main accumulators that were written
-    // 8 accumulator columns starting at `col`, summed over the partial accumulators
-    auto load8 = [&](int col, float* v) {
-      tmem_ld8(taddr + col, v);
-      if (MODE == TC_TF32X3) {
-        float t[8];
-        for (int a = 1; a < n_main; ++a) {
-          tmem_ld8(taddr + a * BN + col, t);
-          tmem_wait_ld();
+  }
+
+  __syncwarp();  // lanes of the producer / MMA warps rejoin lane 0 before any warp-aligned barrier
+  // ------------------------------------------------------------ epilogue (warps 0-3 do the math)
+  const bool epi_warp = warp < 4;
+  const int row = m0 + warp * 32 + lane;  // meaningful for epilogue warps only
+  const int lrow = warp * 32 + lane;
+  const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+  // the LSTM epilogue's global operands do not depend on the accumulators: fetch them while the main loop runs
+  float pre_c[8], pre_b[4][8];
+  if constexpr (EPI == TC_EPI_LSTM) {
+    constexpr int TH = BN / 4;
+    constexpr int TH_OWN = TH / SPLITK;
+    if (TH_OWN == 8 && epi_warp) {
+      const int H = p.N;
+      const int hidb = n_tile * TH + rank * TH_OWN;
 #pragma unroll
-          for (int u = 0; u < 8; ++u) v[u] += t[u];
-        }
-        tmem_ld8(taddr + NACC * BN + col, t);
+      for (int u = 0; u < 8; ++u) {
+        const int hid = hidb + u;
+        const bool okh = hid < H;
+        pre_c[u] = (okh && row < p.M) ? p.c_prev[(size_t)row * H + hid] : 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pre_b[q][u] = okh ? p.bias[q * H + hid] : 0.f;
+      }
+    }
+  }
+  bool ready = false;
+  if (epi_warp) {
+    ready = (total_kb == 0) ? (SPLITK > 1) : mbar_wait(&accum_bar, 0, &abort_s, p.err, 3);
+    tc_fence_after();
+  }
+  ZR_STAMP(2);
+  const int n_main = total_kb < NACC ? total_kb : NACC;  // main accumulators that were written
+  // 8 accumulator columns starting at `col` from TMEM, summed over the partial accumulators
+  auto load8_tmem = [&](int col, float* v) {
+    if (total_kb == 0) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = 0.f;
+      return;
+    }
+    tmem_ld8(taddr + col, v);
+    if (MODE == TC_TF32X3) {
+      float t[8];
+      for (int a = 1; a < n_main; ++a) {
+        tmem_ld8(taddr + a * BN + col, t);
         tmem_wait_ld();
 #pragma unroll
         for (int u = 0; u < 8; ++u) v[u] += t[u];
       }
+      tmem_ld8(taddr + NACC * BN + col, t);
       tmem_wait_ld();
-    };
-    if (ready) {
-      const bool row_ok = row < p.M;
-      const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
-      if (EPI == TC_EPI_LSTM) {
-        constexpr int TH = BN / 4;
-        const int H = p.N;
-        const int hid0 = n_tile * TH;
-        for (int j0 = 0; j0 < TH; j0 += 8) {
-          float g[4][8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) load8(q * TH + j0, g[q]);
-          if (row_ok) {
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int hid = hid0 + j0 + u;
-              if (hid < H) {
-                const float gi = sigmoid_acc(g[0][u] + p.bias[hid]);
-                const float gf = sigmoid_acc(g[1][u] + p.bias[H + hid]);
-                const float gg = tanhf(g[2][u] + p.bias[2 * H + hid]);
-                const float go = sigmoid_acc(g[3][u] + p.bias[3 * H + hid]);
-                const size_t idx = (size_t)row * H + hid;
-                float c = gf * p.c_prev[idx] + gi * gg;
-                float h = go * tanhf(c);
-                h *= mk;
-                c *= mk;
-                p.c_out[idx] = c;
-                if (p.C) p.C[(size_t)row * p.ldc + hid] = h;
-                store_operand(p, (size_t)row * p.ld_op + hid, h);
-              }
-            }
-          }
+      for (int u = 0; u < 8; ++u) v[u] += t[u];
+    }
+    tmem_wait_ld();
+  };
+  // slots[q][row][PLD]: contribution of cluster rank q to this CTA's columns (split-K only), placed after the ring.
+  // Column order inside a slot: LSTM -> gate*TH_OWN + j (this CTA's hidden units, all four gates); otherwise the
+  // CTA's OWNC consecutive columns.
+  float* slots = reinterpret_cast<float*>(tiles + (size_t)ST * STAGE);
+  if (SPLITK > 1) {
+    if (epi_warp && ready) {
+      const uint32_t my_slot = smem_u32(slots + ((size_t)rank * 128 + lrow) * PLD);
+      for (int c0 = 0; c0 < BN; c0 += 8) {
+        float v[8];
+        load8_tmem(c0, v);
+        int owner, lcol;
+        if (EPI == TC_EPI_LSTM) {
+          constexpr int TH = BN / 4, TH_OWN = TH / SPLITK;
+          const int gate = c0 / TH, j = c0 % TH;
+          owner = j / TH_OWN;
+          lcol = gate * TH_OWN + (j % TH_OWN);
+        } else {
+          owner = c0 / OWNC;
+          lcol = c0 % OWNC;
         }
-      } else if (EPI == TC_EPI_STORE) {
-        const int n0 = n_tile * BN;
-        for (int c0 = 0; c0 < BN; c0 += 8) {
-          float v[8];
-          load8(c0, v);
-          if (row_ok) {
+        const uint32_t dst = cluster_map(my_slot + (uint32_t)(lcol * 4), (uint32_t)owner);
+        st_cluster_v4(dst, v[0], v[1], v[2], v[3]);
+        st_cluster_v4(dst + 16, v[4], v[5], v[6], v[7]);
+      }
+    }
+    tc_fence_before();
+    ZR_STAMP(3);
+    cluster_sync_all();  // release/acquire: every CTA's pushes are visible to their owners
+    ZR_STAMP(4);
+  }
+  // 8 finished accumulator columns: `col` is a tile column (SPLITK == 1) or a slot column (SPLITK > 1)
+  auto load8 = [&](int col, float* v) {
+    if (SPLITK == 1) {
+      load8_tmem(col, v);
+    } else {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int n = n0 + c0 + u;
-              if (n < p.N) {
-                float x = v[u] + (p.bias ? p.bias[n] : 0.f);
-                if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) x = tanhf(x);
-                x *= mk;
-                if (p.C) p.C[(size_t)row * p.ldc + n] = x;
-                store_operand(p, (size_t)row * p.ld_op + n, x);
-              }
-            }
-          }
-        }
-      } else {  // TC_EPI_LSE
-        const int n0 = n_tile * BN;
-        const int tg = (p.target && row_ok) ? p.target[row] - p.target_offset : -1;
-        float mx = -INFINITY, sm = 0.f;
-        for (int c0 = 0; c0 < BN; c0 += 8) {
-          float v[8];
-          load8(c0, v);
-          float cm = -INFINITY;
+      for (int u = 0; u < 8; ++u) v[u] = 0.f;
+#pragma unroll
+      for (int q = 0; q < SPLITK; ++q) {
+        const float4* src = reinterpret_cast<const float4*>(slots + ((size_t)q * 128 + lrow) * PLD + col);
+        const float4 a = src[0], b = src[1];
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      }
+    }
+  };
+  if (epi_warp && ready) {
+    const bool row_ok = row < p.M;
+    const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
+    if constexpr (EPI == TC_EPI_LSTM) {
+      constexpr int TH = BN / 4;
+      constexpr int TH_OWN = TH / SPLITK;  // hidden units finished by this CTA
+      static_assert(TH_OWN % 8 == 0, "each CTA must own a multiple of 8 hidden units");
+      const int H = p.N;
+      const int hid0 = n_tile * TH;
+      for (int j0 = rank * TH_OWN; j0 < (rank + 1) * TH_OWN; j0 += 8) {
+        float g[4][8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) load8(SPLITK == 1 ? q * TH + j0 : q * TH_OWN + (j0 - rank * TH_OWN), g[q]);
+        ZR_STAMP(5);
+        if (row_ok) {
+          const int hb = hid0 + j0;
+          const int nvalid = H - hb >= 8 ? 8 : (H - hb > 0 ? H - hb : 0);
+          const bool pf = (TH_OWN == 8);  // operands were prefetched
+          float hv[8], cvv[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int n = n0 + c0 + u;
-            v[u] = (n < p.N) ? v[u] + (p.bias ? p.bias[n] : 0.f) : -INFINITY;
-            cm = fmaxf(cm, v[u]);
-            if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
+            const int hid = hb + u;
+            const bool okh = u < nvalid;
+            const float b0 = pf ? pre_b[0][u] : (okh ? p.bias[hid] : 0.f);
+            const float b1 = pf ? pre_b[1][u] : (okh ? p.bias[H + hid] : 0.f);
+            const float b2 = pf ? pre_b[2][u] : (okh ? p.bias[2 * H + hid] : 0.f);
+            const float b3 = pf ? pre_b[3][u] : (okh ? p.bias[3 * H + hid] : 0.f);
+            const float cp = pf ? pre_c[u] : (okh ? p.c_prev[(size_t)row * H + hid] : 0.f);
+            const float gi = act_sigmoid<MODE>(g[0][u] + b0);
+            const float gf = act_sigmoid<MODE>(g[1][u] + b1);
+            const float gg = act_tanh<MODE>(g[2][u] + b2);
+            const float go = act_sigmoid<MODE>(g[3][u] + b3);
+            const float c = gf * cp + gi * gg;
+            hv[u] = go * act_tanh<MODE>(c) * mk;
+            cvv[u] = c * mk;
           }
-          if (cm > mx) {
-            sm *= expf(mx - cm);  // expf(-inf) = 0 on the first chunk
-            mx = cm;
-          }
-          if (mx != -INFINITY) {
-#pragma unroll
-            for (int u = 0; u < 8; ++u) sm += expf(v[u] - mx);
+          ZR_STAMP(6);
+          if (nvalid > 0) {
+            store8_f32(p.c_out, (size_t)row * H + hb, cvv, nvalid);
+            if (p.C) store8_f32(p.C, (size_t)row * p.ldc + hb, hv, nvalid);
+            store8_operand(p, (size_t)row * p.ld_op + hb, hv, nvalid);
           }
         }
+      }
+    } else if constexpr (EPI == TC_EPI_STORE) {
+      constexpr int OWN = BN / SPLITK;
+      static_assert(OWN % 8 == 0, "each CTA must own a multiple of 8 columns");
+      const int n0 = n_tile * BN;
+      for (int c0 = rank * OWN; c0 < (rank + 1) * OWN; c0 += 8) {
+        float v[8];
+        load8(SPLITK == 1 ? c0 : c0 - rank * OWN, v);
         if (row_ok) {
-          p.part_max[(size_t)n_tile * p.M + row] = mx;
-          p.part_sum[(size_t)n_tile * p.M + row] = sm;
+          const int nb = n0 + c0;
+          const int nvalid = p.N - nb >= 8 ? 8 : (p.N - nb > 0 ? p.N - nb : 0);
+          float x[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int n = nb + u;
+            float t = v[u] + ((p.bias && u < nvalid) ? p.bias[n] : 0.f);
+            if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
+            x[u] = t * mk;
+          }
+          if (nvalid > 0) {
+            if (p.C) store8_f32(p.C, (size_t)row * p.ldc + nb, x, nvalid);
+            store8_operand(p, (size_t)row * p.ld_op + nb, x, nvalid);
+          }
         }
+      }
+    } else {  // TC_EPI_LSE
+      constexpr int OWN = BN / SPLITK;
+      const int n0 = n_tile * BN;
+      const int tg = (p.target && row_ok) ? p.target[row] - p.target_offset : -1;
+      float mx = -INFINITY, sm = 0.f;
+      for (int c0 = rank * OWN; c0 < (rank + 1) * OWN; c0 += 8) {
+        float v[8];
+        load8(SPLITK == 1 ? c0 : c0 - rank * OWN, v);
+        float cm = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int n = n0 + c0 + u;
+          v[u] = (n < p.N) ? v[u] + (p.bias ? p.bias[n] : 0.f) : -INFINITY;
+          cm = fmaxf(cm, v[u]);
+          if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
+        }
+        if (cm > mx) {
+          sm *= expf(mx - cm);  // expf(-inf) = 0 on the first chunk
+          mx = cm;
+        }
+        if (mx != -INFINITY) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) sm += expf(v[u] - mx);
+        }
+      }
+      if (row_ok) {
+        const size_t pi = ((size_t)n_tile * SPLITK + rank) * p.M + row;
+        p.part_max[pi] = mx;
+        p.part_sum[pi] = sm;
       }
     }
   }
   tc_fence_before();
-  __syncthreads();
+  ZR_STAMP(7);
+  if (SPLITK > 1) cluster_sync_all();  // nobody leaves while a peer may still read its partial tile
+  else __syncthreads();
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
@@ -359,51 +547,74 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   }
 }
 
-template <int BN, int MODE, int EPI>
+template <int BN, int MODE, int EPI, int SPLITK>
 cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
-  const size_t smem = (size_t)num_stages(BN, MODE) * stage_bytes(BN, MODE) + 1024;
+  const size_t smem = (size_t)num_stages(BN, MODE, SPLITK) * stage_bytes(BN, MODE) + slot_bytes(BN, SPLITK) + 1024;
   static bool configured = false;  // once per instantiation (one device per process)
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, MODE, EPI, SPLITK>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   const int n_rows = (EPI == TC_EPI_LSTM) ? p.N * 4 : p.N;
-  dim3 grid((p.M + 127) / 128, (n_rows + BN - 1) / BN);
+  dim3 grid((p.M + 127) / 128, (n_rows + BN - 1) / BN, SPLITK);
   if (grid.x == 0 || grid.y == 0) return cudaSuccess;
-  tc_gemm_kernel<BN, MODE, EPI><<<grid, 192, smem, st>>>(p);
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = SPLITK;
+  cfg.attrs = attr;
+  cfg.numAttrs = SPLITK > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, MODE, EPI, SPLITK>, p);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 template <int MODE, int EPI>
-cudaError_t launch_bn(const TcParams& p, int BN, cudaStream_t st) {
-  switch (BN) {
-    case 32: return launch_t<32, MODE, EPI>(p, st);
-    case 64: return launch_t<64, MODE, EPI>(p, st);
-    case 128: return launch_t<128, MODE, EPI>(p, st);
-    case 256: return launch_t<256, MODE, EPI>(p, st);
+cudaError_t launch_bn(const TcParams& p, int BN, int splitk, cudaStream_t st) {
+  if (splitk == 1) {
+    switch (BN) {
+      case 32: return launch_t<32, MODE, EPI, 1>(p, st);
+      case 64: return launch_t<64, MODE, EPI, 1>(p, st);
+      case 128: return launch_t<128, MODE, EPI, 1>(p, st);
+      case 256: return launch_t<256, MODE, EPI, 1>(p, st);
+    }
+  } else if (BN == 128) {  // split-K variants exist for the 128-column tile only
+    switch (splitk) {
+      case 2: return launch_t<128, MODE, EPI, 2>(p, st);
+      case 4: return launch_t<128, MODE, EPI, 4>(p, st);
+    }
+    if constexpr (EPI != TC_EPI_LSTM) {
+      if (splitk == 8) return launch_t<128, MODE, EPI, 8>(p, st);
+    }
   }
   return cudaErrorInvalidValue;
 }
 template <int MODE>
-cudaError_t launch_epi(const TcParams& p, int BN, int epi, cudaStream_t st) {
+cudaError_t launch_epi(const TcParams& p, int BN, int epi, int splitk, cudaStream_t st) {
   switch (epi) {
-    case TC_EPI_STORE: return launch_bn<MODE, TC_EPI_STORE>(p, BN, st);
-    case TC_EPI_LSTM: return launch_bn<MODE, TC_EPI_LSTM>(p, BN, st);
-    case TC_EPI_LSE: return launch_bn<MODE, TC_EPI_LSE>(p, BN, st);
+    case TC_EPI_STORE: return launch_bn<MODE, TC_EPI_STORE>(p, BN, splitk, st);
+    case TC_EPI_LSTM: return launch_bn<MODE, TC_EPI_LSTM>(p, BN, splitk, st);
+    case TC_EPI_LSE: return launch_bn<MODE, TC_EPI_LSE>(p, BN, splitk, st);
   }
   return cudaErrorInvalidValue;
 }
 
 }  // namespace
 
-cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st) {
+cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk) {
   switch (mode) {
-    case TC_BF16: return launch_epi<TC_BF16>(p, BN, epi, st);
-    case TC_TF32: return launch_epi<TC_TF32>(p, BN, epi, st);
-    case TC_TF32X3: return launch_epi<TC_TF32X3>(p, BN, epi, st);
+    case TC_BF16: return launch_epi<TC_BF16>(p, BN, epi, splitk, st);
+    case TC_TF32: return launch_epi<TC_TF32>(p, BN, epi, splitk, st);
+    case TC_TF32X3: return launch_epi<TC_TF32X3>(p, BN, epi, splitk, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -45,10 +45,13 @@ struct TcParams {
   float* part_sum;
   float* tgt_logit;  // [M]
   int* err;          // device error word (0 = ok); set when a bounded wait gives up
+  long long* prof;   // optional: 8 globaltimer stamps per CTA (developer profiling)
 };
 
 // BN = N-tile (LSTM: 4*TH). Returns cudaErrorInvalidValue for unsupported (BN, mode, epi) combinations.
-cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st);
+// splitk > 1 (BN == 128 only: 2, 4, and 8 for the non-LSTM epilogues) splits the K axis over a thread-block cluster;
+// the LSE epilogue then produces n_tiles * splitk partial rows.
+cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk = 1);
 
 // Host helpers -------------------------------------------------------------------------------------------
 // 2-D K-major tensor map: `rows` rows of `k` elements, row stride ld (elements); box = (128-byte k-block) x box_rows

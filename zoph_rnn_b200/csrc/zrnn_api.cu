@@ -214,7 +214,7 @@ struct zrnn_lstm_layer {
   float* b = nullptr;   // 4 x H
   DevBuf x;             // gather scratch for zrnn_ih_forward
   // tensor-core form: packed [n_tiles*BN rows] x [nsrc*Kpad] with the K axis = (x | h | htild)
-  int Kpad = 0, BN = 32, n_tiles = 0;
+  int Kpad = 0, BN = 128, n_tiles = 0;
   OpMem Wcat, emb;
   CUtensorMap wmap, wmap_lo;
   DevBuf sc_x, sc_h, sc_q, sc_xl, sc_hl, sc_ql;  // operand scratch for the fp32 layer-level entry points
@@ -238,7 +238,7 @@ struct zrnn_attention {
   const int* len = nullptr;
   const int* off = nullptr;
   DevBuf tq, ctx;
-  int Kpad = 0, BN = 32;
+  int Kpad = 0, BN = 128;
   OpMem WpWaT_op, Wc_op;  // [2H rows x Kpad], [H rows x 2*Kpad]
   CUtensorMap pmap, pmap_lo, cmap, cmap_lo;
   DevBuf ctx_hi, ctx_lo, sc_h, sc_hl;
@@ -266,6 +266,20 @@ struct zrnn_softmax {
 };
 
 namespace {
+
+// split the K axis over a cluster when one launch would otherwise leave most SMs idle
+int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
+  const int ctas = ((m_cols + 127) / 128) * ((n_rows + BN - 1) / BN);
+  int s = 1;
+  if (BN == 128) {
+    if (ctas <= 20) s = 8;
+    else if (ctas <= 40) s = 4;
+    else if (ctas <= 80) s = 2;
+  }
+  return s > max_split ? max_split : s;
+}
+
+long long* g_tc_prof = nullptr;  // developer profiling buffer (see zrnn_debug_tc_profile)
 
 int* tc_error_word() {
   static int* p = nullptr;
@@ -346,9 +360,9 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
   tp.op_lo = out.lo; tp.ld_op = Kpad;
   if (eng == ENG_TF32 && tp.op_hi) tp.op_lo = nullptr;
-  tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word();
+  tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); tp.prof = g_tc_prof;
   KScope ks(KC_LSTM, st);
-  ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st));
+  ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st, pick_splitk(B, 4 * H, L->BN, 4)));
   return ZRNN_OK;
 }
 
@@ -390,7 +404,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
       tp.b = A->pmap; tp.b_lo = A->pmap_lo;
       tp.M = B; tp.N = 2 * H; tp.C = A->tq.as<float>(); tp.ldc = 2 * H; tp.act = 1; tp.act_rows = H;
       tp.err = tc_error_word();
-      ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+      ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st, pick_splitk(B, 2 * H, A->BN, 8)));
     }
     a.tanh1 = A->tq.as<float>(); a.q = A->tq.as<float>() + H; a.ld_tq = 2 * H; a.v_p = A->v_p;
     ZR_CUDA(zrnn::launch_att_local(a, st));
@@ -419,7 +433,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
     tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
     tp.op_lo = out.lo; tp.ld_op = Kpad;
     tp.err = tc_error_word();
-    ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+    ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st, pick_splitk(B, H, A->BN, 8)));
   }
   return ZRNN_OK;
 }
@@ -577,6 +591,12 @@ int zrnn_version(void) { return 100; }
 int zrnn_built_for_sm(void) { return 100; }
 long long zrnn_launch_count(void) { return zrnn::launch_count_value(); }
 void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
+
+/* developer aid, not declared in zrnn.h: LSTM tensor-core launches write 8 globaltimer stamps per CTA into buf */
+int zrnn_debug_tc_profile(long long* d_buf) {
+  g_tc_prof = d_buf;
+  return ZRNN_OK;
+}
 
 int zrnn_tc_error(void) {
   int* d = tc_error_word();
