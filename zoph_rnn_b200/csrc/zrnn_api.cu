@@ -38,12 +38,16 @@ int fail(int code, const std::string& msg) {
     if (_s != ZRNN_OK) return _s;   \
   } while (0)
 
+// bumped whenever any scratch buffer is reallocated; captured graphs that may reference the old memory are dropped
+unsigned long long g_buf_generation = 0;
+
 // device buffer that only grows
 struct DevBuf {
   void* p = nullptr;
   size_t cap = 0;
   cudaError_t reserve(size_t bytes) {
     if (bytes <= cap) return cudaSuccess;
+    ++g_buf_generation;
     if (p) cudaFree(p);
     p = nullptr;
     cap = 0;
@@ -562,7 +566,22 @@ struct zrnn_model {
   const float* last_top = nullptr;
   int last_top_cols = 0;
   std::vector<int> h_tmp;
+  // CUDA graph of one scoring pass, replayed while the shapes, buffers and stream stay the same
+  struct ScoreGraph {
+    int S = -1, T = -1, B = -1;
+    const void *src = nullptr, *tin = nullptr, *tout = nullptr, *out = nullptr;
+    void* ws = nullptr;
+    unsigned long long gen = 0;
+    cudaStream_t stream = nullptr;
+    int seen = 0;
+    cudaGraphExec_t exec = nullptr;
+  } sg;
+  void drop_graph() {
+    if (sg.exec) cudaGraphExecDestroy(sg.exec);
+    sg = ScoreGraph();
+  }
   ~zrnn_model() {
+    drop_graph();
     for (auto* l : src) delete l;
     for (auto* l : tgt) delete l;
     delete att;
@@ -1166,6 +1185,9 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
   return ZRNN_OK;
 }
 
+static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, const int* d_tgt_out,
+                            int T, int B, float* d_logp_out, cudaStream_t s);
+
 int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in,
                             const int* d_tgt_out, int T, int B, float* d_logp_out, void* stream) {
   ZR_CHECK(m && d_tgt_in && d_tgt_out && d_logp_out, "score_batch: null argument");
@@ -1174,6 +1196,50 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
   ZR_CHECK(m->cfg.lm || (d_src_ids && S_max > 0), "score_batch: a sequence-to-sequence model needs source ids");
   if (T == 0 || B == 0) return ZRNN_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  // The pass is a fixed sequence of ~10 launches per time step with no host decisions inside, so the second call
+  // with the same shapes and buffers is captured into a CUDA graph and later calls replay it (launch cost and
+  // tensor-map encoding disappear from the step).  The legacy default stream cannot be captured; kernel timing
+  // needs eager launches; ZRNN_NO_GRAPH=1 turns the graph off.
+  static const bool no_graph = std::getenv("ZRNN_NO_GRAPH") != nullptr;
+  const bool can_graph = !no_graph && s != nullptr && !g_kt.on;
+  auto& sg = m->sg;
+  const bool same = sg.S == S_max && sg.T == T && sg.B == B && sg.src == d_src_ids && sg.tin == d_tgt_in &&
+                    sg.tout == d_tgt_out && sg.out == d_logp_out && sg.stream == s && sg.ws == m->ws.p &&
+                    sg.gen == g_buf_generation;
+  if (can_graph && same && sg.exec) {
+    ZR_CUDA(cudaGraphLaunch(sg.exec, s));
+    return ZRNN_OK;
+  }
+  if (!same) {
+    m->drop_graph();
+    sg.S = S_max; sg.T = T; sg.B = B; sg.src = d_src_ids; sg.tin = d_tgt_in; sg.tout = d_tgt_out; sg.out = d_logp_out;
+    sg.stream = s;
+  }
+  if (can_graph && same && sg.seen >= 1 && !sg.exec) {
+    cudaGraph_t graph = nullptr;
+    ZR_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    const int st = score_batch_body(m, d_src_ids, S_max, d_tgt_in, d_tgt_out, T, B, d_logp_out, s);
+    const cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (st != ZRNN_OK) {
+      if (graph) cudaGraphDestroy(graph);
+      return st;
+    }
+    ZR_CUDA(ce);
+    cudaError_t ie = cudaGraphInstantiate(&sg.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    ZR_CUDA(ie);
+    ZR_CUDA(cudaGraphLaunch(sg.exec, s));
+    return ZRNN_OK;
+  }
+  const int st = score_batch_body(m, d_src_ids, S_max, d_tgt_in, d_tgt_out, T, B, d_logp_out, s);
+  sg.ws = m->ws.p;  // the eager pass has grown every buffer the pass needs
+  sg.gen = g_buf_generation;
+  sg.seen += 1;
+  return st;
+}
+
+static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, const int* d_tgt_out,
+                            int T, int B, float* d_logp_out, cudaStream_t s) {
   const zrnn_model_config& c = m->cfg;
   const int H = c.H, L = c.num_layers;
   const Geom g{H, round64(H), m->eng};
