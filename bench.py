@@ -195,38 +195,15 @@ def cpu_baseline(w):
     return dict(value=toks / dt, unit="tokens/s", cores=ol.num_threads(), kind="port", sample=sample)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32"],
-                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate, 3xTF32 tensor cores when H >= 128)")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    args = ap.parse_args()
-    w = WORKLOADS[args.workload]
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
-    if args.impl == "reference":
-        run_reference(args, w, rank)
-        return
-
+def measure(args, w, cfg, dtype, rank, world, clocks_tag):
+    """Builds the model in `dtype`, times K steps on the device (value), K steps through the host-buffer entry
+    point (e2e) and an instrumented pass for per-kernel durations.  Returns a dict of raw measurements."""
     import torch
     import torch.distributed as dist
     from zoph_rnn_b200 import api
 
-    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    cfg = make_cfg(w)
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
-    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[args.dtype]
+    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[dtype]
     model = api.neuralMT_model(cfg, dtype=dtype_id)
     model.load_weights(weights)
     del weights
@@ -257,13 +234,13 @@ def main():
                                 w["longest_sent"], d_ids, d_len, d_sc)
 
         def step_host():
-            ids, ln, sc = model.decode(srcs, w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
-            return int(np.maximum(ln[:, 0] - 1, 0).sum())
+            model.decode(srcs, w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
         h2d = int(lens.sum()) * 4
         d2h = n * (Lmax + 2) * 4
         step_device()
         torch.cuda.synchronize()
         tokens_per_step = int(np.maximum(d_len.cpu().numpy() - 1, 0).sum())  # emitted 1-best tokens incl. <EOF>
+        ncols = n * synth.beam_cap(w["beam"], w["Vt"])
     else:
         src, tin, tout = inp["src"], inp["tin"], inp["tout"]
         T, B = tin.shape
@@ -279,15 +256,15 @@ def main():
 
         def step_host():
             model.get_error(p_src, p_tin, p_tout)
-            return inp["tokens"]
         h2d = (S * B + 2 * T * B) * 4
         d2h = T * B * 4
         tokens_per_step = inp["tokens"]
+        ncols = T * B
 
     for _ in range(max(args.warmup, 3)):
         step_device()
     barrier()
-    clk_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
+    clk_path = os.path.join(ROOT, "gpurun_out", f"clocks_{clocks_tag}_rank{rank}.csv")
     os.makedirs(os.path.dirname(clk_path), exist_ok=True)
     proc, f = sample_clocks_start(clk_path)
     api.reset_launch_count()
@@ -313,8 +290,10 @@ def main():
     api.lib().zrnn_kernel_timing(0)
     if launches == 0:
         launches = eager_launches  # the timed region replayed a CUDA graph holding this many kernel nodes per K steps
-    # end-to-end through the host-buffer entry point
-    step_host()
+    # end-to-end through the host-buffer entry point (warmed up like the device path: its second call captures the
+    # CUDA graph of the pass on the library's own stream)
+    for _ in range(3):
+        step_host()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -331,6 +310,48 @@ def main():
         tokens_all = int(tk[0])
     else:
         tokens_all = tokens_per_step
+    del model
+    torch.cuda.empty_cache()
+    return dict(ms=ms, e2e_s=e2e_s, tokens_all=tokens_all, launches=int(launches), ktime=ktime, clocks=clocks,
+                h2d=h2d, d2h=d2h, ncols=ncols)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32"],
+                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate, 3xTF32 tensor cores when H >= 128)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-bf16", action="store_true", help="skip the additional bf16 measurement of an f32 run")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    cfg = make_cfg(w)
+    if args.workload == "c5" and args.dtype == "f32":
+        args.dtype = "bf16"  # config 5 is specified with bf16 weights
+    r = measure(args, w, cfg, args.dtype, rank, world, args.dtype)
+    extra = None
+    if args.dtype == "f32" and not args.no_bf16 and cfg["H"] % 8 == 0:
+        extra = measure(args, w, cfg, "bf16", rank, world, "bf16")
     if rank == 0:
         peaks = {}
         pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -338,20 +359,24 @@ def main():
         if os.path.exists(pk_path):
             peaks = json.load(open(pk_path))
             peak_src = "measured"
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        ncols = n * w["beam"] if w["kind"] == "decode" else T * B
-        roof = roofline(w, cfg, ktime, hbm_peak, peak_src, ncols, args.steps)
-        line = dict(metric=metric_name(w), value=tokens_all * args.steps / (ms / 1e3), unit="tokens/s",
-                    n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms / args.steps,
+        roof = roofline(w, cfg, r["ktime"], peaks, peak_src, r["ncols"], args.dtype)
+        line = dict(metric=metric_name(w), value=r["tokens_all"] * args.steps / (r["ms"] / 1e3), unit="tokens/s",
+                    n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=r["ms"] / args.steps,
                     higher_is_better=True, scaling="weak", vs_baseline=None, dtype=args.dtype, data="synthetic",
                     config=dict(workload=args.workload + ": " + w["desc"], sharding="sentences by rank, no collective",
                                 arithmetic=ARITH[args.dtype],
                                 l2="weights and embeddings (>1 GB) exceed the 126 MB L2 every step"),
-                    clocks=clocks, gpu_launches=int(launches),
+                    clocks=r["clocks"], gpu_launches=r["launches"],
                     launch_mode="CUDA graph replay of the scoring pass" if w["kind"] != "decode" else "eager launches",
-                    e2e=dict(value=tokens_all * args.steps / e2e_s, unit="tokens/s", h2d_bytes_per_step=h2d,
-                             d2h_bytes_per_step=d2h),
-                    roofline=roof, kernels=ktime)
+                    e2e=dict(value=r["tokens_all"] * args.steps / r["e2e_s"], unit="tokens/s",
+                             h2d_bytes_per_step=r["h2d"], d2h_bytes_per_step=r["d2h"]),
+                    roofline=roof, kernels=r["ktime"])
+        if extra:
+            line["bf16"] = dict(value=extra["tokens_all"] * args.steps / (extra["ms"] / 1e3), unit="tokens/s",
+                                ms_per_step=extra["ms"] / args.steps, arithmetic=ARITH["bf16"],
+                                e2e=extra["tokens_all"] * args.steps / extra["e2e_s"], kernels=extra["ktime"],
+                                roofline=roofline(w, cfg, extra["ktime"], peaks, peak_src, extra["ncols"], "bf16"),
+                                clocks=extra["clocks"])
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line))
@@ -359,36 +384,49 @@ def main():
         dist.destroy_process_group()
 
 
-def roofline(w, cfg, ktime, hbm_peak, peak_src, softmax_cols, steps):
-    """Roofline of the dominant kernel class, from CUDA-event durations recorded around every launch of that
-    class inside the timed region.  Algorithmic bytes per launch follow the per-unit figures of DESIGN.md."""
+# DRAM traffic per launch of the dominant kernels from ncu (dram__bytes_read.sum + dram__bytes_write.sum), captured on
+# the c2s stand-in, whose layer shapes are config 2's (see profiles/*.md); keyed by (kernel class, dtype).
+NCU_TRAFFIC = {}
+
+
+def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
+    """Roofline of the dominant kernel class.  Durations are CUDA-event pairs around every launch of the class in
+    the instrumented pass; algorithmic bytes / flops per launch follow DESIGN.md section 3."""
     if not ktime:
         return None
     top = max(ktime, key=lambda k: ktime[k]["ms"])
-    H, B = cfg["H"], w["B"] * (w.get("beam", 1) if w["kind"] == "decode" else 1)
+    H = cfg["H"]
+    B = w["B"] * (w.get("beam", 1) if w["kind"] == "decode" else 1)
     n = ktime[top]["launches"]
     avg_s = ktime[top]["ms"] / 1e3 / max(n, 1)
-    if top == "lstm_cell":
-        # weights once per step (8 HxH matrices; 12 on target layer 0 with feed-input) + biases + x,h,c in / h,c out
+    wbytes = 2 if dtype == "bf16" else 4   # bytes per weight as the reference stores them (fp32) or bf16
+    out = dict(kernel=top, launches=n, avg_launch_us=avg_s * 1e6, peak_source=peak_src,
+               traffic=NCU_TRAFFIC.get((top, dtype)))
+    if top == "softmax_gemm" and softmax_cols * cfg["V_tgt"] > 5e7:
+        flops = 2.0 * cfg["V_tgt"] * H * softmax_cols
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        out.update(bound="tensor", unit="TFLOP/s", peak=peak, achieved=flops / avg_s / 1e12,
+                   algorithmic_flops_per_launch=flops,
+                   note="2*V*H*N flops; peak = measured sustained bf16 cuBLAS (also the denominator for the 3xTF32 "
+                        "fp32-accurate mode, which spends 3 tensor-core passes per product)")
+    elif top == "lstm_cell":
         L = cfg["num_layers"]
         mats = 8.0
         if cfg["feed_input"] and not cfg["lm"]:
             mats = (8.0 * (2 * L - 1) + 12.0) / (2 * L) if w["kind"] != "decode" else (8.0 * (L - 1) + 12.0) / L
-        alg = (mats * H * H + 4 * H + 5.0 * H * B) * 4
-        unit_note = f"avg {mats:.2f} HxH fp32 matrices + 5 HxB activations per launch"
+        alg = mats * H * H * wbytes + (4 * H + 5.0 * H * B) * 4
+        out.update(bound="hbm", unit="GB/s", peak=float(peaks.get("hbm_gbs", 6650.0)), achieved=alg / avg_s / 1e9,
+                   algorithmic_bytes_per_launch=alg,
+                   note=f"avg {mats:.2f} HxH matrices of {wbytes}-byte weights + 5 HxB fp32 activations per launch")
     elif top == "softmax_gemm":
-        N = softmax_cols
-        alg = (cfg["V_tgt"] * H + H * N + 2 * N) * 4
-        unit_note = "D once + h columns + 2 floats per column"
+        alg = cfg["V_tgt"] * H * wbytes + (H * softmax_cols + 2 * softmax_cols) * 4
+        out.update(bound="hbm", unit="GB/s", peak=float(peaks.get("hbm_gbs", 6650.0)), achieved=alg / avg_s / 1e9,
+                   algorithmic_bytes_per_launch=alg, note="D once + h columns + 2 floats per column")
     else:
-        alg = None
-        unit_note = "no algorithmic-bytes model for this class"
-    out = dict(kernel=top, bound="hbm", unit="GB/s", peak=hbm_peak, peak_source=peak_src, launches=n,
-               avg_launch_us=avg_s * 1e6, traffic=None, note=unit_note)
-    if alg:
-        out["achieved"] = alg / avg_s / 1e9
-        out["frac"] = out["achieved"] / hbm_peak
-        out["algorithmic_bytes_per_launch"] = alg
+        out.update(bound="hbm", unit="GB/s", peak=float(peaks.get("hbm_gbs", 6650.0)), achieved=None,
+                   note="no algorithmic-bytes model for this class")
+    if out.get("achieved"):
+        out["frac"] = out["achieved"] / out["peak"]
     return out
 
 

@@ -547,6 +547,268 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------ persistent variant for large GEMMs
+// One CTA per SM walks over output tiles (M tile fastest, so concurrently running CTAs share the same rows of B in
+// L2).  The TMA producer runs ahead across tile boundaries and the accumulator is double-buffered in TMEM, so the
+// epilogue of tile i overlaps the main loop of tile i+1 and the load pipe never drains.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int MODE, int EPI>
+__global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid_constant__ TcParams p, int m_tiles,
+                                                                     int n_tiles) {
+  constexpr int ST = num_stages(BN, MODE);
+  constexpr int STAGE = stage_bytes(BN, MODE);
+  constexpr int BBYTES = BN * 128;
+  constexpr uint32_t IDESC = make_idesc(MODE == TC_BF16 ? 1u : 2u, BN);
+  constexpr int ACC_COLS = (MODE == TC_TF32X3 ? 2 : 1) * BN;  // main accumulator (+ cross-term accumulator)
+  constexpr int TMEM_COLS = 2 * ACC_COLS;                       // double-buffered
+  static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM budget");
+  static_assert(EPI != TC_EPI_LSTM, "the persistent variant has store and log-sum-exp epilogues only");
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[ST];
+  __shared__ __align__(8) uint64_t empty_bar[ST];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  const int total_tiles = m_tiles * n_tiles;
+  int kb_per_tile = 0;
+  for (int s = 0; s < p.nsrc; ++s) kb_per_tile += p.kblocks[s];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer (runs ahead across tiles)
+    if (lane == 0 && kb_per_tile > 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+        for (int s = 0; s < p.nsrc && ok; ++s) {
+          for (int kb = 0; kb < p.kblocks[s]; ++kb, ++it) {
+            const int st = it % ST;
+            const uint32_t ph = (uint32_t)((it / ST) & 1);
+            if (!mbar_wait(&empty_bar[st], ph ^ 1u, &abort_s, p.err, 1)) { ok = false; break; }
+            uint8_t* base = tiles + (size_t)st * STAGE;
+            mbar_expect_tx(&full_bar[st], (uint32_t)STAGE);
+            const int kx = kb * (MODE == TC_BF16 ? 64 : 32);
+            tma_load_2d(base, &p.a[s], &full_bar[st], kx, m0);
+            tma_load_2d(base + kABytes, &p.b, &full_bar[st], p.b_koff[s] + kx, n0);
+            if (MODE == TC_TF32X3) {
+              tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
+              tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], p.b_koff[s] + kx, n0);
+            }
+          }
+        }
+      }
+      if (!ok) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 20000000LL) {}
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && kb_per_tile > 0) {
+      int it = 0, ti = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
+        const int buf = ti & 1;
+        // wait until the epilogue has drained this accumulator buffer (passes at once on its first use)
+        if (!mbar_wait(&acc_empty[buf], (uint32_t)(((ti >> 1) & 1) ^ 1), &abort_s, p.err, 4)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_main = tmem_base + (uint32_t)(buf * ACC_COLS);
+        for (int kk = 0; kk < kb_per_tile; ++kk, ++it) {
+          const int st = it % ST;
+          const uint32_t ph = (uint32_t)((it / ST) & 1);
+          if (!mbar_wait(&full_bar[st], ph, &abort_s, p.err, 2)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)st * STAGE);
+          const uint32_t b_addr = a_addr + kABytes;
+          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t acc = (kk > 0 || k > 0) ? 1u : 0u;
+            umma<MODE != TC_BF16>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
+            if (MODE == TC_TF32X3) {
+              const uint64_t dal = make_smem_desc(b_addr + BBYTES), dbl = make_smem_desc(b_addr + BBYTES + kABytes);
+              umma<1>(d_main + BN, dal + 2 * k, db + 2 * k, IDESC, acc);
+              umma<1>(d_main + BN, da + 2 * k, dbl + 2 * k, IDESC, 1u);
+            }
+          }
+          umma_commit(&empty_bar[st]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else if (kb_per_tile > 0) {
+    // ------------------------------------------------------------ epilogue warps 0-3
+    int ti = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+      const int buf = ti & 1;
+      const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
+      const int row = m_tile * 128 + warp * 32 + lane;
+      const bool row_ok = row < p.M;
+      if (!mbar_wait(&acc_full[buf], (uint32_t)((ti >> 1) & 1), &abort_s, p.err, 3)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * ACC_COLS);
+      const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
+      const int n0 = n_tile * BN;
+      if constexpr (EPI == TC_EPI_STORE) {
+        for (int c0 = 0; c0 < BN; c0 += 8) {
+          float v[8];
+          tmem_ld8(taddr + c0, v);
+          if (MODE == TC_TF32X3) {
+            float t[8];
+            tmem_ld8(taddr + BN + c0, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] += t[u];
+          }
+          tmem_wait_ld();
+          if (row_ok) {
+            const int nb = n0 + c0;
+            const int nvalid = p.N - nb >= 8 ? 8 : (p.N - nb > 0 ? p.N - nb : 0);
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              const int n = nb + u;
+              float t = v[u] + ((p.bias && u < nvalid) ? p.bias[n] : 0.f);
+              if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
+              x[u] = t * mk;
+            }
+            if (nvalid > 0) {
+              if (p.C) store8_f32(p.C, (size_t)row * p.ldc + nb, x, nvalid);
+              store8_operand(p, (size_t)row * p.ld_op + nb, x, nvalid);
+            }
+          }
+        }
+      } else {  // TC_EPI_LSE
+        const int tg = (p.target && row_ok) ? p.target[row] - p.target_offset : -1;
+        float mx = -INFINITY, sm = 0.f;
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
+          if (MODE == TC_TF32X3) {
+            float t[32];
+            tmem_ld32(taddr + BN + c0, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int u = 0; u < 32; ++u) v[u] += t[u];
+          }
+          tmem_wait_ld();
+          float cm = -INFINITY;
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            const int n = n0 + c0 + u;
+            v[u] = (n < p.N) ? v[u] + (p.bias ? __ldg(p.bias + n) : 0.f) : -INFINITY;
+            cm = fmaxf(cm, v[u]);
+            if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
+          }
+          if (cm > mx) {
+            sm *= expf(mx - cm);
+            mx = cm;
+          }
+          if (mx != -INFINITY) {
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+            for (int u = 0; u < 32; u += 4) {
+              s0 += expf(v[u] - mx); s1 += expf(v[u + 1] - mx); s2 += expf(v[u + 2] - mx); s3 += expf(v[u + 3] - mx);
+            }
+            sm += (s0 + s1) + (s2 + s3);
+          }
+        }
+        if (row_ok) {
+          const size_t pi = (size_t)n_tile * p.M + row;
+          p.part_max[pi] = mx;
+          p.part_sum[pi] = sm;
+        }
+      }
+      // this warp's TMEM reads are complete: hand the buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int MODE, int EPI>
+cudaError_t launch_persistent_t(const TcParams& p, cudaStream_t st) {
+  const size_t smem = (size_t)num_stages(BN, MODE) * stage_bytes(BN, MODE) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_persistent_kernel<BN, MODE, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int m_tiles = (p.M + 127) / 128, n_tiles = (p.N + BN - 1) / BN;
+  const int total = m_tiles * n_tiles;
+  if (total == 0) return cudaSuccess;
+  const int grid = total < sm_count() ? total : sm_count();
+  tc_gemm_persistent_kernel<BN, MODE, EPI><<<grid, 192, smem, st>>>(p, m_tiles, n_tiles);
+  count_launch();
+  return cudaGetLastError();
+}
+
 template <int BN, int MODE, int EPI, int SPLITK>
 cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   const size_t smem = (size_t)num_stages(BN, MODE, SPLITK) * stage_bytes(BN, MODE) + slot_bytes(BN, SPLITK) + 1024;
@@ -609,6 +871,20 @@ cudaError_t launch_epi(const TcParams& p, int BN, int epi, int splitk, cudaStrea
 }
 
 }  // namespace
+
+cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cudaStream_t st) {
+  // tile widths: 256 columns for bf16 / tf32, 128 for 3xTF32 (its second, cross-term accumulator doubles the TMEM need)
+  if (epi == TC_EPI_LSE) {
+    if (mode == TC_BF16) return launch_persistent_t<256, TC_BF16, TC_EPI_LSE>(p, st);
+    if (mode == TC_TF32) return launch_persistent_t<256, TC_TF32, TC_EPI_LSE>(p, st);
+    if (mode == TC_TF32X3) return launch_persistent_t<128, TC_TF32X3, TC_EPI_LSE>(p, st);
+  } else if (epi == TC_EPI_STORE) {
+    if (mode == TC_BF16) return launch_persistent_t<256, TC_BF16, TC_EPI_STORE>(p, st);
+    if (mode == TC_TF32) return launch_persistent_t<256, TC_TF32, TC_EPI_STORE>(p, st);
+    if (mode == TC_TF32X3) return launch_persistent_t<128, TC_TF32X3, TC_EPI_STORE>(p, st);
+  }
+  return cudaErrorInvalidValue;
+}
 
 cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk) {
   switch (mode) {

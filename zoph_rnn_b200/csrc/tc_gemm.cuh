@@ -53,6 +53,10 @@ struct TcParams {
 // the LSE epilogue then produces n_tiles * splitk partial rows.
 cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk = 1);
 
+// Persistent one-CTA-per-SM variant for large problems (store and log-sum-exp epilogues).  The B tensor map must use
+// 256-row boxes for TC_BF16 / TC_TF32 and 128-row boxes for TC_TF32X3; LSE partials are indexed [n_tile x M].
+cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cudaStream_t st);
+
 // Host helpers -------------------------------------------------------------------------------------------
 // 2-D K-major tensor map: `rows` rows of `k` elements, row stride ld (elements); box = (128-byte k-block) x box_rows
 // elem_bytes 2 (bf16) or 4 (fp32).  Returns false when the driver entry point is unavailable or arguments are

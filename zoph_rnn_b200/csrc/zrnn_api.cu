@@ -478,7 +478,7 @@ int softmax_partials_launch(zrnn_softmax* S, const Act& h, const int* targets, i
   tp.err = tc_error_word();
   *n_parts = np; *pm = tp.part_max; *ps = tp.part_sum;
   KScope ks(KC_SOFTMAX_GEMM, st);
-  ZR_CUDA(zrnn::launch_tc_gemm(tp, S->BN, eng_tcmode(eng), zrnn::TC_EPI_LSE, st));
+  ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_LSE, st));
   return ZRNN_OK;
 }
 
@@ -513,7 +513,7 @@ int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, i
     tp.M = N; tp.N = S->V; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = S->V;
     tp.err = tc_error_word();
     KScope ks(KC_SOFTMAX_GEMM, st);
-    ZR_CUDA(zrnn::launch_tc_gemm(tp, S->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
+    ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
   }
   KScope ks(KC_SOFTMAX_REDUCE, st);
   ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st));
