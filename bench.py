@@ -316,6 +316,46 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
                 h2d=h2d, d2h=d2h, ncols=ncols)
 
 
+def run_c5_sharded(args, w, cfg, rank, world):
+    """Config 5 on N GPUs: ONE minibatch scored by all ranks (strong scaling).  Sentences are sharded for the
+    recurrent stack, the softmax matrix is sharded by vocabulary rows; two NCCL all-gathers per batch (top-layer
+    vectors, then 3 floats per token).  Timed end to end from host id arrays to host log-probs."""
+    import torch
+    import torch.distributed as dist
+    from zoph_rnn_b200 import sharded
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[args.dtype]
+    scorer = sharded.VocabShardedScorer(sharded.CudaEngine(cfg, weights, rank, world, dtype=dtype_id), rank, world)
+    del weights
+    inp = make_inputs(w, 1234)  # the same minibatch on every rank
+    for _ in range(max(args.warmup, 3)):
+        scorer.score(None, inp["tin"], inp["tout"])
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        scorer.score(None, inp["tin"], inp["tout"])
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    if rank == 0:
+        val = inp["tokens"] * args.steps / (ms / 1e3)
+        T, B = inp["tin"].shape
+        print(json.dumps(dict(metric=metric_name(w), value=val, unit="tokens/s", n_gpus=world, steps=args.steps,
+                              warmup=max(args.warmup, 3), ms_per_step=ms / args.steps, higher_is_better=True,
+                              scaling="strong", vs_baseline=None, dtype=args.dtype, data="synthetic",
+                              config=dict(workload=args.workload + ": " + w["desc"],
+                                          sharding="sentences by rank for the LSTM stack + vocabulary rows of D by rank; "
+                                                   "NCCL all-gather of top-layer vectors and of (max, sum, target) per token",
+                                          arithmetic=ARITH[args.dtype]),
+                              e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=2 * T * B * 4,
+                                       d2h_bytes_per_step=T * B * 4))))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -348,6 +388,10 @@ def main():
     cfg = make_cfg(w)
     if args.workload == "c5" and args.dtype == "f32":
         args.dtype = "bf16"  # config 5 is specified with bf16 weights
+    if args.workload == "c5" and world > 1:
+        run_c5_sharded(args, w, cfg, rank, world)
+        dist.destroy_process_group()
+        return
     r = measure(args, w, cfg, args.dtype, rank, world, args.dtype)
     extra = None
     if args.dtype == "f32" and not args.no_bf16 and cfg["H"] % 8 == 0:

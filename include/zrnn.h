@@ -213,6 +213,11 @@ int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tg
 /* Same, with ids already on the device and results left on the device; asynchronous on `stream`. */
 int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in,
                             const int* d_tgt_out, int T, int B, float* d_logp_out, void* stream);
+/* The recurrent part of getError only (encoder, decoder stack, attention): writes the H x (T*B) vectors that the
+ * reference hands to softmax_layer::backprop_prep_GPU (src/model.hpp:1752,1785) into d_top_out and skips the
+ * softmax.  Used when the softmax is vocabulary-sharded over several GPUs. */
+int zrnn_forward_states_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, int T, int B,
+                               float* d_top_out, void* stream);
 /* Copies the top-layer vectors the last scoring call handed to the softmax (H x (T*B)) into d_out, which holds
  * capacity_cols columns; *n_cols receives the number of columns available.  For layer-level checks. */
 int zrnn_model_copy_top_states(zrnn_model* m, float* d_out, int capacity_cols, int* n_cols, void* stream);

@@ -167,3 +167,18 @@ def test_error_statuses(api):
     sm = api.softmax_layer(10, 4, shard_lo=0, shard_hi=5)
     with pytest.raises(api.ZrnnError):
         sm.compute_loss(torch.zeros(4, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"), None)
+
+
+@pytest.mark.parametrize("dtype", [3, 4])
+def test_vocab_sharded_scorer_on_one_gpu(api, oracle, dtype):
+    """The multi-GPU scorer with world size 1 (no collective) equals the plain scoring call and the oracle."""
+    from zoph_rnn_b200 import sharded
+    cfg = synth.make_cfg(2, 128, 0, 3001, lm=1)
+    w = synth.make_weights(cfg, seed=6, scale=0.1)
+    tin, tout = synth.make_lm_batch(3001, 9, 7, seed=2, zipf_s=1.05)
+    tout[-2:, 3] = -1
+    tin[-2:, 3] = -1
+    scorer = sharded.VocabShardedScorer(sharded.CudaEngine(cfg, w, 0, 1, dtype=dtype), 0, 1)
+    got = scorer.score(None, tin, tout)
+    want = oracle.OracleModel(cfg, w).score_batch(None, tin, tout)
+    helpers.assert_logp_close(got, want)

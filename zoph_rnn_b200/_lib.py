@@ -85,6 +85,8 @@ SIGNATURES = {
                                         ctypes.c_int, c_void_p, ctypes.POINTER(ctypes.c_double)]),
     "zrnn_score_batch_device": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p, ctypes.c_int,
                                                ctypes.c_int, c_void_p, c_void_p]),
+    "zrnn_forward_states_device": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, c_void_p, ctypes.c_int, ctypes.c_int,
+                                                  c_void_p, c_void_p]),
     "zrnn_model_copy_top_states": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, c_int_p, c_void_p]),
     "zrnn_model_softmax": (c_void_p, [c_void_p]),
     "zrnn_beam_decode_batch": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,

@@ -64,9 +64,12 @@ class _LstmLayer:
         check(lib().zrnn_lstm_load(self._h, arr, len(keep)))
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            lib().zrnn_lstm_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                lib().zrnn_lstm_destroy(self._h)
+                self._h = None
+        except TypeError:  # interpreter shutdown: module globals are already gone
+            pass
 
 
 class Input_To_Hidden_Layer(_LstmLayer):
@@ -139,9 +142,12 @@ class attention_layer:
         return (out, al) if want_alignments else out
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            lib().zrnn_att_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                lib().zrnn_att_destroy(self._h)
+                self._h = None
+        except TypeError:
+            pass
 
 
 class softmax_layer:
@@ -200,9 +206,12 @@ class softmax_layer:
         return val.view(N, k), idx.view(N, k), eos
 
     def __del__(self):
-        if getattr(self, "_h", None) and self._owned:
-            lib().zrnn_softmax_destroy(self._h)
-        self._h = None
+        try:
+            if getattr(self, "_h", None) and self._owned:
+                lib().zrnn_softmax_destroy(self._h)
+            self._h = None
+        except TypeError:
+            pass
 
 
 class neuralMT_model:
@@ -269,6 +278,10 @@ class neuralMT_model:
         check(lib().zrnn_score_batch_device(self._h, _ptr(d_src), S, _ptr(d_tin), _ptr(d_tout), T, B, _ptr(d_logp),
                                             _stream()))
 
+    def forward_states_device(self, d_src, S, d_tin, T, B, d_top):
+        """Recurrent stack only: fills d_top (float32 CUDA tensor, H x (T*B) column-major) and skips the softmax."""
+        check(lib().zrnn_forward_states_device(self._h, _ptr(d_src), S, _ptr(d_tin), T, B, _ptr(d_top), _stream()))
+
     def last_top_states(self):
         """The vectors the last scoring call handed to the softmax, flat column-major H x (T*B)."""
         n = ctypes.c_int()
@@ -304,9 +317,12 @@ class neuralMT_model:
                                                   _ptr(d_ids), _ptr(d_len), _ptr(d_score), _stream()))
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            lib().zrnn_model_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None):
+                lib().zrnn_model_destroy(self._h)
+                self._h = None
+        except TypeError:
+            pass
 
 
 def launch_count():

@@ -1185,6 +1185,7 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
   return ZRNN_OK;
 }
 
+// d_logp_out == nullptr: stop after the recurrent stack (the top-layer vectors stay in m->last_top)
 static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, const int* d_tgt_out,
                             int T, int B, float* d_logp_out, cudaStream_t s);
 
@@ -1302,7 +1303,23 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
   const Act& top = c.attention ? hts : tseq[L - 1];
   m->last_top = top.f32;
   m->last_top_cols = (int)nT;
+  if (!d_logp_out) return ZRNN_OK;
   return softmax_score_act(m->sm, top, tout_id, tout_mk, (int)nT, d_logp_out, s);
+}
+
+int zrnn_forward_states_device(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, int T, int B,
+                               float* d_top_out, void* stream) {
+  ZR_CHECK(m && d_tgt_in && d_top_out, "forward_states: null argument");
+  if (!m->finalized) return fail(ZRNN_E_STATE, "forward_states: model weights not finalized");
+  ZR_CHECK(T >= 0 && B >= 0, "forward_states: negative size");
+  ZR_CHECK(m->cfg.lm || (d_src_ids && S_max > 0), "forward_states: a sequence-to-sequence model needs source ids");
+  if (T == 0 || B == 0) return ZRNN_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  m->drop_graph();
+  // the target-output ids only feed the softmax, which is skipped: reuse the inputs as a placeholder
+  ZR_TRY(score_batch_body(m, d_src_ids, S_max, d_tgt_in, d_tgt_in, T, B, nullptr, s));
+  ZR_CUDA(cudaMemcpyAsync(d_top_out, m->last_top, sizeof(float) * (size_t)T * B * m->cfg.H, cudaMemcpyDeviceToDevice, s));
+  return ZRNN_OK;
 }
 
 int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tgt_in, const int* tgt_out, int T,
