@@ -42,6 +42,10 @@ WORKLOADS = {
     "c4": dict(desc="beam decode 2x1000 V=50k global-dot attention beam 12, 64 sentences S~U[10,50]", kind="decode",
                L=2, H=1000, Vs=50000, Vt=50000, B=64, S=(10, 50), T=None, att=2, feed=1, scale=0.1,
                dist="uniform", zipf=1.1, beam=12, max_ratio=2.0, min_ratio=0.5, longest_sent=100),
+    # short-sentence stand-in with config 4's shapes (768 hypothesis columns, V=50k) for profiler captures
+    "c4s": dict(desc="profiling stand-in: beam decode 2x1000 V=50k global-dot attention beam 12, 64 sentences S~U[4,6]",
+                kind="decode", L=2, H=1000, Vs=50000, Vt=50000, B=64, S=(4, 6), T=None, att=2, feed=1, scale=0.1,
+                dist="uniform", zipf=1.1, beam=12, max_ratio=2.0, min_ratio=0.5, longest_sent=100),
     "c5": dict(desc="LM 2x2048 V=200k B=256 T=64", kind="lm", L=2, H=2048, Vs=0, Vt=200000, B=256, S=0, T=64,
                att=0, feed=0, scale=0.02, dist="normal", zipf=1.05),
 }

@@ -492,45 +492,53 @@ cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tg
 // per-column top-k of log-softmax(z): one CTA per column
 // ------------------------------------------------------------------------------------------
 #define ZR_TOPK_MAX 16
+#define ZR_TOPK_CAND 512
+// Two passes over the column.  Pass 1: per-thread online (max, sum exp) and per-thread maximum; the k-th largest of
+// the 256 thread maxima is a lower bound of the column's k-th largest value.  Pass 2: every element >= that bound
+// becomes a candidate (a handful for real logits), and the k best candidates are picked by k block-wide argmax
+// rounds.  Only if more than ZR_TOPK_CAND elements reach the bound (massive ties) the bound is raised and pass 2
+// repeated.
+// With part_max / part_sum (n_parts row-tile partials per column, laid out [part][N], as the GEMM epilogue writes
+// them) pass 1 reads those few values instead of the whole column.
 __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict__ z, int V, int N, int k,
+                                                         const float* __restrict__ part_max,
+                                                         const float* __restrict__ part_sum, int n_parts,
                                                          float* __restrict__ val_out, int* __restrict__ idx_out,
                                                          float* __restrict__ logp_eos) {
-  __shared__ float lv[ZR_TOPK_MAX][256];
-  __shared__ int li[ZR_TOPK_MAX][256];
+  __shared__ float tmax[256];
+  __shared__ float cval[ZR_TOPK_CAND];
+  __shared__ int cidx[ZR_TOPK_CAND];
   __shared__ float red_m[8], red_s[8];
   __shared__ float win_v[8];
-  __shared__ int win_t[8];
-  __shared__ float s_M, s_logS;
-  __shared__ int s_winner;
+  __shared__ int win_i[8], win_p[8];
+  __shared__ float s_M, s_logS, s_thr;
+  __shared__ int s_count, s_win;
   const int col = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const float* zc = z + (size_t)col * V;
-  int cnt = 0;
-  float thr = -INFINITY;  // value of the last kept element once the list is full
   float m = -INFINITY, s = 0.f;
-  for (int i = tid; i < V; i += 256) {
-    const float v = zc[i];
-    if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
-    else s += expf(v - m);
-    if (cnt < k || v > thr) {
-      int pos = (cnt < k) ? cnt : k - 1;
-      while (pos > 0 && lv[pos - 1][tid] < v) {
-        lv[pos][tid] = lv[pos - 1][tid];
-        li[pos][tid] = li[pos - 1][tid];
-        --pos;
-      }
-      lv[pos][tid] = v;
-      li[pos][tid] = i;
-      if (cnt < k) ++cnt;
-      if (cnt == k) thr = lv[k - 1][tid];
+  const bool sum_in_pass2 = part_max && !part_sum;  // only tile maxima are known: sum exp(v - M) during the scan
+  if (part_max) {
+    for (int j = tid; j < n_parts; j += 256) {
+      const float pm = part_max[(size_t)j * N + col];
+      const float ps = part_sum ? part_sum[(size_t)j * N + col] : 0.f;
+      if (pm > m) { s = s * expf(m - pm) + ps; m = pm; }
+      else if (pm != -INFINITY) s += ps * expf(pm - m);
+    }
+  } else {
+    for (int i = tid; i < V; i += 256) {
+      const float v = zc[i];
+      if (v > m) { s = s * expf(m - v) + 1.f; m = v; }
+      else s += expf(v - m);
     }
   }
-  // block (max, sum)
+  tmax[tid] = m;
   float wm = m;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
   float ws = (m == -INFINITY) ? 0.f : s * expf(m - wm);
   ws = warp_sum(ws);
   if (lane == 0) { red_m[w] = wm; red_s[w] = ws; }
+  if (tid == 0) s_count = 0;
   __syncthreads();
   if (tid == 0) {
     float M = -INFINITY;
@@ -542,43 +550,103 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
     s_logS = (float)log(S);
     if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - M) - s_logS : -INFINITY;
   }
+  // rank of this thread's maximum among the 256 maxima (ties broken by thread id)
+  {
+    int rank = 0;
+    for (int j = 0; j < 256; ++j) {
+      const float o = tmax[j];
+      rank += (o > m || (o == m && j < tid)) ? 1 : 0;
+    }
+    const int want = (k < 256 ? k : 256) - 1;
+    if (rank == want) s_thr = m;
+  }
   __syncthreads();
-  int head = 0;
+  float thr = s_thr;
+  float s2 = 0.f;
+  const float Mall = s_M;
+  for (int attempt = 0; attempt < 4; ++attempt) {
+    for (int i = tid; i < V; i += 256) {
+      const float v = zc[i];
+      if (sum_in_pass2 && attempt == 0) s2 += expf(v - Mall);
+      if (v >= thr && v != -INFINITY) {
+        const int p = atomicAdd(&s_count, 1);
+        if (p < ZR_TOPK_CAND) { cval[p] = v; cidx[p] = i; }
+      }
+    }
+    __syncthreads();
+    if (s_count <= ZR_TOPK_CAND) break;
+    // too many candidates (massive ties): raise the bound just above the k-th largest distinct stored value, which
+    // is still a lower bound of the column's k-th largest distinct value, and collect again
+    if (tid < 32) {
+      float best = INFINITY;
+      for (int r = 0; r < k; ++r) {
+        float vmax = -INFINITY;
+        for (int j = lane; j < ZR_TOPK_CAND; j += 32)
+          if (cval[j] < best) vmax = fmaxf(vmax, cval[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        if (vmax == -INFINITY) break;
+        best = vmax;
+      }
+      if (lane == 0) {
+        s_thr = (best > thr && best != INFINITY) ? best : nextafterf(thr, INFINITY);
+        s_count = 0;
+      }
+    }
+    __syncthreads();
+    thr = s_thr;
+  }
+  if (sum_in_pass2) {  // finish the normaliser now that the whole column has been seen
+    s2 = warp_sum(s2);
+    if (lane == 0) red_s[w] = s2;
+    __syncthreads();
+    if (tid == 0) {
+      double S = 0.0;
+      for (int i = 0; i < 8; ++i) S += (double)red_s[i];
+      s_logS = (float)log(S);
+      if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - s_M) - s_logS : -INFINITY;
+    }
+    __syncthreads();
+  }
+  const int nc = s_count < ZR_TOPK_CAND ? s_count : ZR_TOPK_CAND;
+  // k rounds of block-wide argmax over the candidates (value, then lower word id)
   for (int r = 0; r < k; ++r) {
-    float v = (head < cnt) ? lv[head][tid] : -INFINITY;
-    int id = (head < cnt) ? li[head][tid] : 0x7fffffff;
-    int t = tid;
+    float v = -INFINITY;
+    int id = 0x7fffffff, pos = -1;
+    for (int j = tid; j < nc; j += 256) {
+      const float cv = cval[j];
+      const int ci = cidx[j];
+      if (cv > v || (cv == v && ci < id)) { v = cv; id = ci; pos = j; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, v, o);
       const int oi = __shfl_xor_sync(0xffffffffu, id, o);
-      const int ot = __shfl_xor_sync(0xffffffffu, t, o);
-      if (ov > v || (ov == v && oi < id)) { v = ov; id = oi; t = ot; }
+      const int op = __shfl_xor_sync(0xffffffffu, pos, o);
+      if (ov > v || (ov == v && oi < id)) { v = ov; id = oi; pos = op; }
     }
-    if (lane == 0) { win_v[w] = v; win_t[w] = t; red_m[w] = __int_as_float(id); }
+    if (lane == 0) { win_v[w] = v; win_i[w] = id; win_p[w] = pos; }
     __syncthreads();
     if (tid == 0) {
       float bv = win_v[0];
-      int bt = win_t[0], bi = __float_as_int(red_m[0]);
-      for (int i = 1; i < 8; ++i) {
-        const int oi = __float_as_int(red_m[i]);
-        if (win_v[i] > bv || (win_v[i] == bv && oi < bi)) { bv = win_v[i]; bt = win_t[i]; bi = oi; }
-      }
-      s_winner = bt;
-      const bool ok = bv != -INFINITY;
+      int bi = win_i[0], bp = win_p[0];
+      for (int i = 1; i < 8; ++i)
+        if (win_v[i] > bv || (win_v[i] == bv && win_i[i] < bi)) { bv = win_v[i]; bi = win_i[i]; bp = win_p[i]; }
+      const bool ok = bp >= 0 && bv != -INFINITY;
       val_out[(size_t)col * k + r] = ok ? (bv - s_M) - s_logS : -INFINITY;
       idx_out[(size_t)col * k + r] = ok ? bi : -1;
+      s_win = bp;
     }
     __syncthreads();
-    if (tid == s_winner) ++head;
+    if (tid == 0 && s_win >= 0) cval[s_win] = -INFINITY;  // remove the winner
     __syncthreads();
   }
 }
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
-                             cudaStream_t st) {
+                             cudaStream_t st, const float* part_max, const float* part_sum, int n_parts) {
   if (N <= 0) return cudaSuccess;
   if (k < 1 || k > ZR_TOPK_MAX) return cudaErrorInvalidValue;
-  topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, val_out, idx_out, logp_eos);
+  topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, part_max, part_sum, n_parts, val_out, idx_out, logp_eos);
   count_launch();
   return cudaGetLastError();
 }

@@ -694,6 +694,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
       const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
       const int n0 = n_tile * BN;
       if constexpr (EPI == TC_EPI_STORE) {
+        const bool want_max = p.part_max != nullptr;  // also emit the per-tile maximum of the stored values
+        const bool want_lse = want_max && p.part_sum != nullptr;  // ... and sum exp(x - max)
+        float mx = -INFINITY, sm = 0.f;
         for (int c0 = 0; c0 < BN; c0 += 8) {
           float v[8];
           tmem_ld8(taddr + c0, v);
@@ -709,18 +712,33 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
             const int nb = n0 + c0;
             const int nvalid = p.N - nb >= 8 ? 8 : (p.N - nb > 0 ? p.N - nb : 0);
             float x[8];
+            float cm = -INFINITY;
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               const int n = nb + u;
               float t = v[u] + ((p.bias && u < nvalid) ? p.bias[n] : 0.f);
               if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
               x[u] = t * mk;
+              if (u < nvalid) cm = fmaxf(cm, x[u]);
             }
             if (nvalid > 0) {
               if (p.C) store8_f32(p.C, (size_t)row * p.ldc + nb, x, nvalid);
               store8_operand(p, (size_t)row * p.ld_op + nb, x, nvalid);
+              if (want_lse) {
+                if (cm > mx) { sm *= expf(mx - cm); mx = cm; }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                  if (u < nvalid) sm += expf(x[u] - mx);
+              } else if (want_max) {
+                mx = fmaxf(mx, cm);
+              }
             }
           }
+        }
+        if (want_max && row_ok) {
+          const size_t pi = (size_t)n_tile * p.M + row;
+          p.part_max[pi] = mx;
+          if (want_lse) p.part_sum[pi] = sm;
         }
       } else {  // TC_EPI_LSE
         const int tg = (p.target && row_ok) ? p.target[row] - p.target_offset : -1;

@@ -495,6 +495,8 @@ int softmax_score_act(zrnn_softmax* S, const Act& h, const int* targets, const i
 
 int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
   ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
+  const float *pm = nullptr, *ps = nullptr;
+  int np = 0;
   if (S->eng == ENG_SIMT) {
     zrnn::GemmArgs g;
     std::memset(&g, 0, sizeof(g));
@@ -505,18 +507,24 @@ int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, i
     ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
   } else {
     const int eng = S->eng;
+    np = S->n_tiles;
+    ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
     zrnn::TcParams tp;
     std::memset(&tp, 0, sizeof(tp));
     ZR_TRY(act_maps(h, eng, S->H, S->Kpad, N, &tp.a[0], &tp.a_lo[0]));
     tp.nsrc = 1; tp.kblocks[0] = (S->H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
     tp.b = S->dmap; tp.b_lo = S->dmap_lo;
     tp.M = N; tp.N = S->V; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = S->V;
+    // the epilogue also leaves each tile's maximum: the top-k kernel derives its threshold and the column maximum
+    // from them and needs a single pass over the logits
+    tp.part_max = S->parts.as<float>(); tp.part_sum = nullptr;
+    pm = tp.part_max; ps = nullptr;
     tp.err = tc_error_word();
     KScope ks(KC_SOFTMAX_GEMM, st);
     ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
   }
   KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st));
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, ps, np));
   return ZRNN_OK;
 }
 
