@@ -785,8 +785,100 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
     att_store_op(a, b, i, acc);
   }
 }
+// Single-pass variant for H % 4 == 0, H <= 1024: one CTA per target column, each of its 8 warps walks over every 8th
+// source position, keeps the position's vector in registers for both the score and the context (so the source memory
+// is read once, with 16-byte loads), and carries a running (max, sum, context); the 8 partial results are merged through
+// shared memory at the end.
+__global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
+  __shared__ float s_m[8], s_l[8];
+  __shared__ float4 s_ctx[8][256];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int H = a.H, H4 = H >> 2, sb = b / a.cols_per_sent;
+  float* c = a.c_t + (size_t)b * H;
+  if (a.mask && a.mask[b] != 1) {
+    for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
+    if (a.align_out)
+      for (int s = tid; s < a.S_max; s += blockDim.x) a.align_out[(size_t)s * a.B + b] = 0.f;
+    return;
+  }
+  const int len = a.len[sb], off = a.offset[sb];
+  const float4* h4 = reinterpret_cast<const float4*>(a.h_t + (size_t)b * H);
+  float4 hv[8], ctx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int j = lane + 32 * i;
+    hv[i] = j < H4 ? h4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ctx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int pos = w; pos < len; pos += 8) {
+    const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)(len - 1 - pos + off) * a.B_src + sb) * H);
+    float4 rv[8];
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j = lane + 32 * i;
+      rv[i] = j < H4 ? __ldg(r4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      sc += rv[i].x * hv[i].x + rv[i].y * hv[i].y + rv[i].z * hv[i].z + rv[i].w * hv[i].w;
+    }
+    sc = warp_sum(sc);
+    if (a.align_out && lane == 0) a.align_out[(size_t)pos * a.B + b] = sc;  // raw score, normalised below
+    const float mn = fmaxf(m, sc);
+    const float scale = expf(m - mn), e = expf(sc - mn);
+    l = l * scale + e;
+    m = mn;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ctx[i].x = ctx[i].x * scale + e * rv[i].x;
+      ctx[i].y = ctx[i].y * scale + e * rv[i].y;
+      ctx[i].z = ctx[i].z * scale + e * rv[i].z;
+      ctx[i].w = ctx[i].w * scale + e * rv[i].w;
+    }
+  }
+  if (lane == 0) { s_m[w] = m; s_l[w] = l; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_ctx[w][lane + 32 * i] = ctx[i];
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) M = fmaxf(M, s_m[q]);
+  float Lsum = 0.f, wq[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    wq[q] = (s_m[q] == -INFINITY) ? 0.f : expf(s_m[q] - M);
+    Lsum += s_l[q] * wq[q];
+  }
+  const float inv = 1.0f / Lsum;
+  if (tid < H4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 v = s_ctx[q][tid];
+      acc.x += wq[q] * v.x; acc.y += wq[q] * v.y; acc.z += wq[q] * v.z; acc.w += wq[q] * v.w;
+    }
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    reinterpret_cast<float4*>(c)[tid] = acc;
+    att_store_op(a, b, 4 * tid + 0, acc.x);
+    att_store_op(a, b, 4 * tid + 1, acc.y);
+    att_store_op(a, b, 4 * tid + 2, acc.z);
+    att_store_op(a, b, 4 * tid + 3, acc.w);
+  }
+  if (a.align_out) {
+    __syncthreads();
+    for (int pos = tid; pos < a.S_max; pos += blockDim.x) {
+      const size_t idx = (size_t)pos * a.B + b;
+      a.align_out[idx] = pos < len ? expf(a.align_out[idx] - M) * inv : 0.f;
+    }
+  }
+}
+
 cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
   if (a.B <= 0) return cudaSuccess;
+  if ((a.H & 3) == 0 && a.H <= 1024) {
+    att_global_fast_kernel<<<a.B, 256, 0, st>>>(a);
+    count_launch();
+    return cudaGetLastError();
+  }
   const size_t smem = sizeof(float) * (size_t)(a.S_max > 0 ? a.S_max : 1);
   if (smem > 40 * 1024) return cudaErrorInvalidValue;
   att_global_kernel<<<a.B, 256, smem, st>>>(a);

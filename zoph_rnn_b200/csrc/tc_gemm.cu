@@ -199,10 +199,14 @@ __device__ __forceinline__ long long gtime() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-#define ZR_STAMP(i)                                                                                         \
-  do {                                                                                                      \
-    if (p.prof && (threadIdx.x == 0))                                                                       \
-      p.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = gtime(); \
+#define ZR_STAMP(i)                                                                                           \
+  do {                                                                                                        \
+    if (p.prof && (threadIdx.x == 0)) {                                                                       \
+      if (p.prof_slot < 0)                                                                                    \
+        p.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (i)] = gtime(); \
+      else if (blockIdx.x + blockIdx.y + blockIdx.z == 0)                                                     \
+        p.prof[(size_t)p.prof_slot * 8 + (i)] = gtime();                                                      \
+    }                                                                                                         \
   } while (0)
 
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
@@ -591,6 +595,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const int total_tiles = m_tiles * n_tiles;
+  ZR_STAMP(0);
   int kb_per_tile = 0;
   for (int s = 0; s < p.nsrc; ++s) kb_per_tile += p.kblocks[s];
 
@@ -790,6 +795,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  ZR_STAMP(7);
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)

@@ -46,6 +46,7 @@ struct TcParams {
   float* tgt_logit;  // [M]
   int* err;          // device error word (0 = ok); set when a bounded wait gives up
   long long* prof;   // optional: 8 globaltimer stamps per CTA (developer profiling)
+  int prof_slot;     // >= 0: only CTA (0,0,0) stamps, into prof[prof_slot*8 ..] (timeline of many launches)
 };
 
 // BN = N-tile (LSTM: 4*TH). Returns cudaErrorInvalidValue for unsupported (BN, mode, epi) combinations.

@@ -284,6 +284,16 @@ int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
 }
 
 long long* g_tc_prof = nullptr;  // developer profiling buffer (see zrnn_debug_tc_profile)
+int g_tc_prof_slot = -1;          // >= 0: timeline mode, one slot per tensor-core launch
+int g_tc_prof_cap = 0;
+void prof_attach(zrnn::TcParams& tp) {
+  tp.prof = g_tc_prof;
+  tp.prof_slot = -1;
+  if (g_tc_prof && g_tc_prof_slot >= 0) {
+    if (g_tc_prof_slot < g_tc_prof_cap) tp.prof_slot = g_tc_prof_slot++;
+    else tp.prof = nullptr;
+  }
+}
 
 int* tc_error_word() {
   static int* p = nullptr;
@@ -364,7 +374,7 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
   tp.op_lo = out.lo; tp.ld_op = Kpad;
   if (eng == ENG_TF32 && tp.op_hi) tp.op_lo = nullptr;
-  tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); tp.prof = g_tc_prof;
+  tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); prof_attach(tp);
   KScope ks(KC_LSTM, st);
   ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st, pick_splitk(B, 4 * H, L->BN, 4)));
   return ZRNN_OK;
@@ -408,6 +418,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
       tp.b = A->pmap; tp.b_lo = A->pmap_lo;
       tp.M = B; tp.N = 2 * H; tp.C = A->tq.as<float>(); tp.ldc = 2 * H; tp.act = 1; tp.act_rows = H;
       tp.err = tc_error_word();
+      if (g_tc_prof_slot >= 0) prof_attach(tp);
       ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st, pick_splitk(B, 2 * H, A->BN, 8)));
     }
     a.tanh1 = A->tq.as<float>(); a.q = A->tq.as<float>() + H; a.ld_tq = 2 * H; a.v_p = A->v_p;
@@ -437,6 +448,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
     tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
     tp.op_lo = out.lo; tp.ld_op = Kpad;
     tp.err = tc_error_word();
+    if (g_tc_prof_slot >= 0) prof_attach(tp);
     ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st, pick_splitk(B, H, A->BN, 8)));
   }
   return ZRNN_OK;
@@ -476,6 +488,7 @@ int softmax_partials_launch(zrnn_softmax* S, const Act& h, const int* targets, i
   tp.target = targets; tp.target_offset = S->lo;
   tp.part_max = S->parts.as<float>(); tp.part_sum = S->parts.as<float>() + (size_t)np * N; tp.tgt_logit = tgt;
   tp.err = tc_error_word();
+  if (g_tc_prof_slot >= 0) prof_attach(tp);
   *n_parts = np; *pm = tp.part_max; *ps = tp.part_sum;
   KScope ks(KC_SOFTMAX_GEMM, st);
   ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_LSE, st));
@@ -622,6 +635,14 @@ void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
 /* developer aid, not declared in zrnn.h: LSTM tensor-core launches write 8 globaltimer stamps per CTA into buf */
 int zrnn_debug_tc_profile(long long* d_buf) {
   g_tc_prof = d_buf;
+  g_tc_prof_slot = -1;
+  return ZRNN_OK;
+}
+/* timeline mode: every tensor-core launch gets the next of `slots` 8-stamp records (CTA 0 only) */
+int zrnn_debug_tc_timeline(long long* d_buf, int slots) {
+  g_tc_prof = d_buf;
+  g_tc_prof_slot = d_buf ? 0 : -1;
+  g_tc_prof_cap = slots;
   return ZRNN_OK;
 }
 
@@ -1179,15 +1200,16 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
                        cudaStream_t s) {
   const int L = m->cfg.num_layers;
   ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
-  for (int t = 0; t < S; ++t) {
-    Act x = act_at(X0, (size_t)t * B, g);
-    for (int l = 0; l < L; ++l) {
+  // Layer by layer, not step by step: layer l only needs layer l-1's finished sequence, and running all S steps
+  // of one layer back to back keeps that layer's weights resident in the 126 MB L2 (all layers together do not fit).
+  for (int l = 0; l < L; ++l) {
+    for (int t = 0; t < S; ++t) {
+      const Act x = l == 0 ? act_at(X0, (size_t)t * B, g) : act_at(seq[l - 1], (size_t)t * B, g);
       const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
       const Act out = act_at(seq[l], (size_t)t * B, g);
       const int cu = cur[l];
       ZR_TRY(cell_forward(m->src[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], s));
       cur[l] = cu ^ 1;
-      x = out;
     }
   }
   return ZRNN_OK;
