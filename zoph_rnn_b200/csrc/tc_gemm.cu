@@ -7,6 +7,7 @@
 #include "tc_gemm.cuh"
 
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 
 #include "kernels.cuh"
@@ -209,6 +210,12 @@ __device__ __forceinline__ long long gtime() {
     }                                                                                                         \
   } while (0)
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while
+// its predecessor is still draining; pdl_wait() blocks until the predecessor has completed and its writes are
+// visible, pdl_trigger() tells the runtime that the successor may be scheduled.  Both are no-ops otherwise.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
@@ -280,6 +287,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   ZR_STAMP(1);
+  pdl_wait();  // everything above touched only this CTA's shared memory and TMEM
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
@@ -370,6 +378,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
     tc_fence_after();
   }
   ZR_STAMP(2);
+  pdl_trigger();  // the successor may begin its prologue while this kernel runs its epilogue
   const int n_main = total_kb < NACC ? total_kb : NACC;  // main accumulators that were written
   // 8 accumulator columns starting at `col` from TMEM, summed over the partial accumulators
   auto load8_tmem = [&](int col, float* v) {
@@ -621,6 +630,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  pdl_wait();
 
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (runs ahead across tiles)
@@ -833,6 +843,8 @@ cudaError_t launch_persistent_t(const TcParams& p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+static const bool g_use_pdl = std::getenv("ZRNN_NO_PDL") == nullptr;
+
 template <int BN, int MODE, int EPI, int SPLITK>
 cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   const size_t smem = (size_t)num_stages(BN, MODE, SPLITK) * stage_bytes(BN, MODE) + slot_bytes(BN, SPLITK) + 1024;
@@ -852,13 +864,22 @@ cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = SPLITK;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (SPLITK > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = SPLITK;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = SPLITK > 1 ? 1 : 0;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, tc_gemm_kernel<BN, MODE, EPI, SPLITK>, p);
   count_launch();
   return e;
