@@ -52,6 +52,11 @@ const char* zrnn_last_error(void);
 /* library version, and the compute capability the kernels were built for (100 = sm_100a) */
 int zrnn_version(void);
 int zrnn_built_for_sm(void);
+/* Device selection for the calling thread.  The reference binds a model to devices with --multi-gpu and
+ * cudaSetDevice before every allocation (src/main.cu:28-30 of the option list, src/model.hpp:3-60); here one
+ * device holds a whole model, so the caller selects it once before creating the model. */
+int zrnn_device_count(int* n);
+int zrnn_set_device(int device);
 /* number of kernels this library has launched on the calling thread since the last reset */
 long long zrnn_launch_count(void);
 void zrnn_reset_launch_count(void);
@@ -203,6 +208,14 @@ int zrnn_model_finalize(zrnn_model* m);
  * has attention (the reference has no flag for the type), D is --attention-width. */
 int zrnn_model_load_file(const char* path, int att_type_override, int D, int dtype, zrnn_model** out);
 int zrnn_model_get_config(zrnn_model* m, zrnn_model_config* cfg);
+/* Host-only pieces of the same loader (no device is touched).  zrnn_model_file_header reads line 1 of a model.nn
+ * (header[9], zero-filled beyond the *n_header_ints integers the file carries; src/add_model_info.h:7-9) and counts
+ * the vocabulary lines.  zrnn_model_file_read parses the first n_matrices matrices (rows[i] x cols[i], in file
+ * order) into the caller's column-major host buffers: read_matrix_GPU without the upload
+ * (src/Eigen_Util.h:83-112). */
+int zrnn_model_file_header(const char* path, int* header, int* n_header_ints, int* n_source_words,
+                           int* n_target_words);
+int zrnn_model_file_read(const char* path, int n_matrices, const int* rows, const int* cols, float* const* h_out);
 
 /* neuralMT_model::getError / get_perplexity (src/model.hpp:1463-1802, 2281-2355) for one minibatch.
  * Host buffers: src_ids [S_max*B] reversed + left-padded with -1 (NULL for a language model),

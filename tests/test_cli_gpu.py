@@ -1,0 +1,90 @@
+"""Front end on a device: text in, the reference's output files out, checked against the CPU oracle run on the
+integer files prepared by the plain-Python restatement of the reference's data preparation."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import textprep
+from zoph_rnn_b200 import synth
+from tests.helpers import make_text_fixture, run_cli
+
+pytestmark = pytest.mark.gpu
+
+
+def records(text):
+    lines = text.split("\n")[:-1]
+    return [[[int(x) for x in l.split()] for l in lines[i:i + 4]] for i in range(0, len(lines), 4)]
+
+
+def oracle_unit_sums(om, recs, minibatch, lm):
+    """Sum of ln p per minibatch of the integer file, one forward pass per minibatch as the reference does."""
+    sums = []
+    for u in range(0, len(recs), minibatch):
+        grp = recs[u:u + minibatch]
+        tin = np.array([r[2] for r in grp], dtype=np.int32).T
+        tout = np.array([r[3] for r in grp], dtype=np.int32).T
+        src = None if lm else np.array([r[0] for r in grp], dtype=np.int32).T
+        sums.append(float(om.score_batch(src, np.ascontiguousarray(tin), np.ascontiguousarray(tout)).sum()))
+    return sums
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f32-simt"])
+@pytest.mark.parametrize("att", [1, 0])
+def test_force_decode_seq2seq(tmp_path, oracle, att, dtype):
+    cfg = synth.make_cfg(2, 128, 300, 400, attention=att, feed_input=att, D=4)
+    model, sp, tp, w = make_text_fixture(str(tmp_path), cfg, 61, seed=12, max_len=17)
+    rc, out = run_cli(["-f", sp, tp, model, "scores.txt", "-L", "18", "--attention-width", "4", "--dtype", dtype,
+                       "--device-batch", "16", "--logfile", "log.txt"], tmp_path)
+    assert rc == 0, out
+    recs = records(textprep.integerize_nonlm(model, sp, tp, 18, 1))
+    want = oracle_unit_sums(oracle.OracleModel(cfg, w), recs, 1, False)
+    got = [float(x) for x in open(os.path.join(str(tmp_path), "scores.txt")).read().split()]
+    assert len(got) == len(want) and len(got) > 20
+    np.testing.assert_allclose(got, want, rtol=2e-5)  # 6 printed digits on top of the 1e-5 path tolerance
+    words = sum(sum(1 for x in r[2] if x != -1) for r in recs)
+    assert f"Total target words: {words}" in out
+    ppl = float(out.split("Perplexity dev set: ")[1].split()[0])
+    np.testing.assert_allclose(ppl, np.exp(-sum(want) / words), rtol=2e-5)
+    assert "Perplexity dev set" in open(os.path.join(str(tmp_path), "log.txt")).read()
+    assert not [d for d in os.listdir(str(tmp_path)) if d.startswith("zoph_tmp_")]  # tmp directory removed
+
+
+@pytest.mark.parametrize("minibatch", [1, 4])
+def test_force_decode_sequence(tmp_path, oracle, minibatch):
+    cfg = synth.make_cfg(2, 128, 0, 400, lm=True)
+    model, _, tp, w = make_text_fixture(str(tmp_path), cfg, 50, seed=13, max_len=17)
+    rc, out = run_cli(["-s", "-f", tp, model, "scores.txt", "-L", "16", "-m", minibatch], tmp_path)
+    assert rc == 0, out
+    recs = records(textprep.integerize_lm(model, tp, 16, minibatch))
+    want = oracle_unit_sums(oracle.OracleModel(cfg, w), recs, minibatch, True)
+    got = [float(x) for x in open(os.path.join(str(tmp_path), "scores.txt")).read().split()]
+    assert len(got) == len(want)
+    np.testing.assert_allclose(got, want, rtol=2e-5)
+
+
+@pytest.mark.parametrize("print_score", [0, 1])
+def test_decode(tmp_path, oracle, print_score):
+    cfg = synth.make_cfg(2, 64, 200, 300, attention=1, feed_input=1, D=3)
+    model, sp, _, w = make_text_fixture(str(tmp_path), cfg, 24, seed=14, max_len=12, scale=0.25)
+    rc, out = run_cli(["-k", "2", model, "kbest.txt", "--decode-main-data-files", sp, "-b", "6", "-L", "40",
+                       "--attention-width", "3", "--dec-ratio", "0.5", "2.0", "-p", "0.1", "--print-score", print_score,
+                       "--device-batch", "7"], tmp_path)
+    assert rc == 0, out
+    _, sents = textprep.integerize_kbest(model, sp, 40)
+    ids, ln, sc = oracle.OracleModel(cfg, w).beam_decode([np.array(s, dtype=np.int32) for s in sents], beam=6, k_best=2,
+                                                         min_ratio=0.5, max_ratio=2.0, penalty=0.1, longest_sent=40)
+    hyps = [[(list(ids[s, h, :ln[s, h]]), float(sc[s, h])) for h in range(2) if ln[s, h] > 0] for s in range(len(sents))]
+    got = open(os.path.join(str(tmp_path), "kbest.txt")).read()
+    if not print_score:
+        assert got == textprep.unint(model, textprep.format_kbest_ints(hyps, False))
+    else:
+        want = textprep.unint(model, textprep.format_kbest_ints(hyps, True)).split("\n")
+        lines = got.split("\n")
+        assert len(lines) == len(want)
+        for g, x in zip(lines, want):
+            if x.startswith("-Score: "):
+                np.testing.assert_allclose(float(g[8:]), float(x[8:]), rtol=1e-4, atol=1e-4)
+            else:
+                assert g == x
+    assert got.count("<START>") >= len(sents) and got.count("<EOF>") >= len(sents)

@@ -35,6 +35,8 @@ SIGNATURES = {
     "zrnn_last_error": (ctypes.c_char_p, []),
     "zrnn_version": (ctypes.c_int, []),
     "zrnn_built_for_sm": (ctypes.c_int, []),
+    "zrnn_device_count": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "zrnn_set_device": (ctypes.c_int, [ctypes.c_int]),
     "zrnn_launch_count": (ctypes.c_longlong, []),
     "zrnn_reset_launch_count": (None, []),
     "zrnn_kernel_timing": (ctypes.c_int, [ctypes.c_int]),
@@ -80,6 +82,10 @@ SIGNATURES = {
     "zrnn_model_finalize": (ctypes.c_int, [c_void_p]),
     "zrnn_model_load_file": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                             ctypes.POINTER(c_void_p)]),
+    "zrnn_model_file_header": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                              ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
+    "zrnn_model_file_read": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                            ctypes.POINTER(ctypes.c_int), ctypes.POINTER(c_void_p)]),
     "zrnn_model_get_config": (ctypes.c_int, [c_void_p, ctypes.POINTER(ModelConfig)]),
     "zrnn_score_batch": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p, ctypes.c_int,
                                         ctypes.c_int, c_void_p, ctypes.POINTER(ctypes.c_double)]),

@@ -325,6 +325,27 @@ class neuralMT_model:
             pass
 
 
+def read_model_file_header(path):
+    """(header ints [9], how many the file carried, source vocabulary lines, target vocabulary lines) of a
+    model.nn, parsed on the host (src/add_model_info.h:7-9)."""
+    hdr = (ctypes.c_int * 9)()
+    n, ns, nt = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    check(lib().zrnn_model_file_header(str(path).encode(), hdr, ctypes.byref(n), ctypes.byref(ns), ctypes.byref(nt)))
+    return list(hdr), n.value, ns.value, nt.value
+
+
+def read_model_file(path, shapes):
+    """Parses the first len(shapes) matrices ((rows, cols) in file order) of a model.nn on the host and returns
+    them as flat column-major float32 arrays: read_matrix_GPU without the upload (src/Eigen_Util.h:83-112)."""
+    n = len(shapes)
+    rows = (ctypes.c_int * n)(*[int(r) for r, _ in shapes])
+    cols = (ctypes.c_int * n)(*[int(c) for _, c in shapes])
+    outs = [np.empty(int(r) * int(c), dtype=np.float32) for r, c in shapes]
+    ptrs = (ctypes.c_void_p * n)(*[o.ctypes.data for o in outs])
+    check(lib().zrnn_model_file_read(str(path).encode(), n, rows, cols, ptrs))
+    return outs
+
+
 def launch_count():
     return lib().zrnn_launch_count()
 

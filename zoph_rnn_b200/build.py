@@ -6,6 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libzrnn.so")
+CLI = os.path.join(HERE, "bin", "zoph_rnn")
 SOURCES = ["kernels.cu", "tc_gemm.cu", "zrnn_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr"]
@@ -19,9 +20,21 @@ def _newest_source():
     return t
 
 
+def build_cli(force=False):
+    """Compile the command-line front end (host C++ only) against libzrnn.so; returns the binary's path."""
+    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(_newest_source(), os.path.getmtime(LIB)):
+        return CLI
+    os.makedirs(os.path.dirname(CLI), exist_ok=True)
+    cxx = os.environ.get("CXX", "g++")
+    subprocess.check_call([cxx, "-O2", "-std=c++17", "-Wall", "-pthread", os.path.join(CSRC, "cli_main.cpp"), "-o", CLI,
+                           "-L" + HERE, "-lzrnn", "-Wl,-rpath,$ORIGIN/.."])
+    return CLI
+
+
 def build(force=False, verbose=False):
-    """Compile every .cu under csrc/ into libzrnn.so; returns the library path."""
+    """Compile every .cu under csrc/ into libzrnn.so and the front end binary; returns the library path."""
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _newest_source():
+        build_cli()
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objs = []
@@ -31,6 +44,7 @@ def build(force=False, verbose=False):
         subprocess.check_call(cmd)
         objs.append(obj)
     subprocess.check_call([nvcc, "-shared", "-o", LIB] + objs + ["-lcudart"])
+    build_cli(force=True)
     return LIB
 
 

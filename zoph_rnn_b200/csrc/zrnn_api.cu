@@ -629,6 +629,16 @@ const char* zrnn_status_string(int s) {
 const char* zrnn_last_error(void) { return g_err.c_str(); }
 int zrnn_version(void) { return 100; }
 int zrnn_built_for_sm(void) { return 100; }
+int zrnn_device_count(int* n) {
+  ZR_CHECK(n, "device_count: null argument");
+  *n = 0;
+  ZR_CUDA(cudaGetDeviceCount(n));
+  return ZRNN_OK;
+}
+int zrnn_set_device(int device) {
+  ZR_CUDA(cudaSetDevice(device));
+  return ZRNN_OK;
+}
 long long zrnn_launch_count(void) { return zrnn::launch_count_value(); }
 void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
 
@@ -1130,19 +1140,45 @@ int zrnn_model_load_file(const char* path, int att_type_override, int D, int dty
   c.dtype = dtype;
   zrnn_model* m = nullptr;
   ZR_TRY(zrnn_model_create(&c, &m));
-  std::vector<float> buf;
   for (size_t i = 0; i < m->slots.size(); ++i) {
-    buf.resize((size_t)m->slots[i].rows * m->slots[i].cols);
-    if (!rd.read_matrix(m->slots[i].rows, m->slots[i].cols, buf.data(), &err)) {
+    m->staged[i].resize((size_t)m->slots[i].rows * m->slots[i].cols);
+    if (!rd.read_matrix(m->slots[i].rows, m->slots[i].cols, m->staged[i].data(), &err)) {
       const std::string nm = m->slots[i].name;
       delete m;
       return fail(ZRNN_E_IO, "load_file: " + nm + ": " + err);
     }
-    zrnn_model_set_tensor(m, (int)i, buf.data());
   }
   const int st = zrnn_model_finalize(m);
   if (st != ZRNN_OK) { delete m; return st; }
   *out = m;
+  return ZRNN_OK;
+}
+
+int zrnn_model_file_header(const char* path, int* header, int* n_header_ints, int* n_source_words,
+                           int* n_target_words) {
+  ZR_CHECK(path && header, "model_file_header: null argument");
+  zrnn::ModelFileReader rd;
+  zrnn::ModelFileHeader h;
+  std::string err;
+  if (!rd.open(path, &h, &err)) return fail(ZRNN_E_IO, "model_file_header: " + err);
+  const int v[9] = {h.num_layers, h.H, h.V_tgt, h.V_src, h.attention, h.feed_input, h.multi_source, h.combine, h.char_cnn};
+  for (int i = 0; i < 9; ++i) header[i] = v[i];
+  if (n_header_ints) *n_header_ints = h.n_header_ints;
+  if (n_source_words) *n_source_words = (int)rd.source_vocab().size();
+  if (n_target_words) *n_target_words = (int)rd.target_vocab().size();
+  return ZRNN_OK;
+}
+int zrnn_model_file_read(const char* path, int n_matrices, const int* rows, const int* cols, float* const* h_out) {
+  ZR_CHECK(path && rows && cols && h_out && n_matrices >= 0, "model_file_read: bad arguments");
+  zrnn::ModelFileReader rd;
+  zrnn::ModelFileHeader h;
+  std::string err;
+  if (!rd.open(path, &h, &err)) return fail(ZRNN_E_IO, "model_file_read: " + err);
+  for (int i = 0; i < n_matrices; ++i) {
+    ZR_CHECK(rows[i] > 0 && cols[i] > 0 && h_out[i], "model_file_read: bad matrix shape or buffer");
+    if (!rd.read_matrix(rows[i], cols[i], h_out[i], &err))
+      return fail(ZRNN_E_IO, "model_file_read: matrix " + std::to_string(i) + ": " + err);
+  }
   return ZRNN_OK;
 }
 
