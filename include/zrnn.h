@@ -136,6 +136,11 @@ int zrnn_att_set_source(zrnn_attention* att, const float* d_hs, int S_max, int B
  * (2D+1) x B weights stored [j*B+b]; global S_max x B stored [s*B+b] in source-position order. */
 int zrnn_att_forward(zrnn_attention* att, const float* d_h_t, const int* d_mask01, int B, float* d_htild_out,
                      float* d_align_out, void* stream);
+/* The same step with the viterbi alignment of every column: get_viterbi_alignment_kernel
+ * (src/custom_kernels.h:1621-1635, called from src/attention_node.hpp:225-234 when UNK replacement is on).
+ * d_viterbi_out[b] = source position (un-reversed sentence) of the largest weight, -1 for a masked column. */
+int zrnn_att_forward_viterbi(zrnn_attention* att, const float* d_h_t, const int* d_mask01, int B, float* d_htild_out,
+                             int* d_viterbi_out, void* stream);
 int zrnn_att_destroy(zrnn_attention* att);
 
 /* ------------------------------------------------------------------------------------------
@@ -254,6 +259,19 @@ int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len
 int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src_ids_padded, const int* h_src_len, int S_max,
                                   int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
                                   int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score, void* stream);
+/* The same two calls with viterbi-alignment tracking for UNK replacement (BZ_CUDA::unk_replacement,
+ * src/attention_node.hpp:225-234; src/decoder.h:1266-1267, 1281-1282, 683-684): out_align has the shape of out_ids
+ * and holds, for every position of every hypothesis, the source position (in the un-reversed sentence) that had the
+ * largest attention weight at the step that produced the word; -20 at position 0, -1 without attention and under
+ * the padding.  The reference writes align[j+1] for every hypothesis position j that holds <UNK> (id 2) to the
+ * --UNK-decode file (src/decoder.h:1452-1459). */
+int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam,
+                                 int k_best, float min_ratio, float max_ratio, float penalty, int longest_sent,
+                                 int* out_ids, int* out_len, float* out_score, int* out_align);
+int zrnn_beam_decode_batch_align_device(zrnn_model* m, const int* d_src_ids_padded, const int* h_src_len, int S_max,
+                                        int n_sent, int beam, int k_best, float min_ratio, float max_ratio,
+                                        float penalty, int longest_sent, int* d_out_ids, int* d_out_len,
+                                        float* d_out_score, int* d_out_align, void* stream);
 int zrnn_model_destroy(zrnn_model* m);
 
 #ifdef __cplusplus

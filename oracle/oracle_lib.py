@@ -45,6 +45,10 @@ def lib():
         L.orc_beam_decode.argtypes = [ctypes.c_void_p, c_int_p, c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                       ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int,
                                       c_int_p, c_int_p, c_float_p]
+        L.orc_beam_decode_align.argtypes = L.orc_beam_decode.argtypes + [c_int_p]
+        L.orc_attention_viterbi.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                            ctypes.POINTER(c_float_p), c_float_p, c_int_p, c_float_p, ctypes.c_int,
+                                            c_int_p, c_int_p, c_float_p, c_int_p]
         L.orc_gather.argtypes = [c_float_p, ctypes.c_int, c_int_p, ctypes.c_int, c_float_p]
         L.orc_lstm_cell.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_float_p), c_float_p, c_float_p,
                                     c_float_p, c_float_p, c_int_p, c_float_p, c_float_p]
@@ -126,8 +130,10 @@ class OracleModel:
                               out.ctypes.data_as(c_double_p), _fp(top))
         return (out, top) if want_top else out
 
-    def beam_decode(self, sources, beam, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100):
-        """sources: list of reversed id lists. Returns (ids [n,k,Lmax], len [n,k], score [n,k])."""
+    def beam_decode(self, sources, beam, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100,
+                    want_align=False):
+        """sources: list of reversed id lists. Returns (ids [n,k,Lmax], len [n,k], score [n,k]) and, with want_align,
+        the viterbi alignment stored with every hypothesis position [n,k,Lmax]."""
         n = len(sources)
         flat = _i32(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]))
         lens = _i32([len(s) for s in sources])
@@ -135,9 +141,10 @@ class OracleModel:
         ids = np.zeros((n, k_best, Lmax), dtype=np.int32)
         ln = np.zeros((n, k_best), dtype=np.int32)
         sc = np.zeros((n, k_best), dtype=np.float32)
-        lib().orc_beam_decode(self._h, _ip(flat), _ip(lens), n, beam, k_best, min_ratio, max_ratio, penalty,
-                              longest_sent, Lmax, _ip(ids), _ip(ln), _fp(sc))
-        return ids, ln, sc
+        al = np.zeros((n, k_best, Lmax), dtype=np.int32) if want_align else None
+        lib().orc_beam_decode_align(self._h, _ip(flat), _ip(lens), n, beam, k_best, min_ratio, max_ratio, penalty,
+                                    longest_sent, Lmax, _ip(ids), _ip(ln), _fp(sc), _ip(al))
+        return (ids, ln, sc, al) if want_align else (ids, ln, sc)
 
 
 def gather(W, H, ids):
@@ -172,6 +179,19 @@ def attention(att_type, H, B, D, w6, h_t, mask, hs_all, S_max, lens, offs):
     lib().orc_attention(att_type, H, B, D, arr, _fp(h_t), _ip(mask), _fp(hs_all), S_max, _ip(lens), _ip(offs),
                         _fp(out), _fp(al), _ip(idx) if att_type == 1 else None)
     return out, al, idx
+
+
+def attention_viterbi(att_type, H, B, D, w6, h_t, mask, hs_all, S_max, lens, offs):
+    """The attention step's viterbi alignment per column (get_viterbi_alignment_kernel)."""
+    keep = [_f32(a).reshape(-1) for a in w6]
+    arr = (c_float_p * 6)(*[_fp(a) for a in keep])
+    h_t, hs_all = _f32(h_t).reshape(-1), _f32(hs_all).reshape(-1)
+    mask, lens, offs = _i32(mask), _i32(lens), _i32(offs)
+    out = np.zeros(H * B, dtype=np.float32)
+    vit = np.zeros(B, dtype=np.int32)
+    lib().orc_attention_viterbi(att_type, H, B, D, arr, _fp(h_t), _ip(mask), _fp(hs_all), S_max, _ip(lens), _ip(offs),
+                                _fp(out), _ip(vit))
+    return out, vit
 
 
 def softmax_logp(V, H, N, Dm, b_d, h, target, want_all=False):

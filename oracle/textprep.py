@@ -148,6 +148,16 @@ def format_kbest_ints(hyps, print_score):
     return "".join(out)
 
 
+def format_unk_file(hyps):
+    """The --UNK-decode file (src/decoder.h:1452-1459): one line per printed hypothesis; for every position j that
+    holds <UNK> (id 2) the alignment stored at j + 1.  hyps = per sentence a list of (ids, alignments)."""
+    out = []
+    for sent in hyps:
+        for ids, align in sent:
+            out.append("".join(f"{align[j + 1]} " for j in range(len(ids)) if ids[j] == 2) + "\n")
+    return "".join(out)
+
+
 def unint(model_path, text, decoder=True):
     """unint_file (src/input_file_prep.h:3137-3205)."""
     _, _, tgt = read_vocab(model_path)

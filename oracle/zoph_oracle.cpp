@@ -223,7 +223,7 @@ void lstm_cell(int H, int B, const LstmW& w, const float* x, const float* h_prev
 // index table idx_out[j*B+b]; for global S_max x B stored [s*B+b] (position order).
 void attention(int type, int H, int B, int D, const AttW& w, const float* h_t, const int* mask,
                const float* hs_all, int S_max, const int* len, const int* offset, float* htild_out,
-               float* align_out, int* idx_out) {
+               float* align_out, int* idx_out, int* viterbi_out = nullptr, float viterbi_init = -1.f) {
   const size_t HB = (size_t)H * B;
   std::vector<float> c_t(HB, 0.f), tmp1(HB), tmp2(HB);
   if (type == ATT_LOCAL_P) {
@@ -288,6 +288,18 @@ void attention(int type, int H, int B, int D, const AttW& w, const float* h_t, c
         } else a = 0;
       }
     }
+    // get_viterbi_alignment_kernel ck:1621-1635 (attention_node.hpp:225-234): the window index of the largest
+    // weight; the running maximum starts at -1 and only a strictly larger weight replaces it.  The decoder then
+    // re-derives the index from the weights per source position with a maximum that starts at 0
+    // (ensembles_models, ensemble_factory.hpp:812-834): viterbi_init = 0 gives that result.
+    if (viterbi_out)
+      for (int b = 0; b < B; ++b) {
+        float max_val = viterbi_init;
+        int max_index = -1;
+        for (int j = 0; j < Wn; ++j)
+          if (max_val < align[(size_t)j * B + b]) { max_val = align[(size_t)j * B + b]; max_index = ind[(size_t)j * B + b]; }
+        viterbi_out[b] = max_index;
+      }
     // create_c_t_kernel ck:1802-1813
     for (int b = 0; b < B; ++b)
       for (int i = 0; i < H; ++i) {
@@ -300,6 +312,7 @@ void attention(int type, int H, int B, int D, const AttW& w, const float* h_t, c
   } else {
     for (int b = 0; b < B; ++b) {
       if (align_out) for (int s = 0; s < S_max; ++s) align_out[(size_t)s * B + b] = 0;
+      if (viterbi_out) viterbi_out[b] = -1;
       if (mask[b] != 1) continue;
       const int L = len[b];
       std::vector<double> e(L);
@@ -314,8 +327,10 @@ void attention(int type, int H, int B, int D, const AttW& w, const float* h_t, c
       double sum = 0;
       for (int s = 0; s < L; ++s) { e[s] = std::exp(e[s] - mx); sum += e[s]; }
       std::vector<double> ctx(H, 0.0);
+      float best = viterbi_init;
       for (int s = 0; s < L; ++s) {
         const float a = (float)(e[s] / sum);
+        if (viterbi_out && best < a) { best = a; viterbi_out[b] = s; }  // same rule over every source position
         if (align_out) align_out[(size_t)s * B + b] = a;
         const float* hsv = hs_all + (size_t)(L - 1 - s + offset[b]) * HB + (size_t)b * H;
         for (int i = 0; i < H; ++i) ctx[i] += (double)a * (double)hsv[i];
@@ -453,7 +468,7 @@ double score_batch(const Model& m, const int* src_ids, int S_max, const int* tgt
 // forward_prop_source / forward_prop_target / swap_decoding_states src/model.hpp:2367-2452,
 // 2573-2726, decoder::expand_hypothesis_without_fsa src/decoder.h:1157-1315,
 // finish_current_hypotheses :672-688, output_k_best_hypotheses :1386-1463.
-struct Hyp { std::vector<int> ids; float score; };
+struct Hyp { std::vector<int> ids; std::vector<int> align; float score; };
 
 void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best, float min_ratio, float max_ratio,
                      float penalty, int longest_sent_internal, std::vector<Hyp>& out) {
@@ -489,6 +504,9 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
   std::vector<std::vector<float>> hp(L, std::vector<float>(HB)), cp(L, std::vector<float>(HB));
   std::vector<float> x(HB), htild(HB, 0.f), htild_feed(HB, 0.f), P((size_t)V * beam), tmp(HB);
   std::vector<int> ones(beam, 1), ids(beam), lenv(beam, S), offv(beam, 0);
+  // viterbi alignment per beam column of the last forward step (BZ_CUDA::viterbi_alignments; -1 without attention,
+  // decoder.h:1174-1178) and per position of every beam entry (top_sentences_viterbi, initialised to -20, :1335)
+  std::vector<int> vit(beam, -1), top_vit((size_t)beam * Lmax, -20), top_vit_tmp((size_t)beam * Lmax, -20);
 
   auto forward_target = [&](int idx) {
     if (idx == 0)  // transfer_decoding_states_GPU: replicate the source's last (h,c) over the beam
@@ -507,7 +525,7 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
     const float* top = h[L - 1].data();
     if (c.attention) {
       attention(c.attention, H, beam, c.D, m.att, h[L - 1].data(), ones.data(), hs_all.data(), S, lenv.data(),
-                offv.data(), htild.data(), nullptr, nullptr);
+                offv.data(), htild.data(), nullptr, nullptr, vit.data(), 0.f);
       top = htild.data();
     }
     softmax_dist(V, H, beam, m.D, m.b_d, top, P.data());
@@ -542,6 +560,7 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
     while (i < beam) {
       if (global.empty()) {
         std::memcpy(&top_tmp[(size_t)i * Lmax], &top_sent[0], sizeof(int) * Lmax);
+        std::memcpy(&top_vit_tmp[(size_t)i * Lmax], &top_vit[0], sizeof(int) * Lmax);  // decoder.h:1237
         top_tmp[(size_t)i * Lmax + current_index + 1] = START;
         cur[i] = INVALID; changes[i] = 0; scores_tmp[i] = 0;
         ++i;
@@ -554,16 +573,20 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
         Hyp hy;
         hy.ids.assign(&top_sent[(size_t)t.beam_idx * Lmax], &top_sent[(size_t)t.beam_idx * Lmax] + current_index + 2);
         hy.ids[current_index + 1] = END;
+        hy.align.assign(&top_vit[(size_t)t.beam_idx * Lmax], &top_vit[(size_t)t.beam_idx * Lmax] + current_index + 2);
+        hy.align[current_index + 1] = vit[t.beam_idx];  // decoder.h:1266-1267
         hy.score = t.val + penalty;
         hyps.push_back(hy);
       } else {
         std::memcpy(&top_tmp[(size_t)i * Lmax], &top_sent[(size_t)t.beam_idx * Lmax], sizeof(int) * Lmax);
         top_tmp[(size_t)i * Lmax + current_index + 1] = t.vocab;
+        std::memcpy(&top_vit_tmp[(size_t)i * Lmax], &top_vit[(size_t)t.beam_idx * Lmax], sizeof(int) * Lmax);
+        top_vit_tmp[(size_t)i * Lmax + current_index + 1] = vit[t.beam_idx];  // decoder.h:1281-1282
         cur[i] = t.vocab; changes[i] = t.beam_idx; scores_tmp[i] = t.val + penalty;
         ++i;
       }
     }
-    top_sent = top_tmp; scores = scores_tmp; current_index += 1;
+    top_sent = top_tmp; top_vit = top_vit_tmp; scores = scores_tmp; current_index += 1;
     // ---- swap_decoding_states + target_copy_prev_states (model.hpp:2691-2726)
     for (int l = 0; l < L; ++l)
       for (int j = 0; j < beam; ++j) {
@@ -583,6 +606,8 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
     scores[i] += std::log(P[(size_t)i * V + 1]) + penalty;
     Hyp hy;
     hy.ids.assign(&top_sent[(size_t)i * Lmax], &top_sent[(size_t)i * Lmax] + current_index + 2);
+    hy.align.assign(&top_vit[(size_t)i * Lmax], &top_vit[(size_t)i * Lmax] + current_index + 2);
+    hy.align[current_index + 1] = vit[i];  // decoder.h:683-684
     hy.score = scores[i];
     hyps.push_back(hy);
   }
@@ -648,9 +673,10 @@ double orc_score_batch(void* p, const int* src_ids, int S_max, const int* tgt_in
 // src_ids: concatenated reversed source ids; src_len[n_sent]; longest_sent is the user-level
 // -L value (the reference adds 4 internally, src/main.cu:408).
 // out_ids[n_sent*k_best*Lmax] (-1 padded), out_len[n_sent*k_best] (0 = no hypothesis), out_score.
-void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best, float min_ratio,
-                     float max_ratio, float penalty, int longest_sent, int Lmax_out, int* out_ids, int* out_len,
-                     float* out_score) {
+// out_align (optional, same shape as out_ids): the viterbi alignment stored with every position of the hypothesis.
+void orc_beam_decode_align(void* p, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best,
+                           float min_ratio, float max_ratio, float penalty, int longest_sent, int Lmax_out, int* out_ids,
+                           int* out_len, float* out_score, int* out_align) {
   const Model& m = *(Model*)p;
   size_t pos = 0;
   for (int s = 0; s < n_sent; ++s) {
@@ -659,10 +685,13 @@ void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent
     pos += src_len[s];
     for (int k = 0; k < k_best; ++k) {
       int* dst = out_ids + ((size_t)s * k_best + k) * Lmax_out;
+      int* adst = out_align ? out_align + ((size_t)s * k_best + k) * Lmax_out : nullptr;
       for (int i = 0; i < Lmax_out; ++i) dst[i] = -1;
+      if (adst) for (int i = 0; i < Lmax_out; ++i) adst[i] = -1;
       if (k < (int)res.size()) {
         const int n = std::min((int)res[k].ids.size(), Lmax_out);
         for (int i = 0; i < n; ++i) dst[i] = res[k].ids[i];
+        if (adst) for (int i = 0; i < n; ++i) adst[i] = res[k].align[i];
         out_len[(size_t)s * k_best + k] = (int)res[k].ids.size();
         out_score[(size_t)s * k_best + k] = res[k].score;
       } else {
@@ -671,6 +700,13 @@ void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent
       }
     }
   }
+}
+
+void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best, float min_ratio,
+                     float max_ratio, float penalty, int longest_sent, int Lmax_out, int* out_ids, int* out_len,
+                     float* out_score) {
+  orc_beam_decode_align(p, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio, penalty, longest_sent, Lmax_out,
+                        out_ids, out_len, out_score, nullptr);
 }
 
 // ---- layer-level entry points for per-kernel parity tests
@@ -698,6 +734,14 @@ void orc_attention(int type, int H, int B, int D, const float* const* w, const f
   AttW aw;
   aw.W_a = w[0]; aw.W_p = w[1]; aw.v_p = w[2]; aw.output_bias = w[3]; aw.W_c_p1 = w[4]; aw.W_c_p2 = w[5];
   attention(type, H, B, D, aw, h_t, mask, hs_all, S_max, len, offset, htild_out, align_out, idx_out);
+}
+// the same step, also returning the viterbi alignment per column
+void orc_attention_viterbi(int type, int H, int B, int D, const float* const* w, const float* h_t, const int* mask,
+                           const float* hs_all, int S_max, const int* len, const int* offset, float* htild_out,
+                           int* viterbi_out) {
+  AttW aw;
+  aw.W_a = w[0]; aw.W_p = w[1]; aw.v_p = w[2]; aw.output_bias = w[3]; aw.W_c_p1 = w[4]; aw.W_c_p2 = w[5];
+  attention(type, H, B, D, aw, h_t, mask, hs_all, S_max, len, offset, htild_out, nullptr, nullptr, viterbi_out);
 }
 
 void orc_softmax_logp(int V, int H, int N, const float* D, const float* b_d, const float* h, const int* target,

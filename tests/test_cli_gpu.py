@@ -88,3 +88,32 @@ def test_decode(tmp_path, oracle, print_score):
             else:
                 assert g == x
     assert got.count("<START>") >= len(sents) and got.count("<EOF>") >= len(sents)
+
+
+def test_decode_unk_replacement_file(tmp_path, oracle):
+    """--UNK-decode: the alignment file lists, per hypothesis, the source position aligned to every <UNK>."""
+    cfg = synth.make_cfg(2, 64, 200, 30, attention=1, feed_input=1, D=3)  # small target vocabulary: many <UNK>
+    model, sp, _, w = make_text_fixture(str(tmp_path), cfg, 20, seed=15, max_len=12, scale=0.25)
+    # make <UNK> (id 2) likely: raise its softmax bias
+    from zoph_rnn_b200.model_file import write_model_nn
+    w[-1] = np.array(w[-1], dtype=np.float32)
+    w[-1][2] += 1.5
+    write_model_nn(model, cfg, w)
+    rc, out = run_cli(["-k", "2", model, "kbest.txt", "--decode-main-data-files", sp, "-b", "5", "-L", "40",
+                       "--attention-width", "3", "--UNK-decode", "unk.txt"], tmp_path)
+    assert rc == 0, out
+    _, sents = textprep.integerize_kbest(model, sp, 40)
+    ids, ln, sc, al = oracle.OracleModel(cfg, w).beam_decode([np.array(s, dtype=np.int32) for s in sents], beam=5,
+                                                             k_best=2, longest_sent=40, want_align=True)
+    hyps = [[(list(ids[s, h, :ln[s, h]]), list(al[s, h, :ln[s, h] + 1])) for h in range(2) if ln[s, h] > 0]
+            for s in range(len(sents))]
+    want_text = textprep.unint(model, textprep.format_kbest_ints([[(i, 0.0) for i, _ in sent] for sent in hyps], False))
+    got_text = open(os.path.join(str(tmp_path), "kbest.txt")).read()
+    got_unk = open(os.path.join(str(tmp_path), "unk.txt")).read()
+    want_unk = textprep.format_unk_file(hyps)
+    assert got_unk.count("\n") == want_unk.count("\n") == sum(len(s) for s in hyps)
+    assert sum(len(l.split()) for l in want_unk.split("\n")) > 10  # the fixture does produce <UNK>s
+    if got_text == want_text:  # same hypotheses: the alignments must match line by line (near-ties aside)
+        g, x = got_unk.split("\n"), want_unk.split("\n")
+        same = sum(a == b for a, b in zip(g, x))
+        assert same >= 0.95 * len(x), (same, len(x))

@@ -154,6 +154,16 @@ def test_attention_matches_oracle(api, oracle, att_type, H, B, D, S_max):
         np.testing.assert_allclose(al.cpu().numpy(), want_al, rtol=max(rtol, 3e-5), atol=atol, err_msg=f"dtype {dtype}")
         np.testing.assert_allclose(out.cpu().numpy(), want, rtol=max(rtol, 3e-5), atol=max(atol, 3e-6), err_msg=f"dtype {dtype}")
         assert np.all(out.cpu().numpy().reshape(B, H)[mask == 0] == 0.0)
+        # viterbi alignment: bit-exact wherever the two largest weights are not within rounding of each other
+        _, want_vit = oracle.attention_viterbi(att_type, H, B, max(D, 1), w6, h_t, mask, hs, S_max, lens, offs)
+        out2, vit = att.forward_prop_viterbi(dev(h_t), dev(mask))
+        torch.cuda.synchronize()
+        assert np.array_equal(out2.cpu().numpy(), out.cpu().numpy())
+        wal = want_al.reshape(-1, B)
+        top2 = np.sort(wal, axis=0)[-2:]
+        clear = (top2[1] - top2[0] > 1e-4 * np.abs(top2[1])) | (mask == 0)
+        assert np.array_equal(vit.cpu().numpy()[clear], want_vit[clear]), f"dtype {dtype}"
+        assert np.all(want_vit[mask == 0] == -1) and clear.mean() > 0.7
 
 
 def test_attention_shared_source_columns(api, oracle):

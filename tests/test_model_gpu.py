@@ -117,6 +117,17 @@ def test_decoding_matches_oracle(api, oracle, att, feed, dtype):
     # batched decoding equals one-sentence-at-a-time decoding
     one_i, one_l, one_s = m.decode(srcs[3:4], **kw)
     assert np.array_equal(one_i[0], gi[3]) and np.array_equal(one_l[0], gl[3])
+    # viterbi alignments carried with every hypothesis (UNK replacement): same hypotheses, and the same alignments
+    # wherever the hypotheses agree (an alignment can only differ at a near-tie of two attention weights)
+    _, _, _, wal = om.beam_decode(srcs, want_align=True, **kw)
+    ai, al_len, _, gal = m.decode(srcs, want_align=True, **kw)
+    assert np.array_equal(ai, gi) and np.array_equal(al_len, gl)
+    same = (gal == wal)[agree]
+    assert same.mean() >= 0.995, f"alignment agreement {same.mean():.4f}"
+    assert np.all(gal[:, :, 0][gl > 0] == -20)
+    if att == 0:
+        pos = np.arange(gal.shape[2])[None, None, :]
+        assert np.all(gal[(pos >= 1) & (pos < gl[:, :, None])] == -1)
 
 
 @pytest.mark.parametrize("dtype,name", [(1, "bf16"), (2, "tf32")])

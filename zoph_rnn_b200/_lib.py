@@ -60,6 +60,8 @@ SIGNATURES = {
     "zrnn_att_set_source": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, c_void_p, c_void_p,
                                            ctypes.c_int]),
     "zrnn_att_forward": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p, c_void_p]),
+    "zrnn_att_forward_viterbi": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p,
+                                                c_void_p]),
     "zrnn_att_destroy": (ctypes.c_int, [c_void_p]),
     "zrnn_softmax_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                            ctypes.POINTER(c_void_p)]),
@@ -102,6 +104,13 @@ SIGNATURES = {
                                                      ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float,
                                                      ctypes.c_float, ctypes.c_int, c_void_p, c_void_p, c_void_p,
                                                      c_void_p]),
+    "zrnn_beam_decode_batch_align": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int,
+                                                    ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                                    ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zrnn_beam_decode_batch_align_device": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int,
+                                                           ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float,
+                                                           ctypes.c_float, ctypes.c_int, c_void_p, c_void_p, c_void_p,
+                                                           c_void_p, c_void_p]),
     "zrnn_model_destroy": (ctypes.c_int, [c_void_p]),
 }
 

@@ -141,6 +141,15 @@ class attention_layer:
         check(lib().zrnn_att_forward(self._h, _ptr(h_t), _ptr(mask01), B, _ptr(out), _ptr(al), _stream()))
         return (out, al) if want_alignments else out
 
+    def forward_prop_viterbi(self, h_t, mask01):
+        """forward_prop plus get_viterbi_alignment_kernel (src/custom_kernels.h:1621-1635): returns
+        (h_tilde, viterbi [B] int32)."""
+        B = h_t.numel() // self.H
+        out = torch.empty_like(h_t)
+        vit = torch.zeros(B, dtype=torch.int32, device="cuda")
+        check(lib().zrnn_att_forward_viterbi(self._h, _ptr(h_t), _ptr(mask01), B, _ptr(out), _ptr(vit), _stream()))
+        return out, vit
+
     def __del__(self):
         try:
             if getattr(self, "_h", None):
@@ -293,9 +302,11 @@ class neuralMT_model:
     def softmax(self):
         return softmax_layer(self.cfg["V_tgt"], self.cfg["H"], _borrowed=lib().zrnn_model_softmax(self._h))
 
-    def decode(self, sources, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100):
+    def decode(self, sources, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100,
+               want_align=False):
         """ensemble_factory::decode_file_batch (src/ensemble_factory.hpp:583-765) for a list of reversed source
-        id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k])."""
+        id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k]); with want_align also the viterbi
+        alignment stored with every hypothesis position [n,k,longest_sent+4] (src/decoder.h:1266-1267)."""
         n = len(sources)
         flat = np.ascontiguousarray(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]), dtype=np.int32)
         lens = np.ascontiguousarray([len(s) for s in sources], dtype=np.int32)
@@ -303,6 +314,14 @@ class neuralMT_model:
         ids = np.empty((n, k_best, Lmax), dtype=np.int32)
         ln = np.empty((n, k_best), dtype=np.int32)
         sc = np.empty((n, k_best), dtype=np.float32)
+        if want_align:
+            al = np.empty((n, k_best, Lmax), dtype=np.int32)
+            check(lib().zrnn_beam_decode_batch_align(self._h, ctypes.c_void_p(flat.ctypes.data),
+                                                     ctypes.c_void_p(lens.ctypes.data), n, beam, k_best, min_ratio,
+                                                     max_ratio, penalty, longest_sent, ctypes.c_void_p(ids.ctypes.data),
+                                                     ctypes.c_void_p(ln.ctypes.data), ctypes.c_void_p(sc.ctypes.data),
+                                                     ctypes.c_void_p(al.ctypes.data)))
+            return ids, ln, sc, al
         check(lib().zrnn_beam_decode_batch(self._h, ctypes.c_void_p(flat.ctypes.data), ctypes.c_void_p(lens.ctypes.data),
                                            n, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
                                            ctypes.c_void_p(ids.ctypes.data), ctypes.c_void_p(ln.ctypes.data),

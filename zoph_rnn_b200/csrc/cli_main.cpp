@@ -487,6 +487,8 @@ int run_decode(const Options& opt, Params& p) {
   std::vector<int> all_len((size_t)n * num_hypotheses, 0);
   std::vector<float> all_score((size_t)n * num_hypotheses, 0.f);
   std::vector<int> all_ids((size_t)n * num_hypotheses * Lmax, -1);
+  const bool unk = !p.unk_file.empty();  // --UNK-decode: BZ_CUDA::unk_replacement (src/main.cu:410-412)
+  std::vector<int> all_align(unk ? (size_t)n * num_hypotheses * Lmax : 0, -1);
   // decode the sentences in groups of similar length; results go back to file order
   std::vector<int> order(n);
   std::iota(order.begin(), order.end(), 0);
@@ -505,15 +507,18 @@ int run_decode(const Options& opt, Params& p) {
     }
     std::vector<int> ids((size_t)ng * num_hypotheses * Lmax), len((size_t)ng * num_hypotheses);
     std::vector<float> score((size_t)ng * num_hypotheses);
-    check_status(zrnn_beam_decode_batch(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses, (float)p.min_ratio,
-                                        (float)p.max_ratio, (float)p.penalty, p.longest_sent, ids.data(), len.data(),
-                                        score.data()), "decoding");
+    std::vector<int> align(unk ? ids.size() : 0);
+    check_status(zrnn_beam_decode_batch_align(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses,
+                                              (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
+                                              ids.data(), len.data(), score.data(), unk ? align.data() : nullptr),
+                 "decoding");
     for (int i = 0; i < ng; ++i) {
       const size_t dst = (size_t)order[g0 + i] * num_hypotheses;
       for (int h = 0; h < num_hypotheses; ++h) {
         all_len[dst + h] = len[(size_t)i * num_hypotheses + h];
         all_score[dst + h] = score[(size_t)i * num_hypotheses + h];
         std::memcpy(&all_ids[(dst + h) * Lmax], &ids[((size_t)i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
+        if (unk) std::memcpy(&all_align[(dst + h) * Lmax], &align[((size_t)i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
         out_words += all_len[dst + h];
       }
     }
@@ -523,6 +528,11 @@ int run_decode(const Options& opt, Params& p) {
   {
     std::ofstream os(int_out.c_str());
     if (!os) die("cannot write " + int_out);
+    std::ofstream unk_os;
+    if (unk) {
+      unk_os.open(p.unk_file.c_str());
+      if (!unk_os) die("cannot write " + p.unk_file);
+    }
     for (int s = 0; s < n; ++s) {
       os << "------------------------------------------------\n";
       for (int h = 0; h < num_hypotheses; ++h) {
@@ -531,6 +541,13 @@ int run_decode(const Options& opt, Params& p) {
         if (p.print_score) os << "-Score: " << all_score[at] << "\n";
         for (int j = 0; j < all_len[at]; ++j) os << all_ids[at * Lmax + j] << " ";
         os << "\n";
+        if (unk) {
+          // one line per hypothesis: for every <UNK> (id 2) at position j the alignment stored at j + 1
+          // (src/decoder.h:1452-1459)
+          for (int j = 0; j < all_len[at]; ++j)
+            if (all_ids[at * Lmax + j] == 2 && j + 1 < Lmax) unk_os << all_align[at * Lmax + j + 1] << " ";
+          unk_os << "\n";
+        }
       }
       os << "\n";
     }
@@ -615,7 +632,6 @@ int main(int argc, char** argv) {
   }
   if (p.minibatch <= 0) die("minibatch size must be positive");
   if (p.longest_sent < 4) die("longest-sent is too small");
-  if (!p.unk_file.empty()) die("--UNK-decode is not available in this program yet");
   int rc = 0;
   if (opt.has("decode")) rc = run_decode(opt, p);
   else if (opt.has("force-decode")) rc = run_force_decode(opt, p);

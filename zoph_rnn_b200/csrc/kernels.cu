@@ -668,6 +668,7 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
     for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
     if (a.align_out)
       for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
     return;
   }
   float part = 0.f;
@@ -714,6 +715,13 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
         if (sum != 0.f) s_al[j] = (s_al[j] / sum) * gs;
       }
     }
+    if (a.viterbi_out) {  // only a strictly larger weight replaces the running maximum
+      float best = a.viterbi_init;
+      int best_pos = -1;
+      for (int j = 0; j < Wn; ++j)
+        if (best < s_al[j]) { best = s_al[j]; best_pos = (s_slot[j] != -1) ? lo + j : -1; }
+      a.viterbi_out[b] = best_pos;
+    }
   }
   __syncthreads();
   if (a.align_out)
@@ -746,6 +754,7 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
     for (int s = tid; s < a.S_max; s += blockDim.x) a.align_out[(size_t)s * a.B + b] = 0.f;
   if (a.mask && a.mask[b] != 1) {
     for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
+    if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
     return;
   }
   const int len = a.len[sb], off = a.offset[sb];
@@ -777,6 +786,13 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
   const float inv = 1.0f / sum;
   if (a.align_out)
     for (int pos = tid; pos < len; pos += blockDim.x) a.align_out[(size_t)pos * a.B + b] = s_sc[pos] * inv;
+  if (a.viterbi_out && tid == 0) {
+    float best = a.viterbi_init;
+    int best_pos = -1;
+    for (int pos = 0; pos < len; ++pos)
+      if (best < s_sc[pos] * inv) { best = s_sc[pos] * inv; best_pos = pos; }
+    a.viterbi_out[b] = best_pos;
+  }
   for (int i = tid; i < H; i += blockDim.x) {
     float acc = 0.f;
     for (int pos = 0; pos < len; ++pos)
@@ -790,7 +806,8 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
 // is read once, with 16-byte loads), and carries a running (max, sum, context); the 8 partial results are merged through
 // shared memory at the end.
 __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
-  __shared__ float s_m[8], s_l[8];
+  __shared__ float s_m[8], s_l[8], s_bsc[8];
+  __shared__ int s_bpos[8];
   __shared__ float4 s_ctx[8][256];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int H = a.H, H4 = H >> 2, sb = b / a.cols_per_sent;
@@ -799,6 +816,7 @@ __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
     for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
     if (a.align_out)
       for (int s = tid; s < a.S_max; s += blockDim.x) a.align_out[(size_t)s * a.B + b] = 0.f;
+    if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
     return;
   }
   const int len = a.len[sb], off = a.offset[sb];
@@ -810,7 +828,8 @@ __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
     hv[i] = j < H4 ? h4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
     ctx[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  float m = -INFINITY, l = 0.f;
+  float m = -INFINITY, l = 0.f, bsc = -INFINITY;
+  int bpos = -1;
   for (int pos = w; pos < len; pos += 8) {
     const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)(len - 1 - pos + off) * a.B_src + sb) * H);
     float4 rv[8];
@@ -823,6 +842,7 @@ __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
     }
     sc = warp_sum(sc);
     if (a.align_out && lane == 0) a.align_out[(size_t)pos * a.B + b] = sc;  // raw score, normalised below
+    if (sc > bsc) { bsc = sc; bpos = pos; }
     const float mn = fmaxf(m, sc);
     const float scale = expf(m - mn), e = expf(sc - mn);
     l = l * scale + e;
@@ -835,10 +855,17 @@ __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
       ctx[i].w = ctx[i].w * scale + e * rv[i].w;
     }
   }
-  if (lane == 0) { s_m[w] = m; s_l[w] = l; }
+  if (lane == 0) { s_m[w] = m; s_l[w] = l; s_bsc[w] = bsc; s_bpos[w] = bpos; }
 #pragma unroll
   for (int i = 0; i < 8; ++i) s_ctx[w][lane + 32 * i] = ctx[i];
   __syncthreads();
+  if (a.viterbi_out && tid == 0) {  // largest score = largest weight; the lowest position wins a tie
+    float best = -INFINITY;
+    int best_pos = -1;
+    for (int q = 0; q < 8; ++q)
+      if (s_bpos[q] >= 0 && (s_bsc[q] > best || (s_bsc[q] == best && s_bpos[q] < best_pos))) { best = s_bsc[q]; best_pos = s_bpos[q]; }
+    a.viterbi_out[b] = best_pos;
+  }
   float M = -INFINITY;
 #pragma unroll
   for (int q = 0; q < 8; ++q) M = fmaxf(M, s_m[q]);
@@ -887,12 +914,55 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------
+// ensemble: log of the mean of K softmax distributions, one CTA per column
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ensemble_logmean_kernel(const EnsembleArgs a) {
+  __shared__ float red[32];
+  __shared__ float s_max[ZR_ENSEMBLE_MAX], s_inv[ZR_ENSEMBLE_MAX];
+  const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
+  const size_t col = (size_t)n * a.V;
+  for (int k = 0; k < a.K; ++k) {
+    const float* z = a.logits[k] + col;
+    float mx = -INFINITY;
+    for (int v = tid; v < a.V; v += blockDim.x) mx = fmaxf(mx, z[v]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[w] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int i = 1; i < nw; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float part = 0.f;
+    for (int v = tid; v < a.V; v += blockDim.x) part += expf(z[v] - mx);
+    const float sum = block_sum(part, red);
+    if (tid == 0) { s_max[k] = mx; s_inv[k] = 1.0f / (sum * (float)a.K); }
+    __syncthreads();
+  }
+  for (int v = tid; v < a.V; v += blockDim.x) {
+    float p = 0.f;
+    for (int k = 0; k < a.K; ++k) p += expf(a.logits[k][col + v] - s_max[k]) * s_inv[k];
+    a.out[col + v] = logf(p);
+  }
+}
+cudaError_t launch_ensemble_logmean(const EnsembleArgs& a, cudaStream_t st) {
+  if (a.N <= 0) return cudaSuccess;
+  if (a.K < 1 || a.K > ZR_ENSEMBLE_MAX) return cudaErrorInvalidValue;
+  ensemble_logmean_kernel<<<a.N, 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------
 // beam bookkeeping, one CTA per sentence
 // ------------------------------------------------------------------------------------------
 __global__ void beam_init_kernel(const BeamArgs a) {
   const int s = blockIdx.x, tid = threadIdx.x;
   const size_t rowbase = (size_t)s * a.beam * a.Lmax;
   for (int i = tid; i < a.beam * a.Lmax; i += blockDim.x) { a.top_sent[rowbase + i] = 0; a.top_tmp[rowbase + i] = 0; }
+  if (a.vit_rows) {
+    for (int i = tid; i < a.beam * a.Lmax; i += blockDim.x) { a.vit_rows[rowbase + i] = -20; a.vit_tmp[rowbase + i] = -20; }
+    for (int i = tid; i < a.k_best * a.Lmax; i += blockDim.x) a.best_align[(size_t)s * a.k_best * a.Lmax + i] = -1;
+  }
   for (int i = tid; i < a.beam; i += blockDim.x) {
     a.scores[s * a.beam + i] = 0.f;
     a.cur_ids[s * a.beam + i] = 0;
@@ -909,7 +979,9 @@ cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st) {
 }
 
 // insert (prefix of `row` up to position last_pos, then <EOF>) with `score` into the sentence's k-best list
-__device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int last_pos, float score) {
+// vrow / last_align: the alignments stored with the prefix and the one of the step that produced <EOF> (tracking on)
+__device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int last_pos, float score, const int* vrow,
+                                int last_align) {
   const int len = last_pos + 2;
   const float ratio = ((float)len) / (float)a.src_len[s];
   if (!(ratio > a.min_ratio)) return;
@@ -919,13 +991,19 @@ __device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int la
   int pos = 0;
   while (pos < a.k_best && lens[pos] != 0 && !(score > sc[pos])) ++pos;
   if (pos >= a.k_best) return;
+  int* al = a.best_align ? a.best_align + (size_t)s * a.k_best * a.Lmax : nullptr;
   for (int j = a.k_best - 1; j > pos; --j) {
     if (lens[j - 1] == 0) continue;
     for (int i = 0; i < a.Lmax; ++i) ids[(size_t)j * a.Lmax + i] = ids[(size_t)(j - 1) * a.Lmax + i];
+    if (al)
+      for (int i = 0; i < a.Lmax; ++i) al[(size_t)j * a.Lmax + i] = al[(size_t)(j - 1) * a.Lmax + i];
     lens[j] = lens[j - 1];
     sc[j] = sc[j - 1];
   }
   for (int i = 0; i < a.Lmax; ++i) ids[(size_t)pos * a.Lmax + i] = (i <= last_pos) ? row[i] : (i == last_pos + 1 ? 1 : -1);
+  if (al)
+    for (int i = 0; i < a.Lmax; ++i)
+      al[(size_t)pos * a.Lmax + i] = (i <= last_pos) ? vrow[i] : (i == last_pos + 1 ? last_align : -1);
   lens[pos] = len;
   sc[pos] = score;
 }
@@ -940,6 +1018,8 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
   const int max_steps = a.max_steps[s];
   int* rows = a.top_sent + (size_t)base * a.Lmax;
   int* tmp = a.top_tmp + (size_t)base * a.Lmax;
+  int* vrows = a.vit_rows ? a.vit_rows + (size_t)base * a.Lmax : nullptr;
+  int* vtmp = a.vit_rows ? a.vit_tmp + (size_t)base * a.Lmax : nullptr;
   if (t > max_steps) {
     if (tid < beam) a.col_map[base + tid] = base + tid;
     return;
@@ -949,7 +1029,8 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
       for (int i = 0; i < beam; ++i) {
         if (a.cur_ids[base + i] == -1) continue;
         const float sc = a.scores[base + i] + (a.logp_eos[base + i] + a.penalty);
-        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, sc);
+        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, sc, vrows ? vrows + (size_t)i * a.Lmax : nullptr,
+                        vrows ? a.viterbi[base + i] : -1);
       }
     if (tid < beam) a.col_map[base + tid] = base + tid;
     return;
@@ -999,7 +1080,8 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
       const int wd = a.cand_idx[(size_t)(base + i) * kc + r];
       if (wd == 0) continue;  // <START> is never extended
       if (wd == 1) {          // <EOF>: finished hypothesis, does not take a slot
-        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, val + a.penalty);
+        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, val + a.penalty, vrows ? vrows + (size_t)i * a.Lmax : nullptr,
+                        vrows ? a.viterbi[base + i] : -1);
       } else {
         n_cur[filled] = wd; n_chg[filled] = i; n_sc[filled] = val + a.penalty;
         ++filled;
@@ -1012,9 +1094,16 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
     int v = rows[(size_t)n_chg[f] * a.Lmax + i];
     if (i == t + 1) v = (n_cur[f] == -1) ? 0 : n_cur[f];
     tmp[e] = v;
+    if (vrows) {
+      int al = vrows[(size_t)n_chg[f] * a.Lmax + i];
+      if (i == t + 1 && n_cur[f] != -1) al = a.viterbi[base + n_chg[f]];
+      vtmp[e] = al;
+    }
   }
   __syncthreads();
   for (int e = tid; e < beam * a.Lmax; e += blockDim.x) rows[e] = tmp[e];
+  if (vrows)
+    for (int e = tid; e < beam * a.Lmax; e += blockDim.x) vrows[e] = vtmp[e];
   if (tid < beam) {
     a.cur_ids[base + tid] = n_cur[tid];
     a.col_map[base + tid] = base + n_chg[tid];

@@ -102,6 +102,13 @@ struct AttArgs {
   int ld_tq;
   float* c_t;          // context out, H x B
   float* align_out;    // optional
+  // optional: per target column the source position with the largest weight, -1 for a masked column
+  // (get_viterbi_alignment_kernel, src/custom_kernels.h:1621-1635)
+  int* viterbi_out;
+  // start value of the running maximum: -1 in the kernel itself; 0 in the decoder, where ensembles_models re-derives
+  // the alignment from the weights with a maximum that starts at 0 (src/ensemble_factory.hpp:812-834), so a column
+  // whose weights are all zero reports -1
+  float viterbi_init;
   // optional copies of the context in tensor-core operand form (row b at + b*ld_op)
   void* op_b16;
   float* op_hi;
@@ -110,6 +117,17 @@ struct AttArgs {
 };
 cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st);
 cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);
+
+// ---- ensemble decoding: out[v + n*V] = log( mean_k softmax(logits_k[:, n])[v] ), the log of the averaged
+// distribution of ensemble_factory::ensembles_models (src/ensemble_factory.hpp:768-795).  The renormalisation the
+// reference applies after averaging is the log-softmax the top-k kernel performs on `out`.
+#define ZR_ENSEMBLE_MAX 8
+struct EnsembleArgs {
+  const float* logits[ZR_ENSEMBLE_MAX];  // each V x N, column-major
+  int K, V, N;
+  float* out;  // V x N
+};
+cudaError_t launch_ensemble_logmean(const EnsembleArgs& a, cudaStream_t st);
 
 // ---- beam bookkeeping (replaces decoder::expand_hypothesis_without_fsa / finish_current_hypotheses /
 // output_k_best_hypotheses, src/decoder.h:1157-1315, 672-688, 1386-1463, run on the host there)
@@ -129,6 +147,13 @@ struct BeamArgs {
   int* best_ids;           // [n_sent][k_best][Lmax]
   int* best_len;           // [n_sent][k_best]
   float* best_score;       // [n_sent][k_best]
+  // optional viterbi-alignment tracking for UNK replacement (all null when off): the attention step's alignment per
+  // column, the alignment stored with every position of every beam entry (top_sentences_viterbi, src/decoder.h:230,
+  // initialised to -20, :1335) and with every position of the k-best hypotheses
+  const int* viterbi;      // [n_sent*beam]
+  int* vit_rows;           // [n_sent][beam][Lmax]
+  int* vit_tmp;            // same size
+  int* best_align;         // [n_sent][k_best][Lmax]
 };
 cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st);
 cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st);

@@ -381,7 +381,7 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
 }
 
 int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const Act& out, float* align,
-                cudaStream_t st) {
+                cudaStream_t st, int* viterbi = nullptr, float viterbi_init = -1.f) {
   const int H = A->H, eng = A->eng, Kpad = A->Kpad;
   ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
   KScope ks(KC_ATT, st);
@@ -389,7 +389,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
   std::memset(&a, 0, sizeof(a));
   a.H = H; a.B = B; a.D = A->D; a.S_max = A->S_max; a.B_src = A->B_src; a.cols_per_sent = A->cols_per_sent;
   a.hs = A->hs; a.len = A->len; a.offset = A->off; a.mask = mask; a.h_t = h_t.f32;
-  a.c_t = A->ctx.as<float>(); a.align_out = align;
+  a.c_t = A->ctx.as<float>(); a.align_out = align; a.viterbi_out = viterbi; a.viterbi_init = viterbi_init;
   Act ctx;
   ctx.f32 = A->ctx.as<float>();
   if (eng != ENG_SIMT) {
@@ -506,9 +506,10 @@ int softmax_score_act(zrnn_softmax* S, const Act& h, const int* targets, const i
   return ZRNN_OK;
 }
 
-int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
+// logits = D h + b_d into S->logits (V x N); tensor-core engines also leave each tile's maximum (*pm, *np tiles)
+int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, const float** pm_out, int* np_out) {
   ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
-  const float *pm = nullptr, *ps = nullptr;
+  const float *pm = nullptr;
   int np = 0;
   if (S->eng == ENG_SIMT) {
     zrnn::GemmArgs g;
@@ -531,13 +532,21 @@ int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, i
     // the epilogue also leaves each tile's maximum: the top-k kernel derives its threshold and the column maximum
     // from them and needs a single pass over the logits
     tp.part_max = S->parts.as<float>(); tp.part_sum = nullptr;
-    pm = tp.part_max; ps = nullptr;
+    pm = tp.part_max;
     tp.err = tc_error_word();
     KScope ks(KC_SOFTMAX_GEMM, st);
     ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
   }
+  *pm_out = pm;
+  *np_out = np;
+  return ZRNN_OK;
+}
+int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
+  const float* pm = nullptr;
+  int np = 0;
+  ZR_TRY(softmax_logits_act(S, h, N, st, &pm, &np));
   KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, ps, np));
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, nullptr, np));
   return ZRNN_OK;
 }
 
@@ -907,6 +916,7 @@ int zrnn_att_set_source(zrnn_attention* A, const float* d_hs, int S_max, int B_s
   A->cols_per_sent = cols_per_sentence;
   return ZRNN_OK;
 }
+static thread_local int* g_att_viterbi_out = nullptr;  // set only inside zrnn_att_forward_viterbi
 int zrnn_att_forward(zrnn_attention* A, const float* d_h_t, const int* d_mask, int B, float* d_htild_out,
                      float* d_align_out, void* stream) {
   ZR_CHECK(A && d_h_t && d_htild_out && B >= 0, "att_forward: bad arguments");
@@ -919,7 +929,15 @@ int zrnn_att_forward(zrnn_attention* A, const float* d_h_t, const int* d_mask, i
   h.f32 = const_cast<float*>(d_h_t);
   out.f32 = d_htild_out;
   if (A->eng != ENG_SIMT) ZR_TRY(to_operand(d_h_t, A->H, A->Kpad, B, A->eng, A->sc_h, A->sc_hl, &h, st));
-  return att_forward(A, h, d_mask, B, out, d_align_out, st);
+  return att_forward(A, h, d_mask, B, out, d_align_out, st, g_att_viterbi_out);
+}
+int zrnn_att_forward_viterbi(zrnn_attention* A, const float* d_h_t, const int* d_mask, int B, float* d_htild_out,
+                             int* d_viterbi_out, void* stream) {
+  ZR_CHECK(d_viterbi_out, "att_forward_viterbi: null output");
+  g_att_viterbi_out = d_viterbi_out;
+  const int st = zrnn_att_forward(A, d_h_t, d_mask, B, d_htild_out, nullptr, stream);
+  g_att_viterbi_out = nullptr;
+  return st;
 }
 int zrnn_att_destroy(zrnn_attention* A) {
   delete A;
@@ -1426,99 +1444,74 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
                                   int beam, int k_best, float min_ratio, float max_ratio, float penalty,
                                   int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score,
                                   void* stream) {
-  ZR_CHECK(m && d_src && h_src_len && d_out_ids && d_out_len && d_out_score, "beam_decode: null argument");
-  if (!m->finalized) return fail(ZRNN_E_STATE, "beam_decode: model weights not finalized");
-  const zrnn_model_config& c = m->cfg;
-  ZR_CHECK(!c.lm, "beam_decode: needs a sequence-to-sequence model");
-  ZR_CHECK(n_sent >= 0 && S_max > 0 && beam >= 1 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
-  if (n_sent == 0) return ZRNN_OK;
-  const int cap = (int)std::sqrt((double)c.V_tgt);  // src/ensemble_factory.hpp:19-21
-  if (beam > cap) beam = cap;
-  ZR_CHECK(beam >= 1 && beam <= 15, "beam_decode: beam must be in [1,15] after the sqrt(V) cap");
-  const int kc = beam + 1;
-  ZR_CHECK(kc <= c.V_tgt, "beam_decode: vocabulary smaller than beam+1");
-  const int Lmax = longest_sent + 4;  // src/main.cu:408
-  cudaStream_t s = (cudaStream_t)stream;
-  const int H = c.H, L = c.num_layers, n = n_sent, NB = n_sent * beam;
-  const Geom g{H, round64(H), m->eng};
-  const bool tc = m->eng != ENG_SIMT;
-  const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
+  return zrnn_beam_decode_batch_align_device(m, d_src, h_src_len, S_max, n_sent, beam, k_best, min_ratio, max_ratio,
+                                             penalty, longest_sent, d_out_ids, d_out_len, d_out_score, nullptr, stream);
+}
 
-  // per-sentence step limits (src/ensemble_factory.hpp:637)
-  m->h_tmp.resize(2 * (size_t)n);
-  int Tmax = 0;
-  for (int i = 0; i < n; ++i) {
-    ZR_CHECK(h_src_len[i] >= 1 && h_src_len[i] <= S_max, "beam_decode: source length out of range");
-    int ms = std::min((int)(max_ratio * h_src_len[i]), Lmax - 2);
-    ZR_CHECK(ms >= 1, "beam_decode: max_ratio*source_length must allow at least one step");
-    m->h_tmp[i] = h_src_len[i];
-    m->h_tmp[n + i] = ms;
-    Tmax = std::max(Tmax, ms);
+}  // extern "C"
+
+namespace {
+// Per-model state of a (possibly ensembled) beam search: encoder outputs and the decoder's recurrent state for
+// n_sent * beam columns.  Everything lives in the model's own workspace.
+struct BeamModel {
+  zrnn_model* m = nullptr;
+  Geom g{0, 0, 0};
+  bool tc = false;
+  int S_max = 0, n = 0, NB = 0, beam = 0;
+  int *src_id = nullptr, *src_mk = nullptr, *len = nullptr, *off = nullptr, *rep_map = nullptr;
+  Act X0, zero, x, htild_new, htild_feed;
+  std::vector<Act> sseq, hp, hn;
+  std::vector<float*> cst[2], cp, cn;
+  std::vector<int> cur;
+  int* vit = nullptr;  // viterbi alignment per column of the last forward step (tracking on)
+
+  size_t bytes(bool track) const {
+    const zrnn_model_config& c = m->cfg;
+    const int H = c.H, L = c.num_layers;
+    const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
+    size_t b = 2 * aligned(sizeof(int) * nS) + 2 * aligned(sizeof(int) * n) + aligned(sizeof(int) * NB);
+    b += act_bytes(g, nS, !tc, true) + (size_t)L * act_bytes(g, nS, true, true) + act_bytes(g, n, true, true);
+    b += 2 * (size_t)L * aligned(sizeof(float) * HBs);
+    b += (2 * (size_t)L + 3) * act_bytes(g, NB, true, true) + 2 * (size_t)L * aligned(sizeof(float) * HB);
+    if (track) b += aligned(sizeof(int) * NB);
+    return b;
   }
-  size_t bytes = 0;
-  bytes += 2 * aligned(sizeof(int) * nS) + 4 * aligned(sizeof(int) * n);
-  bytes += 3 * aligned(sizeof(int) * NB) + 2 * aligned(sizeof(int) * (size_t)NB * Lmax) + aligned(sizeof(int) * (size_t)NB * kc);
-  bytes += act_bytes(g, nS, !tc, true) + (size_t)L * act_bytes(g, nS, true, true) + act_bytes(g, n, true, true);
-  bytes += 2 * (size_t)L * aligned(sizeof(float) * HBs);
-  bytes += (2 * (size_t)L + 3) * act_bytes(g, NB, true, true) + 2 * (size_t)L * aligned(sizeof(float) * HB);
-  bytes += 2 * aligned(sizeof(float) * NB) + aligned(sizeof(float) * (size_t)NB * kc);
-  ZR_CUDA(m->ws.reserve(bytes));
-  Carver cv(m->ws.p);
-  int* src_id = cv.take<int>(nS);
-  int* src_mk = cv.take<int>(nS);
-  int* len = cv.take<int>(n);
-  int* off = cv.take<int>(n);
-  int* d_len_host = cv.take<int>(n);
-  int* max_steps = cv.take<int>(n);
-  int* rep_map = cv.take<int>(NB);
-  int* cur_ids = cv.take<int>(NB);
-  int* col_map = cv.take<int>(NB);
-  int* top_sent = cv.take<int>((size_t)NB * Lmax);
-  int* top_tmp = cv.take<int>((size_t)NB * Lmax);
-  int* cand_idx = cv.take<int>((size_t)NB * kc);
-  const Act X0 = act_take(cv, g, nS, !tc, true);
-  std::vector<Act> sseq(L);
-  for (int l = 0; l < L; ++l) sseq[l] = act_take(cv, g, nS, true, true);
-  const Act zero = act_take(cv, g, n, true, true);
-  std::vector<float*> cst[2];
-  for (int k = 0; k < 2; ++k) { cst[k].resize(L); for (int l = 0; l < L; ++l) cst[k][l] = cv.take<float>(HBs); }
-  std::vector<Act> hp(L), hn(L);
-  std::vector<float*> cp(L), cn(L);
-  for (int l = 0; l < L; ++l) {
-    hp[l] = act_take(cv, g, NB, true, true);
-    hn[l] = act_take(cv, g, NB, true, true);
-    cp[l] = cv.take<float>(HB);
-    cn[l] = cv.take<float>(HB);
+  void carve(Carver& cv, bool track) {
+    const zrnn_model_config& c = m->cfg;
+    const int H = c.H, L = c.num_layers;
+    const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
+    src_id = cv.take<int>(nS);
+    src_mk = cv.take<int>(nS);
+    len = cv.take<int>(n);
+    off = cv.take<int>(n);
+    rep_map = cv.take<int>(NB);
+    X0 = act_take(cv, g, nS, !tc, true);
+    sseq.resize(L);
+    for (int l = 0; l < L; ++l) sseq[l] = act_take(cv, g, nS, true, true);
+    zero = act_take(cv, g, n, true, true);
+    for (int k = 0; k < 2; ++k) { cst[k].resize(L); for (int l = 0; l < L; ++l) cst[k][l] = cv.take<float>(HBs); }
+    hp.resize(L); hn.resize(L); cp.resize(L); cn.resize(L);
+    for (int l = 0; l < L; ++l) {
+      hp[l] = act_take(cv, g, NB, true, true);
+      hn[l] = act_take(cv, g, NB, true, true);
+      cp[l] = cv.take<float>(HB);
+      cn[l] = cv.take<float>(HB);
+    }
+    x = act_take(cv, g, NB, true, true);
+    htild_new = act_take(cv, g, NB, true, true);
+    htild_feed = act_take(cv, g, NB, true, true);
+    vit = track ? cv.take<int>(NB) : nullptr;
   }
-  const Act x = act_take(cv, g, NB, true, true);
-  const Act htild_new = act_take(cv, g, NB, true, true);
-  const Act htild_feed = act_take(cv, g, NB, true, true);
-  float* scores = cv.take<float>(NB);
-  float* logp_eos = cv.take<float>(NB);
-  float* cand_val = cv.take<float>((size_t)NB * kc);
-
-  ZR_CUDA(cudaMemcpyAsync(d_len_host, m->h_tmp.data(), sizeof(int) * n, cudaMemcpyHostToDevice, s));
-  ZR_CUDA(cudaMemcpyAsync(max_steps, m->h_tmp.data() + n, sizeof(int) * n, cudaMemcpyHostToDevice, s));
-  std::vector<int> cur(L, 0);
-  ZR_TRY(act_zero(zero, g, n, s));
-  for (int l = 0; l < L; ++l) ZR_CUDA(cudaMemsetAsync(cst[0][l], 0, sizeof(float) * HBs, s));
-  ZR_CUDA(zrnn::launch_prep_ids(d_src, (int)nS, src_id, src_mk, s));
-  ZR_CUDA(zrnn::launch_src_len(src_mk, S_max, n, len, off, s));
-  ZR_TRY(run_encoder(m, g, src_id, src_mk, S_max, n, X0, zero, sseq, cst, cur, s));
-  if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S_max, n, len, off, beam));
-
-  // column gathers move whole operand rows: express every array as floats-per-column
-  auto add_gather = [&](zrnn::ColGatherArgs* ga, int* n_f32, const Act& srcA, const Act& dstA) {
-    // fp32 part
+  // column gathers move whole operand rows: every array is expressed as floats-per-column
+  void add_gather(zrnn::ColGatherArgs* ga, const Act& srcA, const Act& dstA) const {
     ga[0].src[ga[0].n_arrays] = srcA.f32; ga[0].dst[ga[0].n_arrays++] = dstA.f32;
     if (tc) {
       ga[1].src[ga[1].n_arrays] = (const float*)srcA.hi; ga[1].dst[ga[1].n_arrays++] = (float*)dstA.hi;
       if (g.eng == ENG_X3) { ga[2].src[ga[2].n_arrays] = srcA.lo; ga[2].dst[ga[2].n_arrays++] = dstA.lo; }
     }
-    (void)n_f32;
-  };
-  auto run_gathers = [&](zrnn::ColGatherArgs* ga, const int* map) -> int {
-    ga[0].H = H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad;
+  }
+  int run_gathers(zrnn::ColGatherArgs* ga, const int* map, cudaStream_t s) const {
+    ga[0].H = g.H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad;
     for (int k = 0; k < 3; ++k) {
       if (ga[k].n_arrays == 0) continue;
       ga[k].n_cols = NB; ga[k].map = map;
@@ -1526,18 +1519,142 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
       ZR_CUDA(zrnn::launch_col_gather(ga[k], s));
     }
     return ZRNN_OK;
-  };
-  // replicate the encoder's final (h,c) over the beam (transfer_decoding_states_GPU)
-  ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
-  {
+  }
+  // forward_prop_source + transfer_decoding_states_GPU (src/model.hpp:2367-2452)
+  int encode(const int* d_src, cudaStream_t s) {
+    const zrnn_model_config& c = m->cfg;
+    const int L = c.num_layers;
+    const size_t HBs = (size_t)c.H * n, nS = (size_t)S_max * n;
+    cur.assign(L, 0);
+    ZR_TRY(act_zero(zero, g, n, s));
+    for (int l = 0; l < L; ++l) ZR_CUDA(cudaMemsetAsync(cst[0][l], 0, sizeof(float) * HBs, s));
+    ZR_CUDA(zrnn::launch_prep_ids(d_src, (int)nS, src_id, src_mk, s));
+    ZR_CUDA(zrnn::launch_src_len(src_mk, S_max, n, len, off, s));
+    ZR_TRY(run_encoder(m, g, src_id, src_mk, S_max, n, X0, zero, sseq, cst, cur, s));
+    if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S_max, n, len, off, beam));
+    if (vit) ZR_CUDA(cudaMemsetAsync(vit, 0xff, sizeof(int) * NB, s));  // -1 without attention (src/decoder.h:1174-1178)
+    // replicate the encoder's final (h,c) over the beam
+    ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
     zrnn::ColGatherArgs ga[3];
     std::memset(ga, 0, sizeof(ga));
     for (int l = 0; l < L; ++l) {
-      add_gather(ga, nullptr, act_at(sseq[l], (size_t)(S_max - 1) * n, g), hp[l]);
+      add_gather(ga, act_at(sseq[l], (size_t)(S_max - 1) * n, g), hp[l]);
       ga[0].src[ga[0].n_arrays] = cst[cur[l]][l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
     }
-    ZR_TRY(run_gathers(ga, rep_map));
+    return run_gathers(ga, rep_map, s);
   }
+  // forward_prop_target (src/model.hpp:2573-2689) up to the vector handed to the softmax
+  int forward(int t, const int* cur_ids, Act* top, cudaStream_t s) {
+    const zrnn_model_config& c = m->cfg;
+    ZR_TRY(gather_act(m->tgt[0], cur_ids, NB, x, s));
+    Act xin = x;
+    for (int l = 0; l < c.num_layers; ++l) {
+      const bool use_feed = (l == 0 && c.feed_input && t > 0);
+      ZR_TRY(cell_forward(m->tgt[l], xin, hp[l], use_feed ? &htild_feed : nullptr, nullptr, cp[l], NB, hn[l], cn[l], s));
+      xin = hn[l];
+    }
+    *top = xin;
+    if (c.attention) {
+      ZR_TRY(att_forward(m->att, xin, nullptr, NB, htild_new, nullptr, s, vit, 0.f));
+      *top = htild_new;
+    }
+    return ZRNN_OK;
+  }
+  // swap_decoding_states + target_copy_prev_states (src/model.hpp:2691-2726)
+  int reorder(const int* col_map, cudaStream_t s) {
+    const zrnn_model_config& c = m->cfg;
+    zrnn::ColGatherArgs ga[3];
+    std::memset(ga, 0, sizeof(ga));
+    for (int l = 0; l < c.num_layers; ++l) {
+      add_gather(ga, hn[l], hp[l]);
+      ga[0].src[ga[0].n_arrays] = cn[l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
+    }
+    if (c.feed_input) add_gather(ga, htild_new, htild_feed);
+    return run_gathers(ga, col_map, s);
+  }
+};
+
+// Lock-step beam search of n_sent sentences with K >= 1 models.  With K > 1 the models' output distributions are
+// averaged and renormalised at every step (ensemble_factory::ensembles_models, src/ensemble_factory.hpp:768-795);
+// length limits follow model 0's source lengths (:623).  All models sit on the current device.
+int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, const int* h_src_len,
+                     const int* S_max, int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                     int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score, int* d_out_align,
+                     cudaStream_t s) {
+  ZR_CHECK(K >= 1 && K <= ZR_ENSEMBLE_MAX, "beam_decode: between 1 and 8 models");
+  const int V = models[0]->cfg.V_tgt;
+  for (int k = 0; k < K; ++k) {
+    zrnn_model* m = models[k];
+    ZR_CHECK(m, "beam_decode: null model");
+    if (!m->finalized) return fail(ZRNN_E_STATE, "beam_decode: model weights not finalized");
+    ZR_CHECK(!m->cfg.lm, "beam_decode: needs a sequence-to-sequence model");
+    ZR_CHECK(m->cfg.V_tgt == V, "beam_decode: ensembled models must share the target vocabulary");
+    ZR_CHECK(S_max[k] > 0, "beam_decode: bad sizes");
+  }
+  ZR_CHECK(n_sent >= 0 && beam >= 1 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
+  ZR_CHECK(!(d_out_align && K > 1), "beam_decode: alignment tracking is available with a single model");
+  if (n_sent == 0) return ZRNN_OK;
+  const int cap = (int)std::sqrt((double)V);  // src/ensemble_factory.hpp:19-21
+  if (beam > cap) beam = cap;
+  ZR_CHECK(beam >= 1 && beam <= 15, "beam_decode: beam must be in [1,15] after the sqrt(V) cap");
+  const int kc = beam + 1;
+  ZR_CHECK(kc <= V, "beam_decode: vocabulary smaller than beam+1");
+  const int Lmax = longest_sent + 4;  // src/main.cu:408
+  const int n = n_sent, NB = n_sent * beam;
+  zrnn_model* m0 = models[0];
+
+  // per-sentence step limits (src/ensemble_factory.hpp:637)
+  m0->h_tmp.resize(2 * (size_t)n);
+  int Tmax = 0;
+  for (int i = 0; i < n; ++i) {
+    ZR_CHECK(h_src_len[i] >= 1 && h_src_len[i] <= S_max[0], "beam_decode: source length out of range");
+    int ms = std::min((int)(max_ratio * h_src_len[i]), Lmax - 2);
+    ZR_CHECK(ms >= 1, "beam_decode: max_ratio*source_length must allow at least one step");
+    m0->h_tmp[i] = h_src_len[i];
+    m0->h_tmp[n + i] = ms;
+    Tmax = std::max(Tmax, ms);
+  }
+  const bool track = d_out_align != nullptr;
+  std::vector<BeamModel> bm(K);
+  for (int k = 0; k < K; ++k) {
+    BeamModel& b = bm[k];
+    b.m = models[k];
+    b.g = Geom{models[k]->cfg.H, round64(models[k]->cfg.H), models[k]->eng};
+    b.tc = models[k]->eng != ENG_SIMT;
+    b.S_max = S_max[k]; b.n = n; b.NB = NB; b.beam = beam;
+    size_t bytes = b.bytes(track);
+    if (k == 0) {  // shared bookkeeping lives in model 0's workspace
+      bytes += 2 * aligned(sizeof(int) * n) + 2 * aligned(sizeof(int) * NB) + 2 * aligned(sizeof(int) * (size_t)NB * Lmax);
+      bytes += aligned(sizeof(int) * (size_t)NB * kc) + 2 * aligned(sizeof(float) * NB) + aligned(sizeof(float) * (size_t)NB * kc);
+      if (track) bytes += 2 * aligned(sizeof(int) * (size_t)NB * Lmax);
+      if (K > 1) bytes += aligned(sizeof(float) * (size_t)V * NB);
+    }
+    ZR_CUDA(models[k]->ws.reserve(bytes));
+  }
+  Carver cv0(m0->ws.p);
+  int* d_len_host = cv0.take<int>(n);
+  int* max_steps = cv0.take<int>(n);
+  int* cur_ids = cv0.take<int>(NB);
+  int* col_map = cv0.take<int>(NB);
+  int* top_sent = cv0.take<int>((size_t)NB * Lmax);
+  int* top_tmp = cv0.take<int>((size_t)NB * Lmax);
+  int* cand_idx = cv0.take<int>((size_t)NB * kc);
+  float* scores = cv0.take<float>(NB);
+  float* logp_eos = cv0.take<float>(NB);
+  float* cand_val = cv0.take<float>((size_t)NB * kc);
+  int* vit_rows = track ? cv0.take<int>((size_t)NB * Lmax) : nullptr;
+  int* vit_tmp = track ? cv0.take<int>((size_t)NB * Lmax) : nullptr;
+  float* mean_logits = K > 1 ? cv0.take<float>((size_t)V * NB) : nullptr;
+  bm[0].carve(cv0, track);
+  for (int k = 1; k < K; ++k) {
+    Carver cv(models[k]->ws.p);
+    bm[k].carve(cv, false);
+  }
+
+  ZR_CUDA(cudaMemcpyAsync(d_len_host, m0->h_tmp.data(), sizeof(int) * n, cudaMemcpyHostToDevice, s));
+  ZR_CUDA(cudaMemcpyAsync(max_steps, m0->h_tmp.data() + n, sizeof(int) * n, cudaMemcpyHostToDevice, s));
+  for (int k = 0; k < K; ++k) ZR_TRY(bm[k].encode(d_src[k], s));
+
   zrnn::BeamArgs ba;
   std::memset(&ba, 0, sizeof(ba));
   ba.n_sent = n; ba.beam = beam; ba.k_cand = kc; ba.Lmax = Lmax; ba.k_best = k_best;
@@ -1545,44 +1662,63 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
   ba.cand_val = cand_val; ba.cand_idx = cand_idx; ba.logp_eos = logp_eos; ba.src_len = d_len_host; ba.max_steps = max_steps;
   ba.top_sent = top_sent; ba.top_tmp = top_tmp; ba.scores = scores; ba.cur_ids = cur_ids; ba.col_map = col_map;
   ba.best_ids = d_out_ids; ba.best_len = d_out_len; ba.best_score = d_out_score;
+  ba.viterbi = bm[0].vit; ba.vit_rows = vit_rows; ba.vit_tmp = vit_tmp; ba.best_align = d_out_align;
   ZR_CUDA(zrnn::launch_beam_init(ba, s));
 
   for (int t = 0; t <= Tmax; ++t) {
-    ZR_TRY(gather_act(m->tgt[0], cur_ids, NB, x, s));
-    Act xin = x;
-    for (int l = 0; l < L; ++l) {
-      const bool use_feed = (l == 0 && c.feed_input && t > 0);
-      ZR_TRY(cell_forward(m->tgt[l], xin, hp[l], use_feed ? &htild_feed : nullptr, nullptr, cp[l], NB, hn[l], cn[l], s));
-      xin = hn[l];
+    if (K == 1) {
+      Act top;
+      ZR_TRY(bm[0].forward(t, cur_ids, &top, s));
+      ZR_TRY(softmax_topk_act(m0->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
+    } else {
+      zrnn::EnsembleArgs ea;
+      std::memset(&ea, 0, sizeof(ea));
+      for (int k = 0; k < K; ++k) {
+        Act top;
+        ZR_TRY(bm[k].forward(t, cur_ids, &top, s));
+        const float* pm = nullptr;
+        int np = 0;
+        ZR_TRY(softmax_logits_act(models[k]->sm, top, NB, s, &pm, &np));
+        ea.logits[k] = models[k]->sm->logits.as<float>();
+      }
+      ea.K = K; ea.V = V; ea.N = NB; ea.out = mean_logits;
+      KScope ks(KC_SOFTMAX_REDUCE, s);
+      ZR_CUDA(zrnn::launch_ensemble_logmean(ea, s));
+      ZR_CUDA(zrnn::launch_topk_logp(mean_logits, V, NB, kc, cand_val, cand_idx, logp_eos, s, nullptr, nullptr, 0));
     }
-    Act top = xin;
-    if (c.attention) {
-      ZR_TRY(att_forward(m->att, xin, nullptr, NB, htild_new, nullptr, s));
-      top = htild_new;
-    }
-    ZR_TRY(softmax_topk_act(m->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
     ba.step = t;
     {
       KScope ks(KC_BEAM, s);
       ZR_CUDA(zrnn::launch_beam_step(ba, s));
     }
-    if (t < Tmax) {  // swap_decoding_states + target_copy_prev_states
-      zrnn::ColGatherArgs ga[3];
-      std::memset(ga, 0, sizeof(ga));
-      for (int l = 0; l < L; ++l) {
-        add_gather(ga, nullptr, hn[l], hp[l]);
-        ga[0].src[ga[0].n_arrays] = cn[l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
-      }
-      if (c.feed_input) add_gather(ga, nullptr, htild_new, htild_feed);
-      ZR_TRY(run_gathers(ga, col_map));
-    }
+    if (t < Tmax)
+      for (int k = 0; k < K; ++k) ZR_TRY(bm[k].reorder(col_map, s));
   }
   return ZRNN_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int zrnn_beam_decode_batch_align_device(zrnn_model* m, const int* d_src, const int* h_src_len, int S_max, int n_sent,
+                                        int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                                        int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score,
+                                        int* d_out_align, void* stream) {
+  ZR_CHECK(m && d_src && h_src_len && d_out_ids && d_out_len && d_out_score, "beam_decode: null argument");
+  return beam_decode_core(&m, 1, &d_src, h_src_len, &S_max, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
+                          longest_sent, d_out_ids, d_out_len, d_out_score, d_out_align, (cudaStream_t)stream);
 }
 
 int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam, int k_best,
                            float min_ratio, float max_ratio, float penalty, int longest_sent, int* out_ids,
                            int* out_len, float* out_score) {
+  return zrnn_beam_decode_batch_align(m, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
+                                      longest_sent, out_ids, out_len, out_score, nullptr);
+}
+
+int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam,
+                                 int k_best, float min_ratio, float max_ratio, float penalty, int longest_sent,
+                                 int* out_ids, int* out_len, float* out_score, int* out_align) {
   ZR_CHECK(m && src_ids && src_len && out_ids && out_len && out_score, "beam_decode: null argument");
   ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
   if (n_sent == 0) return ZRNN_OK;
@@ -1600,17 +1736,19 @@ int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len
     pos += src_len[i];
   }
   const size_t nO = (size_t)n_sent * k_best;
-  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * padded.size()) + aligned(sizeof(int) * nO * Lmax) +
+  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * padded.size()) + 2 * aligned(sizeof(int) * nO * Lmax) +
                         aligned(sizeof(int) * nO) + aligned(sizeof(float) * nO)));
   Carver cv(m->io.p);
   int* d_src = cv.take<int>(padded.size());
   int* d_ids = cv.take<int>(nO * Lmax);
   int* d_len = cv.take<int>(nO);
   float* d_sc = cv.take<float>(nO);
+  int* d_al = out_align ? cv.take<int>(nO * Lmax) : nullptr;
   cudaStream_t s = m->stream;
   ZR_CUDA(cudaMemcpyAsync(d_src, padded.data(), sizeof(int) * padded.size(), cudaMemcpyHostToDevice, s));
-  ZR_TRY(zrnn_beam_decode_batch_device(m, d_src, src_len, S_max, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
-                                       longest_sent, d_ids, d_len, d_sc, s));
+  ZR_TRY(zrnn_beam_decode_batch_align_device(m, d_src, src_len, S_max, n_sent, beam, k_best, min_ratio, max_ratio,
+                                             penalty, longest_sent, d_ids, d_len, d_sc, d_al, s));
+  if (out_align) ZR_CUDA(cudaMemcpyAsync(out_align, d_al, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_ids, d_ids, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
