@@ -272,6 +272,17 @@ int zrnn_beam_decode_batch_align_device(zrnn_model* m, const int* d_src_ids_padd
                                         int n_sent, int beam, int k_best, float min_ratio, float max_ratio,
                                         float penalty, int longest_sent, int* d_out_ids, int* d_out_len,
                                         float* d_out_score, int* d_out_align, void* stream);
+/* Ensemble decoding: ensemble_factory with several decoder_model_wrappers (src/ensemble_factory.hpp:13-118,
+ * 583-765) and ensembles_models (:768-795).  Every model runs the same beam in lock step on its own source
+ * sentences (src_ids[k], src_len[k]: the k-th model's reversed ids, --decode-main-data-files gives one file per
+ * model); at every step the models' output distributions are averaged, renormalised and expanded once.  The models
+ * must share the target vocabulary; length limits follow model 0's source lengths (:623, :637).  The reference puts
+ * one model on each GPU; here all models of an ensemble sit on the current device (its memory holds them) and
+ * sentences shard across devices as in the single-model path. */
+int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int* const* src_ids,
+                              const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
+                              float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
+                              float* out_score);
 int zrnn_model_destroy(zrnn_model* m);
 
 #ifdef __cplusplus

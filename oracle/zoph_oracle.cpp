@@ -470,45 +470,44 @@ double score_batch(const Model& m, const int* src_ids, int S_max, const int* tgt
 // finish_current_hypotheses :672-688, output_k_best_hypotheses :1386-1463.
 struct Hyp { std::vector<int> ids; std::vector<int> align; float score; };
 
-void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best, float min_ratio, float max_ratio,
-                     float penalty, int longest_sent_internal, std::vector<Hyp>& out) {
-  const Cfg& c = m.cfg;
-  const int H = c.H, L = c.num_layers, V = c.V_tgt;
-  const int START = 0, END = 1, INVALID = -1;
-  if (beam > (int)std::sqrt((double)V)) beam = (int)std::sqrt((double)V);  // ensemble_factory.hpp:19-21
+// Per-model decoder state: encoder outputs for one sentence and the recurrent state of `beam` columns.
+struct DecModel {
+  const Model* m;
+  int S, beam;
+  std::vector<std::vector<float>> hs, cs, h, cc, hp, cp;
+  std::vector<float> hs_all, x, htild, htild_feed, P;
+  std::vector<int> ones, ids, lenv, offv, vit;
   std::vector<float> scratch;
-  // ---- source, minibatch 1
-  std::vector<std::vector<float>> hs(L, std::vector<float>(H, 0.f)), cs(L, std::vector<float>(H, 0.f));
-  std::vector<float> x1(H), hn1(H), cn1(H);
-  const size_t HB = (size_t)H * beam;
-  std::vector<float> hs_all((size_t)S * HB);  // top source state replicated per beam column (model.hpp:2434-2445)
-  const int one = 1;
-  for (int t = 0; t < S; ++t) {
-    const int id = id_nonm1(src[t]);
-    gather(m.src[0].W, H, &id, 1, x1.data());
-    for (int l = 0; l < L; ++l) {
-      lstm_cell(H, 1, m.src[l], l == 0 ? x1.data() : hs[l - 1].data(), hs[l].data(), cs[l].data(), nullptr, &one,
-                hn1.data(), cn1.data(), scratch);
-      hs[l] = hn1; cs[l] = cn1;
-    }
-    for (int j = 0; j < beam; ++j) std::memcpy(hs_all.data() + (size_t)t * HB + (size_t)j * H, hs[L - 1].data(), sizeof(float) * H);
-  }
-  // ---- decoder state (decoder.h:1317-1337)
-  const int Lmax = longest_sent_internal;
-  std::vector<int> top_sent((size_t)beam * Lmax, START), top_tmp((size_t)beam * Lmax, START);
-  std::vector<float> scores(beam, 0.f), scores_tmp(beam, 0.f);
-  std::vector<int> cur(beam, START), changes(beam, 0);
-  std::vector<Hyp> hyps;
-  int current_index = 0;
-  std::vector<std::vector<float>> h(L, std::vector<float>(HB)), cc(L, std::vector<float>(HB));
-  std::vector<std::vector<float>> hp(L, std::vector<float>(HB)), cp(L, std::vector<float>(HB));
-  std::vector<float> x(HB), htild(HB, 0.f), htild_feed(HB, 0.f), P((size_t)V * beam), tmp(HB);
-  std::vector<int> ones(beam, 1), ids(beam), lenv(beam, S), offv(beam, 0);
-  // viterbi alignment per beam column of the last forward step (BZ_CUDA::viterbi_alignments; -1 without attention,
-  // decoder.h:1174-1178) and per position of every beam entry (top_sentences_viterbi, initialised to -20, :1335)
-  std::vector<int> vit(beam, -1), top_vit((size_t)beam * Lmax, -20), top_vit_tmp((size_t)beam * Lmax, -20);
 
-  auto forward_target = [&](int idx) {
+  void encode(const int* src) {
+    const Cfg& c = m->cfg;
+    const int H = c.H, L = c.num_layers;
+    const size_t HB = (size_t)H * beam;
+    hs.assign(L, std::vector<float>(H, 0.f)); cs.assign(L, std::vector<float>(H, 0.f));
+    std::vector<float> x1(H), hn1(H), cn1(H);
+    hs_all.resize((size_t)S * HB);  // top source state replicated per beam column (model.hpp:2434-2445)
+    const int one = 1;
+    for (int t = 0; t < S; ++t) {
+      const int id = id_nonm1(src[t]);
+      gather(m->src[0].W, H, &id, 1, x1.data());
+      for (int l = 0; l < L; ++l) {
+        lstm_cell(H, 1, m->src[l], l == 0 ? x1.data() : hs[l - 1].data(), hs[l].data(), cs[l].data(), nullptr, &one,
+                  hn1.data(), cn1.data(), scratch);
+        hs[l] = hn1; cs[l] = cn1;
+      }
+      for (int j = 0; j < beam; ++j) std::memcpy(hs_all.data() + (size_t)t * HB + (size_t)j * H, hs[L - 1].data(), sizeof(float) * H);
+    }
+    h.assign(L, std::vector<float>(HB)); cc.assign(L, std::vector<float>(HB));
+    hp.assign(L, std::vector<float>(HB)); cp.assign(L, std::vector<float>(HB));
+    x.resize(HB); htild.assign(HB, 0.f); htild_feed.assign(HB, 0.f); P.resize((size_t)c.V_tgt * beam);
+    ones.assign(beam, 1); ids.resize(beam); lenv.assign(beam, S); offv.assign(beam, 0);
+    // viterbi alignment per beam column of the last forward step (BZ_CUDA::viterbi_alignments; -1 without attention,
+    // decoder.h:1174-1178)
+    vit.assign(beam, -1);
+  }
+  void forward(int idx, const std::vector<int>& cur) {
+    const Cfg& c = m->cfg;
+    const int H = c.H, L = c.num_layers, V = c.V_tgt;
     if (idx == 0)  // transfer_decoding_states_GPU: replicate the source's last (h,c) over the beam
       for (int l = 0; l < L; ++l)
         for (int j = 0; j < beam; ++j) {
@@ -516,19 +515,76 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
           std::memcpy(cp[l].data() + (size_t)j * H, cs[l].data(), sizeof(float) * H);
         }
     for (int j = 0; j < beam; ++j) ids[j] = cur[j] < 0 ? 0 : cur[j];
-    gather(m.tgt[0].W, H, ids.data(), beam, x.data());
+    gather(m->tgt[0].W, H, ids.data(), beam, x.data());
     for (int l = 0; l < L; ++l) {
       const bool feed = (l == 0 && c.feed_input && c.attention && idx != 0);
-      lstm_cell(H, beam, m.tgt[l], l == 0 ? x.data() : h[l - 1].data(), hp[l].data(), cp[l].data(),
+      lstm_cell(H, beam, m->tgt[l], l == 0 ? x.data() : h[l - 1].data(), hp[l].data(), cp[l].data(),
                 feed ? htild_feed.data() : nullptr, ones.data(), h[l].data(), cc[l].data(), scratch);
     }
     const float* top = h[L - 1].data();
     if (c.attention) {
-      attention(c.attention, H, beam, c.D, m.att, h[L - 1].data(), ones.data(), hs_all.data(), S, lenv.data(),
+      attention(c.attention, H, beam, c.D, m->att, h[L - 1].data(), ones.data(), hs_all.data(), S, lenv.data(),
                 offv.data(), htild.data(), nullptr, nullptr, vit.data(), 0.f);
       top = htild.data();
     }
-    softmax_dist(V, H, beam, m.D, m.b_d, top, P.data());
+    softmax_dist(V, H, beam, m->D, m->b_d, top, P.data());
+  }
+  // swap_decoding_states + target_copy_prev_states (model.hpp:2691-2726)
+  void reorder(const std::vector<int>& changes) {
+    const Cfg& c = m->cfg;
+    const int H = c.H, L = c.num_layers;
+    for (int l = 0; l < L; ++l)
+      for (int j = 0; j < beam; ++j) {
+        std::memcpy(hp[l].data() + (size_t)j * H, h[l].data() + (size_t)changes[j] * H, sizeof(float) * H);
+        std::memcpy(cp[l].data() + (size_t)j * H, cc[l].data() + (size_t)changes[j] * H, sizeof(float) * H);
+      }
+    if (c.feed_input && c.attention)
+      for (int j = 0; j < beam; ++j)
+        std::memcpy(htild_feed.data() + (size_t)j * H, htild.data() + (size_t)changes[j] * H, sizeof(float) * H);
+  }
+};
+
+// models.size() > 1: ensemble decoding, ensemble_factory::ensembles_models src/ensemble_factory.hpp:768-795 (the
+// distributions are averaged in double, stored as float, then every column is divided by its sum); each model reads
+// its own source sentence, the length limits follow model 0's (:623, :637).
+void beam_decode_one(const std::vector<const Model*>& models, const std::vector<const int*>& srcs,
+                     const std::vector<int>& Ss, int beam, int k_best, float min_ratio, float max_ratio,
+                     float penalty, int longest_sent_internal, std::vector<Hyp>& out) {
+  const int K = (int)models.size();
+  const int V = models[0]->cfg.V_tgt, S = Ss[0];
+  const int START = 0, END = 1, INVALID = -1;
+  if (beam > (int)std::sqrt((double)V)) beam = (int)std::sqrt((double)V);  // ensemble_factory.hpp:19-21
+  std::vector<DecModel> dm(K);
+  for (int k = 0; k < K; ++k) { dm[k].m = models[k]; dm[k].S = Ss[k]; dm[k].beam = beam; dm[k].encode(srcs[k]); }
+  // ---- decoder state (decoder.h:1317-1337)
+  const int Lmax = longest_sent_internal;
+  std::vector<int> top_sent((size_t)beam * Lmax, START), top_tmp((size_t)beam * Lmax, START);
+  std::vector<float> scores(beam, 0.f), scores_tmp(beam, 0.f);
+  std::vector<int> cur(beam, START), changes(beam, 0);
+  std::vector<Hyp> hyps;
+  int current_index = 0;
+  std::vector<float> Pens;
+  // alignment per position of every beam entry (top_sentences_viterbi, initialised to -20, :1335)
+  std::vector<int> top_vit((size_t)beam * Lmax, -20), top_vit_tmp((size_t)beam * Lmax, -20);
+  const float* Pp = nullptr;
+  const int* vitp = nullptr;
+
+  auto forward_target = [&](int idx) {
+    for (int k = 0; k < K; ++k) dm[k].forward(idx, cur);
+    vitp = dm[0].vit.data();
+    if (K == 1) { Pp = dm[0].P.data(); return; }
+    Pens.resize((size_t)V * beam);
+    for (int j = 0; j < beam; ++j) {
+      float norm = 0.f;
+      for (int i = 0; i < V; ++i) {
+        double t = 0;
+        for (int k = 0; k < K; ++k) t += dm[k].P[(size_t)j * V + i];
+        Pens[(size_t)j * V + i] = (float)(t / K);
+        norm += Pens[(size_t)j * V + i];
+      }
+      for (int i = 0; i < V; ++i) Pens[(size_t)j * V + i] = Pens[(size_t)j * V + i] / norm;
+    }
+    Pp = Pens.data();
   };
 
   struct Cand { float val; int beam_idx; int vocab; };
@@ -546,7 +602,7 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
       // keep the beam+1 largest probabilities of column i
       auto greater_p = [](const std::pair<float, int>& a, const std::pair<float, int>& b) { return a.first > b.first; };
       std::priority_queue<std::pair<float, int>, std::vector<std::pair<float, int>>, decltype(greater_p)> pq(greater_p);
-      const float* col = P.data() + (size_t)i * V;
+      const float* col = Pp + (size_t)i * V;
       for (int j = 0; j < V; ++j) {
         if ((int)pq.size() < beam + 1) pq.push({col[j], j});
         else if (col[j] > pq.top().first) { pq.pop(); pq.push({col[j], j}); }
@@ -574,28 +630,20 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
         hy.ids.assign(&top_sent[(size_t)t.beam_idx * Lmax], &top_sent[(size_t)t.beam_idx * Lmax] + current_index + 2);
         hy.ids[current_index + 1] = END;
         hy.align.assign(&top_vit[(size_t)t.beam_idx * Lmax], &top_vit[(size_t)t.beam_idx * Lmax] + current_index + 2);
-        hy.align[current_index + 1] = vit[t.beam_idx];  // decoder.h:1266-1267
+        hy.align[current_index + 1] = vitp[t.beam_idx];  // decoder.h:1266-1267
         hy.score = t.val + penalty;
         hyps.push_back(hy);
       } else {
         std::memcpy(&top_tmp[(size_t)i * Lmax], &top_sent[(size_t)t.beam_idx * Lmax], sizeof(int) * Lmax);
         top_tmp[(size_t)i * Lmax + current_index + 1] = t.vocab;
         std::memcpy(&top_vit_tmp[(size_t)i * Lmax], &top_vit[(size_t)t.beam_idx * Lmax], sizeof(int) * Lmax);
-        top_vit_tmp[(size_t)i * Lmax + current_index + 1] = vit[t.beam_idx];  // decoder.h:1281-1282
+        top_vit_tmp[(size_t)i * Lmax + current_index + 1] = vitp[t.beam_idx];  // decoder.h:1281-1282
         cur[i] = t.vocab; changes[i] = t.beam_idx; scores_tmp[i] = t.val + penalty;
         ++i;
       }
     }
     top_sent = top_tmp; top_vit = top_vit_tmp; scores = scores_tmp; current_index += 1;
-    // ---- swap_decoding_states + target_copy_prev_states (model.hpp:2691-2726)
-    for (int l = 0; l < L; ++l)
-      for (int j = 0; j < beam; ++j) {
-        std::memcpy(hp[l].data() + (size_t)j * H, h[l].data() + (size_t)changes[j] * H, sizeof(float) * H);
-        std::memcpy(cp[l].data() + (size_t)j * H, cc[l].data() + (size_t)changes[j] * H, sizeof(float) * H);
-      }
-    if (c.feed_input && c.attention)
-      for (int j = 0; j < beam; ++j)
-        std::memcpy(htild_feed.data() + (size_t)j * H, htild.data() + (size_t)changes[j] * H, sizeof(float) * H);
+    for (int k = 0; k < K; ++k) dm[k].reorder(changes);
     last_index = step;
   }
   forward_target(last_index + 1);
@@ -603,11 +651,11 @@ void beam_decode_one(const Model& m, const int* src, int S, int beam, int k_best
   for (int i = 0; i < beam; ++i) {
     if (cur[i] == INVALID) continue;
     top_sent[(size_t)i * Lmax + current_index + 1] = END;
-    scores[i] += std::log(P[(size_t)i * V + 1]) + penalty;
+    scores[i] += std::log(Pp[(size_t)i * V + 1]) + penalty;
     Hyp hy;
     hy.ids.assign(&top_sent[(size_t)i * Lmax], &top_sent[(size_t)i * Lmax] + current_index + 2);
     hy.align.assign(&top_vit[(size_t)i * Lmax], &top_vit[(size_t)i * Lmax] + current_index + 2);
-    hy.align[current_index + 1] = vit[i];  // decoder.h:683-684
+    hy.align[current_index + 1] = vitp[i];  // decoder.h:683-684
     hy.score = scores[i];
     hyps.push_back(hy);
   }
@@ -681,7 +729,7 @@ void orc_beam_decode_align(void* p, const int* src_ids, const int* src_len, int 
   size_t pos = 0;
   for (int s = 0; s < n_sent; ++s) {
     std::vector<Hyp> res;
-    beam_decode_one(m, src_ids + pos, src_len[s], beam, k_best, min_ratio, max_ratio, penalty, longest_sent + 4, res);
+    beam_decode_one({&m}, {src_ids + pos}, {src_len[s]}, beam, k_best, min_ratio, max_ratio, penalty, longest_sent + 4, res);
     pos += src_len[s];
     for (int k = 0; k < k_best; ++k) {
       int* dst = out_ids + ((size_t)s * k_best + k) * Lmax_out;
@@ -707,6 +755,38 @@ void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent
                      float* out_score) {
   orc_beam_decode_align(p, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio, penalty, longest_sent, Lmax_out,
                         out_ids, out_len, out_score, nullptr);
+}
+
+// Ensemble decoding: n_models models, model k reads src_ids[k] / src_len[k] (concatenated reversed ids per sentence).
+void orc_beam_decode_ensemble(void* const* models, int n_models, const int* const* src_ids, const int* const* src_len,
+                              int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                              int longest_sent, int Lmax_out, int* out_ids, int* out_len, float* out_score) {
+  std::vector<size_t> pos(n_models, 0);
+  for (int s = 0; s < n_sent; ++s) {
+    std::vector<const Model*> ms;
+    std::vector<const int*> srcs;
+    std::vector<int> Ss;
+    for (int k = 0; k < n_models; ++k) {
+      ms.push_back((const Model*)models[k]);
+      srcs.push_back(src_ids[k] + pos[k]);
+      Ss.push_back(src_len[k][s]);
+      pos[k] += src_len[k][s];
+    }
+    std::vector<Hyp> res;
+    beam_decode_one(ms, srcs, Ss, beam, k_best, min_ratio, max_ratio, penalty, longest_sent + 4, res);
+    for (int k = 0; k < k_best; ++k) {
+      int* dst = out_ids + ((size_t)s * k_best + k) * Lmax_out;
+      for (int i = 0; i < Lmax_out; ++i) dst[i] = -1;
+      out_len[(size_t)s * k_best + k] = 0;
+      out_score[(size_t)s * k_best + k] = 0;
+      if (k < (int)res.size()) {
+        const int n = std::min((int)res[k].ids.size(), Lmax_out);
+        for (int i = 0; i < n; ++i) dst[i] = res[k].ids[i];
+        out_len[(size_t)s * k_best + k] = (int)res[k].ids.size();
+        out_score[(size_t)s * k_best + k] = res[k].score;
+      }
+    }
+  }
 }
 
 // ---- layer-level entry points for per-kernel parity tests

@@ -60,7 +60,7 @@ def test_prep_decode(tmp_path):
     (["-s", "-f", "a", "b"], "three arguements"),
     (["--no-such-flag"], "unrecognised option"),
     (["-k", "1", "m.nn", "o"], "--decode-main-data-files"),
-    (["-k", "1", "m1.nn", "m2.nn", "o", "--decode-main-data-files", "a", "b"], "ensemble"),
+    (["-k", "1", "m1.nn", "m2.nn", "o", "--decode-main-data-files", "a"], "same number of inputs"),
     (["-k", "1", "m.nn", "o", "--decode-main-data-files", "a", "--dec-ratio", "0.5"], "only two inputs"),
     (["-k", "1", "m.nn", "o", "--decode-main-data-files", "a", "--dec-ratio", "1.5", "0.5"], "min decoding ratio"),
     (["-k", "1", "m.nn", "o", "--decode-main-data-files", "a", "-b", "0"], "beam size"),

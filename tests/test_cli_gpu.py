@@ -117,3 +117,22 @@ def test_decode_unk_replacement_file(tmp_path, oracle):
         g, x = got_unk.split("\n"), want_unk.split("\n")
         same = sum(a == b for a, b in zip(g, x))
         assert same >= 0.95 * len(x), (same, len(x))
+
+
+def test_decode_ensemble_of_two_models(tmp_path, oracle):
+    d1, d2 = tmp_path / "m1", tmp_path / "m2"
+    d1.mkdir(); d2.mkdir()
+    cfg_a = synth.make_cfg(2, 64, 200, 300, attention=1, feed_input=1, D=3)
+    cfg_b = synth.make_cfg(1, 64, 120, 300, attention=0, feed_input=0)
+    ma, sa, _, wa = make_text_fixture(str(d1), cfg_a, 15, seed=16, max_len=10, scale=0.25)
+    mb, sb, _, wb = make_text_fixture(str(d2), cfg_b, 15, seed=17, max_len=10, scale=0.25)
+    rc, out = run_cli(["-k", "1", ma, mb, "kbest.txt", "--decode-main-data-files", sa, sb, "-b", "5", "-L", "40",
+                       "--attention-width", "3", "--device-batch", "4"], tmp_path)
+    assert rc == 0, out
+    _, xa = textprep.integerize_kbest(ma, sa, 40)
+    _, xb = textprep.integerize_kbest(mb, sb, 40)
+    ids, ln, sc = oracle.beam_decode_ensemble([oracle.OracleModel(cfg_a, wa), oracle.OracleModel(cfg_b, wb)],
+                                              [[np.array(s, dtype=np.int32) for s in xa],
+                                               [np.array(s, dtype=np.int32) for s in xb]], beam=5, k_best=1, longest_sent=40)
+    hyps = [[(list(ids[s, 0, :ln[s, 0]]), float(sc[s, 0]))] if ln[s, 0] > 0 else [] for s in range(len(xa))]
+    assert open(os.path.join(str(tmp_path), "kbest.txt")).read() == textprep.unint(ma, textprep.format_kbest_ints(hyps, False))

@@ -193,3 +193,28 @@ def test_vocab_sharded_scorer_on_one_gpu(api, oracle, dtype):
     got = scorer.score(None, tin, tout)
     want = oracle.OracleModel(cfg, w).score_batch(None, tin, tout)
     helpers.assert_logp_close(got, want)
+
+
+@pytest.mark.parametrize("dtype", [3, 4])
+def test_ensemble_decoding_matches_oracle(api, oracle, dtype):
+    """Two models of different shapes (own source vocabulary and sentences, shared target vocabulary) decoded as an
+    ensemble: per-step averaging of the output distributions (src/ensemble_factory.hpp:768-795)."""
+    cfg_a = synth.make_cfg(2, 128, 200, 300, attention=1, feed_input=1, D=3)
+    cfg_b = synth.make_cfg(1, 64, 150, 300, attention=0, feed_input=0)
+    wa = synth.make_weights(cfg_a, seed=41, scale=0.25)
+    wb = synth.make_weights(cfg_b, seed=42, scale=0.25)
+    sa = synth.make_decode_sources(200, 7, 3, 14, seed=6)
+    sb = synth.make_decode_sources(150, 7, 2, 11, seed=7)
+    kw = dict(beam=6, k_best=2, min_ratio=0.5, max_ratio=2.0, penalty=0.1, longest_sent=40)
+    oa, ob = oracle.OracleModel(cfg_a, wa), oracle.OracleModel(cfg_b, wb)
+    ids, ln, sc = oracle.beam_decode_ensemble([oa, ob], [sa, sb], **kw)
+    ma, mb = build_model(api, cfg_a, wa, dtype), build_model(api, cfg_b, wb, dtype)
+    gi, gl, gs = api.decode_ensemble([ma, mb], [sa, sb], **kw)
+    agree = (gl == ln) & np.all(gi == ids, axis=2)
+    assert agree.mean() >= 0.995, f"hypothesis agreement {agree.mean():.3f}"
+    np.testing.assert_allclose(gs[agree], sc[agree], rtol=1e-5, atol=1e-4)
+    # the ensemble differs from either model alone, and an ensemble of one is the single-model decode
+    alone = ma.decode(sa, **kw)
+    assert not np.array_equal(alone[2], gs)
+    one = api.decode_ensemble([ma], [sa], **kw)
+    assert np.array_equal(one[0], alone[0]) and np.array_equal(one[2], alone[2])

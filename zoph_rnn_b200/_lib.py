@@ -111,6 +111,10 @@ SIGNATURES = {
                                                            ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float,
                                                            ctypes.c_float, ctypes.c_int, c_void_p, c_void_p, c_void_p,
                                                            c_void_p, c_void_p]),
+    "zrnn_beam_decode_ensemble": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.POINTER(c_void_p),
+                                                 ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                 ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int, c_void_p,
+                                                 c_void_p, c_void_p]),
     "zrnn_model_destroy": (ctypes.c_int, [c_void_p]),
 }
 

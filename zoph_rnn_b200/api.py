@@ -344,6 +344,27 @@ class neuralMT_model:
             pass
 
 
+def decode_ensemble(models, sources_per_model, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0,
+                    longest_sent=100):
+    """ensemble_factory decoding with several models (src/ensemble_factory.hpp:583-795): sources_per_model[k] is the
+    k-th model's list of reversed source id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k])."""
+    K, n = len(models), len(sources_per_model[0])
+    flats = [np.ascontiguousarray(np.concatenate([np.asarray(s, dtype=np.int32) for s in srcs]), dtype=np.int32)
+             for srcs in sources_per_model]
+    lens = [np.ascontiguousarray([len(s) for s in srcs], dtype=np.int32) for srcs in sources_per_model]
+    Lmax = longest_sent + 4
+    ids = np.empty((n, k_best, Lmax), dtype=np.int32)
+    ln = np.empty((n, k_best), dtype=np.int32)
+    sc = np.empty((n, k_best), dtype=np.float32)
+    hs = (ctypes.c_void_p * K)(*[m._h.value if isinstance(m._h, ctypes.c_void_p) else m._h for m in models])
+    fp = (ctypes.c_void_p * K)(*[f.ctypes.data for f in flats])
+    lp = (ctypes.c_void_p * K)(*[l.ctypes.data for l in lens])
+    check(lib().zrnn_beam_decode_ensemble(hs, K, fp, lp, n, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
+                                          ctypes.c_void_p(ids.ctypes.data), ctypes.c_void_p(ln.ctypes.data),
+                                          ctypes.c_void_p(sc.ctypes.data)))
+    return ids, ln, sc
+
+
 def read_model_file_header(path):
     """(header ints [9], how many the file carried, source vocabulary lines, target vocabulary lines) of a
     model.nn, parsed on the host (src/add_model_info.h:7-9)."""

@@ -12,17 +12,27 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "--expt-relaxed-constexpr"]
 
 
-def _newest_source():
+def _newest(names_ok):
     t = 0.0
     for root in (CSRC, os.path.join(HERE, "..", "include")):
         for f in os.listdir(root):
-            t = max(t, os.path.getmtime(os.path.join(root, f)))
+            if names_ok(f):
+                t = max(t, os.path.getmtime(os.path.join(root, f)))
     return t
+
+
+def _newest_source():
+    """Newest file that goes into libzrnn.so (the front end's own sources do not)."""
+    return _newest(lambda f: f.endswith((".cu", ".cuh", ".h", ".hpp")) and f != "text_data.hpp")
+
+
+def _newest_cli_source():
+    return _newest(lambda f: f in ("cli_main.cpp", "text_data.hpp", "model_file.hpp", "zrnn.h"))
 
 
 def build_cli(force=False):
     """Compile the command-line front end (host C++ only) against libzrnn.so; returns the binary's path."""
-    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(_newest_source(), os.path.getmtime(LIB)):
+    if not force and os.path.exists(CLI) and os.path.getmtime(CLI) >= max(_newest_cli_source(), os.path.getmtime(LIB)):
         return CLI
     os.makedirs(os.path.dirname(CLI), exist_ok=True)
     cxx = os.environ.get("CXX", "g++")

@@ -265,8 +265,9 @@ struct Params {
 
 void remove_tmp_dir(const Params& p) {
   if (p.unique_dir.empty() || p.keep_tmp) return;
-  static const char* names[] = {"validation.txt", "decoder_output.txt", "kbest_tmp_0"};
+  static const char* names[] = {"validation.txt", "decoder_output.txt"};
   for (const char* n : names) unlink((p.unique_dir + "/" + n).c_str());
+  for (int k = 0; k < 8; ++k) unlink((p.unique_dir + "/kbest_tmp_" + std::to_string(k)).c_str());
   rmdir(p.unique_dir.c_str());
 }
 
@@ -447,36 +448,50 @@ int run_decode(const Options& opt, Params& p) {
   std::vector<std::string> model_names(k.begin() + 1, k.end() - 1);
   const std::string final_file = k.back();
   if (model_names.size() != data_files.size()) die("the same number of inputs must be specified as models");
-  if (model_names.size() != 1)
-    die("ensemble decoding (" + std::to_string(model_names.size()) + " models) is not available in this program; pass one model");
+  const int K = (int)model_names.size();
+  if (K > 8) die("at most 8 models can be ensembled");
+  if (K > 1 && !p.unk_file.empty()) die("--UNK-decode is available with a single model");
   if (p.beam <= 0) die("beam size cannot be <=0");
   if (p.penalty < 0) die("penalty cannot be less than zero");
   if (num_hypotheses <= 0) die("the number of outputs must be positive");
   if (p.min_ratio >= p.max_ratio) die("min decoding ratio must be <= max_decoding_ratio");
 
-  Vocab vocab;
+  // every model of an ensemble has its own source vocabulary and data file; they share the target vocabulary, and
+  // the first model's mapping turns the output back into words (src/main.cu:1038-1046, 1611-1613)
+  std::vector<Vocab> vocabs(K);
   std::string err;
-  if (!vocab.load(model_names[0], &err)) die(err);
-  if (vocab.header.lm) die("--decode needs a sequence-to-sequence model");
+  for (int k = 0; k < K; ++k) {
+    if (!vocabs[k].load(model_names[k], &err)) die(err);
+    if (vocabs[k].header.lm) die("--decode needs a sequence-to-sequence model");
+    if (vocabs[k].header.V_tgt != vocabs[0].header.V_tgt) die("ensembled models must share the target vocabulary");
+  }
+  const Vocab& vocab = vocabs[0];
   make_tmp_dir(&p);
-  const std::string int_file = p.unique_dir + "/kbest_tmp_0";
   const std::string int_out = p.unique_dir + "/decoder_output.txt";
-  std::vector<std::vector<int>> sents;
-  std::vector<int> kept;
-  PrepStats st;
-  if (p.int_input) {
-    if (!zrnn::text::read_kbest_file(data_files[0], &sents, &err)) die(err);
-  } else {
-    if (!zrnn::text::prep_kbest(vocab, data_files[0], p.longest_sent, p.legacy, &sents, &kept, &st, &err)) die(err);
-    print_prep_stats(st, true, "kbest");
-    if (!zrnn::text::write_kbest_file(int_file, sents, &err)) die(err);
+  std::vector<std::vector<std::vector<int>>> sents_k(K);
+  for (int k = 0; k < K; ++k) {
+    const std::string int_file = p.unique_dir + "/kbest_tmp_" + std::to_string(k);
+    std::vector<int> kept;
+    PrepStats st;
+    if (p.int_input) {
+      if (!zrnn::text::read_kbest_file(data_files[k], &sents_k[k], &err)) die(err);
+    } else {
+      if (!zrnn::text::prep_kbest(vocabs[k], data_files[k], p.longest_sent, p.legacy, &sents_k[k], &kept, &st, &err)) die(err);
+      print_prep_stats(st, true, "kbest");
+      if (!zrnn::text::write_kbest_file(int_file, sents_k[k], &err)) die(err);
+    }
+    if (p.prep_only) logger << "Integer decode file: " << int_file << "\n";
+    // the reference walks the K integer files in lock step; files that kept different lines would pair up the wrong
+    // sentences, so that case is an error here
+    if (sents_k[k].size() != sents_k[0].size())
+      die("data file " + std::to_string(k) + " keeps " + std::to_string(sents_k[k].size()) + " sentences after the length cut-off, data file 0 keeps " + std::to_string(sents_k[0].size()));
   }
-  if (p.prep_only) {
-    logger << "Integer decode file: " << int_file << "\n";
-    return 0;
-  }
+  if (p.prep_only) return 0;
+  const std::vector<std::vector<int>>& sents = sents_k[0];
   select_device(p);
-  zrnn_model* model = load_model(p, model_names[0]);
+  std::vector<zrnn_model*> models(K);
+  for (int k = 0; k < K; ++k) models[k] = load_model(p, model_names[k]);
+  zrnn_model* model = models[0];
   zrnn_model_config cfg;
   zrnn_model_get_config(model, &cfg);
   const int cap_beam = (int)std::floor(std::sqrt((double)cfg.V_tgt));
@@ -498,20 +513,30 @@ int run_decode(const Options& opt, Params& p) {
   long long out_words = 0;
   for (int g0 = 0; g0 < n; g0 += group) {
     const int g1 = std::min(n, g0 + group), ng = g1 - g0;
-    std::vector<int> flat, lens;
-    for (int i = g0; i < g1; ++i) {
-      const auto& s = sents[order[i]];
-      if (s.empty()) die("source line with no words cannot be decoded");
-      flat.insert(flat.end(), s.begin(), s.end());
-      lens.push_back((int)s.size());
-    }
+    std::vector<std::vector<int>> flat_k(K), lens_k(K);
+    for (int k = 0; k < K; ++k)
+      for (int i = g0; i < g1; ++i) {
+        const auto& s = sents_k[k][order[i]];
+        if (s.empty()) die("source line with no words cannot be decoded");
+        flat_k[k].insert(flat_k[k].end(), s.begin(), s.end());
+        lens_k[k].push_back((int)s.size());
+      }
+    const std::vector<int>&flat = flat_k[0], &lens = lens_k[0];
     std::vector<int> ids((size_t)ng * num_hypotheses * Lmax), len((size_t)ng * num_hypotheses);
     std::vector<float> score((size_t)ng * num_hypotheses);
     std::vector<int> align(unk ? ids.size() : 0);
-    check_status(zrnn_beam_decode_batch_align(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses,
-                                              (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
-                                              ids.data(), len.data(), score.data(), unk ? align.data() : nullptr),
-                 "decoding");
+    if (K == 1) {
+      check_status(zrnn_beam_decode_batch_align(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses,
+                                                (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
+                                                ids.data(), len.data(), score.data(), unk ? align.data() : nullptr),
+                   "decoding");
+    } else {
+      std::vector<const int*> fp(K), lp(K);
+      for (int k = 0; k < K; ++k) { fp[k] = flat_k[k].data(); lp[k] = lens_k[k].data(); }
+      check_status(zrnn_beam_decode_ensemble(models.data(), K, fp.data(), lp.data(), ng, p.beam, num_hypotheses,
+                                             (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
+                                             ids.data(), len.data(), score.data()), "ensemble decoding");
+    }
     for (int i = 0; i < ng; ++i) {
       const size_t dst = (size_t)order[g0 + i] * num_hypotheses;
       for (int h = 0; h < num_hypotheses; ++h) {
@@ -555,7 +580,7 @@ int run_decode(const Options& opt, Params& p) {
   if (!zrnn::text::unint_file(vocab, int_out, final_file, true, &err)) die(err);
   logger << std::setprecision(6) << "Decoded " << n << " sentences in " << sec << " seconds (" << (double)out_words / sec
          << " output words per second)\n";
-  zrnn_model_destroy(model);
+  for (zrnn_model* m : models) zrnn_model_destroy(m);
   return 0;
 }
 
@@ -564,7 +589,8 @@ void print_help() {
       "B200 inference front end for Zoph_RNN models.\n"
       "  -f, --force-decode <source file> <target file> <model.nn> <output file>\n"
       "        with -s: <target file> <model.nn> <output file>; one sum of ln p per minibatch, perplexity to the log\n"
-      "  -k, --decode <how many outputs> <model.nn> <output file>  with  --decode-main-data-files <source file>\n"
+      "  -k, --decode <how many outputs> <model.nn> [<model.nn> ...] <output file>\n"
+      "        with --decode-main-data-files <source file> [<source file> ...], one per model (ensemble decoding)\n"
       "  -s, --sequence          the model is a sequence (language) model\n"
       "  -b, --beam-size N       beam size for --decode (default 12)\n"
       "  -p, --penalty X         word penalty added per target word for --decode (default 0)\n"

@@ -1760,6 +1760,58 @@ int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* s
   return ZRNN_OK;
 }
 
+int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int* const* src_ids,
+                              const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
+                              float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
+                              float* out_score) {
+  ZR_CHECK(models && src_ids && src_len && out_ids && out_len && out_score, "beam_decode_ensemble: null argument");
+  ZR_CHECK(n_models >= 1 && n_models <= ZR_ENSEMBLE_MAX, "beam_decode_ensemble: between 1 and 8 models");
+  ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode_ensemble: bad sizes");
+  if (n_sent == 0) return ZRNN_OK;
+  const int Lmax = longest_sent + 4;
+  const size_t nO = (size_t)n_sent * k_best;
+  cudaStream_t s = models[0] ? models[0]->stream : nullptr;
+  std::vector<const int*> d_src(n_models);
+  std::vector<int> S_max(n_models, 0);
+  int *d_ids = nullptr, *d_len = nullptr;
+  float* d_sc = nullptr;
+  for (int k = 0; k < n_models; ++k) {
+    zrnn_model* m = models[k];
+    ZR_CHECK(m && src_ids[k] && src_len[k], "beam_decode_ensemble: null argument");
+    for (int i = 0; i < n_sent; ++i) {
+      ZR_CHECK(src_len[k][i] >= 1, "beam_decode_ensemble: empty source sentence");
+      S_max[k] = std::max(S_max[k], src_len[k][i]);
+    }
+    // pad on the host into the reference's minibatch layout: time-major, left-padded with -1
+    std::vector<int> padded((size_t)S_max[k] * n_sent, -1);
+    size_t pos = 0;
+    for (int i = 0; i < n_sent; ++i) {
+      for (int t = 0; t < src_len[k][i]; ++t)
+        padded[(size_t)(S_max[k] - src_len[k][i] + t) * n_sent + i] = src_ids[k][pos + t];
+      pos += src_len[k][i];
+    }
+    size_t bytes = aligned(sizeof(int) * padded.size());
+    if (k == 0) bytes += aligned(sizeof(int) * nO * Lmax) + aligned(sizeof(int) * nO) + aligned(sizeof(float) * nO);
+    ZR_CUDA(m->io.reserve(bytes));
+    Carver cv(m->io.p);
+    int* dst = cv.take<int>(padded.size());
+    if (k == 0) { d_ids = cv.take<int>(nO * Lmax); d_len = cv.take<int>(nO); d_sc = cv.take<float>(nO); }
+    // pageable source: the copy has left `padded` when the call returns
+    ZR_CUDA(cudaMemcpyAsync(dst, padded.data(), sizeof(int) * padded.size(), cudaMemcpyHostToDevice, s));
+    ZR_CUDA(cudaStreamSynchronize(s));
+    d_src[k] = dst;
+  }
+  ZR_TRY(beam_decode_core(models, n_models, d_src.data(), src_len[0], S_max.data(), n_sent, beam, k_best, min_ratio,
+                          max_ratio, penalty, longest_sent, d_ids, d_len, d_sc, nullptr, s));
+  ZR_CUDA(cudaMemcpyAsync(out_ids, d_ids, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaStreamSynchronize(s));
+  const int code = zrnn_tc_error();
+  if (code != 0) return fail(ZRNN_E_TIMEOUT, "beam_decode_ensemble: a bounded device wait gave up (role " + std::to_string(code) + ")");
+  return ZRNN_OK;
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------------
