@@ -103,6 +103,20 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
   v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
   v[4] = __uint_as_float(r4); v[5] = __uint_as_float(r5); v[6] = __uint_as_float(r6); v[7] = __uint_as_float(r7);
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -170,10 +184,10 @@ __device__ __forceinline__ float act_sigmoid(float x) {
 
 constexpr int kABytes = 128 * 128;  // A tile: 128 rows x 128-byte k-block
 __host__ __device__ constexpr int stage_bytes(int BN, int mode) { return (mode == TC_TF32X3 ? 2 : 1) * (kABytes + BN * 128); }
-// bytes of the split-K exchange slots: SPLITK slots of 128 rows x (BN/SPLITK + 4) floats.  They must not overlap
+// bytes of the split-K exchange slots: SPLITK slots of (BN/SPLITK)/4 x 128 rows of float4.  They must not overlap
 // the stage ring: a peer that finishes its main loop early pushes into them while this CTA may still be loading.
 __host__ __device__ constexpr int slot_bytes(int BN, int splitk) {
-  return splitk > 1 ? splitk * 128 * (BN / splitk + 4) * 4 : 0;
+  return splitk > 1 ? splitk * 128 * (BN / splitk) * 4 : 0;
 }
 __host__ __device__ constexpr int num_stages(int BN, int mode, int splitk = 1) {
   int s = (225 * 1024 - 1024 - slot_bytes(BN, splitk)) / stage_bytes(BN, mode);
@@ -245,8 +259,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   constexpr int NACC = num_acc(BN, MODE);
   constexpr int TMEM_COLS = tmem_cols(BN, MODE);
   constexpr int OWNC = BN / SPLITK;  // columns finished by each CTA of the cluster
-  constexpr int PLD = OWNC + 4;      // padded row stride (floats) of a slot: conflict-free 16-byte accesses
-  static_assert(SPLITK == 1 || SPLITK * PLD * 128 * 4 == slot_bytes(BN, SPLITK), "slot size mismatch");
+  static_assert(SPLITK == 1 || SPLITK * OWNC * 128 * 4 == slot_bytes(BN, SPLITK), "slot size mismatch");
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[ST];
   __shared__ __align__(8) uint64_t empty_bar[ST];
@@ -403,29 +416,60 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
     }
     tmem_wait_ld();
   };
-  // slots[q][row][PLD]: contribution of cluster rank q to this CTA's columns (split-K only), placed after the ring.
-  // Column order inside a slot: LSTM -> gate*TH_OWN + j (this CTA's hidden units, all four gates); otherwise the
-  // CTA's OWNC consecutive columns.
-  float* slots = reinterpret_cast<float*>(tiles + (size_t)ST * STAGE);
+  // the same for 32 columns with one wait per accumulator (the split-K exchange reads the whole tile)
+  auto load32_tmem = [&](int col, float* v) {
+    if (total_kb == 0) {
+#pragma unroll
+      for (int u = 0; u < 32; ++u) v[u] = 0.f;
+      return;
+    }
+    tmem_ld32(taddr + col, v);
+    if (MODE == TC_TF32X3) {
+      float t[32];
+      for (int a = 1; a < n_main; ++a) {
+        tmem_ld32(taddr + a * BN + col, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 32; ++u) v[u] += t[u];
+      }
+      tmem_ld32(taddr + NACC * BN + col, t);
+      tmem_wait_ld();
+#pragma unroll
+      for (int u = 0; u < 32; ++u) v[u] += t[u];
+    }
+    tmem_wait_ld();
+  };
+  // slots[q][c4][row] (float4 units): contribution of cluster rank q to this CTA's columns (split-K only), placed
+  // after the ring.  Rows are the fastest index, so the 32 lanes of a warp push 512 contiguous bytes per remote store
+  // and read back without bank conflicts.  Column order inside a slot: LSTM -> gate*TH_OWN + j (this CTA's hidden
+  // units, all four gates); otherwise the CTA's OWNC consecutive columns.
+  float4* slots = reinterpret_cast<float4*>(tiles + (size_t)ST * STAGE);
   if (SPLITK > 1) {
     if (epi_warp && ready) {
-      const uint32_t my_slot = smem_u32(slots + ((size_t)rank * 128 + lrow) * PLD);
-      for (int c0 = 0; c0 < BN; c0 += 8) {
-        float v[8];
-        load8_tmem(c0, v);
-        int owner, lcol;
-        if (EPI == TC_EPI_LSTM) {
-          constexpr int TH = BN / 4, TH_OWN = TH / SPLITK;
-          const int gate = c0 / TH, j = c0 % TH;
-          owner = j / TH_OWN;
-          lcol = gate * TH_OWN + (j % TH_OWN);
-        } else {
-          owner = c0 / OWNC;
-          lcol = c0 % OWNC;
+      const uint32_t my_slot = smem_u32(slots + (size_t)rank * (OWNC / 4) * 128 + lrow);
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float v[32];
+        load32_tmem(c0, v);
+#pragma unroll
+        for (int u = 0; u < 32; u += 4) {
+          const int c = c0 + u;
+          int owner, lcol;
+          if (EPI == TC_EPI_LSTM) {
+            constexpr int TH = BN / 4, TH_OWN = TH / SPLITK;
+            const int gate = c / TH, j = c % TH;
+            owner = j / TH_OWN;
+            lcol = gate * TH_OWN + (j % TH_OWN);
+          } else {
+            owner = c / OWNC;
+            lcol = c % OWNC;
+          }
+          const uint32_t local = my_slot + (uint32_t)((lcol / 4) * 128 * 16);
+          if (owner == rank) {
+            slots[((size_t)rank * (OWNC / 4) + lcol / 4) * 128 + lrow] = make_float4(v[u], v[u + 1], v[u + 2], v[u + 3]);
+          } else {
+            st_cluster_v4(cluster_map(local, (uint32_t)owner), v[u], v[u + 1], v[u + 2], v[u + 3]);
+          }
         }
-        const uint32_t dst = cluster_map(my_slot + (uint32_t)(lcol * 4), (uint32_t)owner);
-        st_cluster_v4(dst, v[0], v[1], v[2], v[3]);
-        st_cluster_v4(dst + 16, v[4], v[5], v[6], v[7]);
       }
     }
     tc_fence_before();
@@ -442,8 +486,8 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       for (int u = 0; u < 8; ++u) v[u] = 0.f;
 #pragma unroll
       for (int q = 0; q < SPLITK; ++q) {
-        const float4* src = reinterpret_cast<const float4*>(slots + ((size_t)q * 128 + lrow) * PLD + col);
-        const float4 a = src[0], b = src[1];
+        const float4* src = slots + ((size_t)q * (OWNC / 4) + col / 4) * 128 + lrow;
+        const float4 a = src[0], b = src[128];
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
         v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
       }
@@ -551,8 +595,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   }
   tc_fence_before();
   ZR_STAMP(7);
-  if (SPLITK > 1) cluster_sync_all();  // nobody leaves while a peer may still read its partial tile
-  else __syncthreads();
+  // A CTA's shared memory is written by its peers only before the cluster barrier above and read by nobody else, so
+  // no second cluster barrier is needed before it retires.
+  __syncthreads();
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
@@ -566,20 +611,6 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
 // epilogue of tile i overlaps the main loop of tile i+1 and the load pipe never drains.
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 template <int BN, int MODE, int EPI>
