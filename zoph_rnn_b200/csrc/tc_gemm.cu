@@ -266,11 +266,26 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  // the tile's bias values, read by every epilogue thread for every column: staged once (a weight, so it does not
+  // wait for the predecessor kernel).  LSE: -inf beyond the last valid row, which removes the column from max / sum.
+  __shared__ float s_bias[BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   const int m0 = blockIdx.x * 128;
   const int n_tile = blockIdx.y;
+  for (int i = threadIdx.x; i < BN; i += blockDim.x) {
+    float bv;
+    if (EPI == TC_EPI_LSTM) {
+      constexpr int TH = BN / 4;
+      const int hid = n_tile * TH + (i % TH);
+      bv = hid < p.N ? p.bias[(i / TH) * p.N + hid] : 0.f;
+    } else {
+      const int n = n_tile * BN + i;
+      bv = n < p.N ? (p.bias ? p.bias[n] : 0.f) : (EPI == TC_EPI_LSE ? -INFINITY : 0.f);
+    }
+    s_bias[i] = bv;
+  }
   const int rank = SPLITK > 1 ? (int)blockIdx.z : 0;  // cluster dims (1,1,SPLITK): rank in cluster == blockIdx.z
   int all_kb = 0;
   for (int s = 0; s < p.nsrc; ++s) all_kb += p.kblocks[s];
@@ -368,7 +383,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   const int lrow = warp * 32 + lane;
   const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   // the LSTM epilogue's global operands do not depend on the accumulators: fetch them while the main loop runs
-  float pre_c[8], pre_b[4][8];
+  float pre_c[8];
   if constexpr (EPI == TC_EPI_LSTM) {
     constexpr int TH = BN / 4;
     constexpr int TH_OWN = TH / SPLITK;
@@ -380,8 +395,6 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         const int hid = hidb + u;
         const bool okh = hid < H;
         pre_c[u] = (okh && row < p.M) ? p.c_prev[(size_t)row * H + hid] : 0.f;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) pre_b[q][u] = okh ? p.bias[q * H + hid] : 0.f;
       }
     }
   }
@@ -516,10 +529,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
           for (int u = 0; u < 8; ++u) {
             const int hid = hb + u;
             const bool okh = u < nvalid;
-            const float b0 = pf ? pre_b[0][u] : (okh ? p.bias[hid] : 0.f);
-            const float b1 = pf ? pre_b[1][u] : (okh ? p.bias[H + hid] : 0.f);
-            const float b2 = pf ? pre_b[2][u] : (okh ? p.bias[2 * H + hid] : 0.f);
-            const float b3 = pf ? pre_b[3][u] : (okh ? p.bias[3 * H + hid] : 0.f);
+            const float b0 = s_bias[j0 + u], b1 = s_bias[TH + j0 + u], b2 = s_bias[2 * TH + j0 + u], b3 = s_bias[3 * TH + j0 + u];
             const float cp = pf ? pre_c[u] : (okh ? p.c_prev[(size_t)row * H + hid] : 0.f);
             const float gi = act_sigmoid<MODE>(g[0][u] + b0);
             const float gf = act_sigmoid<MODE>(g[1][u] + b1);
@@ -551,7 +561,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int n = nb + u;
-            float t = v[u] + ((p.bias && u < nvalid) ? p.bias[n] : 0.f);
+            float t = v[u] + s_bias[c0 + u];
             if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
             x[u] = t * mk;
           }
@@ -572,10 +582,16 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
         float cm = -INFINITY;
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          const int n = n0 + c0 + u;
-          v[u] = (n < p.N) ? v[u] + (p.bias ? p.bias[n] : 0.f) : -INFINITY;
+          v[u] += s_bias[c0 + u];
           cm = fmaxf(cm, v[u]);
-          if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
+        }
+        const int rel = tg - (n0 + c0);
+        if ((unsigned)rel < 8u && tg < p.N) {  // the target's logit lies in this chunk (once per row at most)
+          float t = 0.f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (u == rel) t = v[u];
+          p.tgt_logit[row] = t;
         }
         if (cm > mx) {
           sm *= expf(mx - cm);  // expf(-inf) = 0 on the first chunk
@@ -634,6 +650,9 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  // bias values of the tile in flight, double-buffered over tiles: the 128 epilogue threads fill one buffer and meet
+  // at a named barrier, so a thread is never more than one tile ahead of the slowest reader
+  __shared__ __align__(16) float s_bias[2][BN];
   const int total_tiles = m_tiles * n_tiles;
   ZR_STAMP(0);
   int kb_per_tile = 0;
@@ -734,11 +753,17 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
       const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
       const int row = m_tile * 128 + warp * 32 + lane;
       const bool row_ok = row < p.M;
+      float* sb = s_bias[buf];  // filled while the accumulator is still being produced
+      for (int i = threadIdx.x; i < BN; i += 128) {
+        const int n = n_tile * BN + i;
+        sb[i] = n < p.N ? (p.bias ? __ldg(p.bias + n) : 0.f) : (EPI == TC_EPI_LSE ? -INFINITY : 0.f);
+      }
       if (!mbar_wait(&acc_full[buf], (uint32_t)((ti >> 1) & 1), &abort_s, p.err, 3)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * ACC_COLS);
       const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
       const int n0 = n_tile * BN;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
       if constexpr (EPI == TC_EPI_STORE) {
         const bool want_max = p.part_max != nullptr;  // also emit the per-tile maximum of the stored values
         const bool want_lse = want_max && p.part_sum != nullptr;  // ... and sum exp(x - max)
@@ -762,7 +787,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               const int n = nb + u;
-              float t = v[u] + ((p.bias && u < nvalid) ? p.bias[n] : 0.f);
+              float t = v[u] + sb[c0 + u];
               if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
               x[u] = t * mk;
               if (u < nvalid) cm = fmaxf(cm, x[u]);
@@ -802,11 +827,18 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
           tmem_wait_ld();
           float cm = -INFINITY;
 #pragma unroll
-          for (int u = 0; u < 32; ++u) {
-            const int n = n0 + c0 + u;
-            v[u] = (n < p.N) ? v[u] + (p.bias ? __ldg(p.bias + n) : 0.f) : -INFINITY;
-            cm = fmaxf(cm, v[u]);
-            if (n == tg && n < p.N) p.tgt_logit[row] = v[u];
+          for (int u = 0; u < 32; u += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(sb + c0 + u);
+            v[u] += b4.x; v[u + 1] += b4.y; v[u + 2] += b4.z; v[u + 3] += b4.w;
+            cm = fmaxf(fmaxf(cm, fmaxf(v[u], v[u + 1])), fmaxf(v[u + 2], v[u + 3]));
+          }
+          const int rel = tg - (n0 + c0);
+          if ((unsigned)rel < 32u && tg < p.N) {  // the target's logit lies in this chunk (once per row at most)
+            float t = 0.f;
+#pragma unroll
+            for (int u = 0; u < 32; ++u)
+              if (u == rel) t = v[u];
+            p.tgt_logit[row] = t;
           }
           if (cm > mx) {
             sm *= expf(mx - cm);
