@@ -433,57 +433,86 @@ cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, c
 }
 
 // ------------------------------------------------------------------------------------------
-// combine per-tile softmax partials: one thread per column
+// combine per-tile softmax partials.  A CTA of 32 x 8 threads handles 32 consecutive columns: thread (cx, py) walks
+// over parts py, py + 8, ... of column cx (coalesced over cx), the 8 partial results per column meet in shared memory.
+// exp in float, accumulation and the final log in double.
 // ------------------------------------------------------------------------------------------
-__global__ void lse_combine_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
-                                   const float* __restrict__ tgt, int n_parts, int n_tgt, int N,
-                                   const int* __restrict__ mask, float* __restrict__ logp) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
-  if (mask && mask[n] != 1) { logp[n] = 0.f; return; }
+__device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, const float* __restrict__ ps,
+                                                  int n_parts, int N, int n, bool active, float* s_m /*[8][32]*/,
+                                                  double* s_s /*[8][32]*/, float* mx_out, double* sum_out) {
+  const int cx = threadIdx.x, py = threadIdx.y;
   float mx = -INFINITY;
-  for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, pm[(size_t)i * N + n]);
+  if (active)
+    for (int i = py; i < n_parts; i += 8) mx = fmaxf(mx, pm[(size_t)i * N + n]);
+  s_m[py * 32 + cx] = mx;
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < 8; ++q) mx = fmaxf(mx, s_m[q * 32 + cx]);
   double sum = 0.0;
-  for (int i = 0; i < n_parts; ++i) {
-    const float m = pm[(size_t)i * N + n];
-    if (m != -INFINITY) sum += (double)ps[(size_t)i * N + n] * exp((double)m - (double)mx);
+  if (active)
+    for (int i = py; i < n_parts; i += 8) {
+      const float m = pm[(size_t)i * N + n];
+      if (m != -INFINITY) sum += (double)(ps[(size_t)i * N + n] * expf(m - mx));
+    }
+  s_s[py * 32 + cx] = sum;
+  __syncthreads();
+  if (py == 0) {
+    sum = 0.0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) sum += s_s[q * 32 + cx];
   }
+  *mx_out = mx;
+  *sum_out = sum;
+}
+__global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
+                                                           const float* __restrict__ tgt, int n_parts, int n_tgt, int N,
+                                                           const int* __restrict__ mask, float* __restrict__ logp) {
+  __shared__ float s_m[8 * 32];
+  __shared__ double s_s[8 * 32];
+  const int n = blockIdx.x * 32 + threadIdx.x;
+  const bool in = n < N;
+  const bool active = in && !(mask && mask[n] != 1);
+  float mx;
+  double sum;
+  lse_column_reduce(pm, ps, n_parts, N, n, active, s_m, s_s, &mx, &sum);
+  if (threadIdx.y != 0 || !in) return;
+  if (!active) { logp[n] = 0.f; return; }
   double tg = 0.0;
   for (int i = 0; i < n_tgt; ++i) tg += (double)tgt[(size_t)i * N + n];
   logp[n] = (float)((tg - (double)mx) - log(sum));
 }
-__global__ void lse_reduce_kernel(const float* __restrict__ pm, const float* __restrict__ ps, int n_parts, int N,
-                                  float* __restrict__ out_max, float* __restrict__ out_sum) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
-  float mx = -INFINITY;
-  for (int i = 0; i < n_parts; ++i) mx = fmaxf(mx, pm[(size_t)i * N + n]);
-  double sum = 0.0;
-  for (int i = 0; i < n_parts; ++i) {
-    const float m = pm[(size_t)i * N + n];
-    if (m != -INFINITY) sum += (double)ps[(size_t)i * N + n] * exp((double)m - (double)mx);
-  }
+__global__ void __launch_bounds__(256) lse_reduce_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
+                                                          int n_parts, int N, float* __restrict__ out_max,
+                                                          float* __restrict__ out_sum) {
+  __shared__ float s_m[8 * 32];
+  __shared__ double s_s[8 * 32];
+  const int n = blockIdx.x * 32 + threadIdx.x;
+  const bool in = n < N;
+  float mx;
+  double sum;
+  lse_column_reduce(pm, ps, n_parts, N, n, in, s_m, s_s, &mx, &sum);
+  if (threadIdx.y != 0 || !in) return;
   out_max[n] = mx;
   out_sum[n] = (float)sum;
 }
 cudaError_t launch_lse_reduce(const float* pm, const float* ps, int n_parts, int N, float* out_max, float* out_sum,
                               cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_reduce_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, n_parts, N, out_max, out_sum);
+  lse_reduce_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, n_parts, N, out_max, out_sum);
   count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_lse_combine_shards(const float* pm, const float* ps, const float* tgt, int G, int N, const int* mask,
                                       float* logp, cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, tgt, G, G, N, mask, logp);
+  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, G, G, N, mask, logp);
   count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tgt, int n_parts, int N, const int* mask,
                                float* logp, cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 127) / 128, 128, 0, st>>>(pm, ps, tgt, n_parts, 1, N, mask, logp);
+  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, n_parts, 1, N, mask, logp);
   count_launch();
   return cudaGetLastError();
 }
