@@ -136,7 +136,13 @@ __global__ void pack_weights_kernel(const PackArgs a) {
     const int hid = tile * a.TH + j;
     const float v = hid < a.H ? a.src[g][(size_t)k * a.lda + hid] : 0.f;
     const size_t prow = (size_t)tile * rows_per_tile + (size_t)g * a.TH + j;
-    store_op(a.dst_hi, a.dst_lo, a.op_mode, prow * a.ld_dst + a.koff + k, v);
+    size_t at = prow * a.ld_dst + a.koff + k;
+    if (a.tiled_kbtot > 0) {
+      const int kk = a.koff + k;
+      at = (((size_t)tile * a.tiled_kbtot + kk / a.tiled_epk) * rows_per_tile + (size_t)g * a.TH + j) * a.tiled_epk +
+           kk % a.tiled_epk;
+    }
+    store_op(a.dst_hi, a.dst_lo, a.op_mode, at, v);
   }
 }
 cudaError_t launch_pack_weights(const PackArgs& a, cudaStream_t st) {

@@ -169,6 +169,10 @@ struct PackArgs {
   void* dst_hi;
   float* dst_lo;
   int op_mode, ld_dst, koff;
+  // tile-contiguous destination (tiled_kbtot > 0): element (packed row r, K index kk = koff + k) goes to
+  // (((r / rows_per_tile) * tiled_kbtot + kk / epk) * rows_per_tile + r % rows_per_tile) * epk + kk % epk,
+  // i.e. every (row tile, 128-byte k-block) box of the GEMM is one contiguous chunk of memory; ld_dst is unused.
+  int tiled_kbtot, tiled_epk;
 };
 cudaError_t launch_pack_weights(const PackArgs& a, cudaStream_t st);
 // Converts `rows` K-major rows (fp32, stride ld_src) into operand form at dst[r*ld_dst + k].

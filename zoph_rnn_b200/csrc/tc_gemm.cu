@@ -331,11 +331,14 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
           uint8_t* base = tiles + (size_t)st * STAGE;
           mbar_expect_tx(&full_bar[st], (uint32_t)STAGE);
           const int kx = kb * (MODE == TC_BF16 ? 64 : 32);
+          constexpr int EPK = MODE == TC_BF16 ? 64 : 32;  // elements per 128-byte k-block
+          const int bx = p.b_tiled_kbtot > 0 ? 0 : p.b_koff[s] + kx;
+          const int by = p.b_tiled_kbtot > 0 ? (n_tile * p.b_tiled_kbtot + (p.b_koff[s] + kx) / EPK) * BN : n_tile * BN;
           tma_load_2d(base, &p.a[s], &full_bar[st], kx, m0);
-          tma_load_2d(base + kABytes, &p.b, &full_bar[st], p.b_koff[s] + kx, n_tile * BN);
+          tma_load_2d(base + kABytes, &p.b, &full_bar[st], bx, by);
           if (MODE == TC_TF32X3) {
             tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
-            tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], p.b_koff[s] + kx, n_tile * BN);
+            tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], bx, by);
           }
           ++it;
         }

@@ -21,6 +21,9 @@ struct TcParams {
   int nsrc;
   int kblocks[3];  // 128-byte k-blocks per source
   int b_koff[3];   // element offset of each source inside B's K axis
+  // > 0: B is stored tile-contiguously (k-blocks per row tile): the box of (row tile n, k-block kb) is the
+  // rows [(n * b_tiled_kbtot + kb) * BN, + BN) of a 128-byte-wide 2-D array (tc_gemm_kernel only)
+  int b_tiled_kbtot;
   int M;           // batch columns
   int N;           // STORE / LSE: output rows; LSTM: hidden size H (B holds 4H packed rows)
   const float* bias;  // STORE / LSE: [N]; LSTM: [4][H] gate-major (i,f,g,o)

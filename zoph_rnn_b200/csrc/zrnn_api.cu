@@ -219,6 +219,7 @@ struct zrnn_lstm_layer {
   DevBuf x;             // gather scratch for zrnn_ih_forward
   // tensor-core form: packed [n_tiles*BN rows] x [nsrc*Kpad] with the K axis = (x | h | htild)
   int Kpad = 0, BN = 128, n_tiles = 0;
+  int kbtot = 0;  // > 0: weights stored tile-contiguously with this many k-blocks per row tile
   OpMem Wcat, emb;
   CUtensorMap wmap, wmap_lo;
   DevBuf sc_x, sc_h, sc_q, sc_xl, sc_hl, sc_ql;  // operand scratch for the fp32 layer-level entry points
@@ -260,6 +261,7 @@ struct zrnn_softmax {
   float* b = nullptr;  // hi-lo
   DevBuf parts, tgt, logits;
   int Kpad = 0, BN = 128, n_tiles = 0;
+  int kbtot = 0;  // > 0: weights stored tile-contiguously with this many k-blocks per row tile
   OpMem D_op;  // [n_tiles*BN rows x Kpad]
   CUtensorMap dmap, dmap_lo;
   DevBuf sc_h, sc_hl;
@@ -367,7 +369,7 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
     tp.nsrc = 3;
   }
   for (int s = 0; s < 3; ++s) { tp.kblocks[s] = kb; tp.b_koff[s] = s * Kpad; }
-  tp.b = L->wmap; tp.b_lo = L->wmap_lo;
+  tp.b = L->wmap; tp.b_lo = L->wmap_lo; tp.b_tiled_kbtot = L->kbtot;
   tp.M = B; tp.N = H; tp.bias = L->b; tp.mask = mask;
   tp.C = out.f32; tp.ldc = H;
   tp.op_b16 = eng == ENG_BF16 ? (__nv_bfloat16*)out.hi : nullptr;
@@ -552,12 +554,13 @@ int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, i
 
 // pack G column-major (rows x K) matrices into operand form at K offset koff
 int pack_into(OpMem& dst, int eng, const float* const* src, int G, int rows, int K, int lda, int TH, int n_tiles,
-              int ld_dst, int koff) {
+              int ld_dst, int koff, int tiled_kbtot = 0) {
   zrnn::PackArgs pk;
   std::memset(&pk, 0, sizeof(pk));
   for (int g = 0; g < G; ++g) pk.src[g] = src[g];
   pk.G = G; pk.H = rows; pk.K = K; pk.lda = lda; pk.TH = TH; pk.n_tiles = n_tiles;
   pk.dst_hi = dst.hi; pk.dst_lo = dst.lo; pk.op_mode = eng_opmode(eng); pk.ld_dst = ld_dst; pk.koff = koff;
+  pk.tiled_kbtot = tiled_kbtot; pk.tiled_epk = 128 / eng_eb(eng);
   ZR_CUDA(zrnn::launch_pack_weights(pk, nullptr));
   return ZRNN_OK;
 }
@@ -752,12 +755,18 @@ int zrnn_lstm_load(zrnn_lstm_layer* L, const float* const* t, int n) {
     L->n_tiles = (H + TH - 1) / TH;
     const long long rows = (long long)L->n_tiles * L->BN, Kcat = (long long)nsrc * Kpad;
     ZR_TRY(L->Wcat.alloc((size_t)rows * Kcat, L->eng));
+    // Tile-contiguous storage: the 128 rows x 128 bytes a CTA fetches per k-block are one 16 KB chunk of memory
+    // instead of 128 pieces that lie a whole row (8-12 KB) apart, so the weight stream reads whole DRAM pages.
+    static const bool tiled = std::getenv("ZRNN_WEIGHT_ROWMAJOR") == nullptr;
+    const int epk = 128 / eng_eb(L->eng);
+    L->kbtot = tiled ? (int)(Kcat / epk) : 0;
     const float* srcs[3] = {L->Mx, L->Wh, L->Q};
     for (int s = 0; s < nsrc; ++s) {
       const float* g4[4] = {srcs[s], srcs[s] + HH, srcs[s] + 2 * HH, srcs[s] + 3 * HH};
-      ZR_TRY(pack_into(L->Wcat, L->eng, g4, 4, H, H, H, TH, L->n_tiles, (int)Kcat, s * Kpad));
+      ZR_TRY(pack_into(L->Wcat, L->eng, g4, 4, H, H, H, TH, L->n_tiles, (int)Kcat, s * Kpad, L->kbtot));
     }
-    ZR_TRY(weight_maps(L->Wcat, L->eng, Kcat, rows, L->BN, &L->wmap, &L->wmap_lo));
+    if (tiled) ZR_TRY(weight_maps(L->Wcat, L->eng, epk, rows * L->kbtot, L->BN, &L->wmap, &L->wmap_lo));
+    else ZR_TRY(weight_maps(L->Wcat, L->eng, Kcat, rows, L->BN, &L->wmap, &L->wmap_lo));
     if (L->is_ih) {
       ZR_TRY(L->emb.alloc((size_t)L->V * Kpad, L->eng));
       ZR_CUDA(zrnn::launch_convert_rows(L->W, L->V, H, H, eng_opmode(L->eng), L->emb.hi, L->emb.lo, Kpad, nullptr));
