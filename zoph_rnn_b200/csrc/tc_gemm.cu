@@ -189,9 +189,16 @@ __host__ __device__ constexpr int stage_bytes(int BN, int mode) { return (mode =
 __host__ __device__ constexpr int slot_bytes(int BN, int splitk) {
   return splitk > 1 ? splitk * 128 * (BN / splitk) * 4 : 0;
 }
+// 3xTF32 stages are twice as large (hi + lo parts), and with exchange slots of their own only two would fit, too few
+// bytes in flight to keep HBM busy.  In that mode the slots alias the ring instead, which costs one more cluster
+// barrier (nobody may push into a peer's ring before that peer's MMAs have consumed it).
+__host__ __device__ constexpr bool slots_alias_ring(int mode, int splitk) { return mode == TC_TF32X3 && splitk > 1; }
 __host__ __device__ constexpr int num_stages(int BN, int mode, int splitk = 1) {
-  int s = (225 * 1024 - 1024 - slot_bytes(BN, splitk)) / stage_bytes(BN, mode);
+  int s = (225 * 1024 - 1024 - (slots_alias_ring(mode, splitk) ? 0 : slot_bytes(BN, splitk))) / stage_bytes(BN, mode);
   return s > 8 ? 8 : s;
+}
+__host__ __device__ constexpr int smem_bytes(int BN, int mode, int splitk) {
+  return num_stages(BN, mode, splitk) * stage_bytes(BN, mode) + (slots_alias_ring(mode, splitk) ? 0 : slot_bytes(BN, splitk)) + 1024;
 }
 
 // 3xTF32 keeps fp32-level accuracy only if the tensor core's accumulator is not asked to absorb hundreds of
@@ -260,6 +267,8 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   constexpr int TMEM_COLS = tmem_cols(BN, MODE);
   constexpr int OWNC = BN / SPLITK;  // columns finished by each CTA of the cluster
   static_assert(SPLITK == 1 || SPLITK * OWNC * 128 * 4 == slot_bytes(BN, SPLITK), "slot size mismatch");
+  constexpr bool ALIAS = slots_alias_ring(MODE, SPLITK);
+  static_assert(!ALIAS || ST * STAGE >= slot_bytes(BN, SPLITK), "ring too small to hold the exchange slots");
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[ST];
   __shared__ __align__(8) uint64_t empty_bar[ST];
@@ -459,8 +468,13 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   // after the ring.  Rows are the fastest index, so the 32 lanes of a warp push 512 contiguous bytes per remote store
   // and read back without bank conflicts.  Column order inside a slot: LSTM -> gate*TH_OWN + j (this CTA's hidden
   // units, all four gates); otherwise the CTA's OWNC consecutive columns.
-  float4* slots = reinterpret_cast<float4*>(tiles + (size_t)ST * STAGE);
+  float4* slots = reinterpret_cast<float4*>(ALIAS ? tiles : tiles + (size_t)ST * STAGE);
   if (SPLITK > 1) {
+    if (ALIAS) {
+      // every CTA of the cluster is past its main loop (its ring is dead) before anybody pushes into it
+      tc_fence_before();
+      cluster_sync_all();
+    }
     if (epi_warp && ready) {
       const uint32_t my_slot = smem_u32(slots + (size_t)rank * (OWNC / 4) * 128 + lrow);
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -913,7 +927,7 @@ static const bool g_use_pdl = std::getenv("ZRNN_NO_PDL") == nullptr;
 
 template <int BN, int MODE, int EPI, int SPLITK>
 cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
-  const size_t smem = (size_t)num_stages(BN, MODE, SPLITK) * stage_bytes(BN, MODE) + slot_bytes(BN, SPLITK) + 1024;
+  const size_t smem = (size_t)smem_bytes(BN, MODE, SPLITK);
   static bool configured = false;  // once per instantiation (one device per process)
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, MODE, EPI, SPLITK>,
