@@ -771,9 +771,121 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
     att_store_op(a, b, i, acc);
   }
 }
+// Same arithmetic for H % 4 == 0, H <= 1024: 16-byte loads, and no data-dependent branch inside the loops over the
+// window, so the loads of all window slots are in flight together (the generic kernel waits for one L2 round trip
+// per slot).  An empty slot gets weight 0 and reads row 0 of the source memory.
+__global__ void __launch_bounds__(256) att_local_fast_kernel(const AttArgs a) {
+  __shared__ float red[32];
+  __shared__ float s_al[ZR_ATT_MAXW];
+  __shared__ int s_slot[ZR_ATT_MAXW];
+  __shared__ float s_p;
+  __shared__ int s_lo, s_hi;
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int H = a.H, H4 = H >> 2, Wn = 2 * a.D + 1, sb = b / a.cols_per_sent;
+  float* c = a.c_t + (size_t)b * H;
+  if (a.mask && a.mask[b] != 1) {
+    for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
+    if (a.align_out)
+      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
+    return;
+  }
+  float part = 0.f;
+  if (tid < H4) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(a.v_p) + tid);
+    const float4 t = reinterpret_cast<const float4*>(a.tanh1 + (size_t)b * a.ld_tq)[tid];
+    part = v.x * t.x + v.y * t.y + v.z * t.z + v.w * t.w;
+  }
+  const float tot = block_sum(part, red);
+  const int len = a.len[sb], off = a.offset[sb];
+  if (tid == 0) {
+    const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)tot)));
+    const float pt = len * sg;
+    const int ip = (int)pt;
+    s_p = pt;
+    s_lo = (0 > ip - a.D) ? 0 : (ip - a.D);
+    s_hi = ((len - 1) < ip + a.D) ? (len - 1) : (ip + a.D);
+  }
+  __syncthreads();
+  const int lo = s_lo, hi = s_hi;
+  const float4* q4 = reinterpret_cast<const float4*>(a.q + (size_t)b * a.ld_tq);
+  float4 qv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int j4 = lane + 32 * i;
+    qv[i] = j4 < H4 ? q4[j4] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int j = w; j < Wn; j += 8) {
+    const int pos = lo + j;
+    const bool valid = pos <= hi;
+    const int slot = valid ? len - 1 - pos + off : 0;  // an empty slot reads row 0 and is discarded
+    const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)slot * a.B_src + sb) * H);
+    float sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j4 = lane + 32 * i;
+      if (j4 < H4) {
+        const float4 r = __ldg(r4 + j4);
+        sc += r.x * qv[i].x + r.y * qv[i].y + r.z * qv[i].z + r.w * qv[i].w;
+      }
+    }
+    sc = warp_sum(sc);
+    if (lane == 0) { s_al[j] = valid ? sc : 0.f; s_slot[j] = valid ? slot : -1; }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float sum = 0.f, mx = 0.f;  // the reference starts the max at 0
+    for (int j = 0; j < Wn; ++j)
+      if (s_slot[j] != -1 && s_al[j] > mx) mx = s_al[j];
+    for (int j = 0; j < Wn; ++j) {
+      if (s_slot[j] != -1) { s_al[j] = expf(s_al[j] - mx); sum += s_al[j]; }
+      else s_al[j] = 0.f;
+    }
+    const float sigma_sq = (float)((a.D * a.D) / 4.0);
+    for (int j = 0; j < Wn; ++j) {
+      if (s_slot[j] != -1) {
+        const float d = s_p - (float)(lo + j);
+        const float gs = expf((-1.f * d * d) / (2.f * sigma_sq));
+        if (sum != 0.f) s_al[j] = (s_al[j] / sum) * gs;
+      }
+    }
+    if (a.viterbi_out) {
+      float best = a.viterbi_init;
+      int best_pos = -1;
+      for (int j = 0; j < Wn; ++j)
+        if (best < s_al[j]) { best = s_al[j]; best_pos = (s_slot[j] != -1) ? lo + j : -1; }
+      a.viterbi_out[b] = best_pos;
+    }
+    for (int j = 0; j < Wn; ++j)
+      if (s_slot[j] == -1) s_slot[j] = 0;  // weight 0, any readable row
+  }
+  __syncthreads();
+  if (a.align_out)
+    for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+  if (tid < H4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const size_t colb = (size_t)sb * H;
+#pragma unroll 7
+    for (int j = 0; j < Wn; ++j) {
+      const float wj = s_al[j];
+      const float4 r = __ldg(reinterpret_cast<const float4*>(a.hs + (size_t)s_slot[j] * a.B_src * H + colb) + tid);
+      acc.x += wj * r.x; acc.y += wj * r.y; acc.z += wj * r.z; acc.w += wj * r.w;
+    }
+    reinterpret_cast<float4*>(c)[tid] = acc;
+    att_store_op(a, b, 4 * tid + 0, acc.x);
+    att_store_op(a, b, 4 * tid + 1, acc.y);
+    att_store_op(a, b, 4 * tid + 2, acc.z);
+    att_store_op(a, b, 4 * tid + 3, acc.w);
+  }
+}
 cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st) {
   if (a.B <= 0) return cudaSuccess;
   if (2 * a.D + 1 > ZR_ATT_MAXW) return cudaErrorInvalidValue;
+  if ((a.H & 3) == 0 && a.H <= 1024 && (a.ld_tq & 3) == 0) {
+    att_local_fast_kernel<<<a.B, 256, 0, st>>>(a);
+    count_launch();
+    return cudaGetLastError();
+  }
   att_local_kernel<<<a.B, 256, 0, st>>>(a);
   count_launch();
   return cudaGetLastError();
