@@ -88,28 +88,39 @@ struct KTiming {
   bool on = false;
   std::vector<cudaEvent_t> ev;  // pairs
   std::vector<int> cls;
-  size_t used = 0;  // pairs in use
+  std::vector<int> cnt;  // launches covered by the pair
+  size_t used = 0;       // pairs in use
+  int group_cls = -1;    // a group scope of this class is open: its inner scopes do not record
 };
 thread_local KTiming g_kt;
 const size_t KT_CAP = 16384;
+// One event pair around a launch, or (group = true) around `launches` back-to-back launches of one class, so that
+// the per-launch average includes the overlap between consecutive launches and not one event pair's cost each.
 struct KScope {
   long idx = -1;
   cudaStream_t s;
-  KScope(int c, cudaStream_t st) : s(st) {
+  bool group;
+  KScope(int c, cudaStream_t st, int launches = 1, bool grp = false) : s(st), group(grp) {
     if (!g_kt.on || g_kt.used >= KT_CAP) return;
+    if (!grp && g_kt.group_cls == c) return;
     if (g_kt.ev.size() < 2 * (g_kt.used + 1)) {
       cudaEvent_t a, b;
       if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
       g_kt.ev.push_back(a);
       g_kt.ev.push_back(b);
       g_kt.cls.push_back(c);
+      g_kt.cnt.push_back(1);
     }
     idx = (long)g_kt.used++;
     g_kt.cls[idx] = c;
+    g_kt.cnt[idx] = launches;
+    if (grp) g_kt.group_cls = c;
     cudaEventRecord(g_kt.ev[2 * idx], s);
   }
   ~KScope() {
-    if (idx >= 0) cudaEventRecord(g_kt.ev[2 * idx + 1], s);
+    if (idx < 0) return;
+    cudaEventRecord(g_kt.ev[2 * idx + 1], s);
+    if (group) g_kt.group_cls = -1;
   }
 };
 
@@ -691,7 +702,7 @@ int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total
     ZR_CUDA(cudaEventSynchronize(g_kt.ev[2 * i + 1]));
     float ms = 0.f;
     ZR_CUDA(cudaEventElapsedTime(&ms, g_kt.ev[2 * i], g_kt.ev[2 * i + 1]));
-    *launches += 1;
+    *launches += g_kt.cnt[i];
     *total_ms += ms;
   }
   return ZRNN_OK;
@@ -1266,6 +1277,7 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
   // Layer by layer, not step by step: layer l only needs layer l-1's finished sequence, and running all S steps
   // of one layer back to back keeps that layer's weights resident in the 126 MB L2 (all layers together do not fit).
   for (int l = 0; l < L; ++l) {
+    KScope sweep(KC_LSTM, s, S, true);
     for (int t = 0; t < S; ++t) {
       const Act x = l == 0 ? act_at(X0, (size_t)t * B, g) : act_at(seq[l - 1], (size_t)t * B, g);
       const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
