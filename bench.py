@@ -439,7 +439,9 @@ NCU_TRAFFIC = {("lstm_cell", "f32"): 71.7e6, ("lstm_cell", "bf16"): 17.9e6}
 
 def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
     """Roofline of the dominant kernel class.  Durations are CUDA-event pairs around every launch of the class in
-    the instrumented pass; algorithmic bytes / flops per launch follow DESIGN.md section 3."""
+    the instrumented pass (one pair per encoder layer sweep).  Algorithmic bytes per LSTM cell launch: the layer's
+    H x H weight matrices as stored (4 or 2 bytes each) plus 5 H x B fp32 activations; flops of the softmax GEMM:
+    2 V H N."""
     if not ktime:
         return None
     top = max(ktime, key=lambda k: ktime[k]["ms"])
