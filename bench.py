@@ -118,6 +118,14 @@ def sample_clocks_stop(proc, f, path, gpu_index):
     return out
 
 
+def host_cores():
+    """Host threads this process may use."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference(args, w, rank):
     """CPU arm: the oracle (a port of the reference's kernel math; the reference itself cannot be built
     for this machine) on a bounded sample of the workload, all host threads."""
@@ -129,6 +137,7 @@ def run_reference(args, w, rank):
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
     om = ol.OracleModel(cfg, weights)
     ol.set_acc_float(True)  # float accumulation = the reference's SGEMM arithmetic
+    ol.set_num_threads(host_cores())  # launchers such as torchrun export OMP_NUM_THREADS=1
     cores = ol.num_threads()
     if w["kind"] == "decode":
         Bs = 1
@@ -179,6 +188,7 @@ def cpu_baseline(w):
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
     om = ol.OracleModel(cfg, weights)
     ol.set_acc_float(True)
+    ol.set_num_threads(host_cores())
     if w["kind"] == "decode":
         inp = make_inputs(w, 1234, B=1)
         t0 = time.perf_counter()

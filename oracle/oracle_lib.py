@@ -239,3 +239,8 @@ def set_acc_float(on):
 
 def num_threads():
     return lib().orc_num_threads()
+
+
+def set_num_threads(n):
+    """Number of OpenMP threads the oracle's GEMMs use (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().orc_set_num_threads(int(n))

@@ -678,6 +678,14 @@ void beam_decode_one(const std::vector<const Model*>& models, const std::vector<
 extern "C" {
 
 void orc_set_acc_float(int on) { g_acc_float = on != 0; }
+// n <= 0: leave the OpenMP default (OMP_NUM_THREADS or the core count)
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
 int orc_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
