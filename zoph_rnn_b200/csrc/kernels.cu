@@ -6,6 +6,8 @@
 
 #include <cfloat>
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 
 namespace zrnn {
 
@@ -32,6 +34,32 @@ __device__ __forceinline__ void att_store_op(const AttArgs& a, int b, int i, flo
     a.op_hi[idx] = hi;
     if (a.op_lo) a.op_lo[idx] = v - hi;
   }
+}
+
+// Programmatic dependent launch for the kernels that sit between tensor-core launches on the scoring / decoding
+// chain: the kernel may be scheduled while its predecessor drains (the launch latency disappears from the chain),
+// waits for the predecessor's results with griddepcontrol.wait before touching them, and at once allows its own
+// successor to be scheduled (that one waits the same way).
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+static const bool g_pdl = std::getenv("ZRNN_NO_PDL") == nullptr;
+template <class... KArgs, class... Args>
+static cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // block-wide sum; result valid in every thread. `red` needs 32 floats.
@@ -691,6 +719,7 @@ cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* va
 // ------------------------------------------------------------------------------------------
 #define ZR_ATT_MAXW 64
 __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
+  pdl_enter();
   __shared__ float red[32];
   __shared__ float s_al[ZR_ATT_MAXW];
   __shared__ int s_slot[ZR_ATT_MAXW];
@@ -775,6 +804,7 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
 // window, so the loads of all window slots are in flight together (the generic kernel waits for one L2 round trip
 // per slot).  An empty slot gets weight 0 and reads row 0 of the source memory.
 __global__ void __launch_bounds__(256) att_local_fast_kernel(const AttArgs a) {
+  pdl_enter();
   __shared__ float red[32];
   __shared__ float s_al[ZR_ATT_MAXW];
   __shared__ int s_slot[ZR_ATT_MAXW];
@@ -882,16 +912,15 @@ cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st) {
   if (a.B <= 0) return cudaSuccess;
   if (2 * a.D + 1 > ZR_ATT_MAXW) return cudaErrorInvalidValue;
   if ((a.H & 3) == 0 && a.H <= 1024 && (a.ld_tq & 3) == 0) {
-    att_local_fast_kernel<<<a.B, 256, 0, st>>>(a);
     count_launch();
-    return cudaGetLastError();
+    return launch_chain(att_local_fast_kernel, dim3(a.B), dim3(256), 0, st, a);
   }
-  att_local_kernel<<<a.B, 256, 0, st>>>(a);
   count_launch();
-  return cudaGetLastError();
+  return launch_chain(att_local_kernel, dim3(a.B), dim3(256), 0, st, a);
 }
 
 __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
+  pdl_enter();
   extern __shared__ float s_sc[];  // S_max scores
   __shared__ float red[32];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
@@ -953,6 +982,7 @@ __global__ void __launch_bounds__(256) att_global_kernel(const AttArgs a) {
 // is read once, with 16-byte loads), and carries a running (max, sum, context); the 8 partial results are merged through
 // shared memory at the end.
 __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
+  pdl_enter();
   __shared__ float s_m[8], s_l[8], s_bsc[8];
   __shared__ int s_bpos[8];
   __shared__ float4 s_ctx[8][256];
@@ -1049,15 +1079,13 @@ __global__ void __launch_bounds__(256) att_global_fast_kernel(const AttArgs a) {
 cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
   if (a.B <= 0) return cudaSuccess;
   if ((a.H & 3) == 0 && a.H <= 1024) {
-    att_global_fast_kernel<<<a.B, 256, 0, st>>>(a);
     count_launch();
-    return cudaGetLastError();
+    return launch_chain(att_global_fast_kernel, dim3(a.B), dim3(256), 0, st, a);
   }
   const size_t smem = sizeof(float) * (size_t)(a.S_max > 0 ? a.S_max : 1);
   if (smem > 40 * 1024) return cudaErrorInvalidValue;
-  att_global_kernel<<<a.B, 256, smem, st>>>(a);
   count_launch();
-  return cudaGetLastError();
+  return launch_chain(att_global_kernel, dim3(a.B), dim3(256), smem, st, a);
 }
 
 // ------------------------------------------------------------------------------------------
