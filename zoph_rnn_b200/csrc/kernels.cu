@@ -627,13 +627,46 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   float thr = s_thr;
   float s2 = 0.f;
   const float Mall = s_M;
+  const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(zc) & 15) == 0);
   for (int attempt = 0; attempt < 4; ++attempt) {
-    for (int i = tid; i < V; i += 256) {
-      const float v = zc[i];
-      if (sum_in_pass2 && attempt == 0) s2 += expf(v - Mall);
-      if (v >= thr && v != -INFINITY) {
-        const int p = atomicAdd(&s_count, 1);
-        if (p < ZR_TOPK_CAND) { cval[p] = v; cidx[p] = i; }
+    if (vec4) {
+      // 16-byte loads, four independent exp chains per thread
+      const float4* z4 = reinterpret_cast<const float4*>(zc);
+      float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
+      const int n4 = V >> 2;
+      for (int base = tid; base < n4; base += 256 * 4) {
+        float4 v[4];  // four 16-byte loads in flight per thread
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i4 = base + q * 256;
+          v[q] = i4 < n4 ? __ldcs(z4 + i4) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i4 = base + q * 256;
+          if (sum_in_pass2 && attempt == 0) {  // exp(-inf) = 0 for the padding of the last group
+            e0 += expf(v[q].x - Mall); e1 += expf(v[q].y - Mall); e2 += expf(v[q].z - Mall); e3 += expf(v[q].w - Mall);
+          }
+          if (fmaxf(fmaxf(v[q].x, v[q].y), fmaxf(v[q].z, v[q].w)) >= thr) {
+            const float vv[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (vv[u] >= thr && vv[u] != -INFINITY) {
+                const int p = atomicAdd(&s_count, 1);
+                if (p < ZR_TOPK_CAND) { cval[p] = vv[u]; cidx[p] = 4 * i4 + u; }
+              }
+          }
+        }
+      }
+      s2 += (e0 + e1) + (e2 + e3);
+    } else {
+      for (int i = tid; i < V; i += 256) {
+        const float v = zc[i];
+        if (sum_in_pass2 && attempt == 0) s2 += expf(v - Mall);
+        if (v >= thr && v != -INFINITY) {
+          const int p = atomicAdd(&s_count, 1);
+          if (p < ZR_TOPK_CAND) { cval[p] = v; cidx[p] = i; }
+        }
       }
     }
     __syncthreads();
@@ -672,14 +705,17 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
     __syncthreads();
   }
   const int nc = s_count < ZR_TOPK_CAND ? s_count : ZR_TOPK_CAND;
-  // k rounds of block-wide argmax over the candidates (value, then lower word id)
+  // k rounds of argmax over the candidates (value, then lower word id) by one warp: the candidate list is short, and
+  // a warp needs no block barrier between rounds
+  if (w != 0) return;
+  const float M = s_M, logS = s_logS;
   for (int r = 0; r < k; ++r) {
     float v = -INFINITY;
     int id = 0x7fffffff, pos = -1;
-    for (int j = tid; j < nc; j += 256) {
-      const float cv = cval[j];
-      const int ci = cidx[j];
-      if (cv > v || (cv == v && ci < id)) { v = cv; id = ci; pos = j; }
+    for (int jj = lane; jj < nc; jj += 32) {
+      const float cv = cval[jj];
+      const int ci = cidx[jj];
+      if (cv > v || (cv == v && ci < id)) { v = cv; id = ci; pos = jj; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -688,21 +724,13 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
       const int op = __shfl_xor_sync(0xffffffffu, pos, o);
       if (ov > v || (ov == v && oi < id)) { v = ov; id = oi; pos = op; }
     }
-    if (lane == 0) { win_v[w] = v; win_i[w] = id; win_p[w] = pos; }
-    __syncthreads();
-    if (tid == 0) {
-      float bv = win_v[0];
-      int bi = win_i[0], bp = win_p[0];
-      for (int i = 1; i < 8; ++i)
-        if (win_v[i] > bv || (win_v[i] == bv && win_i[i] < bi)) { bv = win_v[i]; bi = win_i[i]; bp = win_p[i]; }
-      const bool ok = bp >= 0 && bv != -INFINITY;
-      val_out[(size_t)col * k + r] = ok ? (bv - s_M) - s_logS : -INFINITY;
-      idx_out[(size_t)col * k + r] = ok ? bi : -1;
-      s_win = bp;
+    if (lane == 0) {
+      const bool ok = pos >= 0 && v != -INFINITY;
+      val_out[(size_t)col * k + r] = ok ? (v - M) - logS : -INFINITY;
+      idx_out[(size_t)col * k + r] = ok ? id : -1;
+      if (pos >= 0) cval[pos] = -INFINITY;  // remove the winner
     }
-    __syncthreads();
-    if (tid == 0 && s_win >= 0) cval[s_win] = -INFINITY;  // remove the winner
-    __syncthreads();
+    __syncwarp();
   }
 }
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
