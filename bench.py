@@ -370,6 +370,43 @@ def run_c5_sharded(args, w, cfg, rank, world):
                                        d2h_bytes_per_step=T * B * 4))))
 
 
+def cell_phases(w, dtype_name):
+    """Runs one hidden-to-hidden LSTM cell (H x B of the workload) with the kernel's phase stamps on and returns, per
+    phase, the min / mean / max over the launch's CTAs in microseconds since the first CTA started."""
+    import ctypes
+    import torch
+    from zoph_rnn_b200 import api
+    H, B = w["H"], w["B"] * (w.get("beam", 1) if w["kind"] == "decode" else 1)
+    rng = np.random.default_rng(0)
+    mats = [(rng.standard_normal(H * H) * 0.02).astype(np.float32) for _ in range(8)]
+    tensors = []
+    for g in range(4):
+        tensors += [mats[g], np.zeros(H, np.float32)]
+    tensors += mats[4:]
+    layer = api.Hidden_To_Hidden_Layer(H, dtype=dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[dtype_name])
+    layer.load_weights(tensors)
+    x, h0, c0 = (torch.randn(H * B, device="cuda") for _ in range(3))
+    mask = torch.ones(B, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        layer.forward_prop(x, mask, h0, c0)
+    torch.cuda.synchronize()
+    buf = torch.zeros(8 * 4096, dtype=torch.int64, device="cuda")
+    api.check(api.lib().zrnn_debug_tc_profile(ctypes.c_void_p(buf.data_ptr())))
+    layer.forward_prop(x, mask, h0, c0)
+    torch.cuda.synchronize()
+    api.check(api.lib().zrnn_debug_tc_profile(None))
+    t = buf.cpu().numpy().reshape(-1, 8)
+    t = t[t[:, 0] > 0]
+    if len(t) == 0:
+        return dict(error="no stamps: this shape does not run the split-K tensor-core cell")
+    rel = (t - t[:, 0].min()) / 1e3
+    names = ["start", "setup_done", "accumulators_complete", "partial_tile_pushed", "cluster_barrier_passed",
+             "slots_read", "gate_math_done", "stores_issued"]
+    return dict(kernel="lstm_cell", H=H, B=B, dtype=dtype_name, ctas=int(len(t)), unit="us",
+                phases={n: dict(min=round(float(rel[:, i].min()), 2), mean=round(float(rel[:, i].mean()), 2),
+                                max=round(float(rel[:, i].max()), 2)) for i, n in enumerate(names)})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -381,6 +418,9 @@ def main():
                     help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate, 3xTF32 tensor cores when H >= 128)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16", action="store_true", help="skip the additional bf16 measurement of an f32 run")
+    ap.add_argument("--cell-phases", action="store_true",
+                    help="diagnostic: device-side phase times of one LSTM cell launch of the workload's layer shape "
+                         "(per-CTA %%globaltimer stamps written by the kernel), printed as one JSON line")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -396,6 +436,10 @@ def main():
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     torch.cuda.set_device(local_rank)
+    if args.cell_phases:
+        if rank == 0:
+            print(json.dumps(cell_phases(w, args.dtype)))
+        return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 

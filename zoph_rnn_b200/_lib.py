@@ -35,6 +35,8 @@ SIGNATURES = {
     "zrnn_last_error": (ctypes.c_char_p, []),
     "zrnn_version": (ctypes.c_int, []),
     "zrnn_built_for_sm": (ctypes.c_int, []),
+    "zrnn_debug_tc_profile": (ctypes.c_int, [c_void_p]),
+    "zrnn_debug_tc_timeline": (ctypes.c_int, [c_void_p, ctypes.c_int]),
     "zrnn_device_count": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "zrnn_set_device": (ctypes.c_int, [ctypes.c_int]),
     "zrnn_launch_count": (ctypes.c_longlong, []),

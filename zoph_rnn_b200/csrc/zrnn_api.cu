@@ -665,7 +665,7 @@ int zrnn_set_device(int device) {
 long long zrnn_launch_count(void) { return zrnn::launch_count_value(); }
 void zrnn_reset_launch_count(void) { zrnn::launch_count_reset(); }
 
-/* developer aid, not declared in zrnn.h: LSTM tensor-core launches write 8 globaltimer stamps per CTA into buf */
+/* developer aid: LSTM tensor-core launches write 8 globaltimer stamps per CTA into buf */
 int zrnn_debug_tc_profile(long long* d_buf) {
   g_tc_prof = d_buf;
   g_tc_prof_slot = -1;
