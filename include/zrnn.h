@@ -38,13 +38,19 @@ typedef enum {
 
 /* Arithmetic of the GEMM-shaped work (state, biases, activations functions and softmax reductions are fp32 in
  * every mode):
- *   ZRNN_F32        fp32-accurate: tcgen05 3xTF32 tensor-core kernels when H >= 128 and H % 4 == 0, else the
- *                   exact fp32 FMA kernels (environment ZRNN_FP32_ENGINE=simt forces the latter)
+ *   ZRNN_F32        fp32-accurate: tcgen05 split-operand tensor-core kernels when H >= 128 and H % 4 == 0 (fp16
+ *                   split, see ZRNN_F32_F16X2), else the exact fp32 FMA kernels.  Environment ZRNN_FP32_ENGINE =
+ *                   simt forces the FMA kernels, = x3 the 3xTF32 kernels.
  *   ZRNN_BF16       tcgen05 tensor cores on bf16-rounded weights and activations (H % 8 == 0)
  *   ZRNN_TF32       tcgen05 tensor cores, single-pass tf32 (H % 4 == 0)
  *   ZRNN_F32_SIMT   always the exact fp32 FMA kernels
- *   ZRNN_F32_3XTF32 always the 3xTF32 tensor-core kernels (H % 4 == 0) */
-typedef enum { ZRNN_F32 = 0, ZRNN_BF16 = 1, ZRNN_TF32 = 2, ZRNN_F32_SIMT = 3, ZRNN_F32_3XTF32 = 4 } zrnn_dtype;
+ *   ZRNN_F32_3XTF32 always the 3xTF32 tensor-core kernels (H % 4 == 0): operands as tf32 hi + fp32 residual
+ *   ZRNN_F32_F16X2  always the fp16-split tensor-core kernels (H % 4 == 0): operands as fp16 hi + fp16 residual
+ *                   scaled by 2^11 (11 + 11 significant bits like 3xTF32, half the bytes and tensor time); weights
+ *                   must lie inside the fp16 range, which the load functions check (ZRNN_E_ARG otherwise) */
+typedef enum {
+  ZRNN_F32 = 0, ZRNN_BF16 = 1, ZRNN_TF32 = 2, ZRNN_F32_SIMT = 3, ZRNN_F32_3XTF32 = 4, ZRNN_F32_F16X2 = 5
+} zrnn_dtype;
 typedef enum { ZRNN_ATT_NONE = 0, ZRNN_ATT_LOCAL_P = 1, ZRNN_ATT_GLOBAL_DOT = 2 } zrnn_attention_type;
 
 const char* zrnn_status_string(int status);
@@ -71,7 +77,8 @@ int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total
 /* The GEMM building block: C[n_rows x m_cols] = W[n_rows x K] * X[K x m_cols], all column-major fp32, as the
  * reference's cublas_gemm_wrapper (src/BZ_CUDA_UTIL.h:691-696) called with CUBLAS_OP_N, CUBLAS_OP_N.
  * mode 0 = exact fp32 FMA kernel; 1 = tcgen05 tensor cores on bf16-rounded operands; 2 = tcgen05 tf32;
- * 3 = tcgen05 3xTF32 (operands split into tf32 hi + lo parts, fp32-level accuracy).  Synchronous; allocates
+ * 3 = tcgen05 3xTF32 (operands split into tf32 hi + lo parts, fp32-level accuracy); 4 = tcgen05 fp16 split (fp16 hi
+ * + scaled fp16 lo parts, fp32-level accuracy for operands inside the fp16 range).  Synchronous; allocates
  * scratch for the packed operands.  Returns ZRNN_E_TIMEOUT if a bounded device-side wait gave up. */
 int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw, const float* d_X, int ldx,
               float* d_C, int ldc, void* stream);

@@ -17,14 +17,15 @@ def api():
 
 
 # (dtype id, relative tolerance, absolute tolerance): exact engines first, then the reduced-precision ones
-EXACT = [(3, 2e-5, 2e-6), (4, 6e-5, 3e-5)]       # ZRNN_F32_SIMT, ZRNN_F32_3XTF32 (tensor-core accumulation truncates)
+# ZRNN_F32_SIMT, ZRNN_F32_3XTF32, ZRNN_F32_F16X2 (tensor-core accumulation truncates)
+EXACT = [(3, 2e-5, 2e-6), (4, 6e-5, 3e-5), (5, 6e-5, 3e-5)]
 LOOSE = [(1, 3e-2, 3e-2), (2, 1e-2, 1e-2)]       # ZRNN_BF16, ZRNN_TF32
 
 
 def engines_for(H):
     out = [EXACT[0]]
     if H % 4 == 0:
-        out += [EXACT[1], LOOSE[1]]
+        out += [EXACT[1], EXACT[2], LOOSE[1]]
     if H % 8 == 0:
         out.append(LOOSE[0])
     return out
@@ -210,14 +211,14 @@ def test_softmax_score_matches_oracle(api, oracle, V, H, N):
         got = sm.compute_loss(dev(h), dev(tgt), dev(mask))
         torch.cuda.synchronize()
         assert api.lib().zrnn_tc_error() == 0
-        if dtype in (3, 4):
+        if dtype in (3, 4, 5):
             helpers.assert_logp_close(got.cpu().numpy(), want)
         else:
             np.testing.assert_allclose(got.cpu().numpy(), want, rtol=rtol, atol=atol * 3, err_msg=f"dtype {dtype}")
         assert np.all(got.cpu().numpy()[mask == 0] == 0.0)
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 @pytest.mark.parametrize("G", [2, 3, 8])
 def test_vocab_sharded_softmax_equals_unsharded(api, oracle, G, dtype):
     import torch
@@ -256,7 +257,7 @@ def test_softmax_topk_matches_oracle(api, oracle, V, H, N, k):
     # indices are exact wherever the oracle's neighbouring probabilities are not within float noise of a tie
     sorted_p = np.take_along_axis(p, np.argsort(-p, axis=1, kind="stable")[:, :k + 1], axis=1)
     gaps = (sorted_p[:, :-1] - sorted_p[:, 1:]) / sorted_p[:, :-1]
-    for dtype in (3, 4):
+    for dtype in (3, 4, 5):
         sm = api.softmax_layer(V, H, dtype=dtype)
         sm.load_weights(D, b)
         val, idx, eos = sm.topk(dev(h), k)

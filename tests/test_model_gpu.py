@@ -23,11 +23,11 @@ def build_model(api, cfg, w, dtype=0):
     return m
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 @pytest.mark.parametrize("name", helpers.golden_cases())
 def test_scoring_matches_golden(api, name, dtype):
     cfg, w, g = helpers.load_golden(name)
-    if dtype == 4 and cfg["H"] % 4:
+    if dtype in (4, 5) and cfg["H"] % 4:
         pytest.skip("3xTF32 needs H % 4 == 0")
     m = build_model(api, cfg, w, dtype)
     src = g["src"] if "src" in g else None
@@ -37,12 +37,12 @@ def test_scoring_matches_golden(api, name, dtype):
     assert np.all(lp[g["tgt_out"] == -1] == 0.0)
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 @pytest.mark.parametrize("name", [n for n in helpers.golden_cases() if n.startswith("s2s")])
 def test_decoding_matches_golden(api, name, dtype):
     from tests.golden.make_golden import DECODE as d
     cfg, w, g = helpers.load_golden(name)
-    if dtype == 4 and cfg["H"] % 4:
+    if dtype in (4, 5) and cfg["H"] % 4:
         pytest.skip("3xTF32 needs H % 4 == 0")
     m = build_model(api, cfg, w, dtype)
     srcs = helpers.split_sources(g["dec_src"], g["dec_len"])
@@ -58,7 +58,7 @@ def test_config1_lm_full_size(api, oracle):
     w = synth.make_weights(cfg, seed=1234, scale=0.08)
     tin, tout = synth.make_lm_batch(10000, 8, 35, seed=1234)
     want = oracle.OracleModel(cfg, w).score_batch(None, tin, tout)
-    for dtype in (3, 4):
+    for dtype in (3, 4, 5):
         m = build_model(api, cfg, w, dtype)
         lp, tot = m.get_error(None, tin, tout)
         helpers.assert_logp_close(lp, want)
@@ -67,7 +67,7 @@ def test_config1_lm_full_size(api, oracle):
         assert abs(ppl_got - ppl_want) / ppl_want < 1e-5
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 @pytest.mark.parametrize("att,L,H,B,S,T", [(2, 4, 96, 16, (12, 12), (11, 11)),     # config 2 shape, scaled down
                                             (1, 2, 128, 16, (5, 40), (4, 20)),      # config 3 shape: ragged + masks
                                             (2, 2, 200, 130, (3, 9), (3, 9)),       # more columns than one tile
@@ -100,7 +100,7 @@ def test_scoring_batch_independence(api):
         helpers.assert_logp_close(one[:, 0], full[:n, b], rtol=2e-5, atol=2e-6)
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 @pytest.mark.parametrize("att,feed", [(0, 0), (1, 1), (2, 1), (2, 0)])
 def test_decoding_matches_oracle(api, oracle, att, feed, dtype):
     cfg = synth.make_cfg(2, 48, 200, 300, attention=att, feed_input=feed, D=3)
@@ -180,7 +180,7 @@ def test_error_statuses(api):
         sm.compute_loss(torch.zeros(4, device="cuda"), torch.zeros(1, dtype=torch.int32, device="cuda"), None)
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 def test_vocab_sharded_scorer_on_one_gpu(api, oracle, dtype):
     """The multi-GPU scorer with world size 1 (no collective) equals the plain scoring call and the oracle."""
     from zoph_rnn_b200 import sharded
@@ -195,7 +195,7 @@ def test_vocab_sharded_scorer_on_one_gpu(api, oracle, dtype):
     helpers.assert_logp_close(got, want)
 
 
-@pytest.mark.parametrize("dtype", [3, 4])
+@pytest.mark.parametrize("dtype", [3, 4, 5])
 def test_ensemble_decoding_matches_oracle(api, oracle, dtype):
     """Two models of different shapes (own source vocabulary and sentences, shared target vocabulary) decoded as an
     ensemble: per-step averaging of the output distributions (src/ensemble_factory.hpp:768-795)."""
@@ -218,3 +218,16 @@ def test_ensemble_decoding_matches_oracle(api, oracle, dtype):
     assert not np.array_equal(alone[2], gs)
     one = api.decode_ensemble([ma], [sa], **kw)
     assert np.array_equal(one[0], alone[0]) and np.array_equal(one[2], alone[2])
+
+
+def test_f16_split_refuses_weights_outside_the_fp16_range(api):
+    """The fp16-split engine cannot represent |w| >= 65504: loading such a model is an argument error that names the
+    3xTF32 engine as the way out, and the 3xTF32 engine takes the same weights."""
+    cfg = synth.make_cfg(1, 128, 0, 300, lm=True)
+    w = [np.array(t, dtype=np.float32) for t in synth.make_weights(cfg, seed=3)]
+    w[0] = w[0].copy()
+    w[0].reshape(-1)[5] = 7.0e4
+    with pytest.raises(api.ZrnnError) as e:
+        build_model(api, cfg, w, 5)
+    assert "fp16 range" in str(e.value)
+    build_model(api, cfg, w, 4)

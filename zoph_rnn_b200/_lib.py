@@ -14,7 +14,7 @@ c_float_p = ctypes.POINTER(ctypes.c_float)
 c_void_p = ctypes.c_void_p
 
 OK, E_ARG, E_CUDA, E_NCCL, E_TIMEOUT, E_IO, E_STATE = range(7)
-F32, BF16, TF32, F32_SIMT, F32_3XTF32 = 0, 1, 2, 3, 4
+F32, BF16, TF32, F32_SIMT, F32_3XTF32, F32_F16X2 = 0, 1, 2, 3, 4, 5
 ATT_NONE, ATT_LOCAL_P, ATT_GLOBAL_DOT = 0, 1, 2
 
 

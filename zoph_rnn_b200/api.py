@@ -11,7 +11,8 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (ATT_GLOBAL_DOT, ATT_LOCAL_P, ATT_NONE, BF16, F32, F32_3XTF32, F32_SIMT, TF32, ModelConfig,  # noqa: F401
+from ._lib import (ATT_GLOBAL_DOT, ATT_LOCAL_P, ATT_NONE, BF16, F32, F32_3XTF32, F32_F16X2, F32_SIMT, TF32,  # noqa: F401
+                   ModelConfig,
                    ZrnnError, check, lib)
 
 

@@ -3,6 +3,7 @@
 #include "kernels.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <cfloat>
 #include <cstdint>
@@ -28,6 +29,11 @@ __device__ __forceinline__ float sigmoidf_acc(float v) { return 1.0f / (1.0f + e
 __device__ __forceinline__ void att_store_op(const AttArgs& a, int b, int i, float v) {
   const size_t idx = (size_t)b * a.ld_op + i;
   if (a.op_b16) reinterpret_cast<__nv_bfloat16*>(a.op_b16)[idx] = __float2bfloat16(v);
+  if (a.op_h_hi) {
+    const __half h = __float2half_rn(v);
+    reinterpret_cast<__half*>(a.op_h_hi)[idx] = h;
+    reinterpret_cast<__half*>(a.op_h_lo)[idx] = __float2half_rn((v - __half2float(h)) * 2048.0f);
+  }
   if (a.op_hi) {
     unsigned u = __float_as_uint(v);
     const float hi = ((u & 0x7f800000u) == 0x7f800000u) ? v : __uint_as_float((u + 0x1000u) & 0xffffe000u);
@@ -144,6 +150,10 @@ __device__ __forceinline__ void store_op(void* hi, float* lo, int mode, size_t i
     reinterpret_cast<__nv_bfloat16*>(hi)[idx] = __float2bfloat16(v);
   } else if (mode == 1) {
     reinterpret_cast<float*>(hi)[idx] = v;
+  } else if (mode == 3) {  // fp16 split: hi = fp16(v), lo = fp16((v - hi) * 2^11); `lo` points to __half storage
+    const __half h = __float2half_rn(v);
+    reinterpret_cast<__half*>(hi)[idx] = h;
+    reinterpret_cast<__half*>(lo)[idx] = __float2half_rn((v - __half2float(h)) * 2048.0f);
   } else {
     const float h = tf32_round_prep(v);
     reinterpret_cast<float*>(hi)[idx] = h;

@@ -113,6 +113,8 @@ struct AttArgs {
   void* op_b16;
   float* op_hi;
   float* op_lo;
+  void* op_h_hi;  // fp16 split operands: fp16 hi part and scaled fp16 lo part
+  void* op_h_lo;
   int ld_op;
 };
 cudaError_t launch_att_local(const AttArgs& a, cudaStream_t st);
@@ -159,7 +161,8 @@ cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st);
 cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st);
 
 // ---- operand preparation for the tensor-core GEMMs (K-major rows; see tc_gemm.cuh)
-// op_mode: 0 = bf16, 1 = fp32 as is, 2 = fp32 split into hi (tf32-representable) + lo (residual)
+// op_mode: 0 = bf16, 1 = fp32 as is, 2 = fp32 split into hi (tf32-representable) + lo (residual),
+// 3 = fp16 split: hi = fp16(v), lo = fp16((v - hi) * 2^11) (dst_lo then points to fp16 storage)
 // Packs G column-major (H x K, leading dimension lda) matrices into K-major rows: packed row
 // r = tile*(G*TH) + g*TH + j holds row hid = tile*TH + j of matrix g (zero when hid >= H), written at
 // dst[r*ld_dst + koff + k].  n_tiles = ceil(H / TH).

@@ -160,6 +160,21 @@ __device__ __forceinline__ void store8_operand(const TcParams& p, size_t idx, co
       for (int u = 0; u < nvalid; ++u) p.op_b16[idx + u] = __float2bfloat16(v[u]);
     }
   }
+  if (p.op_h_hi) {  // fp16 split operands: hi = fp16(v), lo = fp16((v - hi) * 2^11)
+    __align__(16) __half hi[8];
+    __align__(16) __half lo[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      hi[u] = __float2half_rn(v[u]);
+      lo[u] = __float2half_rn((v[u] - __half2float(hi[u])) * 2048.0f);
+    }
+    if (nvalid == 8 && (idx & 7) == 0) {
+      *reinterpret_cast<uint4*>(p.op_h_hi + idx) = *reinterpret_cast<const uint4*>(hi);
+      *reinterpret_cast<uint4*>(p.op_h_lo + idx) = *reinterpret_cast<const uint4*>(lo);
+    } else {
+      for (int u = 0; u < nvalid; ++u) { p.op_h_hi[idx + u] = hi[u]; p.op_h_lo[idx + u] = lo[u]; }
+    }
+  }
   if (p.op_hi) {
     float hi[8], lo[8];
 #pragma unroll
@@ -168,22 +183,35 @@ __device__ __forceinline__ void store8_operand(const TcParams& p, size_t idx, co
     if (p.op_lo) store8_f32(p.op_lo, idx, lo, nvalid);
   }
 }
+// Mode traits.  "Split" modes keep every operand as a hi part plus a residual lo part and spend three MMAs per
+// k-step (hi*hi into the main accumulators, lo*hi and hi*lo into the cross accumulator):
+//   TC_TF32X3: fp32 storage, hi = value rounded to tf32, lo = value - hi
+//   TC_F16X2 : fp16 storage, hi = value rounded to fp16, lo = (value - hi) * 2^11 rounded to fp16; the cross
+//              accumulator is scaled back by 2^-11 in the epilogue.  Same 11 + 11 significant bits, half the bytes
+//              and half the tensor time; operands must stay inside the fp16 range (|x| < 65504).
+__host__ __device__ constexpr bool mode_split(int mode) { return mode == TC_TF32X3 || mode == TC_F16X2; }
+__host__ __device__ constexpr bool mode_exact_math(int mode) { return mode_split(mode); }
+__host__ __device__ constexpr bool mode_kind_tf32(int mode) { return mode == TC_TF32 || mode == TC_TF32X3; }
+__host__ __device__ constexpr int mode_epk(int mode) { return mode_kind_tf32(mode) ? 32 : 64; }  // elements per k-block
+__host__ __device__ constexpr uint32_t mode_fmt(int mode) { return mode == TC_BF16 ? 1u : (mode == TC_F16X2 ? 0u : 2u); }
+__host__ __device__ constexpr float mode_cross_scale(int mode) { return mode == TC_F16X2 ? (1.0f / 2048.0f) : 1.0f; }
+
 // activations: exact for the fp32-accurate mode, hardware approximations (tanh.approx, ~2^-11) for bf16 / tf32
 template <int MODE>
 __device__ __forceinline__ float act_tanh(float x) {
-  if (MODE == TC_TF32X3) return tanhf(x);
+  if (mode_exact_math(MODE)) return tanhf(x);
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 template <int MODE>
 __device__ __forceinline__ float act_sigmoid(float x) {
-  if (MODE == TC_TF32X3) return 1.0f / (1.0f + expf(-x));
+  if (mode_exact_math(MODE)) return 1.0f / (1.0f + expf(-x));
   return fmaf(0.5f, act_tanh<MODE>(0.5f * x), 0.5f);
 }
 
 constexpr int kABytes = 128 * 128;  // A tile: 128 rows x 128-byte k-block
-__host__ __device__ constexpr int stage_bytes(int BN, int mode) { return (mode == TC_TF32X3 ? 2 : 1) * (kABytes + BN * 128); }
+__host__ __device__ constexpr int stage_bytes(int BN, int mode) { return (mode_split(mode) ? 2 : 1) * (kABytes + BN * 128); }
 // bytes of the split-K exchange slots: SPLITK slots of (BN/SPLITK)/4 x 128 rows of float4.  They must not overlap
 // the stage ring: a peer that finishes its main loop early pushes into them while this CTA may still be loading.
 __host__ __device__ constexpr int slot_bytes(int BN, int splitk) {
@@ -192,7 +220,7 @@ __host__ __device__ constexpr int slot_bytes(int BN, int splitk) {
 // 3xTF32 stages are twice as large (hi + lo parts), and with exchange slots of their own only two would fit, too few
 // bytes in flight to keep HBM busy.  In that mode the slots alias the ring instead, which costs one more cluster
 // barrier (nobody may push into a peer's ring before that peer's MMAs have consumed it).
-__host__ __device__ constexpr bool slots_alias_ring(int mode, int splitk) { return mode == TC_TF32X3 && splitk > 1; }
+__host__ __device__ constexpr bool slots_alias_ring(int mode, int splitk) { return mode_split(mode) && splitk > 1; }
 __host__ __device__ constexpr int num_stages(int BN, int mode, int splitk = 1) {
   int s = (225 * 1024 - 1024 - (slots_alias_ring(mode, splitk) ? 0 : slot_bytes(BN, splitk))) / stage_bytes(BN, mode);
   return s > 8 ? 8 : s;
@@ -207,10 +235,10 @@ __host__ __device__ constexpr int smem_bytes(int BN, int mode, int splitk) {
 // 1/NACC of the additions on a smaller partial sum), the two small cross terms go to an accumulator of their own,
 // and the epilogue adds the partial sums with round-to-nearest fp32.
 __host__ __device__ constexpr int num_acc(int BN, int mode) {
-  return mode != TC_TF32X3 ? 1 : (BN <= 32 ? 8 : (BN <= 64 ? 4 : (BN <= 128 ? 2 : 1)));
+  return !mode_split(mode) ? 1 : (BN <= 32 ? 8 : (BN <= 64 ? 4 : (BN <= 128 ? 2 : 1)));
 }
 __host__ __device__ constexpr int tmem_cols(int BN, int mode) {
-  int need = (mode == TC_TF32X3 ? num_acc(BN, mode) + 1 : 1) * BN;
+  int need = (mode_split(mode) ? num_acc(BN, mode) + 1 : 1) * BN;
   int c = 32;
   while (c < need) c *= 2;
   return c;
@@ -262,7 +290,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
   static_assert(ST >= 2, "need at least a double-buffered ring");
-  constexpr uint32_t IDESC = make_idesc(MODE == TC_BF16 ? 1u : 2u, BN);
+  constexpr uint32_t IDESC = make_idesc(mode_fmt(MODE), BN);
   constexpr int NACC = num_acc(BN, MODE);
   constexpr int TMEM_COLS = tmem_cols(BN, MODE);
   constexpr int OWNC = BN / SPLITK;  // columns finished by each CTA of the cluster
@@ -339,13 +367,13 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
           if (!mbar_wait(&empty_bar[st], ph ^ 1u, &abort_s, p.err, 1)) { ok = false; break; }
           uint8_t* base = tiles + (size_t)st * STAGE;
           mbar_expect_tx(&full_bar[st], (uint32_t)STAGE);
-          const int kx = kb * (MODE == TC_BF16 ? 64 : 32);
-          constexpr int EPK = MODE == TC_BF16 ? 64 : 32;  // elements per 128-byte k-block
+          constexpr int EPK = mode_epk(MODE);  // elements per 128-byte k-block
+          const int kx = kb * EPK;
           const int bx = p.b_tiled_kbtot > 0 ? 0 : p.b_koff[s] + kx;
           const int by = p.b_tiled_kbtot > 0 ? (n_tile * p.b_tiled_kbtot + (p.b_koff[s] + kx) / EPK) * BN : n_tile * BN;
           tma_load_2d(base, &p.a[s], &full_bar[st], kx, m0);
           tma_load_2d(base + kABytes, &p.b, &full_bar[st], bx, by);
-          if (MODE == TC_TF32X3) {
+          if (mode_split(MODE)) {
             tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
             tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], bx, by);
           }
@@ -374,12 +402,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
 #pragma unroll
         for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte k-block
           const uint32_t acc = (it >= NACC || k > 0) ? 1u : 0u;
-          umma<MODE != TC_BF16>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
-          if (MODE == TC_TF32X3) {
+          umma<mode_kind_tf32(MODE)>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
+          if (mode_split(MODE)) {
             const uint64_t dal = make_smem_desc(b_addr + BBYTES), dbl = make_smem_desc(b_addr + BBYTES + kABytes);
             const uint32_t d_cross = tmem_base + (uint32_t)(NACC * BN);
-            umma<1>(d_cross, dal + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
-            umma<1>(d_cross, da + 2 * k, dbl + 2 * k, IDESC, 1u);
+            umma<mode_kind_tf32(MODE)>(d_cross, dal + 2 * k, db + 2 * k, IDESC, (it > 0 || k > 0) ? 1u : 0u);
+            umma<mode_kind_tf32(MODE)>(d_cross, da + 2 * k, dbl + 2 * k, IDESC, 1u);
           }
         }
         umma_commit(&empty_bar[st]);
@@ -426,7 +454,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       return;
     }
     tmem_ld8(taddr + col, v);
-    if (MODE == TC_TF32X3) {
+    if (mode_split(MODE)) {
       float t[8];
       for (int a = 1; a < n_main; ++a) {
         tmem_ld8(taddr + a * BN + col, t);
@@ -437,7 +465,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       tmem_ld8(taddr + NACC * BN + col, t);
       tmem_wait_ld();
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] += t[u];
+      for (int u = 0; u < 8; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
     }
     tmem_wait_ld();
   };
@@ -449,7 +477,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       return;
     }
     tmem_ld32(taddr + col, v);
-    if (MODE == TC_TF32X3) {
+    if (mode_split(MODE)) {
       float t[32];
       for (int a = 1; a < n_main; ++a) {
         tmem_ld32(taddr + a * BN + col, t);
@@ -460,7 +488,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       tmem_ld32(taddr + NACC * BN + col, t);
       tmem_wait_ld();
 #pragma unroll
-      for (int u = 0; u < 32; ++u) v[u] += t[u];
+      for (int u = 0; u < 32; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
     }
     tmem_wait_ld();
   };
@@ -652,8 +680,8 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   constexpr int ST = num_stages(BN, MODE);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
-  constexpr uint32_t IDESC = make_idesc(MODE == TC_BF16 ? 1u : 2u, BN);
-  constexpr int ACC_COLS = (MODE == TC_TF32X3 ? 2 : 1) * BN;  // main accumulator (+ cross-term accumulator)
+  constexpr uint32_t IDESC = make_idesc(mode_fmt(MODE), BN);
+  constexpr int ACC_COLS = (mode_split(MODE) ? 2 : 1) * BN;  // main accumulator (+ cross-term accumulator)
   constexpr int TMEM_COLS = 2 * ACC_COLS;                       // double-buffered
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM budget");
   static_assert(EPI != TC_EPI_LSTM, "the persistent variant has store and log-sum-exp epilogues only");
@@ -713,10 +741,10 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
             if (!mbar_wait(&empty_bar[st], ph ^ 1u, &abort_s, p.err, 1)) { ok = false; break; }
             uint8_t* base = tiles + (size_t)st * STAGE;
             mbar_expect_tx(&full_bar[st], (uint32_t)STAGE);
-            const int kx = kb * (MODE == TC_BF16 ? 64 : 32);
+            const int kx = kb * mode_epk(MODE);
             tma_load_2d(base, &p.a[s], &full_bar[st], kx, m0);
             tma_load_2d(base + kABytes, &p.b, &full_bar[st], p.b_koff[s] + kx, n0);
-            if (MODE == TC_TF32X3) {
+            if (mode_split(MODE)) {
               tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
               tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], p.b_koff[s] + kx, n0);
             }
@@ -750,11 +778,11 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t acc = (kk > 0 || k > 0) ? 1u : 0u;
-            umma<MODE != TC_BF16>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
-            if (MODE == TC_TF32X3) {
+            umma<mode_kind_tf32(MODE)>(d_main, da + 2 * k, db + 2 * k, IDESC, acc);
+            if (mode_split(MODE)) {
               const uint64_t dal = make_smem_desc(b_addr + BBYTES), dbl = make_smem_desc(b_addr + BBYTES + kABytes);
-              umma<1>(d_main + BN, dal + 2 * k, db + 2 * k, IDESC, acc);
-              umma<1>(d_main + BN, da + 2 * k, dbl + 2 * k, IDESC, 1u);
+              umma<mode_kind_tf32(MODE)>(d_main + BN, dal + 2 * k, db + 2 * k, IDESC, acc);
+              umma<mode_kind_tf32(MODE)>(d_main + BN, da + 2 * k, dbl + 2 * k, IDESC, 1u);
             }
           }
           umma_commit(&empty_bar[st]);
@@ -788,12 +816,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
         for (int c0 = 0; c0 < BN; c0 += 8) {
           float v[8];
           tmem_ld8(taddr + c0, v);
-          if (MODE == TC_TF32X3) {
+          if (mode_split(MODE)) {
             float t[8];
             tmem_ld8(taddr + BN + c0, t);
             tmem_wait_ld();
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] += t[u];
+            for (int u = 0; u < 8; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
           }
           tmem_wait_ld();
           if (row_ok) {
@@ -834,12 +862,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
           tmem_ld32(taddr + c0, v);
-          if (MODE == TC_TF32X3) {
+          if (mode_split(MODE)) {
             float t[32];
             tmem_ld32(taddr + BN + c0, t);
             tmem_wait_ld();
 #pragma unroll
-            for (int u = 0; u < 32; ++u) v[u] += t[u];
+            for (int u = 0; u < 32; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
           }
           tmem_wait_ld();
           float cm = -INFINITY;
@@ -1003,10 +1031,12 @@ cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cuda
     if (mode == TC_BF16) return launch_persistent_t<256, TC_BF16, TC_EPI_LSE>(p, st);
     if (mode == TC_TF32) return launch_persistent_t<256, TC_TF32, TC_EPI_LSE>(p, st);
     if (mode == TC_TF32X3) return launch_persistent_t<128, TC_TF32X3, TC_EPI_LSE>(p, st);
+    if (mode == TC_F16X2) return launch_persistent_t<128, TC_F16X2, TC_EPI_LSE>(p, st);
   } else if (epi == TC_EPI_STORE) {
     if (mode == TC_BF16) return launch_persistent_t<256, TC_BF16, TC_EPI_STORE>(p, st);
     if (mode == TC_TF32) return launch_persistent_t<256, TC_TF32, TC_EPI_STORE>(p, st);
     if (mode == TC_TF32X3) return launch_persistent_t<128, TC_TF32X3, TC_EPI_STORE>(p, st);
+    if (mode == TC_F16X2) return launch_persistent_t<128, TC_F16X2, TC_EPI_STORE>(p, st);
   }
   return cudaErrorInvalidValue;
 }
@@ -1016,6 +1046,7 @@ cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStr
     case TC_BF16: return launch_epi<TC_BF16>(p, BN, epi, splitk, st);
     case TC_TF32: return launch_epi<TC_TF32>(p, BN, epi, splitk, st);
     case TC_TF32X3: return launch_epi<TC_TF32X3>(p, BN, epi, splitk, st);
+    case TC_F16X2: return launch_epi<TC_F16X2>(p, BN, epi, splitk, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -6,11 +6,12 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 namespace zrnn {
 
-enum { TC_BF16 = 0, TC_TF32 = 1, TC_TF32X3 = 2 };
+enum { TC_BF16 = 0, TC_TF32 = 1, TC_TF32X3 = 2, TC_F16X2 = 3 };
 enum { TC_EPI_STORE = 0, TC_EPI_LSTM = 1, TC_EPI_LSE = 2 };
 
 struct TcParams {
@@ -37,6 +38,8 @@ struct TcParams {
   __nv_bfloat16* op_b16;
   float* op_hi;
   float* op_lo;
+  __half* op_h_hi;  // TC_F16X2 consumers: fp16 hi part and scaled fp16 lo part
+  __half* op_h_lo;
   int ld_op;
   // --- LSTM (gates i,f,g,o): c = f*c_prev + i*g ; h = o*tanh(c) ; (h,c) *= mask ; h -> C (ld = ldc), c -> c_out
   const float* c_prev;

@@ -141,13 +141,19 @@ int check_device() {
 // ENG_X3   : tcgen05 3xTF32 (operands split into hi + lo)   - fp32-level accuracy, H % 4 == 0
 // ENG_BF16 : tcgen05 on bf16-rounded weights / activations  - H % 8 == 0
 // ENG_TF32 : tcgen05 single-pass tf32                       - H % 4 == 0
-enum { ENG_SIMT = 0, ENG_BF16 = 1, ENG_TF32 = 2, ENG_X3 = 3 };
+// ENG_H2   : tcgen05 fp16 split (hi + scaled lo, both fp16)  - fp32-level accuracy for operands inside the fp16
+//            range (|x| < 65504; LSTM activations are bounded by 1, weights are checked at load), H % 4 == 0;
+//            half the bytes and half the tensor time of ENG_X3
+enum { ENG_SIMT = 0, ENG_BF16 = 1, ENG_TF32 = 2, ENG_X3 = 3, ENG_H2 = 4 };
 
 namespace {
 
-int eng_eb(int e) { return e == ENG_BF16 ? 2 : 4; }
-int eng_opmode(int e) { return e == ENG_BF16 ? 0 : (e == ENG_TF32 ? 1 : 2); }
-int eng_tcmode(int e) { return e == ENG_BF16 ? zrnn::TC_BF16 : (e == ENG_TF32 ? zrnn::TC_TF32 : zrnn::TC_TF32X3); }
+int eng_eb(int e) { return (e == ENG_BF16 || e == ENG_H2) ? 2 : 4; }
+int eng_opmode(int e) { return e == ENG_BF16 ? 0 : (e == ENG_TF32 ? 1 : (e == ENG_H2 ? 3 : 2)); }
+int eng_tcmode(int e) {
+  return e == ENG_BF16 ? zrnn::TC_BF16 : (e == ENG_TF32 ? zrnn::TC_TF32 : (e == ENG_H2 ? zrnn::TC_F16X2 : zrnn::TC_TF32X3));
+}
+bool eng_split(int e) { return e == ENG_X3 || e == ENG_H2; }  // operands carry a lo part (same element size as hi)
 int round64(int x) { return (x + 63) / 64 * 64; }
 
 int pick_engine(int dtype, int H, int* eng) {
@@ -155,9 +161,14 @@ int pick_engine(int dtype, int H, int* eng) {
     case ZRNN_F32: {
       const char* e = std::getenv("ZRNN_FP32_ENGINE");
       const bool want_simt = e && std::strcmp(e, "simt") == 0;
-      *eng = (!want_simt && H % 4 == 0 && H >= 128) ? ENG_X3 : ENG_SIMT;
+      const bool want_x3 = e && std::strcmp(e, "x3") == 0;
+      *eng = (!want_simt && H % 4 == 0 && H >= 128) ? (want_x3 ? ENG_X3 : ENG_H2) : ENG_SIMT;
       return ZRNN_OK;
     }
+    case ZRNN_F32_F16X2:
+      ZR_CHECK(H % 4 == 0, "fp16-split arithmetic needs H to be a multiple of 4");
+      *eng = ENG_H2;
+      return ZRNN_OK;
     case ZRNN_F32_SIMT: *eng = ENG_SIMT; return ZRNN_OK;
     case ZRNN_F32_3XTF32:
       ZR_CHECK(H % 4 == 0, "3xTF32 arithmetic needs H to be a multiple of 4");
@@ -175,6 +186,16 @@ int pick_engine(int dtype, int H, int* eng) {
   return fail(ZRNN_E_ARG, "unknown dtype");
 }
 
+// ENG_H2 stores operands as fp16 pairs: every weight must be finite and inside the fp16 range
+int check_f16_range(int eng, const float* p, size_t n, const char* what) {
+  if (eng != ENG_H2) return ZRNN_OK;
+  for (size_t i = 0; i < n; ++i)
+    if (!(std::fabs(p[i]) < 60000.0f))
+      return fail(ZRNN_E_ARG, std::string(what) + ": a weight is not finite or exceeds the fp16 range; use dtype "
+                                  "ZRNN_F32_3XTF32 (or ZRNN_FP32_ENGINE=x3) for this model");
+  return ZRNN_OK;
+}
+
 // weights / tables in tensor-core operand form (K-major rows)
 struct OpMem {
   void* hi = nullptr;
@@ -183,9 +204,9 @@ struct OpMem {
     release();
     ZR_CUDA(cudaMalloc(&hi, elems * eng_eb(eng)));
     ZR_CUDA(cudaMemset(hi, 0, elems * eng_eb(eng)));
-    if (eng == ENG_X3) {
-      ZR_CUDA(cudaMalloc((void**)&lo, elems * 4));
-      ZR_CUDA(cudaMemset(lo, 0, elems * 4));
+    if (eng_split(eng)) {
+      ZR_CUDA(cudaMalloc((void**)&lo, elems * eng_eb(eng)));
+      ZR_CUDA(cudaMemset(lo, 0, elems * eng_eb(eng)));
     }
     return ZRNN_OK;
   }
@@ -210,7 +231,7 @@ Act act_at(const Act& a, size_t col, const Geom& g) {
   Act r;
   r.f32 = a.f32 ? a.f32 + col * g.H : nullptr;
   r.hi = a.hi ? (char*)a.hi + col * g.Kpad * eng_eb(g.eng) : nullptr;
-  r.lo = a.lo ? a.lo + col * g.Kpad : nullptr;
+  r.lo = a.lo ? (float*)((char*)a.lo + col * g.Kpad * eng_eb(g.eng)) : nullptr;  // lo elements have hi's size
   return r;
 }
 
@@ -322,7 +343,7 @@ int act_maps(const Act& a, int eng, int H, int Kpad, int rows, CUtensorMap* hi, 
   if (!a.hi) return fail(ZRNN_E_STATE, "internal: activation has no operand-form copy");
   if (!zrnn::make_kmajor_map(hi, a.hi, eng_eb(eng), H, rows, Kpad, 128))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand");
-  if (eng == ENG_X3 && !zrnn::make_kmajor_map(lo, a.lo, 4, H, rows, Kpad, 128))
+  if (eng_split(eng) && !zrnn::make_kmajor_map(lo, a.lo, eng_eb(eng), H, rows, Kpad, 128))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand (lo)");
   return ZRNN_OK;
 }
@@ -330,11 +351,11 @@ int act_maps(const Act& a, int eng, int H, int Kpad, int rows, CUtensorMap* hi, 
 // fp32 activation (H x cols, column-major) -> operand form in scratch buffers
 int to_operand(const float* f32, int H, int Kpad, int cols, int eng, DevBuf& hi, DevBuf& lo, Act* out, cudaStream_t st) {
   ZR_CUDA(hi.reserve((size_t)cols * Kpad * eng_eb(eng)));
-  if (eng == ENG_X3) ZR_CUDA(lo.reserve((size_t)cols * Kpad * 4));
+  if (eng_split(eng)) ZR_CUDA(lo.reserve((size_t)cols * Kpad * eng_eb(eng)));
   ZR_CUDA(zrnn::launch_convert_rows(f32, cols, H, H, eng_opmode(eng), hi.p, lo.as<float>(), Kpad, st));
   out->f32 = const_cast<float*>(f32);
   out->hi = hi.p;
-  out->lo = eng == ENG_X3 ? lo.as<float>() : nullptr;
+  out->lo = eng_split(eng) ? lo.as<float>() : nullptr;
   return ZRNN_OK;
 }
 
@@ -363,6 +384,20 @@ int lstm_cell_simt(zrnn_lstm_layer* L, const float* x, const int* mask, const fl
   return ZRNN_OK;
 }
 
+// where the epilogue leaves the operand-form copy of its output for the next GEMM
+void set_operand_outputs(zrnn::TcParams& tp, int eng, const Act& out, int Kpad) {
+  tp.ld_op = Kpad;
+  if (eng == ENG_BF16) {
+    tp.op_b16 = (__nv_bfloat16*)out.hi;
+  } else if (eng == ENG_H2) {
+    tp.op_h_hi = (__half*)out.hi;
+    tp.op_h_lo = (__half*)out.lo;
+  } else {
+    tp.op_hi = (float*)out.hi;
+    tp.op_lo = eng == ENG_X3 ? out.lo : nullptr;
+  }
+}
+
 // One LSTM cell.  x / h_prev / htild and the output are activations in the form the layer's engine needs.
 int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, const int* mask, const float* c_prev,
                  int B, const Act& out, float* c_out, cudaStream_t st) {
@@ -383,10 +418,7 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   tp.b = L->wmap; tp.b_lo = L->wmap_lo; tp.b_tiled_kbtot = L->kbtot;
   tp.M = B; tp.N = H; tp.bias = L->b; tp.mask = mask;
   tp.C = out.f32; tp.ldc = H;
-  tp.op_b16 = eng == ENG_BF16 ? (__nv_bfloat16*)out.hi : nullptr;
-  tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
-  tp.op_lo = out.lo; tp.ld_op = Kpad;
-  if (eng == ENG_TF32 && tp.op_hi) tp.op_lo = nullptr;
+  set_operand_outputs(tp, eng, out, Kpad);
   tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); prof_attach(tp);
   KScope ks(KC_LSTM, st);
   ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st, pick_splitk(B, 4 * H, L->BN, 4)));
@@ -407,11 +439,12 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
   ctx.f32 = A->ctx.as<float>();
   if (eng != ENG_SIMT) {
     ZR_CUDA(A->ctx_hi.reserve((size_t)B * Kpad * eng_eb(eng)));
-    if (eng == ENG_X3) ZR_CUDA(A->ctx_lo.reserve((size_t)B * Kpad * 4));
+    if (eng_split(eng)) ZR_CUDA(A->ctx_lo.reserve((size_t)B * Kpad * eng_eb(eng)));
     ctx.hi = A->ctx_hi.p;
-    ctx.lo = eng == ENG_X3 ? A->ctx_lo.as<float>() : nullptr;
+    ctx.lo = eng_split(eng) ? A->ctx_lo.as<float>() : nullptr;
     a.ld_op = Kpad;
     if (eng == ENG_BF16) a.op_b16 = ctx.hi;
+    else if (eng == ENG_H2) { a.op_h_hi = ctx.hi; a.op_h_lo = ctx.lo; }
     else { a.op_hi = (float*)ctx.hi; a.op_lo = ctx.lo; }
   }
   if (A->type == ZRNN_ATT_LOCAL_P) {
@@ -457,9 +490,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
     tp.b = A->cmap; tp.b_lo = A->cmap_lo;
     tp.M = B; tp.N = H; tp.bias = A->bias; tp.mask = mask; tp.act = 1;
     tp.C = out.f32; tp.ldc = H;
-    tp.op_b16 = eng == ENG_BF16 ? (__nv_bfloat16*)out.hi : nullptr;
-    tp.op_hi = eng == ENG_BF16 ? nullptr : (float*)out.hi;
-    tp.op_lo = out.lo; tp.ld_op = Kpad;
+    set_operand_outputs(tp, eng, out, Kpad);
     tp.err = tc_error_word();
     if (g_tc_prof_slot >= 0) prof_attach(tp);
     ZR_CUDA(zrnn::launch_tc_gemm(tp, A->BN, eng_tcmode(eng), zrnn::TC_EPI_STORE, st, pick_splitk(B, H, A->BN, 8)));
@@ -578,7 +609,7 @@ int pack_into(OpMem& dst, int eng, const float* const* src, int G, int rows, int
 int weight_maps(const OpMem& w, int eng, long long K, long long rows, int box_rows, CUtensorMap* hi, CUtensorMap* lo) {
   if (!zrnn::make_kmajor_map(hi, w.hi, eng_eb(eng), K, rows, K, box_rows))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for a weight operand");
-  if (eng == ENG_X3 && !zrnn::make_kmajor_map(lo, w.lo, 4, K, rows, K, box_rows))
+  if (eng_split(eng) && !zrnn::make_kmajor_map(lo, w.lo, eng_eb(eng), K, rows, K, box_rows))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for a weight operand (lo)");
   return ZRNN_OK;
 }
@@ -740,6 +771,12 @@ int zrnn_lstm_load(zrnn_lstm_layer* L, const float* const* t, int n) {
   for (int i = 0; i < n; ++i) ZR_CHECK(t[i], "lstm_load: null tensor " + std::to_string(i));
   const int H = L->H;
   const size_t HH = (size_t)H * H;
+  {
+    int q = 8;
+    for (int g = 0; g < 4; ++g) ZR_TRY(check_f16_range(L->eng, t[2 * g], HH, "lstm_load"));
+    if (L->is_ih) ZR_TRY(check_f16_range(L->eng, t[q++], (size_t)H * L->V, "lstm_load (embedding)"));
+    for (int k = 0; k < (L->feed ? 8 : 4); ++k) ZR_TRY(check_f16_range(L->eng, t[q + k], HH, "lstm_load"));
+  }
   cudaFree(L->W); cudaFree(L->Wh); cudaFree(L->Mx); cudaFree(L->Q); cudaFree(L->b);
   L->W = L->Wh = L->Mx = L->Q = L->b = nullptr;
   L->loaded = false;
@@ -805,7 +842,7 @@ static int gather_act(zrnn_lstm_layer* L, const int* ids, int n, const Act& x, c
   }
   const size_t rb = (size_t)L->Kpad * eng_eb(L->eng);
   ZR_CUDA(zrnn::launch_gather_rows16(L->emb.hi, rb, ids, n, x.hi, st));
-  if (L->eng == ENG_X3) ZR_CUDA(zrnn::launch_gather_rows16(L->emb.lo, (size_t)L->Kpad * 4, ids, n, x.lo, st));
+  if (eng_split(L->eng)) ZR_CUDA(zrnn::launch_gather_rows16(L->emb.lo, rb, ids, n, x.lo, st));
   return ZRNN_OK;
 }
 
@@ -826,9 +863,9 @@ static int layer_forward_f32(zrnn_lstm_layer* L, const int* d_ids, const float* 
   } else {
     if (d_ids) {
       ZR_CUDA(L->sc_x.reserve((size_t)B * L->Kpad * eng_eb(L->eng)));
-      if (L->eng == ENG_X3) ZR_CUDA(L->sc_xl.reserve((size_t)B * L->Kpad * 4));
+      if (eng_split(L->eng)) ZR_CUDA(L->sc_xl.reserve((size_t)B * L->Kpad * eng_eb(L->eng)));
       x.hi = L->sc_x.p;
-      x.lo = L->eng == ENG_X3 ? L->sc_xl.as<float>() : nullptr;
+      x.lo = eng_split(L->eng) ? L->sc_xl.as<float>() : nullptr;
       ZR_TRY(gather_act(L, d_ids, B, x, st));
     } else {
       ZR_TRY(to_operand(d_x, H, L->Kpad, B, L->eng, L->sc_x, L->sc_xl, &x, st));
@@ -887,6 +924,7 @@ int zrnn_att_load(zrnn_attention* A, const float* const* t, int n) {
   for (int i = 0; i < n; ++i) ZR_CHECK(t[i], "att_load: null tensor");
   const int H = A->H;
   const size_t HH = (size_t)H * H;
+  for (int i : {0, 1, 4, 5}) ZR_TRY(check_f16_range(A->eng, t[i], HH, "att_load"));
   cudaFree(A->WpWaT); cudaFree(A->v_p); cudaFree(A->bias); cudaFree(A->Wc1); cudaFree(A->Wc2);
   A->WpWaT = A->v_p = A->bias = A->Wc1 = A->Wc2 = nullptr;
   A->loaded = false;
@@ -974,12 +1012,13 @@ int zrnn_softmax_create(int V, int H, int dtype, int shard_lo, int shard_hi, zrn
   ZR_TRY(check_device());
   auto* S = new zrnn_softmax();
   S->V = V; S->H = H; S->dtype = dtype; S->lo = shard_lo; S->hi = shard_hi; S->eng = eng; S->Kpad = round64(H);
-  S->BN = eng == ENG_X3 ? 128 : 256;
+  S->BN = eng_split(eng) ? 128 : 256;
   *out = S;
   return ZRNN_OK;
 }
 int zrnn_softmax_load(zrnn_softmax* S, const float* h_D, const float* h_b_d) {
   ZR_CHECK(S && h_D && h_b_d, "softmax_load: null argument");
+  ZR_TRY(check_f16_range(S->eng, h_D, (size_t)S->V * S->H, "softmax_load"));
   cudaFree(S->D); cudaFree(S->b);
   S->D = S->b = nullptr;
   S->loaded = false;
@@ -1247,7 +1286,7 @@ static size_t act_bytes(const Geom& g, size_t cols, bool f32, bool op) {
   if (f32) b += aligned(sizeof(float) * cols * g.H);
   if (op && g.eng != ENG_SIMT) {
     b += aligned(cols * g.Kpad * eng_eb(g.eng));
-    if (g.eng == ENG_X3) b += aligned(cols * g.Kpad * 4);
+    if (eng_split(g.eng)) b += aligned(cols * g.Kpad * eng_eb(g.eng));
   }
   return b;
 }
@@ -1256,14 +1295,14 @@ static Act act_take(Carver& cv, const Geom& g, size_t cols, bool f32, bool op) {
   if (f32) a.f32 = cv.take<float>(cols * g.H);
   if (op && g.eng != ENG_SIMT) {
     a.hi = cv.take<char>(cols * g.Kpad * eng_eb(g.eng));
-    if (g.eng == ENG_X3) a.lo = cv.take<float>(cols * g.Kpad);
+    if (eng_split(g.eng)) a.lo = (float*)cv.take<char>(cols * g.Kpad * eng_eb(g.eng));
   }
   return a;
 }
 static int act_zero(const Act& a, const Geom& g, size_t cols, cudaStream_t s) {
   if (a.f32) ZR_CUDA(cudaMemsetAsync(a.f32, 0, sizeof(float) * cols * g.H, s));
   if (a.hi) ZR_CUDA(cudaMemsetAsync(a.hi, 0, cols * g.Kpad * eng_eb(g.eng), s));
-  if (a.lo) ZR_CUDA(cudaMemsetAsync(a.lo, 0, cols * g.Kpad * 4, s));
+  if (a.lo) ZR_CUDA(cudaMemsetAsync(a.lo, 0, cols * g.Kpad * eng_eb(g.eng), s));
   return ZRNN_OK;
 }
 
@@ -1528,11 +1567,11 @@ struct BeamModel {
     ga[0].src[ga[0].n_arrays] = srcA.f32; ga[0].dst[ga[0].n_arrays++] = dstA.f32;
     if (tc) {
       ga[1].src[ga[1].n_arrays] = (const float*)srcA.hi; ga[1].dst[ga[1].n_arrays++] = (float*)dstA.hi;
-      if (g.eng == ENG_X3) { ga[2].src[ga[2].n_arrays] = srcA.lo; ga[2].dst[ga[2].n_arrays++] = dstA.lo; }
+      if (eng_split(g.eng)) { ga[2].src[ga[2].n_arrays] = srcA.lo; ga[2].dst[ga[2].n_arrays++] = dstA.lo; }
     }
   }
   int run_gathers(zrnn::ColGatherArgs* ga, const int* map, cudaStream_t s) const {
-    ga[0].H = g.H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad;
+    ga[0].H = g.H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad * eng_eb(g.eng) / 4;
     for (int k = 0; k < 3; ++k) {
       if (ga[k].n_arrays == 0) continue;
       ga[k].n_cols = NB; ga[k].map = map;
@@ -1919,7 +1958,7 @@ int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw
               float* d_C, int ldc, void* stream) {
   ZR_CHECK(d_W && d_X && d_C && n_rows > 0 && m_cols > 0 && K > 0, "gemm: bad arguments");
   ZR_CHECK(ldw >= n_rows && ldx >= K && ldc >= n_rows, "gemm: leading dimension too small");
-  ZR_CHECK(mode >= 0 && mode <= 3, "gemm: mode must be 0 (fp32 SIMT), 1 (bf16), 2 (tf32) or 3 (3xtf32)");
+  ZR_CHECK(mode >= 0 && mode <= 4, "gemm: mode must be 0 (fp32 SIMT), 1 (bf16), 2 (tf32), 3 (3xtf32) or 4 (fp16 split)");
   cudaStream_t st = (cudaStream_t)stream;
   if (mode == 0) {
     zrnn::GemmArgs g;
@@ -1930,9 +1969,10 @@ int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw
     ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (n_rows >= 256 && m_cols >= 96) ? 1 : 0, st));
     return ZRNN_OK;
   }
-  const int tcm = mode == 1 ? zrnn::TC_BF16 : (mode == 2 ? zrnn::TC_TF32 : zrnn::TC_TF32X3);
-  const int op_mode = mode == 1 ? 0 : (mode == 2 ? 1 : 2);
-  const int eb = mode == 1 ? 2 : 4;
+  const int tcm = mode == 1 ? zrnn::TC_BF16 : (mode == 2 ? zrnn::TC_TF32 : (mode == 3 ? zrnn::TC_TF32X3 : zrnn::TC_F16X2));
+  const int op_mode = mode == 1 ? 0 : (mode == 2 ? 1 : (mode == 3 ? 2 : 3));
+  const int eb = (mode == 1 || mode == 4) ? 2 : 4;
+  const bool split = mode >= 3;
   const int kb_elems = 128 / eb;
   const int Kpad = (K + 63) / 64 * 64;
   const int BN = n_rows >= 256 ? 256 : (n_rows >= 128 ? 128 : (n_rows >= 64 ? 64 : 32));
@@ -1943,11 +1983,11 @@ int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw
   ZR_CUDA(b_hi.reserve(b_elems * eb));
   ZR_CUDA(cudaMemsetAsync(a_hi.p, 0, a_elems * eb, st));
   ZR_CUDA(cudaMemsetAsync(b_hi.p, 0, b_elems * eb, st));
-  if (mode == 3) {
-    ZR_CUDA(a_lo.reserve(a_elems * 4));
-    ZR_CUDA(b_lo.reserve(b_elems * 4));
-    ZR_CUDA(cudaMemsetAsync(a_lo.p, 0, a_elems * 4, st));
-    ZR_CUDA(cudaMemsetAsync(b_lo.p, 0, b_elems * 4, st));
+  if (split) {
+    ZR_CUDA(a_lo.reserve(a_elems * eb));
+    ZR_CUDA(b_lo.reserve(b_elems * eb));
+    ZR_CUDA(cudaMemsetAsync(a_lo.p, 0, a_elems * eb, st));
+    ZR_CUDA(cudaMemsetAsync(b_lo.p, 0, b_elems * eb, st));
   }
   ZR_CUDA(zrnn::launch_convert_rows(d_X, m_cols, K, ldx, op_mode, a_hi.p, a_lo.as<float>(), Kpad, st));
   zrnn::PackArgs pk;
@@ -1959,9 +1999,9 @@ int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw
   std::memset(&tp, 0, sizeof(tp));
   bool ok = zrnn::make_kmajor_map(&tp.a[0], a_hi.p, eb, Kpad, m_cols, Kpad, 128) &&
             zrnn::make_kmajor_map(&tp.b, b_hi.p, eb, Kpad, (long long)n_tiles * BN, Kpad, BN);
-  if (mode == 3)
-    ok = ok && zrnn::make_kmajor_map(&tp.a_lo[0], a_lo.p, 4, Kpad, m_cols, Kpad, 128) &&
-         zrnn::make_kmajor_map(&tp.b_lo, b_lo.p, 4, Kpad, (long long)n_tiles * BN, Kpad, BN);
+  if (split)
+    ok = ok && zrnn::make_kmajor_map(&tp.a_lo[0], a_lo.p, eb, Kpad, m_cols, Kpad, 128) &&
+         zrnn::make_kmajor_map(&tp.b_lo, b_lo.p, eb, Kpad, (long long)n_tiles * BN, Kpad, BN);
   if (!ok) {
     a_hi.release(); a_lo.release(); b_hi.release(); b_lo.release();
     return fail(ZRNN_E_CUDA, "gemm: cannot encode TMA tensor maps");
