@@ -52,8 +52,10 @@ WORKLOADS = {
 
 
 ARITH = {
-    "f32": "fp32-accurate: tcgen05 3xTF32 (hi/lo split operands, fp32 accumulate) when H >= 128, else fp32 FMA",
+    "f32": "fp32-accurate: tcgen05 on split operands (fp16 hi + scaled fp16 lo: 3 MMAs per product, fp32 accumulate) "
+           "when H >= 128, else fp32 FMA",
     "f32_3xtf32": "fp32-accurate: tcgen05 3xTF32 (hi/lo split operands, fp32 accumulate)",
+    "f32_f16x2": "fp32-accurate: tcgen05 on fp16 hi + scaled fp16 lo operands (3 MMAs per product, fp32 accumulate)",
     "f32_simt": "exact fp32 FMA kernels",
     "bf16": "tcgen05 bf16 operands, fp32 accumulate and state",
     "tf32": "tcgen05 tf32 operands, fp32 accumulate and state",
@@ -217,7 +219,7 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
     from zoph_rnn_b200 import api
 
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
-    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[dtype]
+    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4, f32_f16x2=5)[dtype]
     model = api.neuralMT_model(cfg, dtype=dtype_id)
     model.load_weights(weights)
     del weights
@@ -338,7 +340,7 @@ def run_c5_sharded(args, w, cfg, rank, world):
     import torch.distributed as dist
     from zoph_rnn_b200 import sharded
     weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
-    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[args.dtype]
+    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4, f32_f16x2=5)[args.dtype]
     scorer = sharded.VocabShardedScorer(sharded.CudaEngine(cfg, weights, rank, world, dtype=dtype_id), rank, world)
     del weights
     inp = make_inputs(w, 1234)  # the same minibatch on every rank
@@ -383,7 +385,7 @@ def cell_phases(w, dtype_name):
     for g in range(4):
         tensors += [mats[g], np.zeros(H, np.float32)]
     tensors += mats[4:]
-    layer = api.Hidden_To_Hidden_Layer(H, dtype=dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4)[dtype_name])
+    layer = api.Hidden_To_Hidden_Layer(H, dtype=dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4, f32_f16x2=5)[dtype_name])
     layer.load_weights(tensors)
     x, h0, c0 = (torch.randn(H * B, device="cuda") for _ in range(3))
     mask = torch.ones(B, dtype=torch.int32, device="cuda")
@@ -414,8 +416,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32"],
-                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate, 3xTF32 tensor cores when H >= 128)")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32", "f32_f16x2"],
+                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate: split-operand tensor cores when H >= 128)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16", action="store_true", help="skip the additional bf16 measurement of an f32 run")
     ap.add_argument("--cell-phases", action="store_true",
@@ -488,7 +490,8 @@ def main():
 
 # DRAM traffic per launch of the dominant kernels from ncu (dram__bytes_read.sum + dram__bytes_write.sum), captured on
 # the c2s stand-in, whose layer shapes are config 2's (see profiles/*.md); keyed by (kernel class, dtype).
-NCU_TRAFFIC = {("lstm_cell", "f32"): 71.7e6, ("lstm_cell", "bf16"): 17.9e6}
+NCU_TRAFFIC = {("lstm_cell", "f32"): 35.2e6, ("lstm_cell", "f32_f16x2"): 35.2e6, ("lstm_cell", "f32_3xtf32"): 71.6e6,
+               ("lstm_cell", "bf16"): 17.9e6}
 
 
 def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
@@ -511,8 +514,8 @@ def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         out.update(bound="tensor", unit="TFLOP/s", peak=peak, achieved=flops / avg_s / 1e12,
                    algorithmic_flops_per_launch=flops,
-                   note="2*V*H*N flops; peak = measured sustained bf16 cuBLAS (also the denominator for the 3xTF32 "
-                        "fp32-accurate mode, which spends 3 tensor-core passes per product)")
+                   note="2*V*H*N flops; peak = measured sustained bf16 cuBLAS (also the denominator for the "
+                        "fp32-accurate modes, which spend 3 tensor-core passes per product)")
     elif top == "lstm_cell":
         L = cfg["num_layers"]
         mats = 8.0

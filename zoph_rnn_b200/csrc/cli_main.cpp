@@ -94,7 +94,7 @@ const OptSpec kOptions[] = {
     {"print-beam", 0, 1, 'i'},
     // options of this program (no counterpart in the reference)
     {"attention-type", 0, 1, 'i'},  // local-p (default, what the reference's files hold) | global-dot
-    {"dtype", 0, 1, 'i'},           // f32 (default) | bf16 | tf32 | f32-simt
+    {"dtype", 0, 1, 'i'},           // f32 (default) | bf16 | tf32 | f32-simt | f32-3xtf32 | f32-f16x2
     {"device-batch", 0, 1, 'i'},    // columns per device launch group (default 256 scoring, 32 sentences decoding)
     {"prep-only", 0, 0, 'i'},       // stop after writing the integer files into the tmp directory
     {"keep-tmp", 0, 0, 'i'},        // do not delete the tmp directory
@@ -601,7 +601,7 @@ void print_help() {
       "  -M, --multi-gpu I ...   device indices; the first is used\n"
       "      --attention-width D local attention half window (default 10)\n"
       "      --tmp-dir-location DIR, --logfile FILE, --legacy-model B\n"
-      "  options of this program: --attention-type local-p|global-dot, --dtype f32|bf16|tf32|f32-simt,\n"
+      "  options of this program: --attention-type local-p|global-dot, --dtype f32|bf16|tf32|f32-simt|f32-3xtf32|f32-f16x2,\n"
       "      --device-batch N, --prep-only, --keep-tmp, --int-input\n";
 }
 
@@ -654,7 +654,9 @@ int main(int argc, char** argv) {
     else if (t == "bf16") p.dtype = ZRNN_BF16;
     else if (t == "tf32") p.dtype = ZRNN_TF32;
     else if (t == "f32-simt") p.dtype = ZRNN_F32_SIMT;
-    else die("--dtype is f32, bf16, tf32 or f32-simt");
+    else if (t == "f32-3xtf32") p.dtype = ZRNN_F32_3XTF32;
+    else if (t == "f32-f16x2") p.dtype = ZRNN_F32_F16X2;
+    else die("--dtype is f32, bf16, tf32, f32-simt, f32-3xtf32 or f32-f16x2");
   }
   if (p.minibatch <= 0) die("minibatch size must be positive");
   if (p.longest_sent < 4) die("longest-sent is too small");
