@@ -183,6 +183,50 @@ __device__ __forceinline__ void store8_operand(const TcParams& p, size_t idx, co
     if (p.op_lo) store8_f32(p.op_lo, idx, lo, nvalid);
   }
 }
+// four consecutive values (the 8-warp LSTM epilogue): same destinations as store8_f32 / store8_operand
+__device__ __forceinline__ void store4_f32(float* base, size_t idx, const float* v, int nvalid) {
+  if (nvalid == 4 && (idx & 3) == 0) {
+    *reinterpret_cast<float4*>(base + idx) = make_float4(v[0], v[1], v[2], v[3]);
+  } else {
+    for (int u = 0; u < nvalid; ++u) base[idx + u] = v[u];
+  }
+}
+__device__ __forceinline__ void store4_operand(const TcParams& p, size_t idx, const float* v, int nvalid) {
+  const bool vec = nvalid == 4 && (idx & 3) == 0;
+  if (p.op_b16) {
+    if (vec) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&a); pk.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(p.op_b16 + idx) = pk;
+    } else {
+      for (int u = 0; u < nvalid; ++u) p.op_b16[idx + u] = __float2bfloat16(v[u]);
+    }
+  }
+  if (p.op_h_hi) {
+    __align__(8) __half hi[4];
+    __align__(8) __half lo[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      hi[u] = __float2half_rn(v[u]);
+      lo[u] = __float2half_rn((v[u] - __half2float(hi[u])) * 2048.0f);
+    }
+    if (vec) {
+      *reinterpret_cast<uint2*>(p.op_h_hi + idx) = *reinterpret_cast<const uint2*>(hi);
+      *reinterpret_cast<uint2*>(p.op_h_lo + idx) = *reinterpret_cast<const uint2*>(lo);
+    } else {
+      for (int u = 0; u < nvalid; ++u) { p.op_h_hi[idx + u] = hi[u]; p.op_h_lo[idx + u] = lo[u]; }
+    }
+  }
+  if (p.op_hi) {
+    float hi[4], lo[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { hi[u] = tf32_round_dev(v[u]); lo[u] = v[u] - hi[u]; }
+    store4_f32(p.op_hi, idx, hi, nvalid);
+    if (p.op_lo) store4_f32(p.op_lo, idx, lo, nvalid);
+  }
+}
+
 // Mode traits.  "Split" modes keep every operand as a hi part plus a residual lo part and spend three MMAs per
 // k-step (hi*hi into the main accumulators, lo*hi and hi*lo into the cross accumulator):
 //   TC_TF32X3: fp32 storage, hi = value rounded to tf32, lo = value - hi
@@ -285,7 +329,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // in a fixed order.  This keeps the number of CTAs high for skinny problems (one 128-row M tile) without every CTA
 // re-reading the whole A operand.
 template <int BN, int MODE, int EPI, int SPLITK>
-__global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+__global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
   constexpr int ST = num_stages(BN, MODE, SPLITK);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
@@ -423,11 +467,23 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
   const int lrow = warp * 32 + lane;
   const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
   // the LSTM epilogue's global operands do not depend on the accumulators: fetch them while the main loop runs
+  // With a 256-thread block (split-K LSTM cells that own 8 hidden units per CTA) the math after the exchange is
+  // spread over all 8 warps: thread t finishes row t % 128, hidden units 4 * (t / 128) .. + 4 of the CTA's 8.
+  const bool wide = EPI == TC_EPI_LSTM && SPLITK > 1 && BN / 4 / SPLITK == 8 && blockDim.x == 256;
+  const int wrow = m0 + (threadIdx.x & 127), whalf = threadIdx.x >> 7;
   float pre_c[8];
   if constexpr (EPI == TC_EPI_LSTM) {
     constexpr int TH = BN / 4;
     constexpr int TH_OWN = TH / SPLITK;
-    if (TH_OWN == 8 && epi_warp) {
+    if (wide) {
+      const int H = p.N;
+      const int hidb = n_tile * TH + rank * TH_OWN + whalf * 4;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int hid = hidb + u;
+        pre_c[u] = (hid < H && wrow < p.M) ? p.c_prev[(size_t)wrow * H + hid] : 0.f;
+      }
+    } else if (TH_OWN == 8 && epi_warp) {
       const int H = p.N;
       const int hidb = n_tile * TH + rank * TH_OWN;
 #pragma unroll
@@ -551,6 +607,49 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_kernel(const __grid_constant__
       }
     }
   };
+  if constexpr (EPI == TC_EPI_LSTM && SPLITK > 1) {
+    if (wide) {
+      constexpr int TH = BN / 4, TH_OWN = TH / SPLITK;
+      const int H = p.N;
+      if (!abort_s && wrow < p.M) {
+        const int r = threadIdx.x & 127;
+        float g[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int rk = 0; rk < SPLITK; ++rk) {  // fixed order: deterministic sums
+            const float4 t = slots[((size_t)rk * (OWNC / 4) + (q * TH_OWN) / 4 + whalf) * 128 + r];
+            acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+          }
+          g[q][0] = acc.x; g[q][1] = acc.y; g[q][2] = acc.z; g[q][3] = acc.w;
+        }
+        ZR_STAMP(5);
+        const float mk = p.mask ? (float)p.mask[wrow] : 1.0f;
+        const int jb = rank * TH_OWN + whalf * 4;  // first hidden unit inside the tile
+        const int hb = n_tile * TH + jb;
+        const int nvalid = H - hb >= 4 ? 4 : (H - hb > 0 ? H - hb : 0);
+        float hv[4], cvv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float gi = act_sigmoid<MODE>(g[0][u] + s_bias[jb + u]);
+          const float gf = act_sigmoid<MODE>(g[1][u] + s_bias[TH + jb + u]);
+          const float gg = act_tanh<MODE>(g[2][u] + s_bias[2 * TH + jb + u]);
+          const float go = act_sigmoid<MODE>(g[3][u] + s_bias[3 * TH + jb + u]);
+          const float c = gf * pre_c[u] + gi * gg;
+          hv[u] = go * act_tanh<MODE>(c) * mk;
+          cvv[u] = c * mk;
+        }
+        ZR_STAMP(6);
+        if (nvalid > 0) {
+          store4_f32(p.c_out, (size_t)wrow * H + hb, cvv, nvalid);
+          if (p.C) store4_f32(p.C, (size_t)wrow * p.ldc + hb, hv, nvalid);
+          store4_operand(p, (size_t)wrow * p.ld_op + hb, hv, nvalid);
+        }
+      }
+      ready = false;  // the 4-warp epilogue below is skipped
+    }
+  }
   if (epi_warp && ready) {
     const bool row_ok = row < p.M;
     const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
@@ -969,7 +1068,7 @@ cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(192);
+  cfg.blockDim = dim3((EPI == TC_EPI_LSTM && SPLITK > 1 && BN / 4 / SPLITK == 8) ? 256 : 192);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
