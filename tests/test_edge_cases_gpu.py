@@ -1,0 +1,109 @@
+"""Edge cases of the scoring and decoding entry points: empty and ragged minibatches, one-word sentences, columns
+that are padding only, the longest sentences the reference's file preparation lets through, hypothesis lists that
+come back short.  Every result is compared with the CPU oracle on the same inputs."""
+import numpy as np
+import pytest
+
+from zoph_rnn_b200 import synth
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from zoph_rnn_b200 import api as a
+    return a
+
+
+def build(api, cfg, w, dtype):
+    m = api.neuralMT_model(cfg, dtype=dtype)
+    m.load_weights(w)
+    return m
+
+
+@pytest.mark.parametrize("dtype", [3, 5])
+def test_ragged_minibatch_with_padding_only_columns(api, oracle, dtype):
+    """Sentences of length 1 next to the longest ones, and two columns that hold nothing but -1 (the filler rows the
+    reference appends to complete a minibatch): their log-probs are exactly 0 and the other columns are unaffected."""
+    cfg = synth.make_cfg(2, 128, 90, 120, attention=1, feed_input=1, D=2)
+    w = synth.make_weights(cfg, seed=51, scale=0.2)
+    rng = np.random.default_rng(3)
+    B, S, T = 9, 13, 15
+    src = np.full((S, B), -1, np.int32)
+    tin = np.full((T, B), -1, np.int32)
+    tout = np.full((T, B), -1, np.int32)
+    lens_s = [13, 1, 7, 1, 13, 2, 5, 0, 0]
+    lens_t = [14, 1, 1, 14, 6, 2, 9, 0, 0]   # number of target words (the rows hold len + 1 ids)
+    for b in range(B):
+        if lens_s[b] == 0:
+            continue
+        src[S - lens_s[b]:, b] = rng.integers(0, 90, lens_s[b])
+        y = rng.integers(3, 120, lens_t[b])
+        tin[:lens_t[b] + 1, b] = np.concatenate([[0], y])
+        tout[:lens_t[b] + 1, b] = np.concatenate([y, [1]])
+    # padding-only columns still need one source id for the reference's layout; the oracle and the library treat a
+    # column without any source word as length 0, so give them a single <UNK> and an all -1 target
+    src[S - 1, 7:] = 0
+    want = oracle.OracleModel(cfg, w).score_batch(src, tin, tout)
+    got, total = build(api, cfg, w, dtype).get_error(src, tin, tout)
+    helpers.assert_logp_close(got, want, rtol=2e-5, atol=3e-6)
+    assert np.all(got[:, 7:] == 0.0)
+    assert abs(total - want.sum()) < 1e-4 * abs(want.sum())
+
+
+@pytest.mark.parametrize("dtype", [3, 5])
+def test_single_column_single_step(api, oracle, dtype):
+    cfg = synth.make_cfg(1, 128, 0, 64, lm=True)
+    w = synth.make_weights(cfg, seed=52, scale=0.3)
+    tin = np.array([[0]], np.int32)
+    tout = np.array([[1]], np.int32)
+    want = oracle.OracleModel(cfg, w).score_batch(None, tin, tout)
+    got, _ = build(api, cfg, w, dtype).get_error(None, tin, tout)
+    helpers.assert_logp_close(got, want, rtol=2e-5, atol=3e-6)
+
+
+def test_empty_minibatch_is_a_no_op(api):
+    cfg = synth.make_cfg(1, 128, 0, 64, lm=True)
+    m = build(api, cfg, synth.make_weights(cfg, seed=53), 0)
+    lp, total = m.get_error(None, np.zeros((0, 4), np.int32), np.zeros((0, 4), np.int32))
+    assert lp.size == 0 and total == 0.0
+    ids, ln, sc = build(api, synth.make_cfg(1, 128, 50, 64), synth.make_weights(synth.make_cfg(1, 128, 50, 64), seed=54),
+                        0).decode([], beam=4)
+    assert ids.shape[0] == 0 and ln.shape[0] == 0
+
+
+@pytest.mark.parametrize("dtype", [3, 5])
+def test_longest_sentences_the_file_preparation_keeps(api, oracle, dtype):
+    """-L 100: the reference keeps sentences with len + 1 < L - 2, i.e. up to 96 words (97 target positions)."""
+    cfg = synth.make_cfg(1, 128, 300, 300, attention=1, feed_input=1, D=10)
+    w = synth.make_weights(cfg, seed=55, scale=0.15)
+    src, tin, tout = synth.make_s2s_batch(300, 300, 3, 96, 96, 96, 96, seed=8)
+    assert src.shape[0] == 96 and tin.shape[0] >= 96
+    want = oracle.OracleModel(cfg, w).score_batch(src, tin, tout)
+    got, _ = build(api, cfg, w, dtype).get_error(src, tin, tout)
+    helpers.assert_logp_close(got, want, rtol=3e-5, atol=3e-6)
+
+
+@pytest.mark.parametrize("dtype", [3, 5])
+def test_decode_limits_and_short_hypothesis_lists(api, oracle, dtype):
+    """One-word sources (the step limit (int)(max_ratio * S) is 1), a k-best request larger than the number of
+    finished hypotheses, and a min ratio that filters everything: lengths of 0 mark the missing entries."""
+    cfg = synth.make_cfg(1, 128, 80, 100, attention=1, feed_input=1, D=2)
+    w = synth.make_weights(cfg, seed=56, scale=0.3)
+    srcs = [np.array([5], np.int32), np.array([7, 9], np.int32), np.array([3], np.int32)]
+    om = oracle.OracleModel(cfg, w)
+    m = build(api, cfg, w, dtype)
+    short = 0
+    for kw in (dict(beam=3, k_best=8, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=20),
+               dict(beam=3, k_best=2, min_ratio=50.0, max_ratio=60.0, penalty=0.0, longest_sent=20),
+               dict(beam=9, k_best=3, min_ratio=0.0, max_ratio=40.0, penalty=0.5, longest_sent=6)):
+        ids, ln, sc = om.beam_decode(srcs, **kw)
+        gi, gl, gs = m.decode(srcs, **kw)
+        assert np.array_equal(gl, ln), (kw, gl, ln)
+        assert np.array_equal(gi, ids)
+        np.testing.assert_allclose(gs[ln > 0], sc[ln > 0], rtol=1e-5, atol=1e-4)
+        short += int((ln == 0).sum())
+    assert short > 0  # the first two settings leave k-best slots empty

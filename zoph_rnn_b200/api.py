@@ -309,9 +309,13 @@ class neuralMT_model:
         id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k]); with want_align also the viterbi
         alignment stored with every hypothesis position [n,k,longest_sent+4] (src/decoder.h:1266-1267)."""
         n = len(sources)
+        Lmax = longest_sent + 4
+        if n == 0:
+            empty = (np.empty((0, k_best, Lmax), np.int32), np.empty((0, k_best), np.int32),
+                     np.empty((0, k_best), np.float32))
+            return empty + (np.empty((0, k_best, Lmax), np.int32),) if want_align else empty
         flat = np.ascontiguousarray(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]), dtype=np.int32)
         lens = np.ascontiguousarray([len(s) for s in sources], dtype=np.int32)
-        Lmax = longest_sent + 4
         ids = np.empty((n, k_best, Lmax), dtype=np.int32)
         ln = np.empty((n, k_best), dtype=np.int32)
         sc = np.empty((n, k_best), dtype=np.float32)
