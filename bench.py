@@ -86,7 +86,7 @@ def sample_clocks_start(path):
          "clocks_event_reasons.sw_power_cap")
     try:
         f = open(path, "w")
-        return subprocess.Popen(["nvidia-smi", "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "200"],
+        return subprocess.Popen(["nvidia-smi", "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "50"],
                                 stdout=f, stderr=subprocess.DEVNULL), f
     except OSError:
         return None, None
