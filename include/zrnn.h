@@ -299,6 +299,13 @@ int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int
                               const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
                               float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
                               float* out_score);
+/* The same with alignment tracking: the viterbi alignment of a step is the source position with the largest sum
+ * over the models of the attention weight at that position (ensembles_models, src/ensemble_factory.hpp:798-834);
+ * models without attention cast no vote.  out_align as in zrnn_beam_decode_batch_align. */
+int zrnn_beam_decode_ensemble_align(zrnn_model* const* models, int n_models, const int* const* src_ids,
+                                    const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
+                                    float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
+                                    float* out_score, int* out_align);
 int zrnn_model_destroy(zrnn_model* m);
 
 #ifdef __cplusplus

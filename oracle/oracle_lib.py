@@ -52,7 +52,7 @@ def lib():
         L.orc_beam_decode_ensemble.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.POINTER(c_int_p),
                                                ctypes.POINTER(c_int_p), ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int,
-                                               ctypes.c_int, c_int_p, c_int_p, c_float_p]
+                                               ctypes.c_int, c_int_p, c_int_p, c_float_p, c_int_p]
         L.orc_gather.argtypes = [c_float_p, ctypes.c_int, c_int_p, ctypes.c_int, c_float_p]
         L.orc_lstm_cell.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_float_p), c_float_p, c_float_p,
                                     c_float_p, c_float_p, c_int_p, c_float_p, c_float_p]
@@ -152,7 +152,7 @@ class OracleModel:
 
 
 def beam_decode_ensemble(models, sources_per_model, beam, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0,
-                         longest_sent=100):
+                         longest_sent=100, want_align=False):
     """Ensemble beam search (probability averaging, src/ensemble_factory.hpp:768-795): models = OracleModel list,
     sources_per_model[k] = the k-th model's reversed id lists.  Returns (ids [n,k,Lmax], len [n,k], score [n,k])."""
     K, n = len(models), len(sources_per_model[0])
@@ -165,9 +165,10 @@ def beam_decode_ensemble(models, sources_per_model, beam, k_best=1, min_ratio=0.
     hs = (ctypes.c_void_p * K)(*[m._h for m in models])
     fp = (c_int_p * K)(*[_ip(f) for f in flats])
     lp = (c_int_p * K)(*[_ip(l) for l in lens])
+    al = np.zeros((n, k_best, Lmax), dtype=np.int32) if want_align else None
     lib().orc_beam_decode_ensemble(hs, K, fp, lp, n, beam, k_best, min_ratio, max_ratio, penalty, longest_sent, Lmax,
-                                   _ip(ids), _ip(ln), _fp(sc))
-    return ids, ln, sc
+                                   _ip(ids), _ip(ln), _fp(sc), _ip(al))
+    return (ids, ln, sc, al) if want_align else (ids, ln, sc)
 
 
 def gather(W, H, ids):

@@ -478,6 +478,9 @@ struct DecModel {
   std::vector<float> hs_all, x, htild, htild_feed, P;
   std::vector<int> ones, ids, lenv, offv, vit;
   std::vector<float> scratch;
+  // attention weight per source position and beam column of the last forward step, [pos * beam + j]
+  // (BZ_CUDA::alignment_scores, attention_node.hpp:236-262); all zero without attention
+  std::vector<float> pos_score;
 
   void encode(const int* src) {
     const Cfg& c = m->cfg;
@@ -504,6 +507,7 @@ struct DecModel {
     // viterbi alignment per beam column of the last forward step (BZ_CUDA::viterbi_alignments; -1 without attention,
     // decoder.h:1174-1178)
     vit.assign(beam, -1);
+    pos_score.assign((size_t)S * beam, 0.f);
   }
   void forward(int idx, const std::vector<int>& cur) {
     const Cfg& c = m->cfg;
@@ -523,8 +527,22 @@ struct DecModel {
     }
     const float* top = h[L - 1].data();
     if (c.attention) {
+      const int Wn = 2 * c.D + 1;
+      std::vector<float> al((size_t)std::max(Wn, S) * beam, 0.f);
+      std::vector<int> ix((size_t)Wn * beam, -1);
       attention(c.attention, H, beam, c.D, m->att, h[L - 1].data(), ones.data(), hs_all.data(), S, lenv.data(),
-                offv.data(), htild.data(), nullptr, nullptr, vit.data(), 0.f);
+                offv.data(), htild.data(), al.data(), ix.data(), vit.data(), 0.f);
+      std::fill(pos_score.begin(), pos_score.end(), 0.f);
+      if (c.attention == ATT_LOCAL_P) {
+        for (int j = 0; j < Wn; ++j)
+          for (int b = 0; b < beam; ++b) {
+            const int pos = ix[(size_t)j * beam + b];
+            if (pos >= 0) pos_score[(size_t)pos * beam + b] = al[(size_t)j * beam + b];
+          }
+      } else {
+        for (int p2 = 0; p2 < S; ++p2)
+          for (int b = 0; b < beam; ++b) pos_score[(size_t)p2 * beam + b] = al[(size_t)p2 * beam + b];
+      }
       top = htild.data();
     }
     softmax_dist(V, H, beam, m->D, m->b_d, top, P.data());
@@ -568,11 +586,27 @@ void beam_decode_one(const std::vector<const Model*>& models, const std::vector<
   std::vector<int> top_vit((size_t)beam * Lmax, -20), top_vit_tmp((size_t)beam * Lmax, -20);
   const float* Pp = nullptr;
   const int* vitp = nullptr;
+  std::vector<int> ens_vit;
 
   auto forward_target = [&](int idx) {
     for (int k = 0; k < K; ++k) dm[k].forward(idx, cur);
     vitp = dm[0].vit.data();
     if (K == 1) { Pp = dm[0].P.data(); return; }
+    // alignment voting (ensemble_factory.hpp:798-834): sum the models' weights per source position, take the largest
+    // (the running maximum starts at 0: -1 when every sum is zero)
+    ens_vit.assign(beam, -1);
+    int smax = 0;
+    for (int k = 0; k < K; ++k) smax = std::max(smax, dm[k].S);
+    for (int j = 0; j < beam; ++j) {
+      float best = 0.f;
+      for (int p2 = 0; p2 < smax; ++p2) {
+        float sum = 0.f;
+        for (int k = 0; k < K; ++k)
+          if (p2 < dm[k].S) sum += dm[k].pos_score[(size_t)p2 * beam + j];
+        if (sum > best) { best = sum; ens_vit[j] = p2; }
+      }
+    }
+    vitp = ens_vit.data();
     Pens.resize((size_t)V * beam);
     for (int j = 0; j < beam; ++j) {
       float norm = 0.f;
@@ -768,7 +802,8 @@ void orc_beam_decode(void* p, const int* src_ids, const int* src_len, int n_sent
 // Ensemble decoding: n_models models, model k reads src_ids[k] / src_len[k] (concatenated reversed ids per sentence).
 void orc_beam_decode_ensemble(void* const* models, int n_models, const int* const* src_ids, const int* const* src_len,
                               int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
-                              int longest_sent, int Lmax_out, int* out_ids, int* out_len, float* out_score) {
+                              int longest_sent, int Lmax_out, int* out_ids, int* out_len, float* out_score,
+                              int* out_align) {
   std::vector<size_t> pos(n_models, 0);
   for (int s = 0; s < n_sent; ++s) {
     std::vector<const Model*> ms;
@@ -784,12 +819,15 @@ void orc_beam_decode_ensemble(void* const* models, int n_models, const int* cons
     beam_decode_one(ms, srcs, Ss, beam, k_best, min_ratio, max_ratio, penalty, longest_sent + 4, res);
     for (int k = 0; k < k_best; ++k) {
       int* dst = out_ids + ((size_t)s * k_best + k) * Lmax_out;
+      int* adst = out_align ? out_align + ((size_t)s * k_best + k) * Lmax_out : nullptr;
       for (int i = 0; i < Lmax_out; ++i) dst[i] = -1;
+      if (adst) for (int i = 0; i < Lmax_out; ++i) adst[i] = -1;
       out_len[(size_t)s * k_best + k] = 0;
       out_score[(size_t)s * k_best + k] = 0;
       if (k < (int)res.size()) {
         const int n = std::min((int)res[k].ids.size(), Lmax_out);
         for (int i = 0; i < n; ++i) dst[i] = res[k].ids[i];
+        if (adst) for (int i = 0; i < n; ++i) adst[i] = res[k].align[i];
         out_len[(size_t)s * k_best + k] = (int)res[k].ids.size();
         out_score[(size_t)s * k_best + k] = res[k].score;
       }

@@ -218,6 +218,34 @@ def test_ensemble_decoding_matches_oracle(api, oracle, dtype):
     assert not np.array_equal(alone[2], gs)
     one = api.decode_ensemble([ma], [sa], **kw)
     assert np.array_equal(one[0], alone[0]) and np.array_equal(one[2], alone[2])
+    # alignment voting over the models (only the first has attention here, so its weights decide)
+    _, _, _, wal = oracle.beam_decode_ensemble([oa, ob], [sa, sb], want_align=True, **kw)
+    ai, al_len, _, gal = api.decode_ensemble([ma, mb], [sa, sb], want_align=True, **kw)
+    assert np.array_equal(ai, gi) and np.array_equal(al_len, gl)
+    same = (gal == wal)[agree]
+    assert same.mean() >= 0.995, f"alignment agreement {same.mean():.4f}"
+
+
+@pytest.mark.parametrize("dtype", [3, 5])
+def test_ensemble_alignment_voting_of_two_attention_models(api, oracle, dtype):
+    """Both models attend (local-p and global): the alignment of a step is the position with the largest summed
+    weight (src/ensemble_factory.hpp:798-834)."""
+    cfg_a = synth.make_cfg(1, 128, 200, 300, attention=1, feed_input=1, D=3)
+    cfg_b = synth.make_cfg(2, 128, 150, 300, attention=2, feed_input=0)
+    wa = synth.make_weights(cfg_a, seed=43, scale=0.25)
+    wb = synth.make_weights(cfg_b, seed=44, scale=0.25)
+    sa = synth.make_decode_sources(200, 6, 3, 14, seed=8)
+    sb = synth.make_decode_sources(150, 6, 4, 9, seed=9)
+    kw = dict(beam=5, k_best=1, min_ratio=0.5, max_ratio=2.0, penalty=0.0, longest_sent=40)
+    ids, ln, sc, wal = oracle.beam_decode_ensemble([oracle.OracleModel(cfg_a, wa), oracle.OracleModel(cfg_b, wb)],
+                                                   [sa, sb], want_align=True, **kw)
+    gi, gl, gs, gal = api.decode_ensemble([build_model(api, cfg_a, wa, dtype), build_model(api, cfg_b, wb, dtype)],
+                                          [sa, sb], want_align=True, **kw)
+    agree = (gl == ln) & np.all(gi == ids, axis=2)
+    assert agree.mean() >= 0.995
+    same = (gal == wal)[agree]
+    assert same.mean() >= 0.98, f"alignment agreement {same.mean():.4f}"
+    assert (gal[agree][:, 1:3] >= 0).all()
 
 
 def test_f16_split_refuses_weights_outside_the_fp16_range(api):

@@ -117,6 +117,10 @@ SIGNATURES = {
                                                  ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                  ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int, c_void_p,
                                                  c_void_p, c_void_p]),
+    "zrnn_beam_decode_ensemble_align": (ctypes.c_int, [ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.POINTER(c_void_p),
+                                                       ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.c_int,
+                                                       ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                                       ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "zrnn_model_destroy": (ctypes.c_int, [c_void_p]),
 }
 

@@ -350,7 +350,7 @@ class neuralMT_model:
 
 
 def decode_ensemble(models, sources_per_model, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0,
-                    longest_sent=100):
+                    longest_sent=100, want_align=False):
     """ensemble_factory decoding with several models (src/ensemble_factory.hpp:583-795): sources_per_model[k] is the
     k-th model's list of reversed source id arrays.  Returns (ids [n,k,longest_sent+4], len [n,k], score [n,k])."""
     K, n = len(models), len(sources_per_model[0])
@@ -364,6 +364,13 @@ def decode_ensemble(models, sources_per_model, beam=12, k_best=1, min_ratio=0.5,
     hs = (ctypes.c_void_p * K)(*[m._h.value if isinstance(m._h, ctypes.c_void_p) else m._h for m in models])
     fp = (ctypes.c_void_p * K)(*[f.ctypes.data for f in flats])
     lp = (ctypes.c_void_p * K)(*[l.ctypes.data for l in lens])
+    if want_align:  # alignment voting over the models (src/ensemble_factory.hpp:798-834)
+        al = np.empty((n, k_best, Lmax), dtype=np.int32)
+        check(lib().zrnn_beam_decode_ensemble_align(hs, K, fp, lp, n, beam, k_best, min_ratio, max_ratio, penalty,
+                                                    longest_sent, ctypes.c_void_p(ids.ctypes.data),
+                                                    ctypes.c_void_p(ln.ctypes.data), ctypes.c_void_p(sc.ctypes.data),
+                                                    ctypes.c_void_p(al.ctypes.data)))
+        return ids, ln, sc, al
     check(lib().zrnn_beam_decode_ensemble(hs, K, fp, lp, n, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
                                           ctypes.c_void_p(ids.ctypes.data), ctypes.c_void_p(ln.ctypes.data),
                                           ctypes.c_void_p(sc.ctypes.data)))

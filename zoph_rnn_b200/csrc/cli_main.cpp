@@ -450,7 +450,6 @@ int run_decode(const Options& opt, Params& p) {
   if (model_names.size() != data_files.size()) die("the same number of inputs must be specified as models");
   const int K = (int)model_names.size();
   if (K > 8) die("at most 8 models can be ensembled");
-  if (K > 1 && !p.unk_file.empty()) die("--UNK-decode is available with a single model");
   if (p.beam <= 0) die("beam size cannot be <=0");
   if (p.penalty < 0) die("penalty cannot be less than zero");
   if (num_hypotheses <= 0) die("the number of outputs must be positive");
@@ -533,9 +532,10 @@ int run_decode(const Options& opt, Params& p) {
     } else {
       std::vector<const int*> fp(K), lp(K);
       for (int k = 0; k < K; ++k) { fp[k] = flat_k[k].data(); lp[k] = lens_k[k].data(); }
-      check_status(zrnn_beam_decode_ensemble(models.data(), K, fp.data(), lp.data(), ng, p.beam, num_hypotheses,
-                                             (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
-                                             ids.data(), len.data(), score.data()), "ensemble decoding");
+      check_status(zrnn_beam_decode_ensemble_align(models.data(), K, fp.data(), lp.data(), ng, p.beam, num_hypotheses,
+                                                   (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty,
+                                                   p.longest_sent, ids.data(), len.data(), score.data(),
+                                                   unk ? align.data() : nullptr), "ensemble decoding");
     }
     for (int i = 0; i < ng; ++i) {
       const size_t dst = (size_t)order[g0 + i] * num_hypotheses;

@@ -768,8 +768,10 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
   float* c = a.c_t + (size_t)b * H;
   if (a.mask && a.mask[b] != 1) {  // create_indicies_kernel: every window slot is -1 -> context 0
     for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
-    if (a.align_out)
-      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    if (a.align_out) {
+      const int n_out = a.align_by_pos ? a.S_max : Wn;
+      for (int j = tid; j < n_out; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    }
     if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
     return;
   }
@@ -826,8 +828,16 @@ __global__ void __launch_bounds__(256) att_local_kernel(const AttArgs a) {
     }
   }
   __syncthreads();
-  if (a.align_out)
-    for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+  if (a.align_out) {
+    if (a.align_by_pos) {
+      for (int s = tid; s < a.S_max; s += blockDim.x) {
+        const int j = s - lo;
+        a.align_out[(size_t)s * a.B + b] = (j >= 0 && j < Wn && s <= hi) ? s_al[j] : 0.f;
+      }
+    } else {
+      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+    }
+  }
   for (int i = tid; i < H; i += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < Wn; ++j) {
@@ -853,8 +863,10 @@ __global__ void __launch_bounds__(256) att_local_fast_kernel(const AttArgs a) {
   float* c = a.c_t + (size_t)b * H;
   if (a.mask && a.mask[b] != 1) {
     for (int i = tid; i < H; i += blockDim.x) { c[i] = 0.f; att_store_op(a, b, i, 0.f); }
-    if (a.align_out)
-      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    if (a.align_out) {
+      const int n_out = a.align_by_pos ? a.S_max : Wn;
+      for (int j = tid; j < n_out; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = 0.f;
+    }
     if (a.viterbi_out && tid == 0) a.viterbi_out[b] = -1;
     return;
   }
@@ -928,8 +940,16 @@ __global__ void __launch_bounds__(256) att_local_fast_kernel(const AttArgs a) {
       if (s_slot[j] == -1) s_slot[j] = 0;  // weight 0, any readable row
   }
   __syncthreads();
-  if (a.align_out)
-    for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+  if (a.align_out) {
+    if (a.align_by_pos) {
+      for (int s = tid; s < a.S_max; s += blockDim.x) {
+        const int j = s - lo;
+        a.align_out[(size_t)s * a.B + b] = (j >= 0 && j < Wn && s <= hi) ? s_al[j] : 0.f;
+      }
+    } else {
+      for (int j = tid; j < Wn; j += blockDim.x) a.align_out[(size_t)j * a.B + b] = s_al[j];
+    }
+  }
   if (tid < H4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const size_t colb = (size_t)sb * H;
@@ -1156,6 +1176,28 @@ __global__ void __launch_bounds__(256) ensemble_logmean_kernel(const EnsembleArg
     for (int k = 0; k < a.K; ++k) p += expf(a.logits[k][col + v] - s_max[k]) * s_inv[k];
     a.out[col + v] = logf(p);
   }
+}
+__global__ void ensemble_viterbi_kernel(const EnsembleVitArgs a) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= a.N) return;
+  int smax = 0;
+  for (int k = 0; k < a.K; ++k) smax = a.S_max[k] > smax ? a.S_max[k] : smax;
+  float best = 0.f;
+  int best_pos = -1;
+  for (int s = 0; s < smax; ++s) {
+    float sum = 0.f;
+    for (int k = 0; k < a.K; ++k)
+      if (s < a.S_max[k]) sum += a.align[k][(size_t)s * a.N + n];
+    if (sum > best) { best = sum; best_pos = s; }
+  }
+  a.viterbi_out[n] = best_pos;
+}
+cudaError_t launch_ensemble_viterbi(const EnsembleVitArgs& a, cudaStream_t st) {
+  if (a.N <= 0) return cudaSuccess;
+  if (a.K < 1 || a.K > ZR_ENSEMBLE_MAX) return cudaErrorInvalidValue;
+  ensemble_viterbi_kernel<<<(a.N + 127) / 128, 128, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
 }
 cudaError_t launch_ensemble_logmean(const EnsembleArgs& a, cudaStream_t st) {
   if (a.N <= 0) return cudaSuccess;

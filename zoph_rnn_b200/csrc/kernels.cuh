@@ -102,6 +102,9 @@ struct AttArgs {
   int ld_tq;
   float* c_t;          // context out, H x B
   float* align_out;    // optional
+  // local-p only: 0 = align_out holds the (2D+1) window weights [j*B+b]; 1 = S_max x B weights by source position
+  // [s*B+b] with zeros outside the window (what BZ_CUDA::alignment_scores holds, src/attention_node.hpp:236-262)
+  int align_by_pos;
   // optional: per target column the source position with the largest weight, -1 for a masked column
   // (get_viterbi_alignment_kernel, src/custom_kernels.h:1621-1635)
   int* viterbi_out;
@@ -130,6 +133,16 @@ struct EnsembleArgs {
   float* out;  // V x N
 };
 cudaError_t launch_ensemble_logmean(const EnsembleArgs& a, cudaStream_t st);
+// Alignment voting of an ensemble (ensembles_models, src/ensemble_factory.hpp:798-834): per column the source position
+// with the largest sum over the models of the attention weight at that position; the running maximum starts at 0,
+// so a column whose weights are all zero reports -1.  align[k] is S_max[k] x N by position.
+struct EnsembleVitArgs {
+  const float* align[ZR_ENSEMBLE_MAX];
+  int S_max[ZR_ENSEMBLE_MAX];
+  int K, N;
+  int* viterbi_out;  // [N]
+};
+cudaError_t launch_ensemble_viterbi(const EnsembleVitArgs& a, cudaStream_t st);
 
 // ---- beam bookkeeping (replaces decoder::expand_hypothesis_without_fsa / finish_current_hypotheses /
 // output_k_best_hypotheses, src/decoder.h:1157-1315, 672-688, 1386-1463, run on the host there)

@@ -426,7 +426,7 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
 }
 
 int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const Act& out, float* align,
-                cudaStream_t st, int* viterbi = nullptr, float viterbi_init = -1.f) {
+                cudaStream_t st, int* viterbi = nullptr, float viterbi_init = -1.f, bool align_by_pos = false) {
   const int H = A->H, eng = A->eng, Kpad = A->Kpad;
   ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
   KScope ks(KC_ATT, st);
@@ -435,6 +435,7 @@ int att_forward(zrnn_attention* A, const Act& h_t, const int* mask, int B, const
   a.H = H; a.B = B; a.D = A->D; a.S_max = A->S_max; a.B_src = A->B_src; a.cols_per_sent = A->cols_per_sent;
   a.hs = A->hs; a.len = A->len; a.offset = A->off; a.mask = mask; a.h_t = h_t.f32;
   a.c_t = A->ctx.as<float>(); a.align_out = align; a.viterbi_out = viterbi; a.viterbi_init = viterbi_init;
+  a.align_by_pos = align_by_pos ? 1 : 0;
   Act ctx;
   ctx.f32 = A->ctx.as<float>();
   if (eng != ENG_SIMT) {
@@ -1524,8 +1525,9 @@ struct BeamModel {
   std::vector<float*> cst[2], cp, cn;
   std::vector<int> cur;
   int* vit = nullptr;  // viterbi alignment per column of the last forward step (tracking on)
+  float* align_pos = nullptr;  // ensemble tracking: attention weights by source position, S_max x NB
 
-  size_t bytes(bool track) const {
+  size_t bytes(bool track, bool vote = false) const {
     const zrnn_model_config& c = m->cfg;
     const int H = c.H, L = c.num_layers;
     const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
@@ -1534,9 +1536,10 @@ struct BeamModel {
     b += 2 * (size_t)L * aligned(sizeof(float) * HBs);
     b += (2 * (size_t)L + 3) * act_bytes(g, NB, true, true) + 2 * (size_t)L * aligned(sizeof(float) * HB);
     if (track) b += aligned(sizeof(int) * NB);
+    if (vote) b += aligned(sizeof(float) * (size_t)S_max * NB);
     return b;
   }
-  void carve(Carver& cv, bool track) {
+  void carve(Carver& cv, bool track, bool vote = false) {
     const zrnn_model_config& c = m->cfg;
     const int H = c.H, L = c.num_layers;
     const size_t HBs = (size_t)H * n, HB = (size_t)H * NB, nS = (size_t)S_max * n;
@@ -1561,6 +1564,7 @@ struct BeamModel {
     htild_new = act_take(cv, g, NB, true, true);
     htild_feed = act_take(cv, g, NB, true, true);
     vit = track ? cv.take<int>(NB) : nullptr;
+    align_pos = vote ? cv.take<float>((size_t)S_max * NB) : nullptr;
   }
   // column gathers move whole operand rows: every array is expressed as floats-per-column
   void add_gather(zrnn::ColGatherArgs* ga, const Act& srcA, const Act& dstA) const {
@@ -1593,6 +1597,7 @@ struct BeamModel {
     ZR_TRY(run_encoder(m, g, src_id, src_mk, S_max, n, X0, zero, sseq, cst, cur, s));
     if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S_max, n, len, off, beam));
     if (vit) ZR_CUDA(cudaMemsetAsync(vit, 0xff, sizeof(int) * NB, s));  // -1 without attention (src/decoder.h:1174-1178)
+    if (align_pos) ZR_CUDA(cudaMemsetAsync(align_pos, 0, sizeof(float) * (size_t)S_max * NB, s));  // no attention: no votes
     // replicate the encoder's final (h,c) over the beam
     ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
     zrnn::ColGatherArgs ga[3];
@@ -1615,7 +1620,7 @@ struct BeamModel {
     }
     *top = xin;
     if (c.attention) {
-      ZR_TRY(att_forward(m->att, xin, nullptr, NB, htild_new, nullptr, s, vit, 0.f));
+      ZR_TRY(att_forward(m->att, xin, nullptr, NB, htild_new, align_pos, s, vit, 0.f, align_pos != nullptr));
       *top = htild_new;
     }
     return ZRNN_OK;
@@ -1652,7 +1657,6 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
     ZR_CHECK(S_max[k] > 0, "beam_decode: bad sizes");
   }
   ZR_CHECK(n_sent >= 0 && beam >= 1 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
-  ZR_CHECK(!(d_out_align && K > 1), "beam_decode: alignment tracking is available with a single model");
   if (n_sent == 0) return ZRNN_OK;
   const int cap = (int)std::sqrt((double)V);  // src/ensemble_factory.hpp:19-21
   if (beam > cap) beam = cap;
@@ -1675,6 +1679,7 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
     Tmax = std::max(Tmax, ms);
   }
   const bool track = d_out_align != nullptr;
+  const bool vote = track && K > 1;  // alignment voting over the models of an ensemble
   std::vector<BeamModel> bm(K);
   for (int k = 0; k < K; ++k) {
     BeamModel& b = bm[k];
@@ -1682,7 +1687,7 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
     b.g = Geom{models[k]->cfg.H, round64(models[k]->cfg.H), models[k]->eng};
     b.tc = models[k]->eng != ENG_SIMT;
     b.S_max = S_max[k]; b.n = n; b.NB = NB; b.beam = beam;
-    size_t bytes = b.bytes(track);
+    size_t bytes = b.bytes(track && k == 0, vote);
     if (k == 0) {  // shared bookkeeping lives in model 0's workspace
       bytes += 2 * aligned(sizeof(int) * n) + 2 * aligned(sizeof(int) * NB) + 2 * aligned(sizeof(int) * (size_t)NB * Lmax);
       bytes += aligned(sizeof(int) * (size_t)NB * kc) + 2 * aligned(sizeof(float) * NB) + aligned(sizeof(float) * (size_t)NB * kc);
@@ -1705,10 +1710,10 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
   int* vit_rows = track ? cv0.take<int>((size_t)NB * Lmax) : nullptr;
   int* vit_tmp = track ? cv0.take<int>((size_t)NB * Lmax) : nullptr;
   float* mean_logits = K > 1 ? cv0.take<float>((size_t)V * NB) : nullptr;
-  bm[0].carve(cv0, track);
+  bm[0].carve(cv0, track, vote);
   for (int k = 1; k < K; ++k) {
     Carver cv(models[k]->ws.p);
-    bm[k].carve(cv, false);
+    bm[k].carve(cv, false, vote);
   }
 
   ZR_CUDA(cudaMemcpyAsync(d_len_host, m0->h_tmp.data(), sizeof(int) * n, cudaMemcpyHostToDevice, s));
@@ -1742,6 +1747,13 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
         ea.logits[k] = models[k]->sm->logits.as<float>();
       }
       ea.K = K; ea.V = V; ea.N = NB; ea.out = mean_logits;
+      if (vote) {  // ensembles_models: sum the models' weights per source position, take the largest
+        zrnn::EnsembleVitArgs va;
+        std::memset(&va, 0, sizeof(va));
+        for (int k = 0; k < K; ++k) { va.align[k] = bm[k].align_pos; va.S_max[k] = bm[k].S_max; }
+        va.K = K; va.N = NB; va.viterbi_out = bm[0].vit;
+        ZR_CUDA(zrnn::launch_ensemble_viterbi(va, s));
+      }
       KScope ks(KC_SOFTMAX_REDUCE, s);
       ZR_CUDA(zrnn::launch_ensemble_logmean(ea, s));
       ZR_CUDA(zrnn::launch_topk_logp(mean_logits, V, NB, kc, cand_val, cand_idx, logp_eos, s, nullptr, nullptr, 0));
@@ -1824,6 +1836,14 @@ int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int
                               const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
                               float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
                               float* out_score) {
+  return zrnn_beam_decode_ensemble_align(models, n_models, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio,
+                                         penalty, longest_sent, out_ids, out_len, out_score, nullptr);
+}
+
+int zrnn_beam_decode_ensemble_align(zrnn_model* const* models, int n_models, const int* const* src_ids,
+                                    const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
+                                    float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
+                                    float* out_score, int* out_align) {
   ZR_CHECK(models && src_ids && src_len && out_ids && out_len && out_score, "beam_decode_ensemble: null argument");
   ZR_CHECK(n_models >= 1 && n_models <= ZR_ENSEMBLE_MAX, "beam_decode_ensemble: between 1 and 8 models");
   ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode_ensemble: bad sizes");
@@ -1833,7 +1853,7 @@ int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int
   cudaStream_t s = models[0] ? models[0]->stream : nullptr;
   std::vector<const int*> d_src(n_models);
   std::vector<int> S_max(n_models, 0);
-  int *d_ids = nullptr, *d_len = nullptr;
+  int *d_ids = nullptr, *d_len = nullptr, *d_al = nullptr;
   float* d_sc = nullptr;
   for (int k = 0; k < n_models; ++k) {
     zrnn_model* m = models[k];
@@ -1851,18 +1871,22 @@ int zrnn_beam_decode_ensemble(zrnn_model* const* models, int n_models, const int
       pos += src_len[k][i];
     }
     size_t bytes = aligned(sizeof(int) * padded.size());
-    if (k == 0) bytes += aligned(sizeof(int) * nO * Lmax) + aligned(sizeof(int) * nO) + aligned(sizeof(float) * nO);
+    if (k == 0) bytes += 2 * aligned(sizeof(int) * nO * Lmax) + aligned(sizeof(int) * nO) + aligned(sizeof(float) * nO);
     ZR_CUDA(m->io.reserve(bytes));
     Carver cv(m->io.p);
     int* dst = cv.take<int>(padded.size());
-    if (k == 0) { d_ids = cv.take<int>(nO * Lmax); d_len = cv.take<int>(nO); d_sc = cv.take<float>(nO); }
+    if (k == 0) {
+      d_ids = cv.take<int>(nO * Lmax); d_len = cv.take<int>(nO); d_sc = cv.take<float>(nO);
+      d_al = out_align ? cv.take<int>(nO * Lmax) : nullptr;
+    }
     // pageable source: the copy has left `padded` when the call returns
     ZR_CUDA(cudaMemcpyAsync(dst, padded.data(), sizeof(int) * padded.size(), cudaMemcpyHostToDevice, s));
     ZR_CUDA(cudaStreamSynchronize(s));
     d_src[k] = dst;
   }
   ZR_TRY(beam_decode_core(models, n_models, d_src.data(), src_len[0], S_max.data(), n_sent, beam, k_best, min_ratio,
-                          max_ratio, penalty, longest_sent, d_ids, d_len, d_sc, nullptr, s));
+                          max_ratio, penalty, longest_sent, d_ids, d_len, d_sc, d_al, s));
+  if (out_align) ZR_CUDA(cudaMemcpyAsync(out_align, d_al, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_ids, d_ids, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
