@@ -107,3 +107,29 @@ def test_decode_limits_and_short_hypothesis_lists(api, oracle, dtype):
         np.testing.assert_allclose(gs[ln > 0], sc[ln > 0], rtol=1e-5, atol=1e-4)
         short += int((ln == 0).sum())
     assert short > 0  # the first two settings leave k-best slots empty
+
+
+@pytest.mark.parametrize("att,lm,L,H,Vs,Vt,B,S,T", [
+    (1, 0, 1, 132, 333, 1003, 1, (7, 7), (9, 9)),        # one column, hidden size off the 64-element padding
+    (2, 0, 2, 260, 97, 257, 129, (2, 6), (2, 5)),        # one column more than a 128-row tile
+    (0, 1, 3, 1020, 0, 5001, 200, (0, 0), (3, 8)),       # language model, two row tiles, odd vocabulary
+    (1, 0, 1, 512, 64, 129, 7, (1, 30), (1, 3)),         # vocabulary just above one softmax tile
+    (2, 0, 1, 128, 50, 31, 3, (4, 4), (6, 6)),           # vocabulary smaller than any tile
+])
+def test_shape_sweep_against_the_oracle(api, oracle, att, lm, L, H, Vs, Vt, B, S, T):
+    """Shapes around the kernels' tile boundaries, fp32-accurate tensor-core engine and the bf16 engine."""
+    cfg = synth.make_cfg(L, H, Vs, Vt, lm=bool(lm), attention=att, feed_input=1 if att else 0, D=3)
+    w = synth.make_weights(cfg, seed=60 + H, scale=0.1)
+    if lm:
+        tin, tout = synth.make_lm_batch(Vt, B, T[1], seed=5)
+        src = None
+    else:
+        src, tin, tout = synth.make_s2s_batch(Vs, Vt, B, S[0], S[1], T[0], T[1], seed=5)
+    want = oracle.OracleModel(cfg, w).score_batch(src, tin, tout)
+    got, _ = build(api, cfg, w, 5).get_error(src, tin, tout)
+    helpers.assert_logp_close(got, want, rtol=2e-5, atol=3e-6)
+    if H % 8 == 0:
+        got16, _ = build(api, cfg, w, 1).get_error(src, tin, tout)
+        msk = tout != -1
+        assert np.abs(got16[msk] - want[msk]).max() < 0.08
+        assert abs(got16[msk].sum() - want[msk].sum()) < 5e-3 * abs(want[msk].sum())
