@@ -121,3 +121,27 @@ def test_model_file_host_parser(tmp_path):
         api.read_model_file(path, [(700, 300), (3, 300), (2, 2)])
     with pytest.raises(api.ZrnnError):
         api.read_model_file(path, [(700, 301)])
+
+
+def test_prep_decode_legacy_model_prefix(tmp_path):
+    """--legacy-model 1: every integer source line starts with id 0 (src/input_file_prep.h:3108-3110)."""
+    cfg = synth.make_cfg(**S2S)
+    model, sp, _, _ = make_text_fixture(str(tmp_path), cfg, 9, seed=11)
+    rc, out = run_cli(["-k", "1", model, "kbest.txt", "--decode-main-data-files", sp, "--legacy-model", "1",
+                       "--prep-only"], tmp_path)
+    assert rc == 0, out
+    want, sents = textprep.integerize_kbest(model, sp, 100, legacy=True)
+    assert tmp_file(tmp_path, "kbest_tmp_0") == want
+    assert all(s[0] == 0 for s in sents)
+
+
+def test_prep_decode_ensemble_writes_one_file_per_model(tmp_path):
+    d1, d2 = tmp_path / "a", tmp_path / "b"
+    d1.mkdir(); d2.mkdir()
+    cfg = synth.make_cfg(**S2S)
+    m1, s1, _, _ = make_text_fixture(str(d1), cfg, 6, seed=12)
+    m2, s2, _, _ = make_text_fixture(str(d2), cfg, 6, seed=13)
+    rc, out = run_cli(["-k", "1", m1, m2, "kbest.txt", "--decode-main-data-files", s1, s2, "--prep-only"], tmp_path)
+    assert rc == 0, out
+    assert tmp_file(tmp_path, "kbest_tmp_0") == textprep.integerize_kbest(m1, s1, 100)[0]
+    assert tmp_file(tmp_path, "kbest_tmp_1") == textprep.integerize_kbest(m2, s2, 100)[0]

@@ -133,3 +133,30 @@ def test_shape_sweep_against_the_oracle(api, oracle, att, lm, L, H, Vs, Vt, B, S
         msk = tout != -1
         assert np.abs(got16[msk] - want[msk]).max() < 0.08
         assert abs(got16[msk].sum() - want[msk].sum()) < 5e-3 * abs(want[msk].sum())
+
+
+def test_two_devices_in_one_process(api):
+    """zrnn_set_device lets one process put models on several devices in turn: per-device state inside the library
+    (kernel attributes, error word, scratch addresses) must not leak from one device to the other."""
+    import ctypes
+    import torch
+    n = ctypes.c_int()
+    api.check(api.lib().zrnn_device_count(ctypes.byref(n)))
+    assert n.value == torch.cuda.device_count()
+    if n.value < 2:
+        pytest.skip("needs two devices")
+    cfg = synth.make_cfg(2, 256, 300, 400, attention=2, feed_input=1)
+    w = synth.make_weights(cfg, seed=70, scale=0.1)
+    src, tin, tout = synth.make_s2s_batch(300, 400, 8, 4, 12, 4, 12, seed=6)
+    results = []
+    try:
+        for dev in (0, 1):
+            api.check(api.lib().zrnn_set_device(dev))
+            torch.cuda.set_device(dev)
+            m = build(api, cfg, w, 0)
+            results.append(m.get_error(src, tin, tout)[0])
+            del m
+    finally:
+        api.check(api.lib().zrnn_set_device(0))
+        torch.cuda.set_device(0)
+    assert np.array_equal(results[0], results[1])

@@ -1020,6 +1020,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   }
 }
 
+constexpr int kMaxDevices = 64;
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
 static int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -1034,12 +1040,13 @@ static int sm_count() {
 template <int BN, int MODE, int EPI>
 cudaError_t launch_persistent_t(const TcParams& p, cudaStream_t st) {
   const size_t smem = (size_t)num_stages(BN, MODE) * stage_bytes(BN, MODE) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {false};  // the attribute is per device
+  const int dev = current_device();
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_persistent_kernel<BN, MODE, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   const int m_tiles = (p.M + 127) / 128, n_tiles = (p.N + BN - 1) / BN;
   const int total = m_tiles * n_tiles;
@@ -1055,12 +1062,13 @@ static const bool g_use_pdl = std::getenv("ZRNN_NO_PDL") == nullptr;
 template <int BN, int MODE, int EPI, int SPLITK>
 cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   const size_t smem = (size_t)smem_bytes(BN, MODE, SPLITK);
-  static bool configured = false;  // once per instantiation (one device per process)
-  if (!configured) {
+  static bool configured[kMaxDevices] = {false};  // once per instantiation and device
+  const int dev = current_device();
+  if (!configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, MODE, EPI, SPLITK>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   const int n_rows = (EPI == TC_EPI_LSTM) ? p.N * 4 : p.N;
   dim3 grid((p.M + 127) / 128, (n_rows + BN - 1) / BN, SPLITK);

@@ -305,16 +305,31 @@ struct zrnn_softmax {
 
 namespace {
 
-// split the K axis over a cluster when one launch would otherwise leave most SMs idle
+// Split the K axis over a cluster when that shortens the launch: with one CTA per SM a launch runs in
+// ceil(CTAs / SMs) waves, a split by s multiplies the CTAs by s and divides the work of each by s at the price of the
+// exchange.  Picks the s that minimises waves * (1/s + exchange), e.g. 32 CTAs -> 4 (one wave of quarter-size CTAs),
+// 192 CTAs (768 decode columns) -> 2 (three waves of half-size CTAs instead of two of full size).
 int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
+  if (BN != 128) return 1;
   const int ctas = ((m_cols + 127) / 128) * ((n_rows + BN - 1) / BN);
-  int s = 1;
-  if (BN == 128) {
-    if (ctas <= 20) s = 8;
-    else if (ctas <= 40) s = 4;
-    else if (ctas <= 80) s = 2;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
   }
-  return s > max_split ? max_split : s;
+  int best = 1;
+  double best_t = 1e30;
+  for (int s = 1; s <= max_split && s <= 8; s *= 2) {
+    // 8-CTA clusters of one CTA per SM: no more than 8 of them are resident at once on this part (measured: 16 such
+    // clusters ran as two waves)
+    if (s == 8 && ctas > 8) break;
+    const int waves = (ctas * s + sms - 1) / sms;
+    const double t = waves * (1.0 / s + (s > 1 ? 0.08 + 0.01 * s : 0.0));
+    if (t < best_t - 1e-9) { best_t = t; best = s; }
+  }
+  return best;
 }
 
 long long* g_tc_prof = nullptr;  // developer profiling buffer (see zrnn_debug_tc_profile)
@@ -329,13 +344,15 @@ void prof_attach(zrnn::TcParams& tp) {
   }
 }
 
-int* tc_error_word() {
-  static int* p = nullptr;
-  if (!p) {
-    if (cudaMalloc((void**)&p, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, sizeof(int));
+int* tc_error_word() {  // one word per device
+  static int* p[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!p[dev]) {
+    if (cudaMalloc((void**)&p[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p[dev], 0, sizeof(int));
   }
-  return p;
+  return p[dev];
 }
 
 // tensor maps of an activation operand: `rows` rows of H valid elements, stride Kpad
