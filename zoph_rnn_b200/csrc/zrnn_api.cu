@@ -308,7 +308,7 @@ namespace {
 // Split the K axis over a cluster when that shortens the launch: with one CTA per SM a launch runs in
 // ceil(CTAs / SMs) waves, a split by s multiplies the CTAs by s and divides the work of each by s at the price of the
 // exchange.  Picks the s that minimises waves * (1/s + exchange), e.g. 32 CTAs -> 4 (one wave of quarter-size CTAs),
-// 192 CTAs (768 decode columns) -> 2 (three waves of half-size CTAs instead of two of full size).
+// 16 CTAs -> 4, 64 CTAs -> 2, 192 CTAs (768 decode columns) -> 1 (splitting them was measured slightly slower).
 int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
   if (BN != 128) return 1;
   const int ctas = ((m_cols + 127) / 128) * ((n_rows + BN - 1) / BN);
@@ -326,7 +326,7 @@ int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
     // clusters ran as two waves)
     if (s == 8 && ctas > 8) break;
     const int waves = (ctas * s + sms - 1) / sms;
-    const double t = waves * (1.0 / s + (s > 1 ? 0.08 + 0.01 * s : 0.0));
+    const double t = waves * (1.0 / s + (s > 1 ? 0.2 : 0.0));  // exchange ~ 20 % of an unsplit CTA's time (measured)
     if (t < best_t - 1e-9) { best_t = t; best = s; }
   }
   return best;
