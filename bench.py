@@ -53,7 +53,7 @@ WORKLOADS = {
 
 ARITH = {
     "f32": "fp32-accurate: tcgen05 on split operands (fp16 hi + scaled fp16 lo: 3 MMAs per product, fp32 accumulate) "
-           "when H >= 128, else fp32 FMA",
+           "when H >= 64, else fp32 FMA",
     "f32_3xtf32": "fp32-accurate: tcgen05 3xTF32 (hi/lo split operands, fp32 accumulate)",
     "f32_f16x2": "fp32-accurate: tcgen05 on fp16 hi + scaled fp16 lo operands (3 MMAs per product, fp32 accumulate)",
     "f32_simt": "exact fp32 FMA kernels",
@@ -417,7 +417,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16", "tf32", "f32_simt", "f32_3xtf32", "f32_f16x2"],
-                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate: split-operand tensor cores when H >= 128)")
+                    help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate: split-operand tensor cores when H >= 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16", action="store_true", help="skip the additional bf16 measurement of an f32 run")
     ap.add_argument("--cell-phases", action="store_true",

@@ -38,7 +38,7 @@ typedef enum {
 
 /* Arithmetic of the GEMM-shaped work (state, biases, activations functions and softmax reductions are fp32 in
  * every mode):
- *   ZRNN_F32        fp32-accurate: tcgen05 split-operand tensor-core kernels when H >= 128 and H % 4 == 0 (fp16
+ *   ZRNN_F32        fp32-accurate: tcgen05 split-operand tensor-core kernels when H >= 64 and H % 4 == 0 (fp16
  *                   split, see ZRNN_F32_F16X2), else the exact fp32 FMA kernels.  Environment ZRNN_FP32_ENGINE =
  *                   simt forces the FMA kernels, = x3 the 3xTF32 kernels.
  *   ZRNN_BF16       tcgen05 tensor cores on bf16-rounded weights and activations (H % 8 == 0)
