@@ -71,7 +71,8 @@ def test_config1_lm_full_size(api, oracle):
 @pytest.mark.parametrize("att,L,H,B,S,T", [(2, 4, 96, 16, (12, 12), (11, 11)),     # config 2 shape, scaled down
                                             (1, 2, 128, 16, (5, 40), (4, 20)),      # config 3 shape: ragged + masks
                                             (2, 2, 200, 130, (3, 9), (3, 9)),       # more columns than one tile
-                                            (2, 4, 1000, 24, (20, 20), (20, 20))])  # config 2's hidden size
+                                            (2, 4, 1000, 24, (20, 20), (20, 20)),   # config 2's hidden size
+                                            (2, 2, 1000, 700, (2, 4), (2, 3))])     # many columns: 256-row cell tiles
 def test_scoring_matches_oracle_scaled_configs(api, oracle, att, L, H, B, S, T, dtype):
     cfg = synth.make_cfg(L, H, 500, 700, attention=att, feed_input=1, D=10)
     w = synth.make_weights(cfg, seed=42, scale=0.1)

@@ -416,10 +416,20 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
           const int bx = p.b_tiled_kbtot > 0 ? 0 : p.b_koff[s] + kx;
           const int by = p.b_tiled_kbtot > 0 ? (n_tile * p.b_tiled_kbtot + (p.b_koff[s] + kx) / EPK) * BN : n_tile * BN;
           tma_load_2d(base, &p.a[s], &full_bar[st], kx, m0);
-          tma_load_2d(base + kABytes, &p.b, &full_bar[st], bx, by);
-          if (mode_split(MODE)) {
-            tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
-            tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], bx, by);
+          if (mode_split(MODE)) tma_load_2d(base + kABytes + BBYTES, &p.a_lo[s], &full_bar[st], kx, m0);
+          if (p.b_pack_rows > 0 && p.b_pack_rows < BN) {
+            // B was packed for narrower row tiles: this tile is BN / pack consecutive packed tiles, one box each
+            const int parts = BN / p.b_pack_rows, kbg = (p.b_koff[s] + kx) / EPK;
+            for (int h = 0; h < parts; ++h) {
+              const int pt = n_tile * parts + h;
+              const int byh = p.b_tiled_kbtot > 0 ? (pt * p.b_tiled_kbtot + kbg) * p.b_pack_rows : pt * p.b_pack_rows;
+              const size_t off = (size_t)h * p.b_pack_rows * 128;
+              tma_load_2d(base + kABytes + off, &p.b, &full_bar[st], bx, byh);
+              if (mode_split(MODE)) tma_load_2d(base + 2 * kABytes + BBYTES + off, &p.b_lo, &full_bar[st], bx, byh);
+            }
+          } else {
+            tma_load_2d(base + kABytes, &p.b, &full_bar[st], bx, by);
+            if (mode_split(MODE)) tma_load_2d(base + 2 * kABytes + BBYTES, &p.b_lo, &full_bar[st], bx, by);
           }
           ++it;
         }
@@ -661,8 +671,12 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
       const int hid0 = n_tile * TH;
       for (int j0 = rank * TH_OWN; j0 < (rank + 1) * TH_OWN; j0 += 8) {
         float g[4][8];
+        // accumulator column of (gate q, hidden j0): gate blocks of THP hidden units, THP = the packing's tile
+        // (the tile itself unless the weights were packed for narrower tiles)
+        const int THP = (p.b_pack_rows > 0 && p.b_pack_rows < BN) ? p.b_pack_rows / 4 : TH;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) load8(SPLITK == 1 ? q * TH + j0 : q * TH_OWN + (j0 - rank * TH_OWN), g[q]);
+        for (int q = 0; q < 4; ++q)
+          load8(SPLITK == 1 ? (j0 / THP) * (4 * THP) + q * THP + (j0 % THP) : q * TH_OWN + (j0 - rank * TH_OWN), g[q]);
         ZR_STAMP(5);
         if (row_ok) {
           const int hb = hid0 + j0;

@@ -25,6 +25,9 @@ struct TcParams {
   // > 0: B is stored tile-contiguously (k-blocks per row tile): the box of (row tile n, k-block kb) is the
   // rows [(n * b_tiled_kbtot + kb) * BN, + BN) of a 128-byte-wide 2-D array (tc_gemm_kernel only)
   int b_tiled_kbtot;
+  // > 0 and < BN: B was packed for row tiles of this many rows (LSTM: 4 gates x pack/4 hidden units per tile) and the
+  // launch uses a wider tile made of BN / b_pack_rows consecutive packed tiles (tc_gemm_kernel, SPLITK == 1)
+  int b_pack_rows;
   int M;           // batch columns
   int N;           // STORE / LSE: output rows; LSTM: hidden size H (B holds 4H packed rows)
   const float* bias;  // STORE / LSE: [N]; LSTM: [4][H] gate-major (i,f,g,o)

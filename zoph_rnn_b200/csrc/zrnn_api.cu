@@ -439,7 +439,15 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   set_operand_outputs(tp, eng, out, Kpad);
   tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); prof_attach(tp);
   KScope ks(KC_LSTM, st);
-  ZR_CUDA(zrnn::launch_tc_gemm(tp, L->BN, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st, pick_splitk(B, 4 * H, L->BN, 4)));
+  int bn = L->BN;
+  const int splitk = pick_splitk(B, 4 * H, L->BN, 4);
+  // many columns (beam decoding): 128-row tiles would need more than one wave of CTAs; 256-row tiles built from two
+  // packed tiles halve the CTA count and the activation traffic per flop
+  if (splitk == 1 && L->BN == 128 && ((B + 127) / 128) * L->n_tiles > 148) {
+    bn = 256;
+    tp.b_pack_rows = 128;
+  }
+  ZR_CUDA(zrnn::launch_tc_gemm(tp, bn, eng_tcmode(eng), zrnn::TC_EPI_LSTM, st, splitk));
   return ZRNN_OK;
 }
 
