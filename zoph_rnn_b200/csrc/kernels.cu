@@ -572,20 +572,23 @@ cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tg
 // rounds.  Only if more than ZR_TOPK_CAND elements reach the bound (massive ties) the bound is raised and pass 2
 // repeated.
 // With part_max / part_sum (n_parts row-tile partials per column, laid out [part][N], as the GEMM epilogue writes
-// them) pass 1 reads those few values instead of the whole column.
+// them) pass 1 reads those few values instead of the whole column.  With both partials and the tiles' width
+// (part_width rows per tile) pass 2 also skips every tile whose maximum is below the bound: it reads about k tiles
+// of the column instead of all of it.
+#define ZR_TOPK_TILES 1024
 __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict__ z, int V, int N, int k,
                                                          const float* __restrict__ part_max,
                                                          const float* __restrict__ part_sum, int n_parts,
-                                                         float* __restrict__ val_out, int* __restrict__ idx_out,
-                                                         float* __restrict__ logp_eos) {
+                                                         int part_width, float* __restrict__ val_out,
+                                                         int* __restrict__ idx_out, float* __restrict__ logp_eos) {
+  __shared__ int sel[ZR_TOPK_TILES];
+  __shared__ int s_nsel;
   __shared__ float tmax[256];
   __shared__ float cval[ZR_TOPK_CAND];
   __shared__ int cidx[ZR_TOPK_CAND];
   __shared__ float red_m[8], red_s[8];
-  __shared__ float win_v[8];
-  __shared__ int win_i[8], win_p[8];
   __shared__ float s_M, s_logS, s_thr;
-  __shared__ int s_count, s_win;
+  __shared__ int s_count;
   const int col = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const float* zc = z + (size_t)col * V;
   float m = -INFINITY, s = 0.f;
@@ -611,7 +614,7 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   float ws = (m == -INFINITY) ? 0.f : s * expf(m - wm);
   ws = warp_sum(ws);
   if (lane == 0) { red_m[w] = wm; red_s[w] = ws; }
-  if (tid == 0) s_count = 0;
+  if (tid == 0) { s_count = 0; s_nsel = 0; }
   __syncthreads();
   if (tid == 0) {
     float M = -INFINITY;
@@ -638,8 +641,42 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   float s2 = 0.f;
   const float Mall = s_M;
   const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(zc) & 15) == 0);
+  const bool skip = part_max && part_sum && part_width > 0 && n_parts <= ZR_TOPK_TILES;
+  if (skip) {  // the tiles that can hold one of the k largest values (at least k of them, more only on ties)
+    for (int j = tid; j < n_parts; j += 256)
+      if (part_max[(size_t)j * N + col] >= thr) sel[atomicAdd(&s_nsel, 1)] = j;
+    __syncthreads();
+  }
   for (int attempt = 0; attempt < 4; ++attempt) {
-    if (vec4) {
+    if (skip && vec4 && (part_width & 3) == 0) {
+      const float4* z4 = reinterpret_cast<const float4*>(zc);
+      const int w4 = part_width >> 2, n4 = V >> 2, tot = s_nsel * w4;
+      for (int e = tid; e < tot; e += 256) {
+        const int i4 = sel[e / w4] * w4 + e % w4;
+        if (i4 >= n4) continue;
+        const float4 v = __ldcs(z4 + i4);
+        if (fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)) >= thr) {
+          const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (vv[u] >= thr && vv[u] != -INFINITY) {
+              const int p = atomicAdd(&s_count, 1);
+              if (p < ZR_TOPK_CAND) { cval[p] = vv[u]; cidx[p] = 4 * i4 + u; }
+            }
+        }
+      }
+    } else if (skip) {
+      const int tot = s_nsel * part_width;
+      for (int e = tid; e < tot; e += 256) {
+        const int i = sel[e / part_width] * part_width + e % part_width;
+        if (i >= V) continue;
+        const float v = zc[i];
+        if (v >= thr && v != -INFINITY) {
+          const int p = atomicAdd(&s_count, 1);
+          if (p < ZR_TOPK_CAND) { cval[p] = v; cidx[p] = i; }
+        }
+      }
+    } else if (vec4) {
       // 16-byte loads, four independent exp chains per thread
       const float4* z4 = reinterpret_cast<const float4*>(zc);
       float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
@@ -744,10 +781,12 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   }
 }
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
-                             cudaStream_t st, const float* part_max, const float* part_sum, int n_parts) {
+                             cudaStream_t st, const float* part_max, const float* part_sum, int n_parts,
+                             int part_width) {
   if (N <= 0) return cudaSuccess;
   if (k < 1 || k > ZR_TOPK_MAX) return cudaErrorInvalidValue;
-  topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, part_max, part_sum, n_parts, val_out, idx_out, logp_eos);
+  topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, part_max, part_sum, n_parts, part_width, val_out, idx_out,
+                                      logp_eos);
   count_launch();
   return cudaGetLastError();
 }

@@ -82,10 +82,11 @@ cudaError_t launch_lse_reduce(const float* part_max, const float* part_sum, int 
 
 // ---- decode: per column the k largest log-probabilities (sorted) from logits z[V x N] + normaliser
 // part_max / part_sum (optional): n_parts row-tile partials per column [part][N] produced by the logits GEMM, which
-// save the kernel its first pass over the column
+// save the kernel its first pass over the column; with both and part_width (rows of z per tile) the second pass
+// reads only the tiles whose maximum reaches the selection bound
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
                              cudaStream_t st, const float* part_max = nullptr, const float* part_sum = nullptr,
-                             int n_parts = 0);
+                             int n_parts = 0, int part_width = 0);
 
 // ---- attention
 struct AttArgs {

@@ -121,22 +121,11 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ float sigmoid_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float tf32_round_dev(float x) {
   uint32_t u = __float_as_uint(x);
   if ((u & 0x7f800000u) == 0x7f800000u) return x;
   return __uint_as_float((u + 0x1000u) & 0xffffe000u);
 }
-// write the A-operand copies (for the next GEMM) of value v at element index idx
-__device__ __forceinline__ void store_operand(const TcParams& p, size_t idx, float v) {
-  if (p.op_b16) p.op_b16[idx] = __float2bfloat16(v);
-  if (p.op_hi) {
-    const float hi = tf32_round_dev(v);
-    p.op_hi[idx] = hi;
-    if (p.op_lo) p.op_lo[idx] = v - hi;
-  }
-}
-
 // 8 consecutive outputs of one row: vector stores when the group is complete and 16-byte aligned
 __device__ __forceinline__ void store8_f32(float* base, size_t idx, const float* v, int nvalid) {
   if (nvalid == 8 && (idx & 3) == 0) {
@@ -787,16 +776,27 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Warp roles: warps 0-7 run the epilogue (warp w reads TMEM lanes 32 (w % 4) .. +31, the only ones it may access, and
+// the column half w / 4 of the tile), warp 8 is the TMA producer, warp 9 issues the MMAs and owns the TMEM allocation.
+// Every tile therefore leaves kPersistentParts = 2 (max, sum) partials per output row, one per column half.
+constexpr int kXposeBytes = 8 * 32 * 32 * 4;  // one 32 x 32 fp32 transposition buffer per epilogue warp
+__host__ __device__ constexpr int persistent_stages(int BN, int mode) {
+  return (225 * 1024 - 1024 - kXposeBytes) / stage_bytes(BN, mode);
+}
+
 template <int BN, int MODE, int EPI>
-__global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid_constant__ TcParams p, int m_tiles,
+__global__ void __launch_bounds__(320, 1) tc_gemm_persistent_kernel(const __grid_constant__ TcParams p, int m_tiles,
                                                                      int n_tiles) {
-  constexpr int ST = num_stages(BN, MODE);
+  constexpr int ST = persistent_stages(BN, MODE);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
   constexpr uint32_t IDESC = make_idesc(mode_fmt(MODE), BN);
   constexpr int ACC_COLS = (mode_split(MODE) ? 2 : 1) * BN;  // main accumulator (+ cross-term accumulator)
   constexpr int TMEM_COLS = 2 * ACC_COLS;                       // double-buffered
+  constexpr int HC = BN / kPersistentParts;                     // columns per epilogue warp
+  static_assert(ST >= 2, "need at least a double-buffered ring");
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM budget");
+  static_assert(HC % 32 == 0, "the epilogue works on chunks of 32 columns");
   static_assert(EPI != TC_EPI_LSTM, "the persistent variant has store and log-sum-exp epilogues only");
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[ST];
@@ -805,12 +805,11 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  // bias values of the tile whose epilogue is running (two named barriers per tile order its refill)
+  __shared__ __align__(16) float s_bias[BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  // bias values of the tile in flight, double-buffered over tiles: the 128 epilogue threads fill one buffer and meet
-  // at a named barrier, so a thread is never more than one tile ahead of the slowest reader
-  __shared__ __align__(16) float s_bias[2][BN];
   const int total_tiles = m_tiles * n_tiles;
   ZR_STAMP(0);
   int kb_per_tile = 0;
@@ -823,12 +822,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
@@ -840,7 +839,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   const uint32_t tmem_base = tmem_base_s;
   pdl_wait();
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ TMA producer (runs ahead across tiles)
     if (lane == 0 && kb_per_tile > 0) {
       int it = 0;
@@ -869,7 +868,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
         while (clock64() - t0 < 20000000LL) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0 && kb_per_tile > 0) {
       int it = 0, ti = 0;
@@ -904,75 +903,118 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
       }
     }
   } else if (kb_per_tile > 0) {
-    // ------------------------------------------------------------ epilogue warps 0-3
+    // ------------------------------------------------------------ epilogue warps 0-7
+    const int q = warp & 3, half = warp >> 2;
+    float* xp = reinterpret_cast<float*>(tiles + (size_t)ST * STAGE) + warp * 1024;
+    // Stores go through the warp's transposition buffer so that every store instruction writes whole 128-byte lines
+    // (a thread per output row would scatter 16-byte pieces over 32 lines).  That needs 16-byte aligned rows; any
+    // other layout, and launches that also emit operand copies, take the per-row path.
+    const bool fast_store = EPI == TC_EPI_STORE && p.C && (p.ldc & 3) == 0 && (p.N & 3) == 0 &&
+                            (reinterpret_cast<uintptr_t>(p.C) & 15) == 0 && !p.op_b16 && !p.op_hi && !p.op_h_hi;
     int ti = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
       const int buf = ti & 1;
       const int m_tile = tile % m_tiles, n_tile = tile / m_tiles;
-      const int row = m_tile * 128 + warp * 32 + lane;
+      const int row = m_tile * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      float* sb = s_bias[buf];  // filled while the accumulator is still being produced
-      for (int i = threadIdx.x; i < BN; i += 128) {
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // all epilogue threads have finished with the previous bias
+      for (int i = threadIdx.x; i < BN; i += 256) {
         const int n = n_tile * BN + i;
-        sb[i] = n < p.N ? (p.bias ? __ldg(p.bias + n) : 0.f) : (EPI == TC_EPI_LSE ? -INFINITY : 0.f);
+        s_bias[i] = n < p.N ? (p.bias ? __ldg(p.bias + n) : 0.f) : (EPI == TC_EPI_LSE ? -INFINITY : 0.f);
       }
       if (!mbar_wait(&acc_full[buf], (uint32_t)((ti >> 1) & 1), &abort_s, p.err, 3)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * ACC_COLS);
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the new bias values are visible
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ACC_COLS + half * HC);
       const float mk = (p.mask && row_ok) ? (float)p.mask[row] : 1.0f;
-      const int n0 = n_tile * BN;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const int n0 = n_tile * BN + half * HC;  // first output column of this warp
+      const float* sb = s_bias + half * HC;
+      const size_t pi = (size_t)(n_tile * kPersistentParts + half) * p.M + row;
       if constexpr (EPI == TC_EPI_STORE) {
-        const bool want_max = p.part_max != nullptr;  // also emit the per-tile maximum of the stored values
+        const bool want_max = p.part_max != nullptr;  // also emit the maximum of this warp's stored values per row
         const bool want_lse = want_max && p.part_sum != nullptr;  // ... and sum exp(x - max)
         float mx = -INFINITY, sm = 0.f;
-        for (int c0 = 0; c0 < BN; c0 += 8) {
-          float v[8];
-          tmem_ld8(taddr + c0, v);
+        for (int c0 = 0; c0 < HC; c0 += 32) {
+          float v[32];
+          tmem_ld32(taddr + c0, v);
           if (mode_split(MODE)) {
-            float t[8];
-            tmem_ld8(taddr + BN + c0, t);
+            float t[32];
+            tmem_ld32(taddr + BN + c0, t);
             tmem_wait_ld();
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
+            for (int u = 0; u < 32; ++u) v[u] = fmaf(t[u], mode_cross_scale(MODE), v[u]);
           }
           tmem_wait_ld();
-          if (row_ok) {
-            const int nb = n0 + c0;
-            const int nvalid = p.N - nb >= 8 ? 8 : (p.N - nb > 0 ? p.N - nb : 0);
-            float x[8];
-            float cm = -INFINITY;
+          const int nb = n0 + c0;
+          const int nvalid = p.N - nb >= 32 ? 32 : (p.N - nb > 0 ? p.N - nb : 0);
+          float cm = -INFINITY;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int n = nb + u;
-              float t = v[u] + sb[c0 + u];
-              if (p.act == 1 && (p.act_rows == 0 || n < p.act_rows)) t = act_tanh<MODE>(t);
-              x[u] = t * mk;
-              if (u < nvalid) cm = fmaxf(cm, x[u]);
+          for (int u = 0; u < 32; u += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(sb + c0 + u);
+            const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float t = v[u + e] + bb[e];
+              if (p.act == 1 && (p.act_rows == 0 || nb + u + e < p.act_rows)) t = act_tanh<MODE>(t);
+              t *= mk;
+              v[u + e] = t;
+              if (u + e < nvalid) cm = fmaxf(cm, t);
             }
-            if (nvalid > 0) {
-              if (p.C) store8_f32(p.C, (size_t)row * p.ldc + nb, x, nvalid);
-              store8_operand(p, (size_t)row * p.ld_op + nb, x, nvalid);
-              if (want_lse) {
-                if (cm > mx) { sm *= expf(mx - cm); mx = cm; }
+          }
+          if (want_lse) {
+            if (cm > mx) { sm *= expf(mx - cm); mx = cm; }
+            if (mx != -INFINITY) {
+              float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                  if (u < nvalid) sm += expf(x[u] - mx);
-              } else if (want_max) {
-                mx = fmaxf(mx, cm);
+              for (int u = 0; u < 32; u += 4) {
+                s0 += u < nvalid ? expf(v[u] - mx) : 0.f;
+                s1 += u + 1 < nvalid ? expf(v[u + 1] - mx) : 0.f;
+                s2 += u + 2 < nvalid ? expf(v[u + 2] - mx) : 0.f;
+                s3 += u + 3 < nvalid ? expf(v[u + 3] - mx) : 0.f;
+              }
+              sm += (s0 + s1) + (s2 + s3);
+            }
+          } else if (want_max) {
+            mx = fmaxf(mx, cm);
+          }
+          if (fast_store) {
+            // row `lane` of the 32 x 32 chunk, its eight 16-byte pieces XOR-swizzled by the row so that neither
+            // these writes nor the transposed reads below collide on a bank
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(xp + lane * 32 + ((j ^ (lane & 7)) << 2)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // eight lanes per row, four rows per instruction
+              const int r = 4 * i + (lane >> 3), j = lane & 7;
+              const float4 o = *reinterpret_cast<const float4*>(xp + r * 32 + ((j ^ (r & 7)) << 2));
+              const int grow = m_tile * 128 + q * 32 + r, n = nb + 4 * j;
+              if (grow < p.M && n < p.N) *reinterpret_cast<float4*>(p.C + (size_t)grow * p.ldc + n) = o;
+            }
+            __syncwarp();
+          } else if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int nv = nvalid - 8 * g >= 8 ? 8 : (nvalid - 8 * g > 0 ? nvalid - 8 * g : 0);
+              if (nv > 0) {
+                float x8[8];  // a copy: the ragged tail indexes it dynamically, which must not push v out of registers
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x8[u] = v[8 * g + u];
+                if (p.C) store8_f32(p.C, (size_t)row * p.ldc + nb + 8 * g, x8, nv);
+                store8_operand(p, (size_t)row * p.ld_op + nb + 8 * g, x8, nv);
               }
             }
           }
         }
         if (want_max && row_ok) {
-          const size_t pi = (size_t)n_tile * p.M + row;
           p.part_max[pi] = mx;
           if (want_lse) p.part_sum[pi] = sm;
         }
       } else {  // TC_EPI_LSE
         const int tg = (p.target && row_ok) ? p.target[row] - p.target_offset : -1;
         float mx = -INFINITY, sm = 0.f;
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = 0; c0 < HC; c0 += 32) {
           float v[32];
           tmem_ld32(taddr + c0, v);
           if (mode_split(MODE)) {
@@ -1012,7 +1054,6 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
           }
         }
         if (row_ok) {
-          const size_t pi = (size_t)n_tile * p.M + row;
           p.part_max[pi] = mx;
           p.part_sum[pi] = sm;
         }
@@ -1027,7 +1068,7 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_persistent_kernel(const __grid
   tc_fence_before();
   __syncthreads();
   ZR_STAMP(7);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                  : "memory");
@@ -1053,7 +1094,7 @@ static int sm_count() {
 
 template <int BN, int MODE, int EPI>
 cudaError_t launch_persistent_t(const TcParams& p, cudaStream_t st) {
-  const size_t smem = (size_t)num_stages(BN, MODE) * stage_bytes(BN, MODE) + 1024;
+  const size_t smem = (size_t)persistent_stages(BN, MODE) * stage_bytes(BN, MODE) + 1024 + kXposeBytes;
   static bool configured[kMaxDevices] = {false};  // the attribute is per device
   const int dev = current_device();
   if (!configured[dev]) {
@@ -1066,7 +1107,7 @@ cudaError_t launch_persistent_t(const TcParams& p, cudaStream_t st) {
   const int total = m_tiles * n_tiles;
   if (total == 0) return cudaSuccess;
   const int grid = total < sm_count() ? total : sm_count();
-  tc_gemm_persistent_kernel<BN, MODE, EPI><<<grid, 192, smem, st>>>(p, m_tiles, n_tiles);
+  tc_gemm_persistent_kernel<BN, MODE, EPI><<<grid, 320, smem, st>>>(p, m_tiles, n_tiles);
   count_launch();
   return cudaGetLastError();
 }

@@ -64,7 +64,10 @@ struct TcParams {
 cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk = 1);
 
 // Persistent one-CTA-per-SM variant for large problems (store and log-sum-exp epilogues).  The B tensor map must use
-// 256-row boxes for TC_BF16 / TC_TF32 and 128-row boxes for TC_TF32X3; LSE partials are indexed [n_tile x M].
+// 256-row boxes for TC_BF16 / TC_TF32 and 128-row boxes for the split modes.  Two epilogue warps share each output
+// row of a tile, one per half of its columns, so the (max, sum) partials are indexed
+// [(n_tile * kPersistentParts + half) x M] and each covers tile width / kPersistentParts consecutive columns.
+constexpr int kPersistentParts = 2;
 cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cudaStream_t st);
 
 // Host helpers -------------------------------------------------------------------------------------------

@@ -548,7 +548,7 @@ int softmax_partials_launch(zrnn_softmax* S, const Act& h, const int* targets, i
     ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_LSE, tile, st));
     return ZRNN_OK;
   }
-  const int eng = S->eng, np = S->n_tiles;
+  const int eng = S->eng, np = S->n_tiles * zrnn::kPersistentParts;
   ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
   zrnn::TcParams tp;
   std::memset(&tp, 0, sizeof(tp));
@@ -577,8 +577,10 @@ int softmax_score_act(zrnn_softmax* S, const Act& h, const int* targets, const i
   return ZRNN_OK;
 }
 
-// logits = D h + b_d into S->logits (V x N); tensor-core engines also leave each tile's maximum (*pm, *np tiles)
-int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, const float** pm_out, int* np_out) {
+// logits = D h + b_d into S->logits (V x N); tensor-core engines also leave each tile's maximum (*pm, *np tiles) and,
+// when ps_out is given, each tile's sum of exp(x - maximum)
+int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, const float** pm_out, int* np_out,
+                       const float** ps_out = nullptr) {
   ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
   const float *pm = nullptr;
   int np = 0;
@@ -592,7 +594,7 @@ int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, co
     ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
   } else {
     const int eng = S->eng;
-    np = S->n_tiles;
+    np = S->n_tiles * zrnn::kPersistentParts;
     ZR_CUDA(S->parts.reserve(sizeof(float) * 2 * (size_t)np * N));
     zrnn::TcParams tp;
     std::memset(&tp, 0, sizeof(tp));
@@ -600,24 +602,27 @@ int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, co
     tp.nsrc = 1; tp.kblocks[0] = (S->H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
     tp.b = S->dmap; tp.b_lo = S->dmap_lo;
     tp.M = N; tp.N = S->V; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = S->V;
-    // the epilogue also leaves each tile's maximum: the top-k kernel derives its threshold and the column maximum
-    // from them and needs a single pass over the logits
-    tp.part_max = S->parts.as<float>(); tp.part_sum = nullptr;
+    // the epilogue also leaves each tile's maximum and exp-sum: the top-k kernel derives the normaliser and its
+    // selection bound from them and then reads only the few tiles that reach the bound
+    tp.part_max = S->parts.as<float>(); tp.part_sum = ps_out ? tp.part_max + (size_t)np * N : nullptr;
     pm = tp.part_max;
+    if (ps_out) *ps_out = tp.part_sum;
     tp.err = tc_error_word();
     KScope ks(KC_SOFTMAX_GEMM, st);
     ZR_CUDA(zrnn::launch_tc_gemm_persistent(tp, eng_tcmode(eng), zrnn::TC_EPI_STORE, st));
   }
   *pm_out = pm;
   *np_out = np;
+  if (ps_out && !pm) *ps_out = nullptr;
   return ZRNN_OK;
 }
 int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
-  const float* pm = nullptr;
+  const float *pm = nullptr, *ps = nullptr;
   int np = 0;
-  ZR_TRY(softmax_logits_act(S, h, N, st, &pm, &np));
+  ZR_TRY(softmax_logits_act(S, h, N, st, &pm, &np, &ps));
   KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, nullptr, np));
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, ps, np,
+                                 S->BN / zrnn::kPersistentParts));
   return ZRNN_OK;
 }
 
