@@ -264,7 +264,7 @@ __global__ void col_gather_kernel(ColGatherArgs a) {
   const int arr = blockIdx.y;
   const float* src = a.src[arr];
   float* dst = a.dst[arr];
-  const int H = a.H;
+  const int H = a.h_arr[arr] > 0 ? a.h_arr[arr] : a.H;
   for (int col = blockIdx.x; col < a.n_cols; col += gridDim.x) {
     const int sc = a.map[col];
     const float* s = src + (size_t)sc * H;
@@ -616,7 +616,7 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   if (lane == 0) { red_m[w] = wm; red_s[w] = ws; }
   if (tid == 0) { s_count = 0; s_nsel = 0; }
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 32) {  // the normaliser, by a thread of the second warp while the first one selects the bound
     float M = -INFINITY;
     for (int i = 0; i < 8; ++i) M = fmaxf(M, red_m[i]);
     double S = 0.0;
@@ -626,15 +626,33 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
     s_logS = (float)log(S);
     if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - M) - s_logS : -INFINITY;
   }
-  // rank of this thread's maximum among the 256 maxima (ties broken by thread id)
-  {
-    int rank = 0;
-    for (int j = 0; j < 256; ++j) {
-      const float o = tmax[j];
-      rank += (o > m || (o == m && j < tid)) ? 1 : 0;
+  // the k-th largest of the 256 thread maxima (duplicates count): k rounds of a warp-wide argmax over 8 values per
+  // lane, the winner's owner dropping it
+  if (w == 0) {
+    float loc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) loc[i] = tmax[lane + 32 * i];
+    const int rounds = k < 256 ? k : 256;
+    float kth = -INFINITY;
+    for (int r = 0; r < rounds; ++r) {
+      float bm = loc[0];
+      int bi = 0;
+#pragma unroll
+      for (int i = 1; i < 8; ++i)
+        if (loc[i] > bm) { bm = loc[i]; bi = i; }
+      float wmax = bm;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
+      kth = wmax;
+      if (wmax == -INFINITY) break;
+      const unsigned owners = __ballot_sync(0xffffffffu, bm == wmax);
+      if (lane == __ffs(owners) - 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i == bi) loc[i] = -INFINITY;
+      }
     }
-    const int want = (k < 256 ? k : 256) - 1;
-    if (rank == want) s_thr = m;
+    if (lane == 0) s_thr = kth;
   }
   __syncthreads();
   float thr = s_thr;

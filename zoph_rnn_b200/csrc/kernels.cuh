@@ -21,9 +21,10 @@ cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, const int* i
 // (replaces the per-column cudaMemcpy loops of swap_states_decoding / transfer_decoding_states_GPU,
 // src/Input_To_Hidden_Layer.hpp:1231-1260, src/model.hpp:2715-2719)
 struct ColGatherArgs {
-  enum { MAX_ARRAYS = 24 };
+  enum { MAX_ARRAYS = 40 };  // 8 layers x (h: fp32 + two operand parts, c) + the fed-back attention vector
   const float* src[MAX_ARRAYS];
   float* dst[MAX_ARRAYS];
+  int h_arr[MAX_ARRAYS];  // floats per column of each array; 0 = H
   int n_arrays;
   int H, n_cols;
   const int* map;  // n_cols source column indices

@@ -1597,22 +1597,25 @@ struct BeamModel {
     vit = track ? cv.take<int>(NB) : nullptr;
     align_pos = vote ? cv.take<float>((size_t)S_max * NB) : nullptr;
   }
-  // column gathers move whole operand rows: every array is expressed as floats-per-column
+  // column gathers move whole operand rows: every array is expressed as floats-per-column, and all arrays of a
+  // reorder go into one launch
+  void add_plain(zrnn::ColGatherArgs* ga, const float* src, float* dst, int floats_per_col) const {
+    const int i = ga->n_arrays++;
+    ga->src[i] = src; ga->dst[i] = dst; ga->h_arr[i] = floats_per_col;
+  }
   void add_gather(zrnn::ColGatherArgs* ga, const Act& srcA, const Act& dstA) const {
-    ga[0].src[ga[0].n_arrays] = srcA.f32; ga[0].dst[ga[0].n_arrays++] = dstA.f32;
+    add_plain(ga, srcA.f32, dstA.f32, g.H);
     if (tc) {
-      ga[1].src[ga[1].n_arrays] = (const float*)srcA.hi; ga[1].dst[ga[1].n_arrays++] = (float*)dstA.hi;
-      if (eng_split(g.eng)) { ga[2].src[ga[2].n_arrays] = srcA.lo; ga[2].dst[ga[2].n_arrays++] = dstA.lo; }
+      const int opf = g.Kpad * eng_eb(g.eng) / 4;
+      add_plain(ga, (const float*)srcA.hi, (float*)dstA.hi, opf);
+      if (eng_split(g.eng)) add_plain(ga, (const float*)srcA.lo, (float*)dstA.lo, opf);
     }
   }
   int run_gathers(zrnn::ColGatherArgs* ga, const int* map, cudaStream_t s) const {
-    ga[0].H = g.H; ga[1].H = g.Kpad * eng_eb(g.eng) / 4; ga[2].H = g.Kpad * eng_eb(g.eng) / 4;
-    for (int k = 0; k < 3; ++k) {
-      if (ga[k].n_arrays == 0) continue;
-      ga[k].n_cols = NB; ga[k].map = map;
-      KScope ks(KC_REORDER, s);
-      ZR_CUDA(zrnn::launch_col_gather(ga[k], s));
-    }
+    if (ga->n_arrays == 0) return ZRNN_OK;
+    ga->H = g.H; ga->n_cols = NB; ga->map = map;
+    KScope ks(KC_REORDER, s);
+    ZR_CUDA(zrnn::launch_col_gather(*ga, s));
     return ZRNN_OK;
   }
   // forward_prop_source + transfer_decoding_states_GPU (src/model.hpp:2367-2452)
@@ -1631,13 +1634,13 @@ struct BeamModel {
     if (align_pos) ZR_CUDA(cudaMemsetAsync(align_pos, 0, sizeof(float) * (size_t)S_max * NB, s));  // no attention: no votes
     // replicate the encoder's final (h,c) over the beam
     ZR_CUDA(zrnn::launch_div_map(rep_map, NB, beam, s));
-    zrnn::ColGatherArgs ga[3];
-    std::memset(ga, 0, sizeof(ga));
+    zrnn::ColGatherArgs ga;
+    std::memset(&ga, 0, sizeof(ga));
     for (int l = 0; l < L; ++l) {
-      add_gather(ga, act_at(sseq[l], (size_t)(S_max - 1) * n, g), hp[l]);
-      ga[0].src[ga[0].n_arrays] = cst[cur[l]][l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
+      add_gather(&ga, act_at(sseq[l], (size_t)(S_max - 1) * n, g), hp[l]);
+      add_plain(&ga, cst[cur[l]][l], cp[l], c.H);
     }
-    return run_gathers(ga, rep_map, s);
+    return run_gathers(&ga, rep_map, s);
   }
   // forward_prop_target (src/model.hpp:2573-2689) up to the vector handed to the softmax
   int forward(int t, const int* cur_ids, Act* top, cudaStream_t s) {
@@ -1659,14 +1662,14 @@ struct BeamModel {
   // swap_decoding_states + target_copy_prev_states (src/model.hpp:2691-2726)
   int reorder(const int* col_map, cudaStream_t s) {
     const zrnn_model_config& c = m->cfg;
-    zrnn::ColGatherArgs ga[3];
-    std::memset(ga, 0, sizeof(ga));
+    zrnn::ColGatherArgs ga;
+    std::memset(&ga, 0, sizeof(ga));
     for (int l = 0; l < c.num_layers; ++l) {
-      add_gather(ga, hn[l], hp[l]);
-      ga[0].src[ga[0].n_arrays] = cn[l]; ga[0].dst[ga[0].n_arrays++] = cp[l];
+      add_gather(&ga, hn[l], hp[l]);
+      add_plain(&ga, cn[l], cp[l], c.H);
     }
-    if (c.feed_input) add_gather(ga, htild_new, htild_feed);
-    return run_gathers(ga, col_map, s);
+    if (c.feed_input) add_gather(&ga, htild_new, htild_feed);
+    return run_gathers(&ga, col_map, s);
   }
 };
 
