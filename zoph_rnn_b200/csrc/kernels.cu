@@ -593,7 +593,26 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   const float* zc = z + (size_t)col * V;
   float m = -INFINITY, s = 0.f;
   const bool sum_in_pass2 = part_max && !part_sum;  // only tile maxima are known: sum exp(v - M) during the scan
-  if (part_max) {
+  // the value the <EOF> probability needs, requested early by the thread that will use it
+  const float z_eos = (logp_eos && tid == 32 && V > 1) ? zc[1] : 0.f;
+  float pmv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // this thread's tile maxima (n_parts <= 1024)
+  if (part_max && n_parts <= ZR_TOPK_TILES) {
+    float psv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {  // all loads in flight together
+      const int j = tid + 256 * q;
+      if (j < n_parts) {
+        pmv[q] = part_max[(size_t)j * N + col];
+        psv[q] = part_sum ? part_sum[(size_t)j * N + col] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float pm = pmv[q], ps = psv[q];
+      if (pm > m) { s = s * expf(m - pm) + ps; m = pm; }
+      else if (pm != -INFINITY) s += ps * expf(pm - m);
+    }
+  } else if (part_max) {
     for (int j = tid; j < n_parts; j += 256) {
       const float pm = part_max[(size_t)j * N + col];
       const float ps = part_sum ? part_sum[(size_t)j * N + col] : 0.f;
@@ -616,15 +635,18 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   if (lane == 0) { red_m[w] = wm; red_s[w] = ws; }
   if (tid == 0) { s_count = 0; s_nsel = 0; }
   __syncthreads();
-  if (tid == 32) {  // the normaliser, by a thread of the second warp while the first one selects the bound
+  if (w == 1) {  // the normaliser, by the second warp (one warp's term per lane) while the first selects the bound
     float M = -INFINITY;
     for (int i = 0; i < 8; ++i) M = fmaxf(M, red_m[i]);
-    double S = 0.0;
-    for (int i = 0; i < 8; ++i)
-      if (red_m[i] != -INFINITY) S += (double)red_s[i] * exp((double)red_m[i] - (double)M);
-    s_M = M;
-    s_logS = (float)log(S);
-    if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - M) - s_logS : -INFINITY;
+    double S = (lane < 8 && red_m[lane] != -INFINITY) ? (double)red_s[lane] * exp((double)red_m[lane] - (double)M) : 0.0;
+    S += __shfl_xor_sync(0xffffffffu, S, 1);
+    S += __shfl_xor_sync(0xffffffffu, S, 2);
+    S += __shfl_xor_sync(0xffffffffu, S, 4);
+    if (lane == 0) {
+      s_M = M;
+      s_logS = (float)log(S);
+      if (logp_eos) logp_eos[col] = (V > 1) ? (z_eos - M) - s_logS : -INFINITY;
+    }
   }
   // the k-th largest of the 256 thread maxima (duplicates count): k rounds of a warp-wide argmax over 8 values per
   // lane, the winner's owner dropping it
@@ -661,8 +683,9 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   const bool vec4 = (V & 3) == 0 && ((reinterpret_cast<uintptr_t>(zc) & 15) == 0);
   const bool skip = part_max && part_sum && part_width > 0 && n_parts <= ZR_TOPK_TILES;
   if (skip) {  // the tiles that can hold one of the k largest values (at least k of them, more only on ties)
-    for (int j = tid; j < n_parts; j += 256)
-      if (part_max[(size_t)j * N + col] >= thr) sel[atomicAdd(&s_nsel, 1)] = j;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (tid + 256 * q < n_parts && pmv[q] >= thr) sel[atomicAdd(&s_nsel, 1)] = tid + 256 * q;
     __syncthreads();
   }
   for (int attempt = 0; attempt < 4; ++attempt) {
@@ -772,8 +795,28 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   const int nc = s_count < ZR_TOPK_CAND ? s_count : ZR_TOPK_CAND;
   // k rounds of argmax over the candidates (value, then lower word id) by one warp: the candidate list is short, and
   // a warp needs no block barrier between rounds
-  if (w != 0) return;
   const float M = s_M, logS = s_logS;
+  if (nc <= 256) {
+    // few candidates (the normal case): every candidate counts the ones that beat it and writes itself at that rank
+    if (tid < nc) {
+      const float v = cval[tid];
+      const int id = cidx[tid];
+      int rank = 0;
+      for (int i = 0; i < nc; ++i) {
+        const float o = cval[i];
+        rank += (o > v || (o == v && cidx[i] < id)) ? 1 : 0;
+      }
+      if (rank < k) {
+        val_out[(size_t)col * k + rank] = (v - M) - logS;
+        idx_out[(size_t)col * k + rank] = id;
+      }
+    } else if (tid < k) {  // fewer candidates than k: the tail stays empty
+      val_out[(size_t)col * k + tid] = -INFINITY;
+      idx_out[(size_t)col * k + tid] = -1;
+    }
+    return;
+  }
+  if (w != 0) return;
   for (int r = 0; r < k; ++r) {
     float v = -INFINITY;
     int id = 0x7fffffff, pos = -1;
@@ -1322,7 +1365,7 @@ __device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int la
 
 __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
   __shared__ float cv[256];
-  __shared__ int cp[256];  // payload: beam column * 32 + candidate rank
+  __shared__ int ci[256];
   __shared__ int n_chg[16], n_cur[16];
   __shared__ float n_sc[16];
   const int s = blockIdx.x, tid = threadIdx.x, beam = a.beam, kc = a.k_cand, t = a.step;
@@ -1348,59 +1391,74 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
     return;
   }
   // ---- expand
+  // live columns: the leading ones whose current word is set (one load per lane, not a chain of dependent ones)
   int ncols = (t == 0) ? 1 : beam;
   {
-    int v = 0;
-    while (v < ncols && a.cur_ids[base + v] != -1) ++v;
-    ncols = v;
+    const int l = tid & 31;
+    const bool dead = l < ncols && a.cur_ids[base + l] == -1;
+    const unsigned db = __ballot_sync(0xffffffffu, dead);
+    if (db) ncols = __ffs(db) - 1;
   }
   {
     const int i = tid / kc, r = tid % kc;
     float v = -INFINITY;
+    int wd = -1;
     if (i < ncols) {
       const float lp = a.cand_val[(size_t)(base + i) * kc + r];
-      if (a.cand_idx[(size_t)(base + i) * kc + r] >= 0 && lp != -INFINITY) v = lp + a.scores[base + i];
+      wd = a.cand_idx[(size_t)(base + i) * kc + r];
+      if (wd >= 0 && lp != -INFINITY) v = lp + a.scores[base + i];
     }
-    cv[tid] = v;
-    cp[tid] = i * 32 + r;
+    cv[tid] = v;  // candidate tid = beam column * kc + candidate rank
+    ci[tid] = wd;  // its word, kept on chip: the selection below reads one per pick
   }
   __syncthreads();
-  for (int ksz = 2; ksz <= 256; ksz <<= 1)
-    for (int j = ksz >> 1; j > 0; j >>= 1) {
-      const int ixj = tid ^ j;
-      if (ixj > tid) {
-        const bool desc = ((tid & ksz) == 0);
-        const float x = cv[tid], y = cv[ixj];
-        if (desc ? (x < y) : (x > y)) {
-          cv[tid] = y; cv[ixj] = x;
-          const int tp = cp[tid]; cp[tid] = cp[ixj]; cp[ixj] = tp;
-        }
-      }
-      __syncthreads();
-    }
-  if (tid == 0) {
-    int filled = 0, pidx = 0;
+  // One warp walks the candidates in descending score (the lower candidate index wins a tie) until the beam is full:
+  // a warp-wide argmax per pick, the winner's owner dropping it.
+  if (tid < 32) {
+    const int lane = tid;
+    float loc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) loc[j] = cv[lane + 32 * j];
+    int filled = 0;
     while (filled < beam) {
-      if (pidx >= 256 || cv[pidx] == -INFINITY) {
-        n_cur[filled] = -1; n_chg[filled] = 0; n_sc[filled] = 0.f;
-        ++filled;
-        continue;
+      float bv = loc[0];
+      int bj = 0;
+#pragma unroll
+      for (int j = 1; j < 8; ++j)
+        if (loc[j] > bv) { bv = loc[j]; bj = j; }
+      int bidx = lane + 32 * bj;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+        if (ov > bv || (ov == bv && oi < bidx)) { bv = ov; bidx = oi; }
       }
-      const float val = cv[pidx];
-      const int i = cp[pidx] / 32, r = cp[pidx] % 32;
-      ++pidx;
-      const int wd = a.cand_idx[(size_t)(base + i) * kc + r];
+      if (bv == -INFINITY) {  // no candidate left: the remaining slots stay empty
+        if (lane == 0)
+          for (; filled < beam; ++filled) { n_cur[filled] = -1; n_chg[filled] = 0; n_sc[filled] = 0.f; }
+        break;
+      }
+      if ((bidx & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j == (bidx >> 5)) loc[j] = -INFINITY;
+      }
+      const int i = bidx / kc;
+      const int wd = ci[bidx];
       if (wd == 0) continue;  // <START> is never extended
       if (wd == 1) {          // <EOF>: finished hypothesis, does not take a slot
-        beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, val + a.penalty, vrows ? vrows + (size_t)i * a.Lmax : nullptr,
-                        vrows ? a.viterbi[base + i] : -1);
+        if (lane == 0)
+          beam_insert_hyp(a, s, rows + (size_t)i * a.Lmax, t, bv + a.penalty, vrows ? vrows + (size_t)i * a.Lmax : nullptr,
+                          vrows ? a.viterbi[base + i] : -1);
+        __syncwarp();
       } else {
-        n_cur[filled] = wd; n_chg[filled] = i; n_sc[filled] = val + a.penalty;
+        if (lane == 0) { n_cur[filled] = wd; n_chg[filled] = i; n_sc[filled] = bv + a.penalty; }
         ++filled;
       }
     }
   }
   __syncthreads();
+  // the surviving hypotheses' rows go to the other row buffer, which the host makes the current one for the next step
   for (int e = tid; e < beam * a.Lmax; e += blockDim.x) {
     const int f = e / a.Lmax, i = e % a.Lmax;
     int v = rows[(size_t)n_chg[f] * a.Lmax + i];
@@ -1412,10 +1470,6 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
       vtmp[e] = al;
     }
   }
-  __syncthreads();
-  for (int e = tid; e < beam * a.Lmax; e += blockDim.x) rows[e] = tmp[e];
-  if (vrows)
-    for (int e = tid; e < beam * a.Lmax; e += blockDim.x) vrows[e] = vtmp[e];
   if (tid < beam) {
     a.cur_ids[base + tid] = n_cur[tid];
     a.col_map[base + tid] = base + n_chg[tid];

@@ -157,7 +157,7 @@ struct BeamArgs {
   const int* src_len;      // [n_sent]
   const int* max_steps;    // [n_sent]
   int* top_sent;           // [n_sent][beam][Lmax]
-  int* top_tmp;            // same size
+  int* top_tmp;            // same size: the step writes the surviving rows here; the caller swaps the two after it
   float* scores;           // [n_sent][beam]
   int* cur_ids;            // [n_sent*beam] current word per column (-1 invalid)
   int* col_map;            // [n_sent*beam] source column for the state reorder
@@ -169,7 +169,7 @@ struct BeamArgs {
   // initialised to -20, :1335) and with every position of the k-best hypotheses
   const int* viterbi;      // [n_sent*beam]
   int* vit_rows;           // [n_sent][beam][Lmax]
-  int* vit_tmp;            // same size
+  int* vit_tmp;            // same size, swapped with vit_rows like the rows above
   int* best_align;         // [n_sent][k_best][Lmax]
 };
 cudaError_t launch_beam_init(const BeamArgs& a, cudaStream_t st);

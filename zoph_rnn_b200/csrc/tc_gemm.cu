@@ -990,7 +990,8 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_persistent_kernel(const __grid
               const int r = 4 * i + (lane >> 3), j = lane & 7;
               const float4 o = *reinterpret_cast<const float4*>(xp + r * 32 + ((j ^ (r & 7)) << 2));
               const int grow = m_tile * 128 + q * 32 + r, n = nb + 4 * j;
-              if (grow < p.M && n < p.N) *reinterpret_cast<float4*>(p.C + (size_t)grow * p.ldc + n) = o;
+              // streaming stores: the consumer reads a few tiles of the logits once, the weights should stay in L2
+              if (grow < p.M && n < p.N) __stcs(reinterpret_cast<float4*>(p.C + (size_t)grow * p.ldc + n), o);
             }
             __syncwarp();
           } else if (row_ok) {

@@ -1796,6 +1796,9 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
     {
       KScope ks(KC_BEAM, s);
       ZR_CUDA(zrnn::launch_beam_step(ba, s));
+      // the step wrote the surviving rows into the second row buffer: it is the current one from now on
+      std::swap(ba.top_sent, ba.top_tmp);
+      std::swap(ba.vit_rows, ba.vit_tmp);
     }
     if (t < Tmax)
       for (int k = 0; k < K; ++k) ZR_TRY(bm[k].reorder(col_map, s));
