@@ -509,8 +509,14 @@ def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
     wbytes = 2 if dtype == "bf16" else 4   # bytes per weight as the reference stores them (fp32) or bf16
     out = dict(kernel=top, launches=n, avg_launch_us=avg_s * 1e6, peak_source=peak_src,
                traffic=NCU_TRAFFIC.get((top, dtype)))
-    if top == "softmax_gemm" and softmax_cols * cfg["V_tgt"] > 5e7:
-        flops = 2.0 * cfg["V_tgt"] * H * softmax_cols
+    sm_flops = 2.0 * cfg["V_tgt"] * H * softmax_cols
+    sm_bytes = cfg["V_tgt"] * H * wbytes + (H * softmax_cols + 2 * softmax_cols) * 4
+    # the vocabulary GEMM is bound by whichever lower bound is larger: its flops at the tensor peak or its
+    # algorithmic bytes at the copy peak
+    sm_tensor_bound = (sm_flops / (float(peaks.get("bf16_tflops_sustained", 1400.0)) * 1e12)
+                       > sm_bytes / (float(peaks.get("hbm_gbs", 6650.0)) * 1e9))
+    if top == "softmax_gemm" and sm_tensor_bound:
+        flops = sm_flops
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         out.update(bound="tensor", unit="TFLOP/s", peak=peak, achieved=flops / avg_s / 1e12,
                    algorithmic_flops_per_launch=flops,
@@ -526,7 +532,7 @@ def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
                    algorithmic_bytes_per_launch=alg,
                    note=f"avg {mats:.2f} HxH matrices of {wbytes}-byte weights + 5 HxB fp32 activations per launch")
     elif top == "softmax_gemm":
-        alg = cfg["V_tgt"] * H * wbytes + (H * softmax_cols + 2 * softmax_cols) * 4
+        alg = sm_bytes
         out.update(bound="hbm", unit="GB/s", peak=float(peaks.get("hbm_gbs", 6650.0)), achieved=alg / avg_s / 1e9,
                    algorithmic_bytes_per_launch=alg, note="D once + h columns + 2 floats per column")
     else:
