@@ -317,8 +317,10 @@ __device__ __forceinline__ void cluster_sync_all() {
 // trip, remote loads measured ~1.4 us each), a cluster barrier publishes them, and the owner adds its SPLITK slots
 // in a fixed order.  This keeps the number of CTAs high for skinny problems (one 128-row M tile) without every CTA
 // re-reading the whole A operand.
+// The body is a device function over a reference to the kernel parameters, so that one launch can also carry several
+// independent problems (tc_gemm_multi_kernel below).
 template <int BN, int MODE, int EPI, int SPLITK>
-__global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+__device__ __forceinline__ void tc_gemm_body(const TcParams& p, const int m_block) {
   constexpr int ST = num_stages(BN, MODE, SPLITK);
   constexpr int STAGE = stage_bytes(BN, MODE);
   constexpr int BBYTES = BN * 128;
@@ -342,7 +344,7 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  const int m0 = blockIdx.x * 128;
+  const int m0 = m_block * 128;
   const int n_tile = blockIdx.y;
   for (int i = threadIdx.x; i < BN; i += blockDim.x) {
     float bv;
@@ -768,6 +770,18 @@ __global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__
   }
 }
 
+template <int BN, int MODE, int EPI, int SPLITK>
+__global__ void __launch_bounds__(256, 1) tc_gemm_kernel(const __grid_constant__ TcParams p) {
+  tc_gemm_body<BN, MODE, EPI, SPLITK>(p, (int)blockIdx.x);
+}
+// Several independent problems of one column tile each (M <= 128) in one launch: blockIdx.x selects the problem.  The
+// encoder uses it for the LSTM cells of one anti-diagonal (layer l at step t, layer l-1 at step t+1, ...), which do
+// not depend on one another: together they fill the SMs without splitting K, so no partial tiles are exchanged.
+template <int BN, int MODE, int EPI, int SPLITK>
+__global__ void __launch_bounds__(256, 1) tc_gemm_multi_kernel(const __grid_constant__ TcMulti pm) {
+  tc_gemm_body<BN, MODE, EPI, SPLITK>(pm.p[blockIdx.x], 0);
+}
+
 // ------------------------------------------------------------------ persistent variant for large GEMMs
 // One CTA per SM walks over output tiles (M tile fastest, so concurrently running CTAs share the same rows of B in
 // L2).  The TMA producer runs ahead across tile boundaries and the accumulator is double-buffered in TMEM, so the
@@ -1156,6 +1170,55 @@ cudaError_t launch_t(const TcParams& p, cudaStream_t st) {
   return e;
 }
 
+template <int MODE, int SPLITK>
+cudaError_t launch_multi_t(const TcMulti& pm, int n, cudaStream_t st) {
+  constexpr int BN = 128;
+  const size_t smem = (size_t)smem_bytes(BN, MODE, SPLITK);
+  static bool configured[kMaxDevices] = {false};
+  const int dev = current_device();
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_multi_kernel<BN, MODE, TC_EPI_LSTM, SPLITK>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  dim3 grid(n, (pm.p[0].N * 4 + BN - 1) / BN, SPLITK);
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3((SPLITK > 1 && BN / 4 / SPLITK == 8) ? 256 : 192);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (SPLITK > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = SPLITK;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, tc_gemm_multi_kernel<BN, MODE, TC_EPI_LSTM, SPLITK>, pm);
+  count_launch();
+  return e;
+}
+template <int MODE>
+cudaError_t launch_multi_mode(const TcMulti& pm, int n, int splitk, cudaStream_t st) {
+  switch (splitk) {
+    case 1: return launch_multi_t<MODE, 1>(pm, n, st);
+    case 2: return launch_multi_t<MODE, 2>(pm, n, st);
+    case 4: return launch_multi_t<MODE, 4>(pm, n, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
 template <int MODE, int EPI>
 cudaError_t launch_bn(const TcParams& p, int BN, int splitk, cudaStream_t st) {
   if (splitk == 1) {
@@ -1200,6 +1263,19 @@ cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cuda
     if (mode == TC_TF32) return launch_persistent_t<256, TC_TF32, TC_EPI_STORE>(p, st);
     if (mode == TC_TF32X3) return launch_persistent_t<128, TC_TF32X3, TC_EPI_STORE>(p, st);
     if (mode == TC_F16X2) return launch_persistent_t<128, TC_F16X2, TC_EPI_STORE>(p, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_tc_lstm_multi(const TcMulti& pm, int n, int mode, cudaStream_t st, int splitk) {
+  if (n < 1 || n > TcMulti::MAX) return cudaErrorInvalidValue;
+  for (int i = 0; i < n; ++i)
+    if (pm.p[i].M > 128 || pm.p[i].M < 1 || pm.p[i].N != pm.p[0].N) return cudaErrorInvalidValue;
+  switch (mode) {
+    case TC_BF16: return launch_multi_mode<TC_BF16>(pm, n, splitk, st);
+    case TC_TF32: return launch_multi_mode<TC_TF32>(pm, n, splitk, st);
+    case TC_TF32X3: return launch_multi_mode<TC_TF32X3>(pm, n, splitk, st);
+    case TC_F16X2: return launch_multi_mode<TC_F16X2>(pm, n, splitk, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -63,6 +63,14 @@ struct TcParams {
 // the LSE epilogue then produces n_tiles * splitk partial rows.
 cudaError_t launch_tc_gemm(const TcParams& p, int BN, int mode, int epi, cudaStream_t st, int splitk = 1);
 
+// Up to TcMulti::MAX independent LSTM layer-steps (EPI_LSTM, 128-row weight tiles, M <= 128 columns and the same
+// hidden size each) in one launch: grid (n, row tiles, splitk).  Nothing orders the problems among themselves.
+struct TcMulti {
+  enum { MAX = 8 };
+  TcParams p[MAX];
+};
+cudaError_t launch_tc_lstm_multi(const TcMulti& pm, int n, int mode, cudaStream_t st, int splitk);
+
 // Persistent one-CTA-per-SM variant for large problems (store and log-sum-exp epilogues).  The B tensor map must use
 // 256-row boxes for TC_BF16 / TC_TF32 and 128-row boxes for the split modes.  Two epilogue warps share each output
 // row of a tile, one per half of its columns, so the (max, sum) partials are indexed

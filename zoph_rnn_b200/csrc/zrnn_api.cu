@@ -417,13 +417,11 @@ void set_operand_outputs(zrnn::TcParams& tp, int eng, const Act& out, int Kpad) 
 }
 
 // One LSTM cell.  x / h_prev / htild and the output are activations in the form the layer's engine needs.
-int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, const int* mask, const float* c_prev,
-                 int B, const Act& out, float* c_out, cudaStream_t st) {
-  if (L->eng == ENG_SIMT)
-    return lstm_cell_simt(L, x.f32, mask, hp.f32, c_prev, q ? q->f32 : nullptr, B, out.f32, c_out, st);
+// kernel parameters of one tensor-core LSTM layer-step
+int cell_params(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, const int* mask, const float* c_prev,
+                int B, const Act& out, float* c_out, zrnn::TcParams& tp) {
   const int H = L->H, Kpad = L->Kpad, eng = L->eng;
   const int kb = (H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng));
-  zrnn::TcParams tp;
   std::memset(&tp, 0, sizeof(tp));
   ZR_TRY(act_maps(x, eng, H, Kpad, B, &tp.a[0], &tp.a_lo[0]));
   ZR_TRY(act_maps(hp, eng, H, Kpad, B, &tp.a[1], &tp.a_lo[1]));
@@ -438,6 +436,15 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   tp.C = out.f32; tp.ldc = H;
   set_operand_outputs(tp, eng, out, Kpad);
   tp.c_prev = c_prev; tp.c_out = c_out; tp.err = tc_error_word(); prof_attach(tp);
+  return ZRNN_OK;
+}
+int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, const int* mask, const float* c_prev,
+                 int B, const Act& out, float* c_out, cudaStream_t st) {
+  if (L->eng == ENG_SIMT)
+    return lstm_cell_simt(L, x.f32, mask, hp.f32, c_prev, q ? q->f32 : nullptr, B, out.f32, c_out, st);
+  const int H = L->H, eng = L->eng;
+  zrnn::TcParams tp;
+  ZR_TRY(cell_params(L, x, hp, q, mask, c_prev, B, out, c_out, tp));
   KScope ks(KC_LSTM, st);
   int bn = L->BN;
   const int splitk = pick_splitk(B, 4 * H, L->BN, 4);
@@ -670,6 +677,7 @@ struct zrnn_model {
   bool finalized = false;
   cudaStream_t stream = nullptr;
   DevBuf ws, io;
+  zrnn::TcMulti enc_multi;  // parameter block of the encoder's multi-cell launches (host scratch)
   const float* last_top = nullptr;
   int last_top_cols = 0;
   std::vector<int> h_tmp;
@@ -1345,6 +1353,38 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
                        cudaStream_t s) {
   const int L = m->cfg.num_layers;
   ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
+  // Anti-diagonal order: the cells (layer l, step d - l) of diagonal d depend only on diagonal d - 1, so one launch
+  // runs them side by side.  L cells fill the SMs with less (or no) K splitting than one cell alone: each CTA streams a
+  // longer K slice, no partial tiles cross the cluster, and S + L - 1 launches replace S * L.  Needs one column tile
+  // per cell, the tensor-core engine, and all L cells' row tiles resident at once.
+  static const bool by_layers = [] {
+    const char* e = std::getenv("ZRNN_ENCODER_ORDER");
+    return e && std::string(e) == "layers";
+  }();
+  const zrnn_lstm_layer* L0 = m->src[0];
+  int dsplit = 0;
+  if (!by_layers && L >= 2 && L <= zrnn::TcMulti::MAX && L0->eng != ENG_SIMT && B <= 128 && L0->BN == 128)
+    for (int k = 4; k >= 1 && !dsplit; k >>= 1)
+      if (L * L0->n_tiles * k <= 148) dsplit = k;
+  if (dsplit) {
+    KScope sweep(KC_LSTM, s, S * L, true);
+    zrnn::TcMulti* pm = &m->enc_multi;
+    for (int d = 0; d < S + L - 1; ++d) {
+      int n = 0;
+      for (int l = std::max(0, d - S + 1); l <= std::min(L - 1, d); ++l) {
+        const int t = d - l;
+        const Act x = l == 0 ? act_at(X0, (size_t)t * B, g) : act_at(seq[l - 1], (size_t)t * B, g);
+        const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
+        const Act out = act_at(seq[l], (size_t)t * B, g);
+        const int cu = cur[l];
+        ZR_TRY(cell_params(m->src[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], pm->p[n]));
+        cur[l] = cu ^ 1;
+        ++n;
+      }
+      ZR_CUDA(zrnn::launch_tc_lstm_multi(*pm, n, eng_tcmode(L0->eng), s, dsplit));
+    }
+    return ZRNN_OK;
+  }
   // Layer by layer, not step by step: layer l only needs layer l-1's finished sequence, and running all S steps
   // of one layer back to back keeps that layer's weights resident in the 126 MB L2 (all layers together do not fit).
   for (int l = 0; l < L; ++l) {
