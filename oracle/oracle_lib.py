@@ -107,7 +107,7 @@ class OracleModel:
             lib().orc_model_set_tensor(self._h, i, _fp(t), 0)
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:  # module globals may be gone at interpreter shutdown
             lib().orc_model_destroy(self._h)
             self._h = None
 

@@ -262,13 +262,14 @@ __host__ __device__ constexpr int smem_bytes(int BN, int mode, int splitk) {
   return num_stages(BN, mode, splitk) * stage_bytes(BN, mode) + (slots_alias_ring(mode, splitk) ? 0 : slot_bytes(BN, splitk)) + 1024;
 }
 
-// 3xTF32 keeps fp32-level accuracy only if the tensor core's accumulator is not asked to absorb hundreds of
+// The split modes keep fp32-level accuracy only if the tensor core's accumulator is not asked to absorb hundreds of
 // additions: its fp32 accumulation truncates toward zero (measured: a relative shrink of ~8e-6 after 375
-// additions).  So in that mode the hi*hi products are spread round-robin over NACC TMEM accumulators (each sees
+// additions).  So in those modes the hi*hi products are spread round-robin over NACC TMEM accumulators (each sees
 // 1/NACC of the additions on a smaller partial sum), the two small cross terms go to an accumulator of their own,
-// and the epilogue adds the partial sums with round-to-nearest fp32.
+// and the epilogue adds the partial sums with round-to-nearest fp32.  128-column tiles use all 512 TMEM columns:
+// three main accumulators and the cross one (against two: log-prob error at H = 1000, 4 layers 2.0e-6 -> 1.4e-6).
 __host__ __device__ constexpr int num_acc(int BN, int mode) {
-  return !mode_split(mode) ? 1 : (BN <= 32 ? 8 : (BN <= 64 ? 4 : (BN <= 128 ? 2 : 1)));
+  return !mode_split(mode) ? 1 : (BN <= 32 ? 8 : (BN <= 64 ? 4 : (BN <= 128 ? 3 : 1)));  // (NACC + 1) BN <= 512 columns
 }
 __host__ __device__ constexpr int tmem_cols(int BN, int mode) {
   int need = (mode_split(mode) ? num_acc(BN, mode) + 1 : 1) * BN;
