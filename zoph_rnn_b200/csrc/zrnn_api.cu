@@ -449,8 +449,10 @@ int cell_forward(zrnn_lstm_layer* L, const Act& x, const Act& hp, const Act* q, 
   int bn = L->BN;
   const int splitk = pick_splitk(B, 4 * H, L->BN, 4);
   // many columns (beam decoding): 128-row tiles would need more than one wave of CTAs; 256-row tiles built from two
-  // packed tiles halve the CTA count and the activation traffic per flop
-  if (splitk == 1 && L->BN == 128 && ((B + 127) / 128) * L->n_tiles > 148) {
+  // packed tiles halve the CTA count and the activation traffic per flop.  A 256-column tile leaves TMEM room for one
+  // main accumulator only (measured per-token log-prob error at H = 1000: fp16 split 0.8e-6 -> 2.1e-6, 3xTF32
+  // 1.6e-6 -> 3.9e-6), so the 3xTF32 engine, chosen for its accuracy margin, keeps the 128-row tiles.
+  if (splitk == 1 && L->BN == 128 && eng != ENG_X3 && ((B + 127) / 128) * L->n_tiles > 148) {
     bn = 256;
     tp.b_pack_rows = 128;
   }
