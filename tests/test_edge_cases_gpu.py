@@ -115,6 +115,9 @@ def test_decode_limits_and_short_hypothesis_lists(api, oracle, dtype):
     (0, 1, 3, 1020, 0, 5001, 200, (0, 0), (3, 8)),       # language model, two row tiles, odd vocabulary
     (1, 0, 1, 512, 64, 129, 7, (1, 30), (1, 3)),         # vocabulary just above one softmax tile
     (2, 0, 1, 128, 50, 31, 3, (4, 4), (6, 6)),           # vocabulary smaller than any tile
+    (2, 0, 8, 64, 40, 90, 5, (1, 9), (2, 4)),            # eight layers: the widest multi-cell encoder launch
+    (1, 0, 3, 1000, 60, 120, 20, (2, 7), (2, 3)),        # three layers of 32 row tiles: encoder diagonals, K unsplit
+    (2, 0, 5, 1000, 60, 120, 9, (3, 3), (2, 2)),         # five such layers do not fit the SMs: layer-by-layer encoder
 ])
 def test_shape_sweep_against_the_oracle(api, oracle, att, lm, L, H, Vs, Vt, B, S, T):
     """Shapes around the kernels' tile boundaries, fp32-accurate tensor-core engine and the bf16 engine."""
