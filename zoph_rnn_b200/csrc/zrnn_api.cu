@@ -1350,11 +1350,13 @@ static int act_zero(const Act& a, const Geom& g, size_t cols, cudaStream_t s) {
 
 // Encoder over S steps of B columns.  seq[l] receives every step's h of layer l; c ping-pongs in cst.
 // On return cur[l] indexes the final cell state of layer l.
-static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* mask, int S, int B, const Act& X0,
-                       const Act& zero, std::vector<Act>& seq, std::vector<float*> cst[2], std::vector<int>& cur,
-                       cudaStream_t s) {
-  const int L = m->cfg.num_layers;
-  ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
+// A stack of LSTM layers over S steps whose inputs X0 (one slot per step) are all known in advance: the source side
+// always, the target side of language models and of models without feed-input.  h0[l] is layer l's state before
+// step 0; its c comes from cst[cur[l]][l].
+static int run_stack(zrnn_model* m, const std::vector<zrnn_lstm_layer*>& layers, const Geom& g, const int* mask, int S,
+                     int B, const Act& X0, const std::vector<Act>& h0, std::vector<Act>& seq, std::vector<float*> cst[2],
+                     std::vector<int>& cur, cudaStream_t s) {
+  const int L = (int)layers.size();
   // Anti-diagonal order: the cells (layer l, step d - l) of diagonal d depend only on diagonal d - 1, so one launch
   // runs them side by side.  L cells fill the SMs with less (or no) K splitting than one cell alone: each CTA streams a
   // longer K slice, no partial tiles cross the cluster, and S + L - 1 launches replace S * L.  Needs one column tile
@@ -1363,7 +1365,7 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
     const char* e = std::getenv("ZRNN_ENCODER_ORDER");
     return e && std::string(e) == "layers";
   }();
-  const zrnn_lstm_layer* L0 = m->src[0];
+  const zrnn_lstm_layer* L0 = layers[0];
   int dsplit = 0;
   // Not for 3xTF32: its tf32 MMAs cover 8 k-values each, so an unsplit K = 2H chain puts twice as many truncating
   // additions into one accumulator as the fp16 split does (measured at H = 1000, 4 layers: per-token log-prob error
@@ -1384,10 +1386,10 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
       for (int l = std::max(0, d - S + 1); l <= std::min(L - 1, d); ++l) {
         const int t = d - l;
         const Act x = l == 0 ? act_at(X0, (size_t)t * B, g) : act_at(seq[l - 1], (size_t)t * B, g);
-        const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
+        const Act hp = t == 0 ? h0[l] : act_at(seq[l], (size_t)(t - 1) * B, g);
         const Act out = act_at(seq[l], (size_t)t * B, g);
         const int cu = cur[l];
-        ZR_TRY(cell_params(m->src[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], pm->p[n]));
+        ZR_TRY(cell_params(layers[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], pm->p[n]));
         cur[l] = cu ^ 1;
         ++n;
       }
@@ -1401,14 +1403,21 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
     KScope sweep(KC_LSTM, s, S, true);
     for (int t = 0; t < S; ++t) {
       const Act x = l == 0 ? act_at(X0, (size_t)t * B, g) : act_at(seq[l - 1], (size_t)t * B, g);
-      const Act hp = t == 0 ? zero : act_at(seq[l], (size_t)(t - 1) * B, g);
+      const Act hp = t == 0 ? h0[l] : act_at(seq[l], (size_t)(t - 1) * B, g);
       const Act out = act_at(seq[l], (size_t)t * B, g);
       const int cu = cur[l];
-      ZR_TRY(cell_forward(m->src[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], s));
+      ZR_TRY(cell_forward(layers[l], x, hp, nullptr, mask + (size_t)t * B, cst[cu][l], B, out, cst[cu ^ 1][l], s));
       cur[l] = cu ^ 1;
     }
   }
   return ZRNN_OK;
+}
+static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* mask, int S, int B, const Act& X0,
+                       const Act& zero, std::vector<Act>& seq, std::vector<float*> cst[2], std::vector<int>& cur,
+                       cudaStream_t s) {
+  ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
+  const std::vector<Act> h0(m->cfg.num_layers, zero);
+  return run_stack(m, m->src, g, mask, S, B, X0, h0, seq, cst, cur, s);
 }
 
 // d_logp_out == nullptr: stop after the recurrent stack (the top-layer vectors stay in m->last_top)
@@ -1511,20 +1520,33 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
   }
   // target side: layer l starts from the encoder's final (h,c) of layer l (src/model.hpp:1714-1724)
   ZR_TRY(gather_act(m->tgt[0], tin_id, (int)nT, Xt, s));
-  for (int t = 0; t < T; ++t) {
-    Act x = act_at(Xt, (size_t)t * B, g);
-    const int* mk = tin_mk + (size_t)t * B;
-    for (int l = 0; l < L; ++l) {
-      Act hp = t > 0 ? act_at(tseq[l], (size_t)(t - 1) * B, g) : (c.lm ? zero : act_at(sseq[l], (size_t)(S - 1) * B, g));
-      const Act out = act_at(tseq[l], (size_t)t * B, g);
-      const Act feed = act_at(hts, (size_t)(t > 0 ? t - 1 : 0) * B, g);
-      const bool use_feed = (l == 0 && c.feed_input && t > 0);
-      const int cu = cur[l];
-      ZR_TRY(cell_forward(m->tgt[l], x, hp, use_feed ? &feed : nullptr, mk, cst[cu][l], B, out, cst[cu ^ 1][l], s));
-      cur[l] = cu ^ 1;
-      x = out;
+  if (!c.feed_input) {
+    // no cell waits for an attention output: the target side is a plain stack too (anti-diagonal order where it
+    // fits), and attention follows per step on the finished top layer
+    std::vector<Act> h0(L);
+    for (int l = 0; l < L; ++l) h0[l] = c.lm ? zero : act_at(sseq[l], (size_t)(S - 1) * B, g);
+    ZR_TRY(run_stack(m, m->tgt, g, tin_mk, T, B, Xt, h0, tseq, cst, cur, s));
+    if (c.attention)
+      for (int t = 0; t < T; ++t)
+        ZR_TRY(att_forward(m->att, act_at(tseq[L - 1], (size_t)t * B, g), tin_mk + (size_t)t * B, B,
+                           act_at(hts, (size_t)t * B, g), nullptr, s));
+  } else {
+    // feed-input: layer 0 of step t reads the attention output of step t - 1, so the steps form one chain
+    for (int t = 0; t < T; ++t) {
+      Act x = act_at(Xt, (size_t)t * B, g);
+      const int* mk = tin_mk + (size_t)t * B;
+      for (int l = 0; l < L; ++l) {
+        Act hp = t > 0 ? act_at(tseq[l], (size_t)(t - 1) * B, g) : (c.lm ? zero : act_at(sseq[l], (size_t)(S - 1) * B, g));
+        const Act out = act_at(tseq[l], (size_t)t * B, g);
+        const Act feed = act_at(hts, (size_t)(t > 0 ? t - 1 : 0) * B, g);
+        const bool use_feed = (l == 0 && t > 0);
+        const int cu = cur[l];
+        ZR_TRY(cell_forward(m->tgt[l], x, hp, use_feed ? &feed : nullptr, mk, cst[cu][l], B, out, cst[cu ^ 1][l], s));
+        cur[l] = cu ^ 1;
+        x = out;
+      }
+      if (c.attention) ZR_TRY(att_forward(m->att, x, mk, B, act_at(hts, (size_t)t * B, g), nullptr, s));
     }
-    if (c.attention) ZR_TRY(att_forward(m->att, x, mk, B, act_at(hts, (size_t)t * B, g), nullptr, s));
   }
   const Act& top = c.attention ? hts : tseq[L - 1];
   m->last_top = top.f32;
