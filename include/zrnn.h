@@ -174,8 +174,11 @@ int zrnn_softmax_score(zrnn_softmax* sm, const float* d_h, const int* d_targets,
                        float* d_logp_out, void* stream);
 /* Allocation-free variant of zrnn_softmax_score.  No counterpart in the reference: it exists for hosts that
  * cannot allocate device memory once they are running - a server whose own arena already owns the whole GPU,
- * or a latency-bound loop that cannot afford the device-wide stall of cudaMalloc/cudaFree.  Same arguments and
- * results as zrnn_softmax_score, but the per-tile scratch lives in a fixed 16 MiB array inside the library
+ * or a latency-bound loop that cannot afford the device-wide stall of cudaMalloc/cudaFree.  Same arguments as
+ * zrnn_softmax_score.  Arithmetic: always the exact fp32 FMA kernel on the layer's fp32 copy of D, whatever the
+ * layer's zrnn_dtype - for a ZRNN_F32 / ZRNN_F32_SIMT layer the results equal zrnn_softmax_score's to fp32 rounding,
+ * for a ZRNN_BF16 / ZRNN_TF32 layer they are the fp32 results (closer to the reference than that layer's own
+ * tensor-core path, and slower at large V).  The per-tile scratch lives in a fixed 16 MiB array inside the library
  * (zrnn_softmax_score_noalloc_max_floats() floats, present on every GPU that loads the library until the process
  * exits) and the call performs no cudaMalloc, cudaFree or other allocating call.
  * Limit: (2*ceil(V/rows)+1)*N floats must fit, rows = 128 when N >= 96 and V >= 512, else 64; beyond it the call

@@ -132,9 +132,9 @@ def test_decoding_matches_oracle(api, oracle, att, feed, dtype):
 
 
 @pytest.mark.parametrize("dtype,name", [(1, "bf16"), (2, "tf32")])
-def test_reduced_precision_perplexity_and_argmax(api, oracle, dtype, name):
-    """bf16 / tf32 tensor-core paths: perplexity within 0.5 % of the CPU path on identical fp32 weights, and the
-    greedy (beam 1) decode agrees on >= 99.5 % of tokens for sentences that have no near-tie."""
+def test_reduced_precision_perplexity(api, oracle, dtype, name):
+    """bf16 / tf32 tensor-core paths: perplexity within 0.5 % of the CPU path on identical fp32 weights (the token
+    agreement of their greedy and beam decodes is test_fullsize_gpu.py::test_reduced_precision_token_agreement)."""
     cfg = synth.make_cfg(2, 256, 2000, 3000, attention=2, feed_input=1)
     w = synth.make_weights(cfg, seed=33, scale=0.1)
     src, tin, tout = synth.make_s2s_batch(2000, 3000, 32, 5, 20, 5, 20, seed=11)

@@ -215,12 +215,16 @@ cudaError_t launch_convert_rows(const float* src, long long rows, int K, long lo
 // embedding column gather: x[:,n] = W[:,ids[n]] -- a bit copy, 16-byte vectorised when H % 4 == 0.
 // One CTA of 128 threads per 4 columns keeps every load/store a full 128-byte line.
 // ------------------------------------------------------------------------------------------
-__global__ void gather_columns_kernel(const float* __restrict__ W, int H, const int* __restrict__ ids, int n_cols,
-                                      float* __restrict__ x) {
+__global__ void gather_columns_kernel(const float* __restrict__ W, int H, int V, const int* __restrict__ ids, int n_cols,
+                                      float* __restrict__ x, int* err) {
   const int vec = ((H & 3) == 0);
   for (int col = blockIdx.x; col < n_cols; col += gridDim.x) {
     int id = ids[col];
     if (id < 0) id = 0;  // an invalid beam slot; its column is never consumed
+    if (V > 0 && id >= V) {  // an id of another vocabulary: read column 0 instead and report it
+      id = 0;
+      if (err && threadIdx.x == 0) atomicExch(err, kErrBadTokenId);
+    }
     const float* src = W + (size_t)id * H;
     float* dst = x + (size_t)col * H;
     if (vec) {
@@ -232,30 +236,36 @@ __global__ void gather_columns_kernel(const float* __restrict__ W, int H, const 
     }
   }
 }
-cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_cols, float* x, cudaStream_t st) {
+cudaError_t launch_gather_columns(const float* W, int H, int V, const int* ids, int n_cols, float* x, int* err,
+                                  cudaStream_t st) {
   if (n_cols <= 0) return cudaSuccess;
   const int threads = H >= 512 ? 128 : 64;
-  gather_columns_kernel<<<n_cols > 148 * 16 ? 148 * 16 : n_cols, threads, 0, st>>>(W, H, ids, n_cols, x);
+  gather_columns_kernel<<<n_cols > 148 * 16 ? 148 * 16 : n_cols, threads, 0, st>>>(W, H, V, ids, n_cols, x, err);
   count_launch();
   return cudaGetLastError();
 }
 
-__global__ void gather_rows16_kernel(const uint4* __restrict__ src, int vec_per_row, const int* __restrict__ ids,
-                                     int n_rows, uint4* __restrict__ dst) {
+__global__ void gather_rows16_kernel(const uint4* __restrict__ src, int vec_per_row, int n_src_rows,
+                                     const int* __restrict__ ids, int n_rows, uint4* __restrict__ dst, int* err) {
   for (int r = blockIdx.x; r < n_rows; r += gridDim.x) {
     int id = ids[r];
     if (id < 0) id = 0;
+    if (n_src_rows > 0 && id >= n_src_rows) {
+      id = 0;
+      if (err && threadIdx.x == 0) atomicExch(err, kErrBadTokenId);
+    }
     const uint4* s = src + (size_t)id * vec_per_row;
     uint4* d = dst + (size_t)r * vec_per_row;
     for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) d[i] = __ldg(s + i);
   }
 }
-cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, const int* ids, int n_rows, void* dst,
-                                 cudaStream_t st) {
+cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, int n_src_rows, const int* ids, int n_rows,
+                                 void* dst, int* err, cudaStream_t st) {
   if (n_rows <= 0) return cudaSuccess;
   if (row_bytes % 16 != 0) return cudaErrorInvalidValue;
   gather_rows16_kernel<<<n_rows > 148 * 16 ? 148 * 16 : n_rows, 128, 0, st>>>(
-      reinterpret_cast<const uint4*>(src), (int)(row_bytes / 16), ids, n_rows, reinterpret_cast<uint4*>(dst));
+      reinterpret_cast<const uint4*>(src), (int)(row_bytes / 16), n_src_rows, ids, n_rows,
+      reinterpret_cast<uint4*>(dst), err);
   count_launch();
   return cudaGetLastError();
 }

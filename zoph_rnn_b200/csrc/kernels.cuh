@@ -12,10 +12,14 @@ void count_launch(int n = 1);
 cudaError_t launch_prep_ids(const int* raw, int n, int* nonm1, int* mask01, cudaStream_t st);
 
 // ---- embedding column gather (replaces sparse_lookup_kernel, src/custom_kernels.h:340-348)
-cudaError_t launch_gather_columns(const float* W, int H, const int* ids, int n_cols, float* x, cudaStream_t st);
-// same for rows of `row_bytes` bytes (a multiple of 16) of any element type: dst row n = src row ids[n]
-cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, const int* ids, int n_rows, void* dst,
-                                 cudaStream_t st);
+// V > 0: an id >= V reads column 0 instead of memory past the table and sets *err (if given) to kErrBadTokenId
+constexpr int kErrBadTokenId = 100;
+cudaError_t launch_gather_columns(const float* W, int H, int V, const int* ids, int n_cols, float* x, int* err,
+                                  cudaStream_t st);
+// same for rows of `row_bytes` bytes (a multiple of 16) of any element type: dst row n = src row ids[n]; n_src_rows > 0
+// bounds the ids the same way
+cudaError_t launch_gather_rows16(const void* src, size_t row_bytes, int n_src_rows, const int* ids, int n_rows,
+                                 void* dst, int* err, cudaStream_t st);
 
 // ---- generic column gather over several H x ncols arrays at once: dst[a][:,c] = src[a][:,map[c]]
 // (replaces the per-column cudaMemcpy loops of swap_states_decoding / transfer_decoding_states_GPU,

@@ -99,6 +99,13 @@ class ModelFileReader {
         while (p < e && (*p == ' ' || *p == '\t')) ++p;
         const char* w = p;
         while (p < e && *p != ' ' && *p != '\t' && *p != '\r') ++p;
+        // a mapping to an id outside the model's vocabulary would later index past the embedding table
+        const int vsize = (s == 0 && !h->lm) ? h->V_src : h->V_tgt;
+        if (id < 0 || id >= vsize) {
+          *err = "vocabulary line maps '" + std::string(w, p) + "' to id " + std::to_string(id) + ", outside the model's " +
+                 std::to_string(vsize) + " words";
+          return false;
+        }
         dst.emplace_back(id, std::string(w, p));
       }
       if (!found) { *err = "truncated vocabulary section"; return false; }

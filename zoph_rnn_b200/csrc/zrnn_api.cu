@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -203,6 +204,7 @@ struct OpMem {
   float* lo = nullptr;
   int alloc(size_t elems, int eng) {
     release();
+    ++g_buf_generation;  // a captured graph may still hold the old addresses
     ZR_CUDA(cudaMalloc(&hi, elems * eng_eb(eng)));
     ZR_CUDA(cudaMemset(hi, 0, elems * eng_eb(eng)));
     if (eng_split(eng)) {
@@ -212,6 +214,7 @@ struct OpMem {
     return ZRNN_OK;
   }
   void release() {
+    if (hi || lo) ++g_buf_generation;
     cudaFree(hi);
     cudaFree(lo);
     hi = nullptr;
@@ -676,6 +679,8 @@ struct zrnn_model {
   zrnn_softmax* sm = nullptr;
   std::vector<TensorSlot> slots;
   std::vector<std::vector<float>> staged;
+  std::vector<char> have_host;     // per slot: host data staged since the last upload
+  std::set<size_t> group_loaded;   // first slot of every tensor group that is on the device
   bool finalized = false;
   cudaStream_t stream = nullptr;
   DevBuf ws, io;
@@ -707,6 +712,27 @@ struct zrnn_model {
     if (stream) cudaStreamDestroy(stream);
   }
 };
+
+
+namespace {
+// Host id arrays: -1 is padding, everything else must index the vocabulary.  An id from another vocabulary would make
+// the embedding gather read past its table.
+int check_ids(const int* ids, size_t n, int V, const char* what) {
+  for (size_t i = 0; i < n; ++i)
+    if (ids[i] < -1 || ids[i] >= V)
+      return fail(ZRNN_E_ARG, std::string(what) + ": token id " + std::to_string(ids[i]) + " at position " +
+                                  std::to_string(i) + " is outside the vocabulary of " + std::to_string(V) + " words");
+  return ZRNN_OK;
+}
+// Reads and clears the device error word after a synchronised pass and turns it into a status.
+int device_error_status(const char* what) {
+  const int code = zrnn_tc_error();
+  if (code == 0) return ZRNN_OK;
+  if (code == zrnn::kErrBadTokenId)
+    return fail(ZRNN_E_ARG, std::string(what) + ": a token id on the device is outside the vocabulary (column 0 was read instead)");
+  return fail(ZRNN_E_TIMEOUT, std::string(what) + ": a bounded device wait gave up (role " + std::to_string(code) + ")");
+}
+}  // namespace
 
 extern "C" {
 
@@ -819,6 +845,7 @@ int zrnn_lstm_load(zrnn_lstm_layer* L, const float* const* t, int n) {
     if (L->is_ih) ZR_TRY(check_f16_range(L->eng, t[q++], (size_t)H * L->V, "lstm_load (embedding)"));
     for (int k = 0; k < (L->feed ? 8 : 4); ++k) ZR_TRY(check_f16_range(L->eng, t[q + k], HH, "lstm_load"));
   }
+  ++g_buf_generation;  // every weight buffer moves: graphs captured over the old ones must not be replayed
   cudaFree(L->W); cudaFree(L->Wh); cudaFree(L->Mx); cudaFree(L->Q); cudaFree(L->b);
   L->W = L->Wh = L->Mx = L->Q = L->b = nullptr;
   L->loaded = false;
@@ -871,7 +898,7 @@ int zrnn_ih_gather(zrnn_lstm_layer* L, const int* d_ids, int n_cols, float* d_x,
   ZR_CHECK(L && L->is_ih, "ih_gather: not an input layer");
   if (!L->loaded) return fail(ZRNN_E_STATE, "ih_gather: weights not loaded");
   ZR_CHECK(d_ids && d_x && n_cols >= 0, "ih_gather: bad arguments");
-  ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, d_ids, n_cols, d_x, (cudaStream_t)stream));
+  ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, L->V, d_ids, n_cols, d_x, tc_error_word(), (cudaStream_t)stream));
   return ZRNN_OK;
 }
 
@@ -879,12 +906,12 @@ int zrnn_ih_gather(zrnn_lstm_layer* L, const int* d_ids, int n_cols, float* d_x,
 static int gather_act(zrnn_lstm_layer* L, const int* ids, int n, const Act& x, cudaStream_t st) {
   KScope ks(KC_GATHER, st);
   if (L->eng == ENG_SIMT) {
-    ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, ids, n, x.f32, st));
+    ZR_CUDA(zrnn::launch_gather_columns(L->W, L->H, L->V, ids, n, x.f32, tc_error_word(), st));
     return ZRNN_OK;
   }
   const size_t rb = (size_t)L->Kpad * eng_eb(L->eng);
-  ZR_CUDA(zrnn::launch_gather_rows16(L->emb.hi, rb, ids, n, x.hi, st));
-  if (eng_split(L->eng)) ZR_CUDA(zrnn::launch_gather_rows16(L->emb.lo, rb, ids, n, x.lo, st));
+  ZR_CUDA(zrnn::launch_gather_rows16(L->emb.hi, rb, L->V, ids, n, x.hi, tc_error_word(), st));
+  if (eng_split(L->eng)) ZR_CUDA(zrnn::launch_gather_rows16(L->emb.lo, rb, L->V, ids, n, x.lo, tc_error_word(), st));
   return ZRNN_OK;
 }
 
@@ -967,6 +994,7 @@ int zrnn_att_load(zrnn_attention* A, const float* const* t, int n) {
   const int H = A->H;
   const size_t HH = (size_t)H * H;
   for (int i : {0, 1, 4, 5}) ZR_TRY(check_f16_range(A->eng, t[i], HH, "att_load"));
+  ++g_buf_generation;
   cudaFree(A->WpWaT); cudaFree(A->v_p); cudaFree(A->bias); cudaFree(A->Wc1); cudaFree(A->Wc2);
   A->WpWaT = A->v_p = A->bias = A->Wc1 = A->Wc2 = nullptr;
   A->loaded = false;
@@ -1061,6 +1089,7 @@ int zrnn_softmax_create(int V, int H, int dtype, int shard_lo, int shard_hi, zrn
 int zrnn_softmax_load(zrnn_softmax* S, const float* h_D, const float* h_b_d) {
   ZR_CHECK(S && h_D && h_b_d, "softmax_load: null argument");
   ZR_TRY(check_f16_range(S->eng, h_D, (size_t)S->V * S->H, "softmax_load"));
+  ++g_buf_generation;
   cudaFree(S->D); cudaFree(S->b);
   S->D = S->b = nullptr;
   S->loaded = false;
@@ -1191,6 +1220,7 @@ int zrnn_model_create(const zrnn_model_config* c, zrnn_model** out) {
     m->slots.push_back({"softmax.D", c->V_tgt, H, 3, 0, 0});
     m->slots.push_back({"softmax.b_d", c->V_tgt, 1, 3, 0, 1});
     m->staged.resize(m->slots.size());
+    m->have_host.assign(m->slots.size(), 0);
     if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess)
       st = fail(ZRNN_E_CUDA, "model_create: cannot create stream");
   }
@@ -1214,31 +1244,58 @@ int zrnn_model_set_tensor(zrnn_model* m, int i, const float* h_data) {
   ZR_CHECK(m && h_data && i >= 0 && i < (int)m->slots.size(), "set_tensor: bad arguments");
   const size_t n = (size_t)m->slots[i].rows * m->slots[i].cols;
   m->staged[i].assign(h_data, h_data + n);
+  m->have_host[i] = 1;
   m->finalized = false;
+  m->drop_graph();  // a captured scoring pass must not outlive the weights it was captured over
   return ZRNN_OK;
 }
+// Uploads what zrnn_model_set_tensor staged.  Tensors belong to groups that are loaded as a whole (one LSTM layer, the
+// attention layer, the softmax).  The first finalize needs every tensor; a later one re-loads exactly the groups whose
+// tensors were all set again and keeps the others as they are on the device; a group of which only some tensors were
+// set again is an error that names the missing tensor (the host copies of a loaded group are not kept).
 int zrnn_model_finalize(zrnn_model* m) {
   ZR_CHECK(m, "finalize: null model");
-  for (size_t i = 0; i < m->slots.size(); ++i)
-    if (m->staged[i].empty()) return fail(ZRNN_E_STATE, "finalize: tensor " + m->slots[i].name + " was never set");
-  size_t i = 0;
-  auto load_lstm = [&](zrnn_lstm_layer* L, int owner, int layer) -> int {
+  m->drop_graph();
+  const size_t ns = m->slots.size();
+  // groups = maximal runs of slots with the same (owner, layer)
+  struct Group { size_t lo, hi; bool reload; };
+  std::vector<Group> groups;
+  for (size_t i = 0; i < ns;) {
+    size_t j = i;
+    while (j < ns && m->slots[j].owner == m->slots[i].owner && m->slots[j].layer == m->slots[i].layer) ++j;
+    size_t present = 0, first_missing = ns;
+    for (size_t k = i; k < j; ++k) {
+      if (m->have_host[k]) ++present;
+      else if (first_missing == ns) first_missing = k;
+    }
+    const bool was_loaded = m->group_loaded.count(i) != 0;
+    if (present == j - i) groups.push_back({i, j, true});
+    else if (present == 0 && was_loaded) groups.push_back({i, j, false});
+    else if (present == 0)
+      return fail(ZRNN_E_STATE, "finalize: tensor " + m->slots[i].name + " was never set");
+    else
+      return fail(ZRNN_E_STATE, "finalize: tensor " + m->slots[first_missing].name + " must be set again: its layer "
+                                "was only partly updated and is loaded as a whole");
+    i = j;
+  }
+  for (const Group& g : groups) {
+    if (!g.reload) continue;
     std::vector<const float*> ptrs;
-    while (i < m->slots.size() && m->slots[i].owner == owner && m->slots[i].layer == layer) ptrs.push_back(m->staged[i++].data());
-    return zrnn_lstm_load(L, ptrs.data(), (int)ptrs.size());
-  };
-  for (size_t l = 0; l < m->src.size(); ++l) ZR_TRY(load_lstm(m->src[l], 0, (int)l));
-  for (size_t l = 0; l < m->tgt.size(); ++l) {
-    ZR_TRY(load_lstm(m->tgt[l], 1, (int)l));
-    if (m->att && l + 1 == m->tgt.size()) {
-      const float* p[6];
-      for (int k = 0; k < 6; ++k) p[k] = m->staged[i++].data();
-      ZR_TRY(zrnn_att_load(m->att, p, 6));
+    for (size_t k = g.lo; k < g.hi; ++k) ptrs.push_back(m->staged[k].data());
+    const TensorSlot& s0 = m->slots[g.lo];
+    if (s0.owner == 0) ZR_TRY(zrnn_lstm_load(m->src[s0.layer], ptrs.data(), (int)ptrs.size()));
+    else if (s0.owner == 1) ZR_TRY(zrnn_lstm_load(m->tgt[s0.layer], ptrs.data(), (int)ptrs.size()));
+    else if (s0.owner == 2) ZR_TRY(zrnn_att_load(m->att, ptrs.data(), (int)ptrs.size()));
+    else {
+      ZR_CHECK(ptrs.size() == 2, "finalize: internal: softmax group");
+      ZR_TRY(zrnn_softmax_load(m->sm, ptrs[0], ptrs[1]));
+    }
+    m->group_loaded.insert(g.lo);
+    for (size_t k = g.lo; k < g.hi; ++k) {
+      std::vector<float>().swap(m->staged[k]);  // the data now lives on the device
+      m->have_host[k] = 0;
     }
   }
-  ZR_TRY(zrnn_softmax_load(m->sm, m->staged[i].data(), m->staged[i + 1].data()));
-  for (auto& v : m->staged) std::vector<float>().swap(v);
-  m->staged.assign(m->slots.size(), std::vector<float>(1, 0.f));  // mark as "set"; data now lives on the device
   m->finalized = true;
   return ZRNN_OK;
 }
@@ -1261,6 +1318,7 @@ int zrnn_model_load_file(const char* path, int att_type_override, int D, int dty
   ZR_TRY(zrnn_model_create(&c, &m));
   for (size_t i = 0; i < m->slots.size(); ++i) {
     m->staged[i].resize((size_t)m->slots[i].rows * m->slots[i].cols);
+    m->have_host[i] = 1;
     if (!rd.read_matrix(m->slots[i].rows, m->slots[i].cols, m->staged[i].data(), &err)) {
       const std::string nm = m->slots[i].name;
       delete m;
@@ -1578,6 +1636,9 @@ int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tg
   if (T == 0 || B == 0) return ZRNN_OK;
   const size_t nS = m->cfg.lm ? 0 : (size_t)S_max * B, nT = (size_t)T * B;
   ZR_CHECK(m->cfg.lm || src_ids, "score_batch: a sequence-to-sequence model needs source ids");
+  if (nS) ZR_TRY(check_ids(src_ids, nS, m->cfg.V_src, "score_batch (source)"));
+  ZR_TRY(check_ids(tgt_in, nT, m->cfg.V_tgt, "score_batch (target input)"));
+  ZR_TRY(check_ids(tgt_out, nT, m->cfg.V_tgt, "score_batch (target output)"));
   ZR_CUDA(m->io.reserve(aligned(sizeof(int) * (nS + 1)) + 2 * aligned(sizeof(int) * nT) + aligned(sizeof(float) * nT)));
   Carver cv(m->io.p);
   int* d_src = cv.take<int>(nS + 1);
@@ -1591,10 +1652,7 @@ int zrnn_score_batch(zrnn_model* m, const int* src_ids, int S_max, const int* tg
   ZR_TRY(zrnn_score_batch_device(m, nS ? d_src : nullptr, S_max, d_tin, d_tout, T, B, d_lp, s));
   ZR_CUDA(cudaMemcpyAsync(logp_out, d_lp, sizeof(float) * nT, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
-  if (m->eng != ENG_SIMT) {
-    const int code = zrnn_tc_error();
-    if (code != 0) return fail(ZRNN_E_TIMEOUT, "score_batch: a bounded device wait gave up (role " + std::to_string(code) + ")");
-  }
+  ZR_TRY(device_error_status("score_batch"));
   if (total_logp) {
     double tot = 0;
     for (size_t i = 0; i < nT; ++i) tot += logp_out[i];
@@ -1904,10 +1962,13 @@ int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* s
   ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
   if (n_sent == 0) return ZRNN_OK;
   int S_max = 0;
+  size_t n_ids = 0;
   for (int i = 0; i < n_sent; ++i) {
     ZR_CHECK(src_len[i] >= 1, "beam_decode: empty source sentence");
     S_max = std::max(S_max, src_len[i]);
+    n_ids += (size_t)src_len[i];
   }
+  ZR_TRY(check_ids(src_ids, n_ids, m->cfg.V_src, "beam_decode (source)"));
   const int Lmax = longest_sent + 4;
   // pad on the host into the reference's minibatch layout: time-major, left-padded with -1
   std::vector<int> padded((size_t)S_max * n_sent, -1);
@@ -1934,10 +1995,7 @@ int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* s
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
-  if (m->eng != ENG_SIMT) {
-    const int code = zrnn_tc_error();
-    if (code != 0) return fail(ZRNN_E_TIMEOUT, "beam_decode: a bounded device wait gave up (role " + std::to_string(code) + ")");
-  }
+  ZR_TRY(device_error_status("beam_decode"));
   return ZRNN_OK;
 }
 
@@ -1967,10 +2025,13 @@ int zrnn_beam_decode_ensemble_align(zrnn_model* const* models, int n_models, con
   for (int k = 0; k < n_models; ++k) {
     zrnn_model* m = models[k];
     ZR_CHECK(m && src_ids[k] && src_len[k], "beam_decode_ensemble: null argument");
+    size_t n_ids = 0;
     for (int i = 0; i < n_sent; ++i) {
       ZR_CHECK(src_len[k][i] >= 1, "beam_decode_ensemble: empty source sentence");
       S_max[k] = std::max(S_max[k], src_len[k][i]);
+      n_ids += (size_t)src_len[k][i];
     }
+    ZR_TRY(check_ids(src_ids[k], n_ids, m->cfg.V_src, "beam_decode_ensemble (source)"));
     // pad on the host into the reference's minibatch layout: time-major, left-padded with -1
     std::vector<int> padded((size_t)S_max[k] * n_sent, -1);
     size_t pos = 0;
@@ -2000,8 +2061,7 @@ int zrnn_beam_decode_ensemble_align(zrnn_model* const* models, int n_models, con
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
-  const int code = zrnn_tc_error();
-  if (code != 0) return fail(ZRNN_E_TIMEOUT, "beam_decode_ensemble: a bounded device wait gave up (role " + std::to_string(code) + ")");
+  ZR_TRY(device_error_status("beam_decode_ensemble"));
   return ZRNN_OK;
 }
 
