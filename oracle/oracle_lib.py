@@ -46,6 +46,8 @@ def lib():
                                       ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_int, ctypes.c_int,
                                       c_int_p, c_int_p, c_float_p]
         L.orc_beam_decode_align.argtypes = L.orc_beam_decode.argtypes + [c_int_p]
+        L.orc_beam_decode_margins.argtypes = [ctypes.c_void_p, c_int_p, c_int_p, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                                              ctypes.c_float, ctypes.c_float, ctypes.c_int, c_float_p]
         L.orc_attention_viterbi.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                             ctypes.POINTER(c_float_p), c_float_p, c_int_p, c_float_p, ctypes.c_int,
                                             c_int_p, c_int_p, c_float_p, c_int_p]
@@ -149,6 +151,19 @@ class OracleModel:
         lib().orc_beam_decode_align(self._h, _ip(flat), _ip(lens), n, beam, k_best, min_ratio, max_ratio, penalty,
                                     longest_sent, Lmax, _ip(ids), _ip(ln), _fp(sc), _ip(al))
         return (ids, ln, sc, al) if want_align else (ids, ln, sc)
+
+
+def beam_decode_margins(model, sources, beam, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100):
+    """Per sentence the smallest score difference that decided anything in the oracle's beam search: at every step
+    between the last candidate that entered the beam and the best one left behind, and at the end between the best and
+    the second-best hypothesis.  A test aid for telling real disagreements from near-ties."""
+    n = len(sources)
+    flat = _i32(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]))
+    lens = _i32([len(s) for s in sources])
+    out = np.zeros(n, dtype=np.float32)
+    lib().orc_beam_decode_margins(model._h, _ip(flat), _ip(lens), n, beam, min_ratio, max_ratio, penalty, longest_sent,
+                                  _fp(out))
+    return out
 
 
 def beam_decode_ensemble(models, sources_per_model, beam, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0,

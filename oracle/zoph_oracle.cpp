@@ -567,7 +567,12 @@ struct DecModel {
 // its own source sentence, the length limits follow model 0's (:623, :637).
 void beam_decode_one(const std::vector<const Model*>& models, const std::vector<const int*>& srcs,
                      const std::vector<int>& Ss, int beam, int k_best, float min_ratio, float max_ratio,
-                     float penalty, int longest_sent_internal, std::vector<Hyp>& out) {
+                     float penalty, int longest_sent_internal, std::vector<Hyp>& out, float* margin_out = nullptr) {
+  // margin_out (test aid, no counterpart in the reference): the smallest score difference that decided anything in
+  // this search - at every step between the last candidate that entered the beam (or finished) and the best one that
+  // did not, and at the end between the best and the second-best hypothesis.  A search whose margin is below the
+  // arithmetic noise of another implementation may legitimately come out differently there.
+  float margin = 3.0e38f;
   const int K = (int)models.size();
   const int V = models[0]->cfg.V_tgt, S = Ss[0];
   const int START = 0, END = 1, INVALID = -1;
@@ -674,6 +679,10 @@ void beam_decode_one(const std::vector<const Model*>& models, const std::vector<
         top_vit_tmp[(size_t)i * Lmax + current_index + 1] = vitp[t.beam_idx];  // decoder.h:1281-1282
         cur[i] = t.vocab; changes[i] = t.beam_idx; scores_tmp[i] = t.val + penalty;
         ++i;
+        if (i == beam) {  // the beam is full: the best candidate left behind (never <START>) is the runner-up
+          while (!global.empty() && global.top().vocab == START) global.pop();
+          if (!global.empty()) margin = std::min(margin, t.val - global.top().val);
+        }
       }
     }
     top_sent = top_tmp; top_vit = top_vit_tmp; scores = scores_tmp; current_index += 1;
@@ -702,6 +711,8 @@ void beam_decode_one(const std::vector<const Model*>& models, const std::vector<
   std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return hyps[a].score > hyps[b].score; });
   out.clear();
   for (int i = 0; i < (int)order.size() && i < k_best; ++i) out.push_back(hyps[order[i]]);
+  if (order.size() >= 2) margin = std::min(margin, hyps[order[0]].score - hyps[order[1]].score);
+  if (margin_out) *margin_out = margin;
 }
 
 }  // namespace
@@ -789,6 +800,19 @@ void orc_beam_decode_align(void* p, const int* src_ids, const int* src_len, int 
         out_score[(size_t)s * k_best + k] = 0;
       }
     }
+  }
+}
+
+// Test aid: the decision margin of each sentence's search (see beam_decode_one), 1-best only.
+void orc_beam_decode_margins(void* p, const int* src_ids, const int* src_len, int n_sent, int beam, float min_ratio,
+                             float max_ratio, float penalty, int longest_sent, float* out_margin) {
+  const Model& m = *(Model*)p;
+  size_t pos = 0;
+  for (int s = 0; s < n_sent; ++s) {
+    std::vector<Hyp> res;
+    beam_decode_one({&m}, {src_ids + pos}, {src_len[s]}, beam, 1, min_ratio, max_ratio, penalty, longest_sent + 4, res,
+                    out_margin + s);
+    pos += src_len[s];
   }
 }
 
