@@ -84,16 +84,6 @@ int zrnn_gemm(int mode, int n_rows, int m_cols, int K, const float* d_W, int ldw
               float* d_C, int ldc, void* stream);
 /* Reads and clears the device-side error word of the tensor-core kernels (0 = none). */
 int zrnn_tc_error(void);
-/* Developer aids (no reference counterpart): device-side phase stamps of the tensor-core kernels.
- * zrnn_debug_tc_profile(d_buf): while d_buf is set, every CTA of every split-K tensor-core launch writes 8
- * %globaltimer values (ns) to d_buf[cta * 8 ..]: start, set-up done, accumulators complete, partial tile pushed,
- * cluster barrier passed, exchange slots read, gate math done, stores issued.  d_buf must hold 8 values per CTA of
- * the largest launch; NULL switches it off.
- * zrnn_debug_tc_timeline(d_buf, slots): launch i (counted from the call) writes the same 8 stamps of its CTA (0,0,0)
- * to d_buf[i * 8 ..] for i < slots. */
-int zrnn_debug_tc_profile(long long* d_buf);
-int zrnn_debug_tc_timeline(long long* d_buf, int slots);
-
 /* ------------------------------------------------------------------------------------------
  * Input preparation.  Replaces vocab_to_01 / vocab_to_nonM1 (src/custom_kernels.h:9-32), called
  * from Input_To_Hidden_Layer::prep_GPU_vocab_indices (src/Input_To_Hidden_Layer.hpp:1178-1225):

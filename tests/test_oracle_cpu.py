@@ -116,14 +116,14 @@ def test_model_file_writer_layout(tmp_path):
 
 
 def test_library_exports_every_declared_symbol():
-    """The C-ABI library loads without a GPU and exports everything include/zrnn.h declares."""
+    """The C-ABI library loads without a GPU and exports everything include/zrnn.h and include/zrnn_debug.h declare."""
     from zoph_rnn_b200 import _lib
-    hdr = open(os.path.join(ROOT, "include", "zrnn.h")).read()
+    hdr = open(os.path.join(ROOT, "include", "zrnn.h")).read() + open(os.path.join(ROOT, "include", "zrnn_debug.h")).read()
     declared = set(re.findall(r"\b(zrnn_[a-z0-9_]+)\s*\(", hdr))
     assert declared, "no declarations parsed"
     L = ctypes.CDLL(_lib.LIB_PATH)
     for name in sorted(declared):
-        assert hasattr(L, name), f"{name} declared in zrnn.h but not exported"
+        assert hasattr(L, name), f"{name} declared in include/ but not exported"
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
     assert _lib.lib().zrnn_built_for_sm() == 100
 

@@ -29,7 +29,7 @@ class ZrnnError(RuntimeError):
         self.status = status
 
 
-# name -> (restype, argtypes); every symbol include/zrnn.h declares
+# name -> (restype, argtypes); every symbol include/zrnn.h and include/zrnn_debug.h declare
 SIGNATURES = {
     "zrnn_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "zrnn_last_error": (ctypes.c_char_p, []),
@@ -37,6 +37,7 @@ SIGNATURES = {
     "zrnn_built_for_sm": (ctypes.c_int, []),
     "zrnn_debug_tc_profile": (ctypes.c_int, [c_void_p]),
     "zrnn_debug_tc_timeline": (ctypes.c_int, [c_void_p, ctypes.c_int]),
+    "zrnn_debug_decoder_timeline": (ctypes.c_int, [c_void_p, ctypes.c_int]),
     "zrnn_device_count": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "zrnn_set_device": (ctypes.c_int, [ctypes.c_int]),
     "zrnn_launch_count": (ctypes.c_longlong, []),

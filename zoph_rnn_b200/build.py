@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libzrnn.so")
 CLI = os.path.join(HERE, "bin", "zoph_rnn")
-SOURCES = ["kernels.cu", "tc_gemm.cu", "zrnn_api.cu"]
+SOURCES = ["kernels.cu", "tc_gemm.cu", "tc_decoder.cu", "zrnn_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr"]
 

@@ -12,8 +12,10 @@
 #include <vector>
 
 #include "../../include/zrnn.h"
+#include "../../include/zrnn_debug.h"
 #include "kernels.cuh"
 #include "model_file.hpp"
+#include "tc_decoder.cuh"
 #include "tc_gemm.cuh"
 
 namespace {
@@ -92,6 +94,14 @@ struct KTiming {
   std::vector<int> cnt;  // launches covered by the pair
   size_t used = 0;       // pairs in use
   int group_cls = -1;    // a group scope of this class is open: its inner scopes do not record
+  // launches of the persistent decoder kernel: it stamps %globaltimer at every phase boundary into a buffer of its
+  // own, from which the per-class times are taken when the report is read
+  struct DecRun { long long* d_stamps; int T, P, L; };
+  std::vector<DecRun> dec_runs;
+  void drop_dec_runs() {
+    for (auto& r : dec_runs) cudaFree(r.d_stamps);
+    dec_runs.clear();
+  }
 };
 thread_local KTiming g_kt;
 const size_t KT_CAP = 16384;
@@ -336,6 +346,8 @@ int pick_splitk(int m_cols, int n_rows, int BN, int max_split) {
   return best;
 }
 
+long long* g_dec_detail = nullptr;  // developer timeline of the persistent decoder kernel (zrnn_debug_decoder_timeline)
+int g_dec_detail_cta = 0;
 long long* g_tc_prof = nullptr;  // developer profiling buffer (see zrnn_debug_tc_profile)
 int g_tc_prof_slot = -1;          // >= 0: timeline mode, one slot per tensor-core launch
 int g_tc_prof_cap = 0;
@@ -684,6 +696,8 @@ struct zrnn_model {
   bool finalized = false;
   cudaStream_t stream = nullptr;
   DevBuf ws, io;
+  DevBuf dec_counter;       // phase counter of the persistent decoder kernel
+  int persist_state = 0;    // 0 untried, 1 works, -1 refused by the runtime (the per-launch path is used)
   zrnn::TcMulti enc_multi;  // parameter block of the encoder's multi-cell launches (host scratch)
   const float* last_top = nullptr;
   int last_top_cols = 0;
@@ -708,7 +722,7 @@ struct zrnn_model {
     for (auto* l : tgt) delete l;
     delete att;
     delete sm;
-    ws.release(); io.release();
+    ws.release(); io.release(); dec_counter.release();
     if (stream) cudaStreamDestroy(stream);
   }
 };
@@ -778,6 +792,15 @@ int zrnn_debug_tc_timeline(long long* d_buf, int slots) {
   return ZRNN_OK;
 }
 
+/* developer aid: CTA `cta` of every persistent decoder launch writes 8 stamps per phase (phase entered, accumulators
+ * complete, cluster ready, partial tile pushed, exchange complete, results stored, earlier phases complete, counted)
+ * to d_buf[phase * 8 ..]; NULL switches it off */
+int zrnn_debug_decoder_timeline(long long* d_buf, int cta) {
+  g_dec_detail = d_buf;
+  g_dec_detail_cta = cta;
+  return ZRNN_OK;
+}
+
 int zrnn_tc_error(void) {
   int* d = tc_error_word();
   int v = 0;
@@ -789,7 +812,10 @@ int zrnn_tc_error(void) {
 
 int zrnn_kernel_timing(int on) {
   g_kt.on = on != 0;
-  if (on) g_kt.used = 0;
+  if (on) {
+    g_kt.used = 0;
+    g_kt.drop_dec_runs();
+  }
   return ZRNN_OK;
 }
 int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total_ms) {
@@ -803,6 +829,24 @@ int zrnn_kernel_timing_read(int kernel_class, long long* launches, double* total
     ZR_CUDA(cudaEventElapsedTime(&ms, g_kt.ev[2 * i], g_kt.ev[2 * i + 1]));
     *launches += g_kt.cnt[i];
     *total_ms += ms;
+  }
+  if (kernel_class == KC_LSTM || kernel_class == KC_ATT) {
+    // phases of the persistent decoder launches: stamps[0] = kernel start, stamps[1 + ph] = end of phase ph; phases
+    // 0 .. L-1 of a step are the cells, the rest (stacked local-p GEMM, attention, combiner) is the attention group
+    ZR_CUDA(cudaDeviceSynchronize());
+    std::vector<long long> st;
+    for (const auto& r : g_kt.dec_runs) {
+      const int NP = r.T * r.P;
+      st.resize((size_t)NP + 1);
+      ZR_CUDA(cudaMemcpy(st.data(), r.d_stamps, sizeof(long long) * st.size(), cudaMemcpyDeviceToHost));
+      for (int ph = 0; ph < NP; ++ph) {
+        const bool cell = (ph % r.P) < r.L;
+        if (cell != (kernel_class == KC_LSTM) || st[ph + 1] == 0 || st[ph] == 0) continue;
+        *total_ms += (double)(st[ph + 1] - st[ph]) * 1e-6;
+        if (cell) *launches += 1;
+        else if ((ph % r.P) == r.P - 1) *launches += 1;  // one attention group per step
+      }
+    }
   }
   return ZRNN_OK;
 }
@@ -1478,6 +1522,93 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
   return run_stack(m, m->src, g, mask, S, B, X0, h0, seq, cst, cur, s);
 }
 
+// The target side of a feed-input model as ONE launch of the persistent decoder kernel (tc_decoder.cu) instead of
+// L + 2 (or 3) launches per time step.  *done stays false when the shape, the engine or the device cannot run it
+// (the caller then takes the per-launch path); ZRNN_NO_PERSISTENT=1 turns it off.
+static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, int B, const Act& Xt,
+                                  const std::vector<Act>& sseq, const std::vector<Act>& tseq, const Act& hts,
+                                  const int* tin_mk, const int* len, const int* off, std::vector<float*> cst[2],
+                                  std::vector<int>& cur, cudaStream_t s, bool* done) {
+  *done = false;
+  static const bool disabled = std::getenv("ZRNN_NO_PERSISTENT") != nullptr;
+  const zrnn_model_config& c = m->cfg;
+  const int L = c.num_layers, H = c.H, eng = m->eng;
+  zrnn_attention* A = m->att;
+  if (disabled || m->persist_state < 0 || eng == ENG_SIMT || !A || c.lm || !c.feed_input) return ZRNN_OK;
+  if (A->BN != 128 || A->eng != eng) return ZRNN_OK;
+  for (int l = 0; l < L; ++l)
+    if (m->tgt[l]->BN != 128 || m->tgt[l]->eng != eng) return ZRNN_OK;
+  if (!zrnn::tc_decoder_supported(eng_tcmode(eng), H, B, L, c.attention)) return ZRNN_OK;
+  const int eb = eng_eb(eng), epk = 128 / eb, Kpad = g.Kpad;
+  const size_t nT = (size_t)T * B;
+  zrnn::DecParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.H = H; p.Kpad = Kpad; p.B = B; p.T = T; p.L = L; p.att_type = c.attention; p.D = A->D;
+  p.kb = (H + epk - 1) / epk;
+  p.kpb = Kpad / epk;
+  ZR_TRY(act_maps(Xt, eng, H, Kpad, (int)nT, &p.x_hi, &p.x_lo));
+  for (int l = 0; l < L; ++l) {
+    zrnn_lstm_layer* Ly = m->tgt[l];
+    ZR_TRY(act_maps(tseq[l], eng, H, Kpad, (int)nT, &p.h_hi[l], &p.h_lo[l]));
+    ZR_TRY(act_maps(sseq[l], eng, H, Kpad, S * B, &p.h0_hi[l], &p.h0_lo[l]));
+    p.h0_row[l] = (S - 1) * B;
+    p.w_hi[l] = Ly->wmap; p.w_lo[l] = Ly->wmap_lo; p.w_tiled[l] = Ly->kbtot;
+    p.bias[l] = Ly->b;
+    p.c_buf[l][0] = cst[cur[l]][l];
+    p.c_buf[l][1] = cst[cur[l] ^ 1][l];
+    p.h_f32[l] = tseq[l].f32; p.h_op_hi[l] = tseq[l].hi; p.h_op_lo[l] = tseq[l].lo;
+  }
+  ZR_TRY(act_maps(hts, eng, H, Kpad, (int)nT, &p.ht_hi, &p.ht_lo));
+  p.ht_f32 = hts.f32; p.ht_op_hi = hts.hi; p.ht_op_lo = hts.lo;
+  // the step's context vectors and (local-p) the stacked projection live in the attention layer's own buffers
+  ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
+  ZR_CUDA(A->ctx_hi.reserve((size_t)B * Kpad * eb));
+  if (eng_split(eng)) ZR_CUDA(A->ctx_lo.reserve((size_t)B * Kpad * eb));
+  Act ctx;
+  ctx.f32 = A->ctx.as<float>(); ctx.hi = A->ctx_hi.p; ctx.lo = eng_split(eng) ? A->ctx_lo.as<float>() : nullptr;
+  ZR_TRY(act_maps(ctx, eng, H, Kpad, B, &p.ctx_hi, &p.ctx_lo));
+  p.ctx_f32 = ctx.f32; p.ctx_op_hi = ctx.hi; p.ctx_op_lo = ctx.lo;
+  p.wc_hi = A->cmap; p.wc_lo = A->cmap_lo;
+  if (c.attention == ZRNN_ATT_LOCAL_P) {
+    ZR_CUDA(A->tq.reserve(sizeof(float) * (size_t)2 * H * B));
+    p.tq = A->tq.as<float>();
+    p.wp_hi = A->pmap; p.wp_lo = A->pmap_lo;
+    p.v_p = A->v_p;
+  }
+  p.att_bias = A->bias;
+  p.mask = tin_mk;
+  p.hs = sseq[L - 1].f32; p.S_max = S; p.len = len; p.off = off;
+  ZR_CUDA(m->dec_counter.reserve(256));
+  p.counter = m->dec_counter.as<unsigned int>();
+  p.err = tc_error_word();
+  const int P = zrnn::dec_phases_per_step(p);
+  if (g_kt.on) {
+    long long* st = nullptr;
+    ZR_CUDA(cudaMalloc((void**)&st, sizeof(long long) * ((size_t)T * P + 1)));
+    ZR_CUDA(cudaMemsetAsync(st, 0, sizeof(long long) * ((size_t)T * P + 1), s));
+    g_kt.dec_runs.push_back({st, T, P, L});
+    p.stamps = st;
+  }
+  p.detail = g_dec_detail;
+  p.hold_loads = std::getenv("ZRNN_DEC_NO_HOLD") == nullptr;
+  p.w_evict_first = std::getenv("ZRNN_DEC_NO_EVICT") == nullptr;
+  p.detail_cta = g_dec_detail_cta;
+  ZR_CUDA(cudaMemsetAsync(p.counter, 0, sizeof(unsigned int), s));
+  const cudaError_t e = zrnn::launch_tc_decoder(p, eng_tcmode(eng), s);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (m->persist_state == 0) {  // first attempt refused (e.g. the CTAs cannot be co-resident): remember and fall back
+      m->persist_state = -1;
+      return ZRNN_OK;
+    }
+    return fail(ZRNN_E_CUDA, std::string("persistent decoder launch: ") + cudaGetErrorString(e));
+  }
+  m->persist_state = 1;
+  for (int l = 0; l < L; ++l) cur[l] ^= (T & 1);
+  *done = true;
+  return ZRNN_OK;
+}
+
 // d_logp_out == nullptr: stop after the recurrent stack (the top-layer vectors stay in m->last_top)
 static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, const int* d_tgt_in, const int* d_tgt_out,
                             int T, int B, float* d_logp_out, cudaStream_t s);
@@ -1590,7 +1721,9 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
                            act_at(hts, (size_t)t * B, g), nullptr, s));
   } else {
     // feed-input: layer 0 of step t reads the attention output of step t - 1, so the steps form one chain
-    for (int t = 0; t < T; ++t) {
+    bool done = false;
+    ZR_TRY(run_decoder_persistent(m, g, S, T, B, Xt, sseq, tseq, hts, tin_mk, len, off, cst, cur, s, &done));
+    for (int t = 0; t < T && !done; ++t) {
       Act x = act_at(Xt, (size_t)t * B, g);
       const int* mk = tin_mk + (size_t)t * B;
       for (int l = 0; l < L; ++l) {
