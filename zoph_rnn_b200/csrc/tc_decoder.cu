@@ -1,12 +1,15 @@
 // Persistent decoder kernel for sm_100a (see tc_decoder.cuh for what it replaces and why).
 //
-// Work split.  The grid is NT clusters of four CTAs (NT = row tiles of one LSTM layer, 128 packed weight rows = 32
-// hidden units x 4 gates each).  A time step is a fixed list of phases: the L cells, [local-p: the stacked
-// [W_p ; W_a^T] GEMM], the attention proper (SIMT, one target column per CTA in turn), the tanh combiner GEMM.  In a
-// GEMM phase cluster c owns row tile c (clusters beyond the phase's tile count idle) and its four CTAs each take a
-// quarter of every source's k-blocks, accumulate in tensor memory, push the three quarters of the partial tile that
-// they do not own into the owners' shared memory (st.shared::cluster), and finish their own 32 columns: gate math and
-// state update, or bias + tanh + mask.
+// Work split.  A time step is a fixed list of phases: the L cells, [local-p: the stacked [W_p ; W_a^T] GEMM], the
+// attention proper (SIMT, one target column per CTA in turn), the tanh combiner GEMM - a strict chain, every phase
+// needs the one before it.  What bounds such a chain is latency (hand-over, pipeline fill, exchange, epilogue), not
+// bytes, so the batch is cut into `groups` column groups that run the chain independently of one another, each on
+// its own share of the clusters with its own phase counter: while one group hands a phase over, the others keep the
+// memory system and the tensor pipe busy.  (Each group streams the weights itself; HBM has the room.)
+// Inside a group, cluster c owns the row tiles c, c + NC, ... of a GEMM phase (128 packed weight rows = 32 hidden
+// units x 4 gates each) and its four CTAs each take a quarter of every source's k-blocks, accumulate in tensor
+// memory, push the three quarters of the partial tile that they do not own into the owners' shared memory
+// (st.shared::cluster), and finish their own 32 columns: gate math and state update, or bias + tanh + mask.
 //
 // CTA = 10 warps.  Warps 0-7 are the epilogue team, warp 8 lane 0 is the TMA producer, warp 9 lane 0 issues the MMAs
 // and warp 9 owns the tensor-memory allocation.  Weights and activations have rings of their own:
@@ -19,7 +22,7 @@
 //     tile as soon as its own accumulators are complete: a slot is only written for phase q after the phase's last
 //     input exists, i.e. after phase q - 1 is complete everywhere, which includes its owner's reads of phase q - 1.
 // Phases hand over through one monotonic counter in global memory: a CTA adds 1 when its part of a phase is stored;
-// phase q is complete at (q + 1) * CTAs.  Every wait is bounded (about 0.2 s of SM clock); a wait that gives up
+// phase q is complete at (q + 1) * CTAs.  Every wait is bounded (about a second of SM clock); a wait that gives up
 // records where in p.err and makes every role of every CTA leave, so the kernel always returns.
 #include "tc_decoder.cuh"
 
@@ -39,18 +42,18 @@ constexpr int kSplit = 4;    // CTAs per cluster = K split
 constexpr int kOwn = kBN / kSplit;  // tile columns finished by one CTA
 constexpr int kTeam = 256;   // epilogue threads
 constexpr int kThreads = 320;
-constexpr long long kWaitCycles = 400000000LL;
-constexpr int kSlotBytes = kSplit * 128 * kOwn * 4;  // 64 KB: four partial tiles of 128 rows x 32 columns
+constexpr long long kWaitCycles = 2000000000LL;  // about a second of SM clock
+constexpr int kSlotBytes = kSplit * 128 * kOwn * 4;  // 64 KB: four partial tiles of 128 rows x 32 columns, or two sets for 64 rows
+constexpr int kARingBytes = 64 * 1024;               // activation ring
+constexpr int kMaxAStages = 8;
 
 __host__ __device__ constexpr int dec_wstage(int mode) { return (mode_split(mode) ? 2 : 1) * kBN * 128; }
-__host__ __device__ constexpr int dec_astage(int mode) { return (mode_split(mode) ? 2 : 1) * 128 * 128; }
-#ifndef ZRNN_DEC_AKB
-#define ZRNN_DEC_AKB 64
-#endif
-__host__ __device__ constexpr int dec_na(int mode) { return ZRNN_DEC_AKB * 1024 / dec_astage(mode); }          // 2 (split) or 4
-__host__ __device__ constexpr int dec_nw(int mode) { return (160 - ZRNN_DEC_AKB) * 1024 / dec_wstage(mode); }  // 3 (split) or 6
+__host__ __device__ constexpr int dec_nw(int mode) { return 96 * 1024 / dec_wstage(mode); }  // 3 (split) or 6
+// The MMAs always read 128 activation rows; when a group has fewer columns only that many rows are loaded and the
+// rest of the 128-row operand window is whatever follows in shared memory (rows nobody looks at; the window of the
+// last stage runs into the exchange slots, which lie behind the ring).
 __host__ __device__ constexpr int dec_smem(int mode) {
-  return dec_nw(mode) * dec_wstage(mode) + dec_na(mode) * dec_astage(mode) + kSlotBytes + 1024;
+  return dec_nw(mode) * dec_wstage(mode) + kARingBytes + kSlotBytes + 1024;
 }
 
 enum { PH_CELL = 0, PH_PGEMM = 1, PH_ATT = 2, PH_COMB = 3 };
@@ -58,12 +61,12 @@ enum { PH_CELL = 0, PH_PGEMM = 1, PH_ATT = 2, PH_COMB = 3 };
 #define ZD_STAMP(k)                                                                                        \
   do {                                                                                                     \
     if (p.detail && tid == 0) {                                                                            \
-      if (p.detail_cta < 0) p.detail[((size_t)cta_id * NP + ph) * 8 + (k)] = gtime();                      \
-      else if (cta_id == p.detail_cta) p.detail[(size_t)ph * 8 + (k)] = gtime();                           \
+      if (p.detail_cta < 0) p.detail[((size_t)cta_all * NP + ph) * 8 + (k)] = gtime();                     \
+      else if (cta_all == p.detail_cta) p.detail[(size_t)ph * 8 + (k)] = gtime();                          \
     }                                                                                                      \
   } while (0)
 
-// What one CTA does in one phase.
+// What one CTA does for one row tile of one phase.
 struct Plan {
   int kind, layer, t;
   int n_tiles;   // GEMM phases: 128-row tiles of the weight matrix
@@ -71,7 +74,7 @@ struct Plan {
   int src[3];    // position of the source inside the weight matrix's K axis
   int need[3];   // phase that must be complete before the source may be read (-1: written before the kernel)
   int lo[3], cnt[3];  // this CTA's k-block slice of each source
-  int nitems;    // k-blocks this CTA accumulates (0 for an idle CTA and for the attention phase)
+  int nitems;    // k-blocks this CTA accumulates (0 for a tile beyond the phase's tiles and for the attention phase)
 };
 
 __device__ __forceinline__ void make_plan(const DecParams& p, int ph, int P, int rank, int tile, Plan& pl) {
@@ -157,6 +160,19 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
       : "memory");
   return ok != 0;
 }
+// the non-blocking form: try_wait may suspend the thread for a while before it answers "not yet", which a loop that
+// has other things to look at cannot afford
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // arrive on the same barrier in the shared memory of cluster rank `rank`; orders this thread's earlier remote stores
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
   const uint32_t addr = cluster_map(smem_u32(bar), rank);
@@ -220,14 +236,24 @@ __device__ __forceinline__ OpOut make_opout(void* hi, void* lo) {
   return o;
 }
 
+// The slice of the batch one column group works on, and the share of the clusters that works on it.
+struct Group {
+  int b0, nb;     // first column and number of columns
+  int cl, NC;     // this cluster's index inside the group and the group's number of clusters
+  int TPC;        // row tiles of the largest phase that one cluster takes in turn
+  unsigned G;     // CTAs of the group (what one complete phase adds to the group's counter)
+  unsigned* counter;
+};
+
 // One item = one 128-byte k-block of one source: which activation rows and which weight rows feed it.
 struct Item {
   const CUtensorMap *a_hi, *a_lo, *w_hi, *w_lo;
   int ax, ay, wx, wy;
   int need;
 };
-__device__ __forceinline__ void make_item(const DecParams& p, const Plan& pl, int s, int kbi, int tile, int epk, Item& it) {
-  const int sid = pl.src[s], t = pl.t, B = p.B;
+__device__ __forceinline__ void make_item(const DecParams& p, const Plan& pl, int s, int kbi, int tile, int b0, int epk,
+                                          Item& it) {
+  const int sid = pl.src[s], t = pl.t, Bs = p.B;
   it.need = pl.need[s];
   it.ax = kbi * epk;
   if (pl.kind == PH_CELL) {
@@ -235,13 +261,13 @@ __device__ __forceinline__ void make_item(const DecParams& p, const Plan& pl, in
     if (sid == 0) {
       if (l == 0) { it.a_hi = &p.x_hi; it.a_lo = &p.x_lo; }
       else { it.a_hi = &p.h_hi[l - 1]; it.a_lo = &p.h_lo[l - 1]; }
-      it.ay = t * B;
+      it.ay = t * Bs + b0;
     } else if (sid == 1) {
-      if (t == 0) { it.a_hi = &p.h0_hi[l]; it.a_lo = &p.h0_lo[l]; it.ay = p.h0_row[l]; }
-      else { it.a_hi = &p.h_hi[l]; it.a_lo = &p.h_lo[l]; it.ay = (t - 1) * B; }
+      if (t == 0) { it.a_hi = &p.h0_hi[l]; it.a_lo = &p.h0_lo[l]; it.ay = p.h0_row[l] + b0; }
+      else { it.a_hi = &p.h_hi[l]; it.a_lo = &p.h_lo[l]; it.ay = (t - 1) * Bs + b0; }
     } else {
       it.a_hi = &p.ht_hi; it.a_lo = &p.ht_lo;
-      it.ay = (t - 1) * B;
+      it.ay = (t - 1) * Bs + b0;
     }
     it.w_hi = &p.w_hi[l]; it.w_lo = &p.w_lo[l];
     const int kbg = sid * p.kpb + kbi;
@@ -249,83 +275,109 @@ __device__ __forceinline__ void make_item(const DecParams& p, const Plan& pl, in
     else { it.wx = kbg * epk; it.wy = tile * kBN; }
   } else if (pl.kind == PH_PGEMM) {
     it.a_hi = &p.h_hi[p.L - 1]; it.a_lo = &p.h_lo[p.L - 1];
-    it.ay = t * B;
+    it.ay = t * Bs + b0;
     it.w_hi = &p.wp_hi; it.w_lo = &p.wp_lo;
     it.wx = kbi * epk; it.wy = tile * kBN;
   } else {  // PH_COMB
-    if (sid == 0) { it.a_hi = &p.ctx_hi; it.a_lo = &p.ctx_lo; it.ay = 0; }
-    else { it.a_hi = &p.h_hi[p.L - 1]; it.a_lo = &p.h_lo[p.L - 1]; it.ay = t * B; }
+    if (sid == 0) { it.a_hi = &p.ctx_hi; it.a_lo = &p.ctx_lo; it.ay = b0; }
+    else { it.a_hi = &p.h_hi[p.L - 1]; it.a_lo = &p.h_lo[p.L - 1]; it.ay = t * Bs + b0; }
     it.w_hi = &p.wc_hi; it.w_lo = &p.wc_lo;
     it.wx = (sid * p.kpb + kbi) * epk; it.wy = tile * kBN;
   }
 }
 
-// Walks over this CTA's items in issue order, phase after phase.
+// Walks over this CTA's items in issue order: phase after phase, inside a phase tile after tile.
 struct Cursor {
-  int ph, s, k;  // phase, source (in issue order), k-block inside this CTA's slice of the source
-  int first;     // the item is the first of its phase
+  int ph, ti, s, k;  // phase, tile round, source (in issue order), k-block inside this CTA's slice of the source
+  int tile;
   Plan pl;
   bool end;
-  __device__ __forceinline__ void seek(const DecParams& p, int NP, int P, int rank, int tile) {  // first item at or after ph
+  __device__ __forceinline__ void seek(const DecParams& p, int NP, int P, int rank, const Group& gr) {
     while (ph < NP) {
-      make_plan(p, ph, P, rank, tile, pl);
-      s = 0;
-      while (s < pl.nsrc && pl.cnt[s] == 0) ++s;
-      if (s < pl.nsrc) { k = 0; first = 1; end = false; return; }
+      for (; ti < gr.TPC; ++ti) {
+        tile = gr.cl + ti * gr.NC;
+        make_plan(p, ph, P, rank, tile, pl);
+        s = 0;
+        while (s < pl.nsrc && pl.cnt[s] == 0) ++s;
+        if (s < pl.nsrc) { k = 0; end = false; return; }
+      }
       ++ph;
+      ti = 0;
     }
     end = true;
   }
-  __device__ __forceinline__ void start(const DecParams& p, int NP, int P, int rank, int tile) {
+  __device__ __forceinline__ void start(const DecParams& p, int NP, int P, int rank, const Group& gr) {
     ph = 0;
-    seek(p, NP, P, rank, tile);
+    ti = 0;
+    seek(p, NP, P, rank, gr);
   }
-  __device__ __forceinline__ void advance(const DecParams& p, int NP, int P, int rank, int tile) {
-    first = 0;
+  __device__ __forceinline__ void advance(const DecParams& p, int NP, int P, int rank, const Group& gr) {
     if (++k < pl.cnt[s]) return;
     k = 0;
     do { ++s; } while (s < pl.nsrc && pl.cnt[s] == 0);
     if (s < pl.nsrc) return;
-    ++ph;
-    seek(p, NP, P, rank, tile);
+    ++ti;
+    seek(p, NP, P, rank, gr);
   }
 };
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_constant__ DecParams p) {
-  constexpr int NW = dec_nw(MODE), NA = dec_na(MODE);
-  constexpr int WSTAGE = dec_wstage(MODE), ASTAGE = dec_astage(MODE);
-  constexpr int HALF = 128 * 128;  // bytes of one operand part (hi or lo) of a stage
+  constexpr int NW = dec_nw(MODE);
+  constexpr int WSTAGE = dec_wstage(MODE);
+  constexpr int HALF = 128 * 128;  // bytes of one operand part (hi or lo) of a weight stage
+  constexpr int PARTS = mode_split(MODE) ? 2 : 1;
   constexpr int EPK = mode_epk(MODE);
   constexpr uint32_t IDESC = make_idesc(mode_fmt(MODE), kBN);
   constexpr int NACC = num_acc(kBN, MODE);
   constexpr int TMEM_COLS = tmem_cols(kBN, MODE);
   static_assert(kSlotBytes >= kAttGlobalScratchBytes && kSlotBytes >= kAttLocalScratchBytes, "attention scratch");
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t wfull[NW], wempty[NW], afull[NA], aempty[NA];
+  __shared__ __align__(8) uint64_t wfull[NW], wempty[NW], afull[kMaxAStages], aempty[kMaxAStages];
   __shared__ __align__(8) uint64_t accum_bar, tmem_free, xchg_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ int in_exchange;  // experiment: the team is exchanging partial tiles (the producer holds back its loads)
-  __shared__ int prod_done;  // phases the producer has seen complete (saves the team a look at the global counter)
+  __shared__ int in_exchange;  // the team is exchanging partial tiles: the producer holds back its loads meanwhile
+  __shared__ int prod_done;    // phases the producer has seen complete (saves the team a look at the global counter)
   __shared__ float s_bias[kBN];
   __shared__ long long s_push[kTeam / 32];  // developer timeline: when each warp finished pushing
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int rank = (int)blockIdx.x;  // cluster dims (4,1,1): rank in cluster == blockIdx.x
-  const int tile = (int)blockIdx.y;
-  const unsigned G = gridDim.x * gridDim.y;
-  const int cta_id = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+  Group gr;
+  {
+    const int groups = (int)gridDim.z, gi = (int)blockIdx.z;
+    const int Bv = (p.B + groups - 1) / groups;
+    gr.b0 = gi * Bv;
+    gr.nb = p.B - gr.b0 < Bv ? p.B - gr.b0 : Bv;
+    if (gr.nb < 0) gr.nb = 0;
+    gr.cl = (int)blockIdx.y;
+    gr.NC = (int)gridDim.y;
+    gr.TPC = ((4 * p.H + kBN - 1) / kBN + gr.NC - 1) / gr.NC;
+    gr.G = gridDim.x * gridDim.y;
+    gr.counter = p.counter + 32 * gi;  // 128 bytes apart
+  }
+  const unsigned G = gr.G;
+  const int cta_id = (int)(blockIdx.y * gridDim.x + blockIdx.x);       // inside the group
+  const int cta_all = (int)blockIdx.z * (int)G + cta_id;               // inside the grid
   const int P = p.L + (p.att_type == 1 ? 3 : 2), NP = p.T * P;
+  // activation stages hold a_rows rows per part; the ring has as many of them as fit (at most kMaxAStages)
+  const int a_rows = p.a_rows;
+  const int APART = a_rows * 128, ASTAGE = PARTS * APART;
+  const int NA = kARingBytes / ASTAGE < kMaxAStages ? kARingBytes / ASTAGE : kMaxAStages;
+  // exchange slots: [set][rank][8 column quads][SR rows] float4; two sets when 64 rows are enough, used in turn by
+  // consecutive tiles (a peer may push the next tile while this CTA still reads the previous one)
+  const int SR = a_rows <= 64 ? 64 : 128;
+  const int slot_sets = SR == 64 ? 2 : 1;
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   uint8_t* wring = base;
   uint8_t* aring = base + (size_t)NW * WSTAGE;
-  float4* slots = reinterpret_cast<float4*>(aring + (size_t)NA * ASTAGE);
-  unsigned char* scratch = reinterpret_cast<unsigned char*>(slots);  // attention phases: nobody exchanges then
+  float4* slots_all = reinterpret_cast<float4*>(aring + kARingBytes);
+  unsigned char* scratch = reinterpret_cast<unsigned char*>(slots_all);  // attention phases: nobody exchanges then
 
   if (tid == 0) {
     for (int s = 0; s < NW; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
-    for (int s = 0; s < NA; ++s) { mbar_init(&afull[s], 1); mbar_init(&aempty[s], 1); }
+    for (int s = 0; s < kMaxAStages; ++s) { mbar_init(&afull[s], 1); mbar_init(&aempty[s], 1); }
     mbar_init(&accum_bar, 1);
     mbar_init(&tmem_free, kTeam / 32);
     mbar_init(&xchg_bar, kSplit * (kTeam / 32));
@@ -333,7 +385,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
     in_exchange = 0;
     prod_done = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    if (p.stamps && cta_id == 0) p.stamps[0] = gtime();
+    if (p.stamps && cta_all == 0) p.stamps[0] = gtime();
   }
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -348,13 +400,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
   const uint32_t tmem_base = tmem_base_s;
   volatile int* ab = &abort_s;
 
-  if (warp == 8) {
+  if (gr.nb <= 0) {
+    // a group without columns (more groups than the batch can fill): nothing to do, nobody waits for it
+  } else if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint64_t w_policy = p.w_evict_first ? policy_evict_first() : 0;
-      Cursor wc, ac;
-      wc.start(p, NP, P, rank, tile);
-      ac.start(p, NP, P, rank, tile);
+      Cursor wc, ac;  // weights, activations
+      wc.start(p, NP, P, rank, gr);
+      ac.start(p, NP, P, rank, gr);
       int w_it = 0, a_it = 0;
       unsigned done_phases = 0;  // phases known to be complete
       long long t_progress = clock64();
@@ -366,9 +420,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
         // weights: as far ahead as the ring allows
         if (!hold && !wc.end && w_it < a_it + NW) {
           const int st = w_it % NW;
-          if (mbar_try_wait(&wempty[st], (uint32_t)(((w_it / NW) & 1) ^ 1))) {
+          if (mbar_test_wait(&wempty[st], (uint32_t)(((w_it / NW) & 1) ^ 1))) {
             Item it;
-            make_item(p, wc.pl, wc.s, wc.pl.lo[wc.s] + wc.k, tile, EPK, it);
+            make_item(p, wc.pl, wc.s, wc.pl.lo[wc.s] + wc.k, wc.tile, gr.b0, EPK, it);
             uint8_t* dst = wring + (size_t)st * WSTAGE;
             mbar_expect_tx(&wfull[st], (uint32_t)WSTAGE);
             if (w_policy) {
@@ -379,17 +433,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
               if (mode_split(MODE)) tma_load_2d(dst + HALF, it.w_lo, &wfull[st], it.wx, it.wy);
             }
             ++w_it;
-            wc.advance(p, NP, P, rank, tile);
+            wc.advance(p, NP, P, rank, gr);
             progressed = true;
           }
         }
-        // activations: the next k-block, once its data exists and its stage and the aliased region are free
+        // activations: the next k-block, once its data exists and its stage is free
         {
           bool can = !hold;
           Item it;
-          make_item(p, ac.pl, ac.s, ac.pl.lo[ac.s] + ac.k, tile, EPK, it);
+          make_item(p, ac.pl, ac.s, ac.pl.lo[ac.s] + ac.k, ac.tile, gr.b0, EPK, it);
           if (it.need >= 0 && (unsigned)(it.need + 1) > done_phases) {
-            const unsigned c = ld_acquire_gpu(p.counter);
+            const unsigned c = ld_acquire_gpu(gr.counter);
             if (c / G != done_phases) {
               done_phases = c / G;
               st_release_cta_shared(&prod_done, (int)done_phases);
@@ -398,14 +452,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
             else fence_proxy_async();  // the rows were written with ordinary stores; TMA reads them
           }
           const int st = a_it % NA;
-          if (can && !mbar_try_wait(&aempty[st], (uint32_t)(((a_it / NA) & 1) ^ 1))) can = false;
+          if (can && !mbar_test_wait(&aempty[st], (uint32_t)(((a_it / NA) & 1) ^ 1))) can = false;
           if (can) {
             uint8_t* dst = aring + (size_t)st * ASTAGE;
             mbar_expect_tx(&afull[st], (uint32_t)ASTAGE);
             tma_load_2d(dst, it.a_hi, &afull[st], it.ax, it.ay);
-            if (mode_split(MODE)) tma_load_2d(dst + HALF, it.a_lo, &afull[st], it.ax, it.ay);
+            if (mode_split(MODE)) tma_load_2d(dst + APART, it.a_lo, &afull[st], it.ax, it.ay);
             ++a_it;
-            ac.advance(p, NP, P, rank, tile);
+            ac.advance(p, NP, P, rank, gr);
             progressed = true;
           }
         }
@@ -435,40 +489,43 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
       bool ok = true;
       Plan pl;
       for (int ph = 0; ph < NP && ok; ++ph) {
-        make_plan(p, ph, P, rank, tile, pl);
-        if (pl.kind == PH_ATT || tile >= pl.n_tiles) continue;
-        if (g > 0) {  // the team has read the previous phase's accumulators
-          ok = bounded_wait([&] { return mbar_try_wait(&tmem_free, (uint32_t)((g - 1) & 1)); }, ab, p.err, 200000 + ph);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        for (int i = 0; i < pl.nitems; ++i, ++it) {
-          const int ws = it % NW, as = it % NA;
-          ok = bounded_wait([&] { return mbar_try_wait(&wfull[ws], (uint32_t)((it / NW) & 1)); }, ab, p.err, 300000 + ph) &&
-               bounded_wait([&] { return mbar_try_wait(&afull[as], (uint32_t)((it / NA) & 1)); }, ab, p.err, 400000 + ph);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(aring + (size_t)as * ASTAGE), b_addr = smem_u32(wring + (size_t)ws * WSTAGE);
-          const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
-          const uint32_t d_main = tmem_base + (uint32_t)((i % NACC) * kBN);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma<mode_kind_tf32(MODE)>(d_main, da + 2 * k, db + 2 * k, IDESC, (i >= NACC || k > 0) ? 1u : 0u);
-            if (mode_split(MODE)) {
-              const uint64_t dal = make_smem_desc(a_addr + HALF), dbl = make_smem_desc(b_addr + HALF);
-              const uint32_t d_cross = tmem_base + (uint32_t)(NACC * kBN);
-              umma<mode_kind_tf32(MODE)>(d_cross, dal + 2 * k, db + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-              umma<mode_kind_tf32(MODE)>(d_cross, da + 2 * k, dbl + 2 * k, IDESC, 1u);
-            }
+        for (int ti = 0; ti < gr.TPC && ok; ++ti) {
+          const int tile = gr.cl + ti * gr.NC;
+          make_plan(p, ph, P, rank, tile, pl);
+          if (pl.kind == PH_ATT || tile >= pl.n_tiles) continue;
+          if (g > 0) {  // the team has read the previous tile's accumulators
+            ok = bounded_wait([&] { return mbar_try_wait(&tmem_free, (uint32_t)((g - 1) & 1)); }, ab, p.err, 200000 + ph);
+            if (!ok) break;
           }
-          umma_commit(&wempty[ws]);
-          umma_commit(&aempty[as]);
+          tc_fence_after();
+          for (int i = 0; i < pl.nitems; ++i, ++it) {
+            const int ws = it % NW, as = it % NA;
+            ok = bounded_wait([&] { return mbar_try_wait(&wfull[ws], (uint32_t)((it / NW) & 1)); }, ab, p.err, 300000 + ph) &&
+                 bounded_wait([&] { return mbar_try_wait(&afull[as], (uint32_t)((it / NA) & 1)); }, ab, p.err, 400000 + ph);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(aring + (size_t)as * ASTAGE), b_addr = smem_u32(wring + (size_t)ws * WSTAGE);
+            const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
+            const uint32_t d_main = tmem_base + (uint32_t)((i % NACC) * kBN);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              umma<mode_kind_tf32(MODE)>(d_main, da + 2 * k, db + 2 * k, IDESC, (i >= NACC || k > 0) ? 1u : 0u);
+              if (mode_split(MODE)) {
+                const uint64_t dal = make_smem_desc(a_addr + (uint32_t)APART), dbl = make_smem_desc(b_addr + HALF);
+                const uint32_t d_cross = tmem_base + (uint32_t)(NACC * kBN);
+                umma<mode_kind_tf32(MODE)>(d_cross, dal + 2 * k, db + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                umma<mode_kind_tf32(MODE)>(d_cross, da + 2 * k, dbl + 2 * k, IDESC, 1u);
+              }
+            }
+            umma_commit(&wempty[ws]);
+            umma_commit(&aempty[as]);
+          }
+          if (ok) {
+            if (pl.nitems > 0) umma_commit(&accum_bar);
+            else mbar_arrive_local(&accum_bar);  // nothing to accumulate (fewer k-blocks than CTAs): the team reads zeros
+          }
+          ++g;
         }
-        if (ok) {
-          if (pl.nitems > 0) umma_commit(&accum_bar);
-          else mbar_arrive_local(&accum_bar);  // nothing to accumulate (fewer k-blocks than CTAs): the team reads zeros
-        }
-        ++g;
       }
     }
   } else {
@@ -477,28 +534,29 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
     const int lrow = q * 32 + lane;                // tile row (= batch column) behind this thread's TMEM lane
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
     const int r = tid & 127, whalf = tid >> 7;     // after the exchange: row r, half whalf of this CTA's columns
-    const int H = p.H, B = p.B;
+    const int H = p.H, Bs = p.B, b0 = gr.b0, nb = gr.nb;
+    const bool my_rows = q * 32 < SR;              // this warp's accumulator rows can hold columns of the group
     int g = 0;
     unsigned done_phases = 0;
     Plan pl;
     for (int ph = 0; ph < NP; ++ph) {
-      make_plan(p, ph, P, rank, tile, pl);
+      make_plan(p, ph, P, rank, gr.cl, pl);
       const int t = pl.t;
-      const int* mask = p.mask + (size_t)t * B;
+      const int* mask = p.mask + (size_t)t * Bs + b0;
       ZD_STAMP(0);
       if (pl.kind == PH_ATT) {
         // ---- attention proper: scores, softmax, context; one column per CTA in turn
         if (tid == 0) {
           const unsigned want = (unsigned)ph * G;  // phases 0 .. ph-1 complete
-          bounded_wait([&] { return ld_acquire_gpu(p.counter) >= want; }, ab, p.err, 500000 + ph);
+          bounded_wait([&] { return ld_acquire_gpu(gr.counter) >= want; }, ab, p.err, 500000 + ph);
         }
         ZD_STAMP(1);
         team_sync();
         if (!*ab) {
           AttArgs a;
-          a.H = H; a.B = B; a.D = p.D; a.S_max = p.S_max; a.B_src = B; a.cols_per_sent = 1;
-          a.hs = p.hs; a.len = p.len; a.offset = p.off; a.mask = mask;
-          a.h_t = p.h_f32[p.L - 1] + (size_t)t * B * H;
+          a.H = H; a.B = Bs; a.D = p.D; a.S_max = p.S_max; a.B_src = Bs; a.cols_per_sent = 1;
+          a.hs = p.hs; a.len = p.len; a.offset = p.off; a.mask = p.mask + (size_t)t * Bs;
+          a.h_t = p.h_f32[p.L - 1] + (size_t)t * Bs * H;
           a.tanh1 = p.tq; a.q = p.tq ? p.tq + H : nullptr; a.ld_tq = 2 * H; a.v_p = p.v_p;
           a.c_t = p.ctx_f32; a.align_out = nullptr; a.align_by_pos = 0; a.viterbi_out = nullptr; a.viterbi_init = -1.f;
           a.op_b16 = MODE == TC_BF16 ? p.ctx_op_hi : nullptr;
@@ -507,175 +565,182 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
           a.op_hi = (MODE == TC_TF32 || MODE == TC_TF32X3) ? (float*)p.ctx_op_hi : nullptr;
           a.op_lo = MODE == TC_TF32X3 ? (float*)p.ctx_op_lo : nullptr;
           a.ld_op = p.Kpad;
-          for (int b = cta_id; b < B; b += (int)G) {
+          for (int b = b0 + cta_id; b < b0 + nb; b += (int)G) {
             if (p.att_type == 1) att_local_fast_body(a, b, tid, scratch, SyncTeam());
             else att_global_fast_body(a, b, tid, scratch, SyncTeam());
             team_sync();  // the scratch is free for the next column
           }
         }
-      } else if (tile < pl.n_tiles) {
-        // ---- GEMM phase: exchange the partial tiles, finish this CTA's 32 columns
-        const int n_main = pl.nitems < NACC ? pl.nitems : NACC;
-        // bias of the tile (a weight: no dependency on the phase's inputs)
-        if (tid < kBN) {
-          float bv = 0.f;
-          if (pl.kind == PH_CELL) {
-            const int hid = tile * (kBN / 4) + (tid % (kBN / 4));
-            if (hid < H) bv = __ldg(p.bias[pl.layer] + (size_t)(tid / (kBN / 4)) * H + hid);
-          } else if (pl.kind == PH_COMB) {
-            const int n = tile * kBN + tid;
-            if (n < H) bv = __ldg(p.att_bias + n);
+      } else {
+        for (int ti = 0; ti < gr.TPC; ++ti) {
+          const int tile = gr.cl + ti * gr.NC;
+          if (tile >= pl.n_tiles) break;
+          if (ti > 0) make_plan(p, ph, P, rank, tile, pl);
+          // ---- one row tile of a GEMM phase: exchange the partial tiles, finish this CTA's 32 columns
+          float4* slots = slots_all + (size_t)((slot_sets == 2) ? (g & 1) : 0) * (kSplit * (kOwn / 4) * 64);
+          const int n_main = pl.nitems < NACC ? pl.nitems : NACC;
+          // bias of the tile (a weight: no dependency on the phase's inputs)
+          if (tid < kBN) {
+            float bv = 0.f;
+            if (pl.kind == PH_CELL) {
+              const int hid = tile * (kBN / 4) + (tid % (kBN / 4));
+              if (hid < H) bv = __ldg(p.bias[pl.layer] + (size_t)(tid / (kBN / 4)) * H + hid);
+            } else if (pl.kind == PH_COMB) {
+              const int n = tile * kBN + tid;
+              if (n < H) bv = __ldg(p.att_bias + n);
+            }
+            s_bias[tid] = bv;
           }
-          s_bias[tid] = bv;
-        }
-        float pre_c[4] = {0.f, 0.f, 0.f, 0.f};
-        const float mk = ((pl.kind == PH_CELL || pl.kind == PH_COMB) && r < B) ? (float)mask[r] : 1.0f;
-        if (pl.kind == PH_CELL && r < B) {  // this thread's old cell state: it wrote it itself one step ago
-          const float* cp = p.c_buf[pl.layer][t & 1];
-          const int hb = tile * (kBN / 4) + rank * 8 + whalf * 4;
+          float pre_c[4] = {0.f, 0.f, 0.f, 0.f};
+          const float mk = ((pl.kind == PH_CELL || pl.kind == PH_COMB) && r < nb) ? (float)mask[r] : 1.0f;
+          if (pl.kind == PH_CELL && r < nb) {  // this thread's old cell state: it wrote it itself one step ago
+            const float* cp = p.c_buf[pl.layer][t & 1];
+            const int hb = tile * (kBN / 4) + rank * 8 + whalf * 4;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) pre_c[u] = (hb + u < H) ? cp[(size_t)r * H + hb + u] : 0.f;
-        }
-        warp_bounded_wait([&] { return mbar_try_wait(&accum_bar, (uint32_t)(g & 1)); }, lane, ab, p.err, 600000 + ph);
-        tc_fence_after();
-        ZD_STAMP(1);
-        if (tid == 0) *reinterpret_cast<volatile int*>(&in_exchange) = 1;
-        if (pl.nitems == 0 && tid == 0 && ph > 0) {
-          // A CTA without k-blocks (fewer k-blocks than CTAs) has nothing that ties it to the phase's inputs: it must
-          // not push its zeros before the owners have finished with the previous phase's slots.
-          const unsigned want = (unsigned)ph * G;
-          bounded_wait([&] { return ld_acquire_gpu(p.counter) >= want; }, ab, p.err, 700000 + ph);
-        }
-        team_sync();  // (and the tile's bias values are in place)
-        {
-          const uint32_t my_slot = smem_u32(slots + (size_t)rank * (kOwn / 4) * 128 + lrow);
-          for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
-            float v[32];
-            if (pl.nitems == 0) {
+            for (int u = 0; u < 4; ++u) pre_c[u] = (hb + u < H) ? cp[(size_t)(b0 + r) * H + hb + u] : 0.f;
+          }
+          warp_bounded_wait([&] { return mbar_try_wait(&accum_bar, (uint32_t)(g & 1)); }, lane, ab, p.err, 600000 + ph);
+          tc_fence_after();
+          ZD_STAMP(1);
+          if (tid == 0) *reinterpret_cast<volatile int*>(&in_exchange) = 1;
+          if (pl.nitems == 0 && tid == 0 && ph > 0) {
+            // A CTA without k-blocks (fewer k-blocks than CTAs) has nothing that ties it to the phase's inputs: it must
+            // not push its zeros before the owners have finished with the previous phase's slots.
+            const unsigned want = (unsigned)ph * G;
+            bounded_wait([&] { return ld_acquire_gpu(gr.counter) >= want; }, ab, p.err, 700000 + ph);
+          }
+          team_sync();  // (and the tile's bias values are in place)
+          if (my_rows) {
+            const uint32_t my_slot = smem_u32(slots + (size_t)rank * (kOwn / 4) * SR + lrow);
+            for (int c0 = chalf * 64; c0 < chalf * 64 + 64; c0 += 32) {
+              float v[32];
+              if (pl.nitems == 0) {
 #pragma unroll
-              for (int u = 0; u < 32; ++u) v[u] = 0.f;
-            } else {
-              tmem_ld32(taddr + c0, v);
-              if (mode_split(MODE)) {
-                float tv[32];
-                for (int a = 1; a < n_main; ++a) {
-                  tmem_ld32(taddr + a * kBN + c0, tv);
+                for (int u = 0; u < 32; ++u) v[u] = 0.f;
+              } else {
+                tmem_ld32(taddr + c0, v);
+                if (mode_split(MODE)) {
+                  float tv[32];
+                  for (int a = 1; a < n_main; ++a) {
+                    tmem_ld32(taddr + a * kBN + c0, tv);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < 32; ++u) v[u] += tv[u];
+                  }
+                  tmem_ld32(taddr + NACC * kBN + c0, tv);
                   tmem_wait_ld();
 #pragma unroll
-                  for (int u = 0; u < 32; ++u) v[u] += tv[u];
+                  for (int u = 0; u < 32; ++u) v[u] = fmaf(tv[u], mode_cross_scale(MODE), v[u]);
                 }
-                tmem_ld32(taddr + NACC * kBN + c0, tv);
                 tmem_wait_ld();
-#pragma unroll
-                for (int u = 0; u < 32; ++u) v[u] = fmaf(tv[u], mode_cross_scale(MODE), v[u]);
               }
-              tmem_wait_ld();
-            }
 #pragma unroll
-            for (int u = 0; u < 32; u += 4) {
-              const int c = c0 + u;
-              int owner, lcol;
-              if (pl.kind == PH_CELL) {  // tile column = gate * 32 + hidden unit; a CTA owns 8 hidden units, all gates
-                const int gate = c / 32, j = c % 32;
-                owner = j / 8;
-                lcol = gate * 8 + (j % 8);
-              } else {
-                owner = c / kOwn;
-                lcol = c % kOwn;
-              }
-              if (owner == rank) {
-                slots[((size_t)rank * (kOwn / 4) + lcol / 4) * 128 + lrow] = make_float4(v[u], v[u + 1], v[u + 2], v[u + 3]);
-              } else {
-                const uint32_t local = my_slot + (uint32_t)((lcol / 4) * 128 * 16);
-                st_cluster_v4(cluster_map(local, (uint32_t)owner), v[u], v[u + 1], v[u + 2], v[u + 3]);
+              for (int u = 0; u < 32; u += 4) {
+                const int c = c0 + u;
+                int owner, lcol;
+                if (pl.kind == PH_CELL) {  // tile column = gate * 32 + hidden unit; a CTA owns 8 hidden units, all gates
+                  const int gate = c / 32, j = c % 32;
+                  owner = j / 8;
+                  lcol = gate * 8 + (j % 8);
+                } else {
+                  owner = c / kOwn;
+                  lcol = c % kOwn;
+                }
+                if (owner == rank) {
+                  slots[((size_t)rank * (kOwn / 4) + lcol / 4) * SR + lrow] = make_float4(v[u], v[u + 1], v[u + 2], v[u + 3]);
+                } else {
+                  const uint32_t local = my_slot + (uint32_t)((lcol / 4) * SR * 16);
+                  st_cluster_v4(cluster_map(local, (uint32_t)owner), v[u], v[u + 1], v[u + 2], v[u + 3]);
+                }
               }
             }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        ZD_STAMP(3);
-        if (p.detail && lane == 0) s_push[warp] = gtime();
-        if (lane == 0) {
-          mbar_arrive_local(&tmem_free);  // this warp's accumulator reads are complete
-          for (int c = 0; c < kSplit; ++c) mbar_arrive_remote(&xchg_bar, (uint32_t)c);
-        }
-        warp_bounded_wait([&] { return mbar_try_wait_cluster(&xchg_bar, (uint32_t)(g & 1)); }, lane, ab, p.err, 800000 + ph);
-        ZD_STAMP(4);
-        if (tid == 0) *reinterpret_cast<volatile int*>(&in_exchange) = 0;
-        if (p.detail && tid == 0) {  // slot 2 of the timeline: the last warp of this CTA to finish pushing
-          long long mx = 0;
-          for (int i = 0; i < kTeam / 32; ++i) mx = s_push[i] > mx ? s_push[i] : mx;
-          if (p.detail_cta < 0) p.detail[((size_t)cta_id * NP + ph) * 8 + 2] = mx;
-          else if (cta_id == p.detail_cta) p.detail[(size_t)ph * 8 + 2] = mx;
-        }
-        ++g;
-        if (pl.kind == PH_CELL) {
-          const int l = pl.layer;
-          float gsum[4][4];
-#pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int rk = 0; rk < kSplit; ++rk) {  // fixed order: deterministic sums
-              const float4 tv = slots[((size_t)rk * (kOwn / 4) + gq * 2 + whalf) * 128 + r];
-              acc.x += tv.x; acc.y += tv.y; acc.z += tv.z; acc.w += tv.w;
-            }
-            gsum[gq][0] = acc.x; gsum[gq][1] = acc.y; gsum[gq][2] = acc.z; gsum[gq][3] = acc.w;
+          tc_fence_before();
+          __syncwarp();
+          ZD_STAMP(3);
+          if (p.detail && lane == 0) s_push[warp] = gtime();
+          if (lane == 0) {
+            mbar_arrive_local(&tmem_free);  // this warp's accumulator reads are complete
+            for (int c = 0; c < kSplit; ++c) mbar_arrive_remote(&xchg_bar, (uint32_t)c);
           }
-          if (r < B) {
-            const int jb = rank * 8 + whalf * 4;  // first hidden unit inside the tile
-            const int hb = tile * 32 + jb;
-            const int nvalid = H - hb >= 4 ? 4 : (H - hb > 0 ? H - hb : 0);
-            float hv[4], cv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const float gi = act_sigmoid<MODE>(gsum[0][u] + s_bias[jb + u]);
-              const float gf = act_sigmoid<MODE>(gsum[1][u] + s_bias[32 + jb + u]);
-              const float gg = act_tanh<MODE>(gsum[2][u] + s_bias[64 + jb + u]);
-              const float go = act_sigmoid<MODE>(gsum[3][u] + s_bias[96 + jb + u]);
-              const float c = gf * pre_c[u] + gi * gg;
-              hv[u] = go * act_tanh<MODE>(c) * mk;
-              cv[u] = c * mk;
-            }
-            if (nvalid > 0) {
-              const size_t row = (size_t)t * B + r;
-              store4_f32(p.c_buf[l][(t + 1) & 1], (size_t)r * H + hb, cv, nvalid);
-              store4_f32(p.h_f32[l], row * H + hb, hv, nvalid);
-              store4_operand(make_opout<MODE>(p.h_op_hi[l], p.h_op_lo[l]), row * p.Kpad + hb, hv, nvalid);
-            }
+          warp_bounded_wait([&] { return mbar_try_wait_cluster(&xchg_bar, (uint32_t)(g & 1)); }, lane, ab, p.err, 800000 + ph);
+          ZD_STAMP(4);
+          if (tid == 0) *reinterpret_cast<volatile int*>(&in_exchange) = 0;
+          if (p.detail && tid == 0) {  // slot 2 of the timeline: the last warp of this CTA to finish pushing
+            long long mx = 0;
+            for (int i = 0; i < kTeam / 32; ++i) mx = s_push[i] > mx ? s_push[i] : mx;
+            if (p.detail_cta < 0) p.detail[((size_t)cta_all * NP + ph) * 8 + 2] = mx;
+            else if (cta_all == p.detail_cta) p.detail[(size_t)ph * 8 + 2] = mx;
           }
-        } else {
-          // store epilogue: this CTA's 32 tile columns, thread = (row r, columns 16 * whalf .. + 16)
-          const int N = pl.kind == PH_PGEMM ? 2 * H : H;
+          ++g;
+          if (pl.kind == PH_CELL) {
+            const int l = pl.layer;
+            if (r < nb) {
+              float gsum[4][4];
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const int lc = whalf * 16 + c4 * 4;  // column inside this CTA's 32
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int gq = 0; gq < 4; ++gq) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int rk = 0; rk < kSplit; ++rk) {
-              const float4 tv = slots[((size_t)rk * (kOwn / 4) + lc / 4) * 128 + r];
-              acc.x += tv.x; acc.y += tv.y; acc.z += tv.z; acc.w += tv.w;
+                for (int rk = 0; rk < kSplit; ++rk) {  // fixed order: deterministic sums
+                  const float4 tv = slots[((size_t)rk * (kOwn / 4) + gq * 2 + whalf) * SR + r];
+                  acc.x += tv.x; acc.y += tv.y; acc.z += tv.z; acc.w += tv.w;
+                }
+                gsum[gq][0] = acc.x; gsum[gq][1] = acc.y; gsum[gq][2] = acc.z; gsum[gq][3] = acc.w;
+              }
+              const int jb = rank * 8 + whalf * 4;  // first hidden unit inside the tile
+              const int hb = tile * 32 + jb;
+              const int nvalid = H - hb >= 4 ? 4 : (H - hb > 0 ? H - hb : 0);
+              float hv[4], cv[4];
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float gi = act_sigmoid<MODE>(gsum[0][u] + s_bias[jb + u]);
+                const float gf = act_sigmoid<MODE>(gsum[1][u] + s_bias[32 + jb + u]);
+                const float gg = act_tanh<MODE>(gsum[2][u] + s_bias[64 + jb + u]);
+                const float go = act_sigmoid<MODE>(gsum[3][u] + s_bias[96 + jb + u]);
+                const float c = gf * pre_c[u] + gi * gg;
+                hv[u] = go * act_tanh<MODE>(c) * mk;
+                cv[u] = c * mk;
+              }
+              if (nvalid > 0) {
+                const size_t row = (size_t)t * Bs + b0 + r;
+                store4_f32(p.c_buf[l][(t + 1) & 1], (size_t)(b0 + r) * H + hb, cv, nvalid);
+                store4_f32(p.h_f32[l], row * H + hb, hv, nvalid);
+                store4_operand(make_opout<MODE>(p.h_op_hi[l], p.h_op_lo[l]), row * p.Kpad + hb, hv, nvalid);
+              }
             }
-            const int n0 = tile * kBN + rank * kOwn + lc;
-            const int nvalid = N - n0 >= 4 ? 4 : (N - n0 > 0 ? N - n0 : 0);
-            float x[4] = {acc.x, acc.y, acc.z, acc.w};
+          } else if (r < nb) {
+            // store epilogue: this CTA's 32 tile columns, thread = (row r, columns 16 * whalf .. + 16)
+            const int N = pl.kind == PH_PGEMM ? 2 * H : H;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              float v = x[u] + s_bias[rank * kOwn + lc + u];
-              if (pl.kind == PH_COMB || n0 + u < H) v = act_tanh<MODE>(v);
-              x[u] = v * mk;
-            }
-            if (r < B && nvalid > 0) {
-              if (pl.kind == PH_PGEMM) {
-                store4_f32(p.tq, (size_t)r * (2 * H) + n0, x, nvalid);
-              } else {
-                const size_t row = (size_t)t * B + r;
-                store4_f32(p.ht_f32, row * H + n0, x, nvalid);
-                store4_operand(make_opout<MODE>(p.ht_op_hi, p.ht_op_lo), row * p.Kpad + n0, x, nvalid);
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const int lc = whalf * 16 + c4 * 4;  // column inside this CTA's 32
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int rk = 0; rk < kSplit; ++rk) {
+                const float4 tv = slots[((size_t)rk * (kOwn / 4) + lc / 4) * SR + r];
+                acc.x += tv.x; acc.y += tv.y; acc.z += tv.z; acc.w += tv.w;
+              }
+              const int n0 = tile * kBN + rank * kOwn + lc;
+              const int nvalid = N - n0 >= 4 ? 4 : (N - n0 > 0 ? N - n0 : 0);
+              float x[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                float v = x[u] + s_bias[rank * kOwn + lc + u];
+                if (pl.kind == PH_COMB || n0 + u < H) v = act_tanh<MODE>(v);
+                x[u] = v * mk;
+              }
+              if (nvalid > 0) {
+                if (pl.kind == PH_PGEMM) {
+                  store4_f32(p.tq, (size_t)(b0 + r) * (2 * H) + n0, x, nvalid);
+                } else {
+                  const size_t row = (size_t)t * Bs + b0 + r;
+                  store4_f32(p.ht_f32, row * H + n0, x, nvalid);
+                  store4_operand(make_opout<MODE>(p.ht_op_hi, p.ht_op_lo), row * p.Kpad + n0, x, nvalid);
+                }
               }
             }
           }
+          if (ti + 1 < gr.TPC) team_sync();  // the bias values and (single slot set) the slots are free for the next tile
         }
       }
       // ---- hand the phase over: results visible to ordinary loads and to TMA, then count this CTA
@@ -688,16 +753,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_decoder_kernel(const __grid_co
         // active CTA knows that already (its producer needed them for this phase's inputs); an idle one has to look.
         if (done_phases < (unsigned)ph) {
           if (ld_acquire_cta_shared(&prod_done) < ph) {
+            // (with a pause between looks: dozens of idle CTAs reading one word back to back get in the way of the
+            // working CTAs' additions to it)
             const unsigned want = (unsigned)ph * G;
-            bounded_wait([&] { return ld_acquire_gpu(p.counter) >= want; }, ab, p.err, 900000 + ph);
+            bounded_wait([&] {
+              if (ld_acquire_gpu(gr.counter) >= want) return true;
+              __nanosleep(300);
+              return false;
+            }, ab, p.err, 900000 + ph);
           }
           done_phases = (unsigned)ph;
         }
         ZD_STAMP(6);
         if (!*ab)  // release: cumulative over the team's stores, which the barrier above ordered before this thread
-          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.counter) : "memory");
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gr.counter) : "memory");
         ZD_STAMP(7);
-        if (p.stamps && cta_id == 0) p.stamps[1 + ph] = gtime();
+        if (p.stamps && cta_all == 0) p.stamps[1 + ph] = gtime();
       }
     }
   }
@@ -755,10 +826,15 @@ cudaError_t launch_mode(const DecParams& p, cudaStream_t st) {
   cudaError_t e = configure<MODE>(&max_clusters);
   if (e != cudaSuccess) return e;
   const int NT = (4 * p.H + kBN - 1) / kBN;
-  if (NT > max_clusters) return cudaErrorInvalidConfiguration;
+  const int groups = p.groups < 1 ? 1 : p.groups;
+  int NC = max_clusters / groups;  // clusters per column group
+  if (NC > NT) NC = NT;
+  if (NC < 1 || p.a_rows < 8 || p.a_rows > 128 || (p.a_rows & 7) != 0) return cudaErrorInvalidConfiguration;
+  // one set of exchange slots (more than 64 columns per group) serves one row tile per phase only
+  if (p.a_rows > 64 && NC < NT) return cudaErrorInvalidConfiguration;
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(kSplit, NT, 1);
+  cfg.gridDim = dim3(kSplit, NC, groups);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = dec_smem(MODE);
   cfg.stream = st;
@@ -805,6 +881,18 @@ bool tc_decoder_supported(int mode, int H, int B, int L, int att_type) {
     return false;
   }
   return (4 * H + kBN - 1) / kBN <= max_clusters;
+}
+
+int tc_decoder_default_groups(int B) {
+  static const int forced = [] {
+    const char* e = std::getenv("ZRNN_DEC_GROUPS");
+    return e ? std::atoi(e) : 0;
+  }();
+  int g = forced > 0 ? forced : (B >= 32 ? 2 : 1);
+  if (g > 4) g = 4;
+  while (g > 1 && (B + g - 1) / g > 64) g *= 2;  // not reachable for B <= 128; keeps the 64-column rule explicit
+  while (g > 1 && B < 8 * g) g /= 2;
+  return g;
 }
 
 cudaError_t launch_tc_decoder(const DecParams& p, int mode, cudaStream_t st) {

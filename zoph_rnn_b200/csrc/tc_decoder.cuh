@@ -13,6 +13,8 @@ namespace zrnn {
 struct DecParams {
   enum { MAXL = 4 };
   int H, Kpad, B, T, L;      // B <= 128 columns, L <= MAXL layers
+  int groups;                // column groups that run the chain of phases independently (1, 2 or 4)
+  int a_rows;                // rows per activation box = columns of a group rounded up to 8 (the tensor maps' box height)
   int att_type;              // 1 = local-p, 2 = global dot
   int D;                     // local-p half window
   int kb;                    // 128-byte k-blocks that cover H elements
@@ -63,6 +65,9 @@ inline int dec_phases_per_step(const DecParams& p) { return p.L + (p.att_type ==
 
 // Can the kernel run this shape on the current device?  (tile count against the clusters that fit at once)
 bool tc_decoder_supported(int mode, int H, int B, int L, int att_type);
+// Column groups to cut a batch of B columns into (every group needs 64 columns or fewer to take more than one row
+// tile per phase, which it must when the clusters are shared among groups).
+int tc_decoder_default_groups(int B);
 // mode: TC_BF16 / TC_TF32 / TC_TF32X3 / TC_F16X2.  The counter must be zero when the kernel starts.
 cudaError_t launch_tc_decoder(const DecParams& p, int mode, cudaStream_t st);
 

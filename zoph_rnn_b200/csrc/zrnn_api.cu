@@ -372,11 +372,11 @@ int* tc_error_word() {  // one word per device
 }
 
 // tensor maps of an activation operand: `rows` rows of H valid elements, stride Kpad
-int act_maps(const Act& a, int eng, int H, int Kpad, int rows, CUtensorMap* hi, CUtensorMap* lo) {
+int act_maps(const Act& a, int eng, int H, int Kpad, int rows, CUtensorMap* hi, CUtensorMap* lo, int box_rows = 128) {
   if (!a.hi) return fail(ZRNN_E_STATE, "internal: activation has no operand-form copy");
-  if (!zrnn::make_kmajor_map(hi, a.hi, eng_eb(eng), H, rows, Kpad, 128))
+  if (!zrnn::make_kmajor_map(hi, a.hi, eng_eb(eng), H, rows, Kpad, box_rows))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand");
-  if (eng_split(eng) && !zrnn::make_kmajor_map(lo, a.lo, eng_eb(eng), H, rows, Kpad, 128))
+  if (eng_split(eng) && !zrnn::make_kmajor_map(lo, a.lo, eng_eb(eng), H, rows, Kpad, box_rows))
     return fail(ZRNN_E_CUDA, "cannot encode a TMA tensor map for an activation operand (lo)");
   return ZRNN_OK;
 }
@@ -710,6 +710,7 @@ struct zrnn_model {
     unsigned long long gen = 0;
     cudaStream_t stream = nullptr;
     int seen = 0;
+    int persistent = 0;  // the pass was recorded with the persistent decoder kernel switched on
     cudaGraphExec_t exec = nullptr;
   } sg;
   void drop_graph() {
@@ -1523,14 +1524,18 @@ static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* 
 }
 
 // The target side of a feed-input model as ONE launch of the persistent decoder kernel (tc_decoder.cu) instead of
-// L + 2 (or 3) launches per time step.  *done stays false when the shape, the engine or the device cannot run it
-// (the caller then takes the per-launch path); ZRNN_NO_PERSISTENT=1 turns it off.
+// L + 2 (or 3) launches per time step.  Opt-in (environment ZRNN_PERSISTENT=1, read at every call): on the shapes
+// measured so far the per-launch path, replayed as a CUDA graph with programmatic dependent launch, is as fast or
+// faster - a phase of the persistent kernel pays for its grid-wide hand-over and keeps fewer bytes in flight per SM
+// (its exchange slots cannot alias the operand ring) - so that path stays the default.  *done stays false when the
+// kernel is off or the shape, the engine or the device cannot run it (the caller then takes the per-launch path).
 static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, int B, const Act& Xt,
                                   const std::vector<Act>& sseq, const std::vector<Act>& tseq, const Act& hts,
                                   const int* tin_mk, const int* len, const int* off, std::vector<float*> cst[2],
                                   std::vector<int>& cur, cudaStream_t s, bool* done) {
   *done = false;
-  static const bool disabled = std::getenv("ZRNN_NO_PERSISTENT") != nullptr;
+  const char* want = std::getenv("ZRNN_PERSISTENT");
+  const bool disabled = !(want && want[0] == '1');
   const zrnn_model_config& c = m->cfg;
   const int L = c.num_layers, H = c.H, eng = m->eng;
   zrnn_attention* A = m->att;
@@ -1546,11 +1551,14 @@ static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, in
   p.H = H; p.Kpad = Kpad; p.B = B; p.T = T; p.L = L; p.att_type = c.attention; p.D = A->D;
   p.kb = (H + epk - 1) / epk;
   p.kpb = Kpad / epk;
-  ZR_TRY(act_maps(Xt, eng, H, Kpad, (int)nT, &p.x_hi, &p.x_lo));
+  p.groups = zrnn::tc_decoder_default_groups(B);
+  const int ar = std::min(128, ((B + p.groups - 1) / p.groups + 7) / 8 * 8);
+  p.a_rows = ar;
+  ZR_TRY(act_maps(Xt, eng, H, Kpad, (int)nT, &p.x_hi, &p.x_lo, ar));
   for (int l = 0; l < L; ++l) {
     zrnn_lstm_layer* Ly = m->tgt[l];
-    ZR_TRY(act_maps(tseq[l], eng, H, Kpad, (int)nT, &p.h_hi[l], &p.h_lo[l]));
-    ZR_TRY(act_maps(sseq[l], eng, H, Kpad, S * B, &p.h0_hi[l], &p.h0_lo[l]));
+    ZR_TRY(act_maps(tseq[l], eng, H, Kpad, (int)nT, &p.h_hi[l], &p.h_lo[l], ar));
+    ZR_TRY(act_maps(sseq[l], eng, H, Kpad, S * B, &p.h0_hi[l], &p.h0_lo[l], ar));
     p.h0_row[l] = (S - 1) * B;
     p.w_hi[l] = Ly->wmap; p.w_lo[l] = Ly->wmap_lo; p.w_tiled[l] = Ly->kbtot;
     p.bias[l] = Ly->b;
@@ -1558,7 +1566,7 @@ static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, in
     p.c_buf[l][1] = cst[cur[l] ^ 1][l];
     p.h_f32[l] = tseq[l].f32; p.h_op_hi[l] = tseq[l].hi; p.h_op_lo[l] = tseq[l].lo;
   }
-  ZR_TRY(act_maps(hts, eng, H, Kpad, (int)nT, &p.ht_hi, &p.ht_lo));
+  ZR_TRY(act_maps(hts, eng, H, Kpad, (int)nT, &p.ht_hi, &p.ht_lo, ar));
   p.ht_f32 = hts.f32; p.ht_op_hi = hts.hi; p.ht_op_lo = hts.lo;
   // the step's context vectors and (local-p) the stacked projection live in the attention layer's own buffers
   ZR_CUDA(A->ctx.reserve(sizeof(float) * (size_t)H * B));
@@ -1566,7 +1574,7 @@ static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, in
   if (eng_split(eng)) ZR_CUDA(A->ctx_lo.reserve((size_t)B * Kpad * eb));
   Act ctx;
   ctx.f32 = A->ctx.as<float>(); ctx.hi = A->ctx_hi.p; ctx.lo = eng_split(eng) ? A->ctx_lo.as<float>() : nullptr;
-  ZR_TRY(act_maps(ctx, eng, H, Kpad, B, &p.ctx_hi, &p.ctx_lo));
+  ZR_TRY(act_maps(ctx, eng, H, Kpad, B, &p.ctx_hi, &p.ctx_lo, ar));
   p.ctx_f32 = ctx.f32; p.ctx_op_hi = ctx.hi; p.ctx_op_lo = ctx.lo;
   p.wc_hi = A->cmap; p.wc_lo = A->cmap_lo;
   if (c.attention == ZRNN_ATT_LOCAL_P) {
@@ -1578,7 +1586,7 @@ static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, in
   p.att_bias = A->bias;
   p.mask = tin_mk;
   p.hs = sseq[L - 1].f32; p.S_max = S; p.len = len; p.off = off;
-  ZR_CUDA(m->dec_counter.reserve(256));
+  ZR_CUDA(m->dec_counter.reserve(1024));  // one counter per column group, 128 bytes apart
   p.counter = m->dec_counter.as<unsigned int>();
   p.err = tc_error_word();
   const int P = zrnn::dec_phases_per_step(p);
@@ -1593,7 +1601,7 @@ static int run_decoder_persistent(zrnn_model* m, const Geom& g, int S, int T, in
   p.hold_loads = std::getenv("ZRNN_DEC_NO_HOLD") == nullptr;
   p.w_evict_first = std::getenv("ZRNN_DEC_NO_EVICT") == nullptr;
   p.detail_cta = g_dec_detail_cta;
-  ZR_CUDA(cudaMemsetAsync(p.counter, 0, sizeof(unsigned int), s));
+  ZR_CUDA(cudaMemsetAsync(p.counter, 0, 1024, s));
   const cudaError_t e = zrnn::launch_tc_decoder(p, eng_tcmode(eng), s);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -1628,9 +1636,11 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
   static const bool no_graph = std::getenv("ZRNN_NO_GRAPH") != nullptr;
   const bool can_graph = !no_graph && s != nullptr && !g_kt.on;
   auto& sg = m->sg;
+  const char* pe = std::getenv("ZRNN_PERSISTENT");
+  const int persistent = (pe && pe[0] == '1') ? 1 : 0;
   const bool same = sg.S == S_max && sg.T == T && sg.B == B && sg.src == d_src_ids && sg.tin == d_tgt_in &&
                     sg.tout == d_tgt_out && sg.out == d_logp_out && sg.stream == s && sg.ws == m->ws.p &&
-                    sg.gen == g_buf_generation;
+                    sg.gen == g_buf_generation && sg.persistent == persistent;
   if (can_graph && same && sg.exec) {
     ZR_CUDA(cudaGraphLaunch(sg.exec, s));
     return ZRNN_OK;
@@ -1639,6 +1649,7 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
     m->drop_graph();
     sg.S = S_max; sg.T = T; sg.B = B; sg.src = d_src_ids; sg.tin = d_tgt_in; sg.tout = d_tgt_out; sg.out = d_logp_out;
     sg.stream = s;
+    sg.persistent = persistent;
   }
   if (can_graph && same && sg.seen >= 1 && !sg.exec) {
     cudaGraph_t graph = nullptr;
