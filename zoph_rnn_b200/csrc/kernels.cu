@@ -1031,6 +1031,260 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------
+// resident-weight LSTM sequence kernel (small layers)
+// ------------------------------------------------------------------------------------------
+// xp[(n*H + j)*4 + g] = sum_k Mx[g][j,k] * x[k, n] for every column n = t*B + b of the sequence
+__global__ void __launch_bounds__(128) lstm_seq_xpart_kernel(const SeqArgs a) {
+  const int H = a.H, N = a.S * a.B;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t HH = (size_t)H * H;
+  for (int n = blockIdx.y; n < N; n += gridDim.y) {
+    const float* x;
+    if (a.x_seq) {
+      x = a.x_seq + (size_t)n * H;
+    } else {
+      int id = a.ids[n];
+      if (id < 0) id = 0;
+      if (a.V > 0 && id >= a.V) {
+        id = 0;
+        if (a.err && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.err, kErrBadTokenId);
+      }
+      x = a.emb + (size_t)id * H;
+    }
+    if (j < H) {
+      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+      for (int k = 0; k < H; ++k) {
+        const float xv = __ldg(x + k);
+        const size_t at = (size_t)k * H + j;
+        acc0 = fmaf(__ldg(a.Mx + at), xv, acc0);
+        acc1 = fmaf(__ldg(a.Mx + HH + at), xv, acc1);
+        acc2 = fmaf(__ldg(a.Mx + 2 * HH + at), xv, acc2);
+        acc3 = fmaf(__ldg(a.Mx + 3 * HH + at), xv, acc3);
+      }
+      reinterpret_cast<float4*>(a.xp)[(size_t)n * H + j] = make_float4(acc0, acc1, acc2, acc3);
+    }
+  }
+}
+
+__device__ __forceinline__ void seq_store_op(const SeqArgs& a, size_t n, int i, float v) {
+  const size_t idx = n * a.ld_op + i;
+  if (a.op_b16) reinterpret_cast<__nv_bfloat16*>(a.op_b16)[idx] = __float2bfloat16(v);
+  if (a.op_h_hi) {
+    const __half h = __float2half_rn(v);
+    reinterpret_cast<__half*>(a.op_h_hi)[idx] = h;
+    reinterpret_cast<__half*>(a.op_h_lo)[idx] = __float2half_rn((v - __half2float(h)) * 2048.0f);
+  }
+  if (a.op_hi) {
+    unsigned u = __float_as_uint(v);
+    const float hi = ((u & 0x7f800000u) == 0x7f800000u) ? v : __uint_as_float((u + 0x1000u) & 0xffffe000u);
+    a.op_hi[idx] = hi;
+    if (a.op_lo) a.op_lo[idx] = v - hi;
+  }
+}
+
+// One cluster of C CTAs per launch.  CTA r keeps Wt[k][jl] = (Wh_i, Wh_f, Wh_g, Wh_o)[j0 + jl, k] for its Hc hidden
+// units in shared memory; thread (jl, cg) owns the cell of unit j0 + jl for CPT consecutive columns.  h_{t-1} lives in
+// every CTA's shared memory (hb[buf][k][column], double-buffered); after a step each thread writes its new h values
+// into all C copies and a cluster barrier closes the step.
+// Shared memory is the bound: a thread reads its unit's four weights once per k for all of its columns, so the more
+// columns a thread owns the fewer times the weight slice is read per step (CPT = 8: once for 8 columns).
+template <int CPT>
+__global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_kernel(const SeqArgs a, int Hc, int CG) {
+  extern __shared__ __align__(16) unsigned char seq_smem[];
+  const int H = a.H, B = a.B, Bp = CG * CPT;
+  float4* Wt = reinterpret_cast<float4*>(seq_smem);                       // [H][Hc]
+  float* hb = reinterpret_cast<float*>(seq_smem + (size_t)H * Hc * 16);   // [2][H][Bp]
+  unsigned rank, csize;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+  const int j0 = (int)rank * Hc;
+  const int nj = H - j0 < Hc ? (H - j0 > 0 ? H - j0 : 0) : Hc;  // units of this CTA
+  const int tid = threadIdx.x;
+  const size_t HH = (size_t)H * H;
+  for (int e = tid; e < H * Hc; e += blockDim.x) {
+    const int k = e / Hc, jl = e - k * Hc;
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (jl < nj) {
+      const size_t at = (size_t)k * H + j0 + jl;
+      w = make_float4(__ldg(a.Wh + at), __ldg(a.Wh + HH + at), __ldg(a.Wh + 2 * HH + at), __ldg(a.Wh + 3 * HH + at));
+    }
+    Wt[e] = w;
+  }
+  for (int e = tid; e < H * Bp; e += blockDim.x) {
+    const int k = e / Bp, c = e - k * Bp;
+    hb[e] = c < B ? a.h0[(size_t)c * H + k] : 0.f;
+    hb[(size_t)H * Bp + e] = 0.f;
+  }
+  const int jl = tid % Hc, cg = tid / Hc;
+  const bool active = cg < CG && jl < nj;
+  const int j = j0 + jl, cb = cg * CPT;  // unit and first column of this thread
+  float cst[CPT];
+  float bi = 0.f, bf = 0.f, bg = 0.f, bo = 0.f;
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) cst[c] = (active && cb + c < B) ? a.c0[(size_t)(cb + c) * H + j] : 0.f;
+  if (active) { bi = a.bias[j]; bf = a.bias[H + j]; bg = a.bias[2 * H + j]; bo = a.bias[3 * H + j]; }
+  // every copy of h_0 is in place before anybody reads or overwrites one
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  uint32_t hb_remote[8];
+  {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(hb);
+    for (unsigned q = 0; q < 8; ++q) {
+      uint32_t r = local;
+      if (q < csize) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(q));
+      hb_remote[q] = r;
+    }
+  }
+  for (int t = 0; t < a.S; ++t) {
+    const float* hcur = hb + (size_t)(t & 1) * H * Bp;
+    const size_t nb = (size_t)t * B;
+    float4 xp[CPT];
+    float mk[CPT];
+    if (active) {  // the inputs of the epilogue do not depend on the recurrence: request them before the k loop
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const bool okc = cb + c < B;
+        xp[c] = okc ? reinterpret_cast<const float4*>(a.xp)[(nb + cb + c) * H + j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        mk[c] = okc ? (float)a.mask[nb + cb + c] : 0.f;
+      }
+    }
+    float ai[CPT], af[CPT], ag[CPT], ao[CPT], hnew[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) ai[c] = af[c] = ag[c] = ao[c] = hnew[c] = 0.f;
+    if (active) {
+      const float4* wp = Wt + jl;
+      const float* hp = hcur + cb;
+#pragma unroll 4
+      for (int k = 0; k < H; ++k) {
+        const float4 w = wp[(size_t)k * Hc];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const float hv = hp[(size_t)k * Bp + c];
+          ai[c] = fmaf(w.x, hv, ai[c]);
+          af[c] = fmaf(w.y, hv, af[c]);
+          ag[c] = fmaf(w.z, hv, ag[c]);
+          ao[c] = fmaf(w.w, hv, ao[c]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        if (cb + c < B) {
+          const float gi = sigmoidf_acc(ai[c] + xp[c].x + bi);
+          const float gf = sigmoidf_acc(af[c] + xp[c].y + bf);
+          const float gg = tanhf(ag[c] + xp[c].z + bg);
+          const float go = sigmoidf_acc(ao[c] + xp[c].w + bo);
+          const float cn = gf * cst[c] + gi * gg;
+          const float hn = go * tanhf(cn) * mk[c];
+          cst[c] = cn * mk[c];
+          hnew[c] = hn;
+          // the new h into every CTA's copy of the other buffer
+          const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + cb + c) * 4);
+          for (unsigned q = 0; q < csize; ++q)
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(hb_remote[q] + off), "f"(hn) : "memory");
+        }
+      }
+    }
+    // the arrival publishes the exchange; the copies for the consumers outside the kernel go out while the barrier
+    // completes (they need not be visible to the cluster, so they stay off the step's critical path)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    if (active) {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        if (cb + c < B) {
+          const size_t n = nb + cb + c;
+          a.h_seq[n * H + j] = hnew[c];
+          seq_store_op(a, n, j, hnew[c]);
+        }
+      }
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+  if (active)
+#pragma unroll
+    for (int c = 0; c < CPT; ++c)
+      if (cb + c < B) a.c_out[(size_t)(cb + c) * H + j] = cst[c];
+}
+
+namespace {
+struct SeqPlan { int C, Hc, CG, CPT, threads; size_t smem; };
+bool seq_plan(int H, int B, SeqPlan* p) {
+  if (H < 1 || B < 1 || B > 32) return false;
+  // A step is a chain of short dependent stages (matrix-vector product, gate math, exchange), so what pays is
+  // parallelism: the largest cluster that leaves every CTA a few hidden units, and one column per thread as long as
+  // the block holds that many threads (measured at H = 100, B = 8: 8 CTAs x 1 column per thread 3.7 us per step,
+  // 1 CTA x 8 columns per thread 9.7 us).
+  static const int force_cpt = std::getenv("ZRNN_SEQ_CPT") ? std::atoi(std::getenv("ZRNN_SEQ_CPT")) : 0;
+  static const int force_c = std::getenv("ZRNN_SEQ_C") ? std::atoi(std::getenv("ZRNN_SEQ_C")) : 0;
+  int C = 8;
+  while (C > 1 && (H + C - 1) / C < 8) C /= 2;
+  if (force_c == 1 || force_c == 2 || force_c == 4 || force_c == 8) C = force_c;
+  for (; C <= 8; C *= 2) {
+    const int Hc = (H + C - 1) / C;
+    for (int CPT = 1; CPT <= 8; CPT *= 2) {
+      if (force_cpt && CPT != force_cpt) continue;
+      const int CG = (B + CPT - 1) / CPT;
+      const int threads = (Hc * CG + 31) / 32 * 32;
+      const size_t smem = (size_t)H * Hc * 16 + 2 * (size_t)H * CG * CPT * 4;
+      if (threads <= (CPT >= 4 ? 256 : 1024) && smem <= 200 * 1024) {
+        *p = SeqPlan{C, Hc, CG, CPT, threads, smem};
+        return true;
+      }
+    }
+  }
+  return false;
+}
+template <int CPT>
+cudaError_t launch_seq_t(const SeqArgs& a, const SeqPlan& pl, cudaStream_t st) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(lstm_seq_resident_kernel<CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(lstm_seq_resident_kernel<CPT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(pl.C);
+  cfg.blockDim = dim3(pl.threads);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = pl.C;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  count_launch();
+  return cudaLaunchKernelEx(&cfg, lstm_seq_resident_kernel<CPT>, a, pl.Hc, pl.CG);
+}
+}  // namespace
+
+bool lstm_seq_resident_supported(int H, int B) {
+  SeqPlan pl;
+  return seq_plan(H, B, &pl);
+}
+cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st) {
+  SeqPlan pl;
+  if (!seq_plan(a.H, a.B, &pl) || a.S < 1) return cudaErrorInvalidValue;
+  const int N = a.S * a.B;
+  dim3 grid((a.H + 127) / 128, N > 2048 ? 2048 : N);
+  lstm_seq_xpart_kernel<<<grid, 128, 0, st>>>(a);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  switch (pl.CPT) {
+    case 1: return launch_seq_t<1>(a, pl, st);
+    case 2: return launch_seq_t<2>(a, pl, st);
+    case 4: return launch_seq_t<4>(a, pl, st);
+    case 8: return launch_seq_t<8>(a, pl, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------------------------------
 // ensemble: log of the mean of K softmax distributions, one CTA per column
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) ensemble_logmean_kernel(const EnsembleArgs a) {

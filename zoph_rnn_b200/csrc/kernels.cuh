@@ -75,6 +75,44 @@ struct GemmArgs {
 cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, cudaStream_t st);
 int gemm_rows_per_tile(int gates, int tile);
 
+// ---- small layers: a whole sequence of LSTM steps in one launch with the recurrent weights resident on chip
+// For hidden sizes whose four H x H recurrent matrices fit the shared memory of a cluster of up to 8 CTAs (H <= 320),
+// one layer's S steps run as ONE kernel: each CTA keeps the weight rows of its slice of hidden units in shared memory
+// for the whole sequence, h_t is exchanged through distributed shared memory and c_t never leaves registers, so a step
+// costs a cluster barrier instead of a kernel launch and no weight byte is read twice.  The input half of the
+// pre-activations (M x for every step; it does not depend on the recurrence) is formed first by one batched kernel.
+// Exact fp32 FMA arithmetic.  Replaces the per-step loop of src/model.hpp:1581-1600 / :1765-1795 over
+// LSTM_IH_Node / LSTM_HH_Node::forward_prop_GPU (src/LSTM.hpp:76-421, src/LSTM_HH.hpp:103-333) for layers without
+// feed-input.
+struct SeqArgs {
+  int H, B, S;           // hidden size, columns, steps
+  const float* Mx;       // 4 x (H x H) input matrices, gate order i,f,g,o, each column-major
+  const float* Wh;       // 4 x (H x H) recurrent matrices
+  const float* bias;     // 4 x H
+  // layer input: either x_seq (H x (S*B), the layer below) or an embedding gather (emb H x V, ids [S*B], -1 free)
+  const float* x_seq;
+  const float* emb;
+  const int* ids;
+  int V;                 // rows of the embedding table (ids >= V read column 0 and set *err)
+  int* err;
+  const int* mask;       // [S*B] 0/1
+  const float* h0;       // H x B state before step 0
+  const float* c0;
+  float* h_seq;          // H x (S*B) out
+  float* c_out;          // H x B: cell state after the last step
+  float* xp;             // scratch: 4 floats per (step, column, hidden unit)
+  // optional operand-form copies of h_seq for the tensor-core consumers (row n at + n*ld_op), as AttArgs
+  void* op_b16;
+  float* op_hi;
+  float* op_lo;
+  void* op_h_hi;
+  void* op_h_lo;
+  int ld_op;
+};
+// false when the shape does not fit (H > 320, B > 32, ...): the caller keeps its per-step path
+bool lstm_seq_resident_supported(int H, int B);
+cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st);
+
 // ---- softmax partial combine: logp[n] = (tgt - M) - log(sum_i s_i exp(m_i - M)); 0 where mask==0
 cudaError_t launch_lse_combine(const float* part_max, const float* part_sum, const float* tgt_logit, int n_parts,
                                int N, const int* mask, float* logp, cudaStream_t st);

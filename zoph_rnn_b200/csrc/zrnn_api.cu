@@ -697,6 +697,7 @@ struct zrnn_model {
   cudaStream_t stream = nullptr;
   DevBuf ws, io;
   DevBuf dec_counter;       // phase counter of the persistent decoder kernel
+  DevBuf seq_xp;            // input half of the pre-activations for the resident-weight sequence kernel
   int persist_state = 0;    // 0 untried, 1 works, -1 refused by the runtime (the per-launch path is used)
   zrnn::TcMulti enc_multi;  // parameter block of the encoder's multi-cell launches (host scratch)
   const float* last_top = nullptr;
@@ -723,7 +724,7 @@ struct zrnn_model {
     for (auto* l : tgt) delete l;
     delete att;
     delete sm;
-    ws.release(); io.release(); dec_counter.release();
+    ws.release(); io.release(); dec_counter.release(); seq_xp.release();
     if (stream) cudaStreamDestroy(stream);
   }
 };
@@ -1456,10 +1457,45 @@ static int act_zero(const Act& a, const Geom& g, size_t cols, cudaStream_t s) {
 // A stack of LSTM layers over S steps whose inputs X0 (one slot per step) are all known in advance: the source side
 // always, the target side of language models and of models without feed-input.  h0[l] is layer l's state before
 // step 0; its c comes from cst[cur[l]][l].
+// Small layers take the resident-weight sequence kernel (see run_stack); it gathers its layer-0 inputs itself.
+static bool stack_is_resident(const Geom& g, int B) {
+  static const bool no_resident = std::getenv("ZRNN_NO_RESIDENT") != nullptr;
+  return !no_resident && zrnn::lstm_seq_resident_supported(g.H, B);
+}
 static int run_stack(zrnn_model* m, const std::vector<zrnn_lstm_layer*>& layers, const Geom& g, const int* mask, int S,
                      int B, const Act& X0, const std::vector<Act>& h0, std::vector<Act>& seq, std::vector<float*> cst[2],
-                     std::vector<int>& cur, cudaStream_t s) {
+                     std::vector<int>& cur, cudaStream_t s, const int* ids0 = nullptr) {
   const int L = (int)layers.size();
+  // Small layers: the recurrent weights fit the shared memory of one cluster, so a layer's S steps run as one launch
+  // with the weights resident on chip (kernels.cu, lstm_seq_resident_kernel; exact fp32 arithmetic whatever the
+  // engine).  ZRNN_NO_RESIDENT=1 keeps the per-step launches.
+  if (ids0 && S >= 1 && stack_is_resident(g, B)) {
+    ZR_CUDA(m->seq_xp.reserve(sizeof(float) * 4 * (size_t)S * B * g.H));
+    KScope sweep(KC_LSTM, s, S * L, true);
+    for (int l = 0; l < L; ++l) {
+      zrnn_lstm_layer* Ly = layers[l];
+      zrnn::SeqArgs a;
+      std::memset(&a, 0, sizeof(a));
+      a.H = g.H; a.B = B; a.S = S;
+      a.Mx = Ly->Mx; a.Wh = Ly->Wh; a.bias = Ly->b;
+      if (l == 0) { a.emb = Ly->W; a.ids = ids0; a.V = Ly->V; a.err = tc_error_word(); }
+      else a.x_seq = seq[l - 1].f32;
+      a.mask = mask;
+      a.h0 = h0[l].f32;
+      const int cu = cur[l];
+      a.c0 = cst[cu][l];
+      a.c_out = cst[cu ^ 1][l];
+      cur[l] = cu ^ 1;
+      a.h_seq = seq[l].f32;
+      a.xp = m->seq_xp.as<float>();
+      a.ld_op = g.Kpad;
+      if (g.eng == ENG_BF16) a.op_b16 = seq[l].hi;
+      else if (g.eng == ENG_H2) { a.op_h_hi = seq[l].hi; a.op_h_lo = seq[l].lo; }
+      else if (g.eng != ENG_SIMT) { a.op_hi = (float*)seq[l].hi; a.op_lo = g.eng == ENG_X3 ? seq[l].lo : nullptr; }
+      ZR_CUDA(zrnn::launch_lstm_seq_resident(a, s));
+    }
+    return ZRNN_OK;
+  }
   // Anti-diagonal order: the cells (layer l, step d - l) of diagonal d depend only on diagonal d - 1, so one launch
   // runs them side by side.  L cells fill the SMs with less (or no) K splitting than one cell alone: each CTA streams a
   // longer K slice, no partial tiles cross the cluster, and S + L - 1 launches replace S * L.  Needs one column tile
@@ -1518,9 +1554,9 @@ static int run_stack(zrnn_model* m, const std::vector<zrnn_lstm_layer*>& layers,
 static int run_encoder(zrnn_model* m, const Geom& g, const int* ids, const int* mask, int S, int B, const Act& X0,
                        const Act& zero, std::vector<Act>& seq, std::vector<float*> cst[2], std::vector<int>& cur,
                        cudaStream_t s) {
-  ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
+  if (!stack_is_resident(g, B)) ZR_TRY(gather_act(m->src[0], ids, S * B, X0, s));
   const std::vector<Act> h0(m->cfg.num_layers, zero);
-  return run_stack(m, m->src, g, mask, S, B, X0, h0, seq, cst, cur, s);
+  return run_stack(m, m->src, g, mask, S, B, X0, h0, seq, cst, cur, s, ids);
 }
 
 // The target side of a feed-input model as ONE launch of the persistent decoder kernel (tc_decoder.cu) instead of
@@ -1719,13 +1755,13 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
     if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S, B, len, off, 1));
   }
   // target side: layer l starts from the encoder's final (h,c) of layer l (src/model.hpp:1714-1724)
-  ZR_TRY(gather_act(m->tgt[0], tin_id, (int)nT, Xt, s));
+  if (c.feed_input || !stack_is_resident(g, B)) ZR_TRY(gather_act(m->tgt[0], tin_id, (int)nT, Xt, s));
   if (!c.feed_input) {
     // no cell waits for an attention output: the target side is a plain stack too (anti-diagonal order where it
     // fits), and attention follows per step on the finished top layer
     std::vector<Act> h0(L);
     for (int l = 0; l < L; ++l) h0[l] = c.lm ? zero : act_at(sseq[l], (size_t)(S - 1) * B, g);
-    ZR_TRY(run_stack(m, m->tgt, g, tin_mk, T, B, Xt, h0, tseq, cst, cur, s));
+    ZR_TRY(run_stack(m, m->tgt, g, tin_mk, T, B, Xt, h0, tseq, cst, cur, s, tin_id));
     if (c.attention)
       for (int t = 0; t < T; ++t)
         ZR_TRY(att_forward(m->att, act_at(tseq[L - 1], (size_t)t * B, g), tin_mk + (size_t)t * B, B,
