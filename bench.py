@@ -7,8 +7,13 @@ One "step" = one pass of the hot path over one synthetic minibatch of the worklo
 scoring: gather -> LSTM stack -> attention -> softmax log-probs; for c4: one batched beam decode).
 Prints ONE JSON line (rank 0).  `value` is whole-job throughput with inputs resident in HBM; `e2e` is the
 same metric through the host-buffer C-ABI call (H2D of the ids and D2H of the results inside the timed
-region).  `--impl reference` times the CPU restatement of the reference's math (the oracle) on the host
-cores on a bounded sample of the same workload.
+region).  The line also carries `parity` (the GPU results of the timed model against the CPU oracle on a
+sample of the same batch), `cpu_baseline`, and - for the default workload - `configs`: the other four
+benchmark configurations, a few steps each.  With --gpus N >= 2 sentences shard by rank (weak scaling, no
+collective) and the line adds `c5_sharded`: configuration 5 with its softmax sharded by vocabulary rows over
+the N ranks (strong scaling, NCCL all-gathers), split by stage.
+`--impl reference` times the CPU restatement of the reference's math (the oracle) on the host cores on a
+bounded sample of the same workload: the full minibatch width, fewer time steps.
 """
 import argparse
 import json
@@ -46,8 +51,8 @@ WORKLOADS = {
     "c4s": dict(desc="profiling stand-in: beam decode 2x1000 V=50k global-dot attention beam 12, 64 sentences S~U[4,6]",
                 kind="decode", L=2, H=1000, Vs=50000, Vt=50000, B=64, S=(4, 6), T=None, att=2, feed=1, scale=0.1,
                 dist="uniform", zipf=1.1, beam=12, max_ratio=2.0, min_ratio=0.5, longest_sent=100),
-    "c5": dict(desc="LM 2x2048 V=200k B=256 T=64", kind="lm", L=2, H=2048, Vs=0, Vt=200000, B=256, S=0, T=64,
-               att=0, feed=0, scale=0.02, dist="normal", zipf=1.05),
+    "c5": dict(desc="LM 2x2048 V=200k B=256 T=64, bf16 weights", kind="lm", L=2, H=2048, Vs=0, Vt=200000, B=256, S=0,
+               T=64, att=0, feed=0, scale=0.02, dist="normal", zipf=1.05, bf16_weights=True),
 }
 
 
@@ -128,6 +133,21 @@ def host_cores():
         return max(1, os.cpu_count() or 1)
 
 
+def reference_sample(w):
+    """The bounded CPU sample of a scoring workload: the FULL minibatch width (so that every weight byte the CPU
+    streams is used for as many columns as on the GPU) and only the first few source / target steps."""
+    inp = make_inputs(w, 1234)
+    Tn = 2 if w["H"] >= 2048 else 4
+    src = inp["src"]
+    if src is not None:
+        src = np.ascontiguousarray(src[-Tn:])  # the reversed source is left-padded: its last rows are the words
+    tin, tout = np.ascontiguousarray(inp["tin"][:Tn]), np.ascontiguousarray(inp["tout"][:Tn])
+    S_full = inp["src"].shape[0] if inp["src"] is not None else 0
+    sample = (f"all {w['B']} sentences x first {Tn} of {inp['tin'].shape[0]} target steps"
+              + (f" and {Tn} of {S_full} source steps" if src is not None else "") + ", full model")
+    return src, tin, tout, sample
+
+
 def run_reference(args, w, rank):
     """CPU arm: the oracle (a port of the reference's kernel math; the reference itself cannot be built
     for this machine) on a bounded sample of the workload, all host threads."""
@@ -136,7 +156,7 @@ def run_reference(args, w, rank):
     from oracle import oracle_lib as ol
     ol.build()
     cfg = make_cfg(w)
-    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"], round_bf16=bool(w.get("bf16_weights")))
     om = ol.OracleModel(cfg, weights)
     ol.set_acc_float(True)  # float accumulation = the reference's SGEMM arithmetic
     ol.set_num_threads(host_cores())  # launchers such as torchrun export OMP_NUM_THREADS=1
@@ -144,22 +164,17 @@ def run_reference(args, w, rank):
     if w["kind"] == "decode":
         Bs = 1
         inp = make_inputs(w, 1234, B=Bs)
-        sample = f"{Bs} of {w['B']} sentences, full beam {w['beam']}"
+        sample = f"{Bs} of {w['B']} sentences, full beam {w['beam']} (the reference decodes one sentence at a time)"
 
         def step():
             ids, ln, sc = om.beam_decode(inp["srcs"], w["beam"], 1, w["min_ratio"], w["max_ratio"], 0.0, w["longest_sent"])
             return int(np.maximum(ln[:, 0] - 1, 0).sum())
     else:
-        Bs = max(1, min(w["B"], 8 if w["H"] >= 1000 else w["B"]))
-        inp = make_inputs(w, 1234, B=Bs)
-        Tn = inp["tin"].shape[0]
-        if w["H"] >= 2048:  # c5: bound the sample further
-            Tn = 4
-        sample = f"{Bs} of {w['B']} sentences x {Tn} of {inp['tin'].shape[0]} target steps, full model"
+        src, tin, tout, sample = reference_sample(w)
 
         def step():
-            om.score_batch(inp["src"], inp["tin"][:Tn], inp["tout"][:Tn])
-            return int((inp["tout"][:Tn] != -1).sum())
+            om.score_batch(src, tin, tout)
+            return int((tout != -1).sum())
     for _ in range(min(args.warmup, 1)):
         step()
     t0 = time.perf_counter()
@@ -172,7 +187,7 @@ def run_reference(args, w, rank):
     line = dict(impl="reference", metric=metric_name(w), value=val, unit=unit, n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=1e3 * dt / args.steps, higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=args.workload + ": " + w["desc"]),
+                config=dict(workload=args.workload + ": " + w["desc"], sample=sample),
                 cpu_baseline=dict(value=val, unit=unit, cores=cores, kind="port", sample=sample),
                 e2e=dict(value=val, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
@@ -187,7 +202,7 @@ def cpu_baseline(w):
     from oracle import oracle_lib as ol
     ol.build()
     cfg = make_cfg(w)
-    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"], round_bf16=bool(w.get("bf16_weights")))
     om = ol.OracleModel(cfg, weights)
     ol.set_acc_float(True)
     ol.set_num_threads(host_cores())
@@ -199,30 +214,88 @@ def cpu_baseline(w):
         toks = int(np.maximum(ln[:, 0] - 1, 0).sum())
         sample = f"1 of {w['B']} sentences, full beam {w['beam']}"
     else:
-        Bs = max(1, min(w["B"], 8 if w["H"] >= 1000 else w["B"]))
-        inp = make_inputs(w, 1234, B=Bs)
-        Tn = 4 if w["H"] >= 2048 else inp["tin"].shape[0]
+        src, tin, tout, sample = reference_sample(w)
         t0 = time.perf_counter()
-        om.score_batch(inp["src"], inp["tin"][:Tn], inp["tout"][:Tn])
+        om.score_batch(src, tin, tout)
         dt = time.perf_counter() - t0
-        toks = int((inp["tout"][:Tn] != -1).sum())
-        sample = f"{Bs} of {w['B']} sentences x {Tn} of {inp['tin'].shape[0]} target steps, full model, 1 pass"
+        toks = int((tout != -1).sum())
+        sample += ", 1 pass"
     ol.set_acc_float(False)
     return dict(value=toks / dt, unit="tokens/s", cores=ol.num_threads(), kind="port", sample=sample)
 
 
-def measure(args, w, cfg, dtype, rank, world, clocks_tag):
+PARITY_SENTENCES = 8
+
+
+def parity_check(w, cfg, weights, model, dtype, inp):
+    """The timed model's results against the CPU oracle (double accumulation) on a sample of the SAME batch: the first
+    PARITY_SENTENCES sentences over all their steps (a sentence scores the same alone as inside the batch).  fp32-
+    accurate modes: largest relative log-prob error against 1e-5, plus the fp32 noise floor of this input (how far
+    the oracle itself moves when its GEMMs accumulate in fp32 like the reference's SGEMM, in three summation orders,
+    instead of in double);
+    bf16 / tf32: perplexity within 0.5 %.  Decoding: the hypotheses of the first sentences, token for token."""
+    from oracle import oracle_lib as ol
+    ol.build()
+    ol.set_num_threads(host_cores())
+    om = ol.OracleModel(cfg, weights)
+    exact = dtype in ("f32", "f32_simt", "f32_3xtf32", "f32_f16x2")
+    if w["kind"] == "decode":
+        n = 2
+        srcs = inp["srcs"][:n]
+        kw = dict(beam=w["beam"], k_best=1, min_ratio=w["min_ratio"], max_ratio=w["max_ratio"], penalty=0.0,
+                  longest_sent=w["longest_sent"])
+        ids, ln, sc = om.beam_decode(srcs, **kw)
+        gi, gl, gs = model.decode(srcs, **kw)
+        same = bool(np.array_equal(ln, gl) and np.array_equal(ids, gi))
+        out = dict(sample=f"first {n} sentences, beam {w['beam']}", hypotheses_identical=same,
+                   max_score_diff=float(np.abs(sc - gs).max()))
+        out["ok"] = same if exact else None
+        return out
+    ns = min(PARITY_SENTENCES, w["B"])
+    Tn = 16 if w["H"] >= 2048 else inp["tin"].shape[0]
+    src = None
+    if inp["src"] is not None:
+        src = np.ascontiguousarray(inp["src"][:, :ns])
+        keep = (src != -1).any(axis=1)  # rows that are padding for all of these sentences
+        src = np.ascontiguousarray(src[keep])
+    tin, tout = np.ascontiguousarray(inp["tin"][:Tn, :ns]), np.ascontiguousarray(inp["tout"][:Tn, :ns])
+    want = om.score_batch(src, tin, tout)
+    got, _ = model.get_error(src, tin, tout)
+    msk = tout != -1
+    out = dict(sample=f"first {ns} sentences x {Tn} target steps of the timed batch, full model")
+    if exact:
+        floor, _ = ol.fp32_noise_floor(lambda: om.score_batch(src, tin, tout)[msk], want[msk])
+        use = msk
+        if cfg["attention"] == 1:
+            # local-p cuts its window at int(p_t): where p_t sits within fp32 rounding of an integer the window may
+            # shift by one position, and feed-input carries that to the end of the sentence; those tokens are set aside
+            clear, margin = ol.localp_clear_tokens(om, src, tin, tout)
+            use = msk & clear
+            out.update(window_margin_min=margin, tokens_after_near_integer_window=int((msk & ~clear).sum()))
+        err = np.abs(got - want)[use] / np.abs(want[use])
+        out.update(tokens=int(use.sum()), max_rel_err=float(err.max()), mean_rel_err=float(err.mean()), tol=1e-5,
+                   fp32_noise_floor=floor, ok=bool(err.max() <= 1e-5 + floor), ok_without_floor=bool(err.max() <= 1e-5))
+    else:
+        n = msk.sum()
+        pg, pw = float(np.exp(-got[msk].sum() / n)), float(np.exp(-want[msk].sum() / n))
+        out.update(ppl=pg, ppl_oracle=pw, ppl_rel_err=abs(pg - pw) / pw, tol=5e-3, ok=bool(abs(pg - pw) / pw <= 5e-3),
+                   max_abs_logp_err=float(np.abs(got - want)[msk].max()))
+    return out
+
+
+def measure(args, w, cfg, dtype, rank, world, steps=None, parity=False):
     """Builds the model in `dtype`, times K steps on the device (value), K steps through the host-buffer entry
     point (e2e) and an instrumented pass for per-kernel durations.  Returns a dict of raw measurements."""
+    import tempfile
     import torch
     import torch.distributed as dist
     from zoph_rnn_b200 import api
 
-    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
+    steps = steps or args.steps
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"], round_bf16=bool(w.get("bf16_weights")))
     dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4, f32_f16x2=5)[dtype]
     model = api.neuralMT_model(cfg, dtype=dtype_id)
     model.load_weights(weights)
-    del weights
     # sentences are sharded by rank (weak scaling: every rank scores/decodes its own minibatch, no collective)
     inp = make_inputs(w, 1234 + rank)
 
@@ -280,14 +353,14 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
     for _ in range(max(args.warmup, 3)):
         step_device()
     barrier()
-    clk_path = os.path.join(ROOT, "gpurun_out", f"clocks_{clocks_tag}_rank{rank}.csv")
-    os.makedirs(os.path.dirname(clk_path), exist_ok=True)
+    clk_dir = tempfile.mkdtemp(prefix="zrnn_bench_")
+    clk_path = os.path.join(clk_dir, f"clocks_{dtype}_rank{rank}.csv")
     proc, f = sample_clocks_start(clk_path)
     api.reset_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         step_device()
     e1.record(stream)
     barrier()
@@ -298,7 +371,7 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
     # durations include any launch gap: they are upper bounds on kernel time, lower bounds on achieved bandwidth.
     api.lib().zrnn_kernel_timing(1)
     api.reset_launch_count()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step_device()
     torch.cuda.synchronize()
     eager_launches = api.launch_count()
@@ -312,11 +385,18 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
         step_host()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step_host()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sample_clocks_stop(proc, f, clk_path, torch.cuda.current_device())
+    try:
+        os.remove(clk_path)
+        os.rmdir(clk_dir)
+    except OSError:
+        pass
+    par = parity_check(w, cfg, weights, model, dtype, inp) if (parity and rank == 0) else None
+    del weights
     if world > 1:
         t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -329,47 +409,73 @@ def measure(args, w, cfg, dtype, rank, world, clocks_tag):
     del model
     torch.cuda.empty_cache()
     return dict(ms=ms, e2e_s=e2e_s, tokens_all=tokens_all, launches=int(launches), ktime=ktime, clocks=clocks,
-                h2d=h2d, d2h=d2h, ncols=ncols)
+                h2d=h2d, d2h=d2h, ncols=ncols, steps=steps, parity=par)
 
 
-def run_c5_sharded(args, w, cfg, rank, world):
-    """Config 5 on N GPUs: ONE minibatch scored by all ranks (strong scaling).  Sentences are sharded for the
-    recurrent stack, the softmax matrix is sharded by vocabulary rows; two NCCL all-gathers per batch (top-layer
-    vectors, then 3 floats per token).  Timed end to end from host id arrays to host log-probs."""
+def run_c5_sharded(args, rank, world, steps):
+    """Config 5 on N GPUs: ONE minibatch scored by all ranks (strong scaling) through zrnn_score_batch_sharded.
+    Sentences are sharded for the recurrent stack, the softmax matrix by vocabulary rows; two NCCL all-gathers per
+    batch (top-layer vectors in operand form, then 3 floats per token), issued by the library behind the C ABI.
+    Timed end to end from host id arrays to host log-probs, max over ranks; the stage split is rank 0's device time."""
     import torch
     import torch.distributed as dist
-    from zoph_rnn_b200 import sharded
-    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"])
-    dtype_id = dict(f32=0, bf16=1, tf32=2, f32_simt=3, f32_3xtf32=4, f32_f16x2=5)[args.dtype]
-    scorer = sharded.VocabShardedScorer(sharded.CudaEngine(cfg, weights, rank, world, dtype=dtype_id), rank, world)
-    del weights
+    from zoph_rnn_b200 import api, sharded
+    w = WORKLOADS["c5"]
+    cfg = make_cfg(w)
+    dtype = "bf16"
+    weights = synth.make_weights(cfg, seed=1234, dist=w["dist"], scale=w["scale"], round_bf16=True)
+    comm = api.Communicator.from_torch_distributed()
+    model = sharded.ShardedModel(cfg, weights, comm, dtype=1)
     inp = make_inputs(w, 1234)  # the same minibatch on every rank
-    for _ in range(max(args.warmup, 3)):
-        scorer.score(None, inp["tin"], inp["tout"])
+    for _ in range(3):
+        model.score(None, inp["tin"], inp["tout"])
     torch.cuda.synchronize()
     dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        scorer.score(None, inp["tin"], inp["tout"])
-    e1.record()
+    stages = {k: 0.0 for k in api.Communicator.STAGES}
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        lp, _ = model.score(None, inp["tin"], inp["tout"])
+        for k, v in comm.last_stage_ms().items():
+            stages[k] += v / steps
     torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    dt = time.perf_counter() - t0
+    t = torch.tensor([dt], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0])
+    dt = float(t[0])
+    out = None
     if rank == 0:
-        val = inp["tokens"] * args.steps / (ms / 1e3)
         T, B = inp["tin"].shape
-        print(json.dumps(dict(metric=metric_name(w), value=val, unit="tokens/s", n_gpus=world, steps=args.steps,
-                              warmup=max(args.warmup, 3), ms_per_step=ms / args.steps, higher_is_better=True,
-                              scaling="strong", vs_baseline=None, dtype=args.dtype, data="synthetic",
-                              config=dict(workload=args.workload + ": " + w["desc"],
-                                          sharding="sentences by rank for the LSTM stack + vocabulary rows of D by rank; "
-                                                   "NCCL all-gather of top-layer vectors and of (max, sum, target) per token",
-                                          arithmetic=ARITH[args.dtype]),
-                              e2e=dict(value=val, unit="tokens/s", h2d_bytes_per_step=2 * T * B * 4,
-                                       d2h_bytes_per_step=T * B * 4))))
+        H, V = cfg["H"], cfg["V_tgt"]
+        Bp = -(-B // world)
+        par = None
+        if not args.no_parity:
+            from oracle import oracle_lib as ol
+            ol.build()
+            ol.set_num_threads(host_cores())
+            ns, Tn = PARITY_SENTENCES, 16
+            tin, tout = np.ascontiguousarray(inp["tin"][:Tn, :ns]), np.ascontiguousarray(inp["tout"][:Tn, :ns])
+            want = ol.OracleModel(cfg, weights).score_batch(None, tin, tout)
+            got = lp[:Tn, :ns]
+            msk = tout != -1
+            n = msk.sum()
+            pg, pw = float(np.exp(-got[msk].sum() / n)), float(np.exp(-want[msk].sum() / n))
+            par = dict(sample=f"first {ns} sentences x {Tn} target steps of the sharded batch against the CPU oracle",
+                       ppl=pg, ppl_oracle=pw, ppl_rel_err=abs(pg - pw) / pw, tol=5e-3, ok=bool(abs(pg - pw) / pw <= 5e-3),
+                       max_abs_logp_err=float(np.abs(got - want)[msk].max()))
+        out = dict(workload="c5: " + w["desc"], metric=metric_name(w), value=inp["tokens"] * steps / dt, unit="tokens/s",
+                   n_gpus=world, steps=steps, warmup=3, ms_per_step=1e3 * dt / steps, scaling="strong", dtype=dtype,
+                   timing="host clock around the host-buffer C-ABI call (ids in, log-probs out), max over ranks",
+                   sharding="sentences by rank for the LSTM stack + vocabulary rows of D by rank; NCCL all-gather of the "
+                            "top-layer vectors (bf16 operand form) and of (max, sum, target) per token, inside the library",
+                   stages_ms_rank0={k: round(v, 4) for k, v in stages.items()},
+                   nvlink_bytes_per_step_per_rank=int((world - 1) * (T * Bp * (-(-H // 64) * 64) * 2 + 3 * 4 * T * Bp * world)),
+                   e2e=dict(value=inp["tokens"] * steps / dt, unit="tokens/s", h2d_bytes_per_step=(T * Bp + T * Bp * world) * 4,
+                            d2h_bytes_per_step=T * Bp * world * 4),
+                   parity=par)
+    del model, weights
+    comm.close()
+    torch.cuda.empty_cache()
+    return out
 
 
 def cell_phases(w, dtype_name):
@@ -420,6 +526,9 @@ def main():
                     help="arithmetic of the GEMM-shaped work (f32 = fp32-accurate: split-operand tensor cores when H >= 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-bf16", action="store_true", help="skip the additional bf16 measurement of an f32 run")
+    ap.add_argument("--no-configs", action="store_true",
+                    help="skip the `configs` block (configurations 1, 3, 4, 5 on one GPU) and the `c5_sharded` block")
+    ap.add_argument("--no-parity", action="store_true", help="skip the comparison with the CPU oracle")
     ap.add_argument("--cell-phases", action="store_true",
                     help="diagnostic: device-side phase times of one LSTM cell launch of the workload's layer shape "
                          "(per-CTA %%globaltimer stamps written by the kernel), printed as one JSON line")
@@ -448,39 +557,40 @@ def main():
     cfg = make_cfg(w)
     if args.workload == "c5" and args.dtype == "f32":
         args.dtype = "bf16"  # config 5 is specified with bf16 weights
-    if args.workload == "c5" and world > 1:
-        run_c5_sharded(args, w, cfg, rank, world)
-        dist.destroy_process_group()
-        return
-    r = measure(args, w, cfg, args.dtype, rank, world, args.dtype)
+    peaks, peak_src = {}, "fallback"
+    pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk_path):
+        peaks, peak_src = json.load(open(pk_path)), "measured"
+    parity = not args.no_parity
+    r = measure(args, w, cfg, args.dtype, rank, world, parity=parity)
     extra = None
     if args.dtype == "f32" and not args.no_bf16 and cfg["H"] % 8 == 0:
-        extra = measure(args, w, cfg, "bf16", rank, world, "bf16")
+        extra = measure(args, w, cfg, "bf16", rank, world, parity=parity)
+    line = None
     if rank == 0:
-        peaks = {}
-        pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        peak_src = "fallback"
-        if os.path.exists(pk_path):
-            peaks = json.load(open(pk_path))
-            peak_src = "measured"
-        roof = roofline(w, cfg, r["ktime"], peaks, peak_src, r["ncols"], args.dtype)
-        line = dict(metric=metric_name(w), value=r["tokens_all"] * args.steps / (r["ms"] / 1e3), unit="tokens/s",
-                    n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=r["ms"] / args.steps,
-                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype=args.dtype, data="synthetic",
-                    config=dict(workload=args.workload + ": " + w["desc"], sharding="sentences by rank, no collective",
-                                arithmetic=ARITH[args.dtype],
-                                l2="weights and embeddings (>1 GB) exceed the 126 MB L2 every step"),
-                    clocks=r["clocks"], gpu_launches=r["launches"],
-                    launch_mode="CUDA graph replay of the scoring pass" if w["kind"] != "decode" else "eager launches",
-                    e2e=dict(value=r["tokens_all"] * args.steps / r["e2e_s"], unit="tokens/s",
-                             h2d_bytes_per_step=r["h2d"], d2h_bytes_per_step=r["d2h"]),
-                    roofline=roof, kernels=r["ktime"])
+        line = summary(args.workload, w, cfg, r, args.dtype, peaks, peak_src, full=True)
+        line.update(n_gpus=world, warmup=max(args.warmup, 3), higher_is_better=True, scaling="weak", vs_baseline=None,
+                    data="synthetic")
+        line["config"].update(sharding="sentences by rank, no collective",
+                              l2="weights and embeddings (>1 GB) exceed the 126 MB L2 every step")
         if extra:
-            line["bf16"] = dict(value=extra["tokens_all"] * args.steps / (extra["ms"] / 1e3), unit="tokens/s",
-                                ms_per_step=extra["ms"] / args.steps, arithmetic=ARITH["bf16"],
-                                e2e=extra["tokens_all"] * args.steps / extra["e2e_s"], kernels=extra["ktime"],
-                                roofline=roofline(w, cfg, extra["ktime"], peaks, peak_src, extra["ncols"], "bf16"),
-                                clocks=extra["clocks"])
+            line["bf16"] = summary(args.workload, w, cfg, extra, "bf16", peaks, peak_src, full=True)
+    # the other benchmark configurations, a few steps each (single GPU: they are parity + throughput records, not
+    # scaling lines)
+    if args.workload == "c2" and world == 1 and not args.no_configs:
+        others = {}
+        for name, dt_name, k in (("c1", "f32", 5), ("c3", "f32", 3), ("c4", "f32", 2), ("c5", "bf16", 2)):
+            wo = WORKLOADS[name]
+            co = make_cfg(wo)
+            ro = measure(args, wo, co, dt_name, rank, world, steps=k, parity=parity)
+            others[name] = summary(name, wo, co, ro, dt_name, peaks, peak_src, full=False)
+        line["configs"] = others
+    # configuration 5 with its softmax sharded by vocabulary rows over the N ranks
+    if world > 1 and args.workload in ("c2", "c5") and not args.no_configs:
+        c5 = run_c5_sharded(args, rank, world, steps=3)
+        if rank == 0:
+            line["c5_sharded"] = c5
+    if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(line))
@@ -488,10 +598,31 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM traffic per launch of the dominant kernels from ncu (dram__bytes_read.sum + dram__bytes_write.sum), captured on
-# the c2s stand-in, whose layer shapes are config 2's (see profiles/*.md); keyed by (kernel class, dtype).
-NCU_TRAFFIC = {("lstm_cell", "f32"): 35.2e6, ("lstm_cell", "f32_f16x2"): 35.2e6, ("lstm_cell", "f32_3xtf32"): 71.6e6,
-               ("lstm_cell", "bf16"): 17.9e6}
+def summary(name, w, cfg, r, dtype, peaks, peak_src, full):
+    """One measured configuration as a JSON object (the headline line when full, else the short form of `configs`)."""
+    k = r["steps"]
+    out = dict(metric=metric_name(w), value=r["tokens_all"] * k / (r["ms"] / 1e3), unit="tokens/s", steps=k,
+               ms_per_step=r["ms"] / k, dtype=dtype,
+               config=dict(workload=name + ": " + w["desc"], arithmetic=ARITH[dtype]),
+               clocks=r["clocks"], gpu_launches=r["launches"],
+               launch_mode="CUDA graph replay of the scoring pass" if w["kind"] != "decode" else "eager launches",
+               e2e=dict(value=r["tokens_all"] * k / r["e2e_s"], unit="tokens/s", h2d_bytes_per_step=r["h2d"],
+                        d2h_bytes_per_step=r["d2h"]),
+               roofline=roofline(w, cfg, r["ktime"], peaks, peak_src, r["ncols"], dtype))
+    if full:
+        out["kernels"] = r["ktime"]
+    else:
+        out["kernel_ms"] = {n: round(v["ms"], 3) for n, v in (r["ktime"] or {}).items()}
+    out["parity"] = r["parity"]
+    return out
+
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the LSTM cell kernel on an 8-matrix
+# layer (no feed-input operand) from an ncu capture, keyed by (kernel class, dtype, H, B): a figure applies only to the
+# shape it was captured on; every other shape reports null.  The capture ran the c2s workload, whose layer shapes are
+# configuration 2's.
+NCU_TRAFFIC = {("lstm_cell", "f32", 1000, 128): 35.2e6, ("lstm_cell", "f32_f16x2", 1000, 128): 35.2e6,
+               ("lstm_cell", "f32_3xtf32", 1000, 128): 71.6e6, ("lstm_cell", "bf16", 1000, 128): 17.9e6}
 
 
 def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
@@ -507,8 +638,7 @@ def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
     n = ktime[top]["launches"]
     avg_s = ktime[top]["ms"] / 1e3 / max(n, 1)
     wbytes = 2 if dtype == "bf16" else 4   # bytes per weight as the reference stores them (fp32) or bf16
-    out = dict(kernel=top, launches=n, avg_launch_us=avg_s * 1e6, peak_source=peak_src,
-               traffic=NCU_TRAFFIC.get((top, dtype)))
+    out = dict(kernel=top, launches=n, avg_launch_us=avg_s * 1e6, peak_source=peak_src, traffic=None)
     sm_flops = 2.0 * cfg["V_tgt"] * H * softmax_cols
     sm_bytes = cfg["V_tgt"] * H * wbytes + (H * softmax_cols + 2 * softmax_cols) * 4
     # the vocabulary GEMM is bound by whichever lower bound is larger: its flops at the tensor peak or its
@@ -528,6 +658,12 @@ def roofline(w, cfg, ktime, peaks, peak_src, softmax_cols, dtype):
         if cfg["feed_input"] and not cfg["lm"]:
             mats = (8.0 * (2 * L - 1) + 12.0) / (2 * L) if w["kind"] != "decode" else (8.0 * (L - 1) + 12.0) / L
         alg = mats * H * H * wbytes + (4 * H + 5.0 * H * B) * 4
+        cap = NCU_TRAFFIC.get((top, dtype, H, B))
+        if cap:  # captured on an 8-matrix launch; the average launch of this workload holds `mats` matrices
+            alg8 = 8.0 * H * H * wbytes + (4 * H + 5.0 * H * B) * 4
+            out["traffic"] = cap * alg / alg8
+            out["traffic_note"] = ("ncu capture of an 8-matrix cell launch of this shape, scaled by the algorithmic "
+                                   "bytes of the workload's average launch")
         out.update(bound="hbm", unit="GB/s", peak=float(peaks.get("hbm_gbs", 6650.0)), achieved=alg / avg_s / 1e9,
                    algorithmic_bytes_per_launch=alg,
                    note=f"avg {mats:.2f} HxH matrices of {wbytes}-byte weights + 5 HxB fp32 activations per launch")

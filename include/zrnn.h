@@ -22,6 +22,8 @@
 #ifndef ZRNN_H
 #define ZRNN_H
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -30,7 +32,7 @@ typedef enum {
   ZRNN_OK = 0,
   ZRNN_E_ARG = 1,     /* bad shape, null pointer, unsupported combination */
   ZRNN_E_CUDA = 2,    /* CUDA runtime error or no device */
-  ZRNN_E_NCCL = 3,    /* reserved for the collective layer */
+  ZRNN_E_NCCL = 3,    /* NCCL could not be loaded, or one of its calls failed (zrnn_last_error() has the text) */
   ZRNN_E_TIMEOUT = 4, /* a bounded device-side wait gave up */
   ZRNN_E_IO = 5,      /* weight file missing, truncated or malformed */
   ZRNN_E_STATE = 6    /* call order violated (e.g. forward before load) */
@@ -193,6 +195,50 @@ int zrnn_softmax_topk(zrnn_softmax* sm, const float* d_h, int N, int k, float* d
 int zrnn_softmax_destroy(zrnn_softmax* sm);
 
 /* ------------------------------------------------------------------------------------------
+ * Collective layer: the output vocabulary sharded over the GPUs of one node.
+ * The reference spreads a model over GPUs layer by layer (-M, src/global_params.h gpu_indicies,
+ * src/model.hpp:80-140) and keeps the whole softmax on the last one (src/softmax.hpp:7-60); at the
+ * sizes where one GPU no longer holds D, or where its V x H read bounds the step, the rows of D are
+ * split here instead: rank r of `world` holds rows [V r / world, V (r + 1) / world)
+ * (zrnn_shard_range).  One process per GPU; the collectives are NCCL's, loaded at first use
+ * (libnccl.so.2), on the caller's stream.  At most 8 ranks.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zrnn_comm zrnn_comm;
+#define ZRNN_COMM_ID_BYTES 128
+/* Rank 0 makes the id and hands it to the other ranks by any host channel (a file, a socket, MPI,
+ * torch.distributed's store); then every rank calls zrnn_comm_create with the same id. */
+int zrnn_comm_unique_id(char* id128);
+/* Collective call: blocks until all `world` ranks have joined.  The calling thread's current device is the
+ * rank's GPU.  world == 1 needs no id (NULL) and no NCCL: its collectives are local copies. */
+int zrnn_comm_create(const char* id128, int rank, int world, zrnn_comm** out);
+int zrnn_comm_rank(const zrnn_comm* c, int* rank, int* world);
+/* d_recv receives world * bytes_per_rank bytes, rank-major. */
+int zrnn_comm_all_gather(zrnn_comm* c, const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream);
+/* Device time of the five stages of this rank's last zrnn_score_batch_sharded call, in milliseconds: [0] id upload +
+ * recurrent stack and attention on the rank's columns, [1] all-gather of the top hidden states (+ operand conversion),
+ * [2] this rank's vocabulary rows against all columns (GEMM with max/sum epilogue, reduce), [3] all-gather of
+ * (max, sum, target logit) + combine, [4] copy of the log-probabilities to the host. */
+int zrnn_comm_last_stage_ms(const zrnn_comm* c, float* ms5);
+int zrnn_comm_destroy(zrnn_comm* c);
+int zrnn_shard_range(int V, int world, int rank, int* lo, int* hi);
+
+/* Sharded decoding, step 1 (a layer created with a vocabulary range): the k best rows of THIS layer's rows per
+ * column, as log-probabilities under the layer's own normaliser, sorted descending; d_idx_out are row numbers
+ * inside the shard (-1 beyond the shard's size); d_lse_out[n] = log of that normaliser; d_logp_eos (optional) is
+ * the <EOF> row's value under it, or -inf when the shard does not hold word 1. */
+int zrnn_softmax_topk_shard(zrnn_softmax* sm, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
+                            float* d_lse_out, float* d_logp_eos, void* stream);
+/* Sharded decoding, step 2: the k best of G shards' lists (d_val / d_idx [G][N][k], d_lse / d_eos [G][N],
+ * d_shard_lo[G] = first word id of every shard) under the global normaliser log sum_g exp(lse_g); word ids are
+ * global, ties go to the lower id, as in zrnn_softmax_topk.  G <= 8. */
+int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, const float* d_eos, const int* d_shard_lo,
+                    int G, int N, int k, float* d_val_out, int* d_idx_out, float* d_eos_out, void* stream);
+/* Both steps with the all-gather between them (k (value, id) pairs and two floats per column and rank): what
+ * zrnn_softmax_topk returns for the whole vocabulary, on every rank.  The layer must hold this rank's range. */
+int zrnn_softmax_topk_sharded(zrnn_softmax* sm, zrnn_comm* c, const float* d_h, int N, int k, float* d_logp_out,
+                              int* d_idx_out, float* d_logp_eos, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Whole model (neuralMT_model, src/model.h / src/model.hpp).
  * ---------------------------------------------------------------------------------------- */
 typedef struct zrnn_model zrnn_model;
@@ -210,6 +256,10 @@ typedef struct {
 
 /* neuralMT_model::initModel / initModel_decoding (src/model.hpp:3-435, 476-698). */
 int zrnn_model_create(const zrnn_model_config* cfg, zrnn_model** out);
+/* The same model with only rows [shard_lo, shard_hi) of the softmax's D and b_d on this GPU (the tensor list and
+ * zrnn_model_set_tensor still take the full matrices; the rows outside the range are dropped at finalize).  Such a
+ * model scores and decodes through the *_sharded calls below, with a zrnn_comm whose rank owns exactly that range. */
+int zrnn_model_create_sharded(const zrnn_model_config* cfg, int shard_lo, int shard_hi, zrnn_model** out);
 /* Tensor list in weight-file order (src/model.hpp:2172-2241). name buffer >= 32 bytes. */
 int zrnn_model_num_tensors(zrnn_model* m);
 int zrnn_model_tensor_info(zrnn_model* m, int i, char* name, int* rows, int* cols);
@@ -299,6 +349,19 @@ int zrnn_beam_decode_ensemble_align(zrnn_model* const* models, int n_models, con
                                     const int* const* src_len, int n_sent, int beam, int k_best, float min_ratio,
                                     float max_ratio, float penalty, int longest_sent, int* out_ids, int* out_len,
                                     float* out_score, int* out_align);
+/* Teacher-forced scoring over the ranks of a communicator.  Every rank passes the SAME host batch and receives the
+ * whole result.  The recurrent stack and the attention run data-parallel over the batch columns (rank r takes
+ * columns [B r / world, B (r + 1) / world)); the top hidden states are all-gathered; every rank scores all columns
+ * against its rows of D; a second all-gather of (max, sum, target logit) per column and the combine follow.
+ * Results equal zrnn_score_batch's of the unsharded model to fp32 rounding of the normaliser. */
+int zrnn_score_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, int S_max, const int* tgt_in,
+                             const int* tgt_out, int T, int B, float* logp_out, double* total_logp);
+/* zrnn_beam_decode_batch over the ranks of a communicator: every rank runs the (replicated) recurrent stack and the
+ * attention on the same hypotheses, the softmax's pre-selection is vocabulary-sharded (zrnn_softmax_topk_sharded),
+ * and every rank returns the same hypotheses. */
+int zrnn_beam_decode_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, const int* src_len, int n_sent,
+                                   int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                                   int longest_sent, int* out_ids, int* out_len, float* out_score);
 int zrnn_model_destroy(zrnn_model* m);
 
 #ifdef __cplusplus

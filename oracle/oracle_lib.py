@@ -153,6 +153,40 @@ class OracleModel:
         return (ids, ln, sc, al) if want_align else (ids, ln, sc)
 
 
+def localp_window_positions(model, src_ids, tgt_in, tgt_out):
+    """The window positions p_t [T,B] (NaN where masked) the oracle's local-p attention computed while scoring the
+    batch.  The window is cut at int(p_t): a test aid for telling a one-position window shift on a near-integer p_t
+    from a real disagreement."""
+    T, B = np.asarray(tgt_in).shape
+    lib().orc_pt_log_start.argtypes = [ctypes.c_int]
+    lib().orc_pt_log_read.argtypes = [c_float_p, ctypes.c_int]
+    lib().orc_pt_log_read.restype = ctypes.c_int
+    lib().orc_pt_log_start(1)
+    try:
+        model.score_batch(src_ids, tgt_in, tgt_out)
+        out = np.full(T * B, np.nan, dtype=np.float32)
+        n = lib().orc_pt_log_read(_fp(out), T * B)
+    finally:
+        lib().orc_pt_log_start(0)
+    assert n == T * B, f"expected {T * B} window positions, the oracle logged {n}"
+    return out.reshape(T, B)
+
+
+def localp_clear_tokens(model, src_ids, tgt_in, tgt_out, rtol=1e-5):
+    """Boolean [T,B]: True for the tokens whose local-p windows, at this and every earlier step of the sentence, were cut
+    at a p_t farther than rtol * p_t from an integer.  From the first near-integer step on, a correct fp32
+    implementation may attend a window shifted by one position, and (with feed-input) carries the difference to the
+    end of the sentence.  Also returns the smallest distance seen."""
+    pt = localp_window_positions(model, src_ids, tgt_in, tgt_out)
+    with np.errstate(invalid="ignore"):
+        fr = pt - np.floor(pt)
+        margin = np.minimum(fr, 1.0 - fr)
+        near = margin < rtol * np.maximum(pt, 1.0)
+    near = np.where(np.isnan(pt), False, near)
+    clear = np.cumsum(near, axis=0) == 0
+    return clear, float(np.nanmin(margin))
+
+
 def beam_decode_margins(model, sources, beam, min_ratio=0.5, max_ratio=1.5, penalty=0.0, longest_sent=100):
     """Per sentence the smallest score difference that decided anything in the oracle's beam search: at every step
     between the last candidate that entered the beam and the best one left behind, and at the end between the best and
@@ -250,7 +284,28 @@ def softmax_dist(V, H, N, Dm, b_d, h):
 
 
 def set_acc_float(on):
-    lib().orc_set_acc_float(1 if on else 0)
+    """GEMM accumulation of the oracle: False / 0 = double (the default), True / 1 = float with k ascending (the
+    reference's SGEMM arithmetic in its plainest order), 2 = float with k descending, 3 = float in blocks of 32."""
+    lib().orc_set_acc_float(int(on))
+
+
+def fp32_noise_floor(score, want=None):
+    """Largest relative deviation of `score()` (a callable returning log-probs) over the float summation orders from
+    its double-accumulating result: how far a correct fp32 implementation may sit from the oracle on this input.
+    Returns (floor, want)."""
+    set_acc_float(0)
+    if want is None:
+        want = score()
+    floor = 0.0
+    try:
+        for mode in (1, 2, 3):
+            set_acc_float(mode)
+            got = score()
+            nz = np.abs(want) > 0
+            floor = max(floor, float((np.abs(got - want)[nz] / np.abs(want)[nz]).max()))
+    finally:
+        set_acc_float(0)
+    return floor, want
 
 
 def num_threads():

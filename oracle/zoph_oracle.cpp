@@ -23,6 +23,7 @@
 #include <cstdio>
 #include <cstring>
 #include <queue>
+#include <type_traits>
 #include <vector>
 #ifdef _OPENMP
 #include <omp.h>
@@ -37,6 +38,15 @@ namespace {
 // oracle is timed as the CPU baseline).
 // ---------------------------------------------------------------------------------
 bool g_acc_float = false;
+// Summation order of the float accumulation (cublasSgemm leaves it unspecified): 0 = k ascending, 1 = k descending,
+// 2 = blocks of 32 k summed separately and then added (how a tiled / split-K kernel sums).  The spread of the results
+// over these orders is the fp32 noise floor of an input.
+int g_acc_order = 0;
+// Test aid: when on, every local-p attention call appends its columns' window positions p_t (NaN for a masked column).
+// The window is cut at (int)p_t, a discontinuity: two correct fp32 implementations may land on different sides of an
+// integer when p_t is within rounding of it, so parity checks need to know how close each decision was.
+bool g_pt_log_on = false;
+std::vector<float> g_pt_log;
 
 template <class Acc>
 void gemm_nn_t(int M, int N, int K, const float* A, int lda, const float* B, int ldb, float* C, int ldc) {
@@ -50,16 +60,25 @@ void gemm_nn_t(int M, int N, int K, const float* A, int lda, const float* B, int
       Acc acc[NB][MB];
       for (int j = 0; j < nn; ++j)
         for (int i = 0; i < mm; ++i) acc[j][i] = 0;
-      for (int k = 0; k < K; ++k) {
+      const int order = std::is_same<Acc, float>::value ? g_acc_order : 0;
+      Acc tot[NB][MB];
+      if (order == 2)
+        for (int j = 0; j < nn; ++j)
+          for (int i = 0; i < mm; ++i) tot[j][i] = 0;
+      for (int kk = 0; kk < K; ++kk) {
+        const int k = order == 1 ? K - 1 - kk : kk;
         const float* a = A + (size_t)k * lda + m0;
         for (int j = 0; j < nn; ++j) {
           const Acc b = B[(size_t)(n0 + j) * ldb + k];
           Acc* ac = acc[j];
           for (int i = 0; i < mm; ++i) ac[i] += (Acc)a[i] * b;
         }
+        if (order == 2 && ((kk & 31) == 31 || kk == K - 1))
+          for (int j = 0; j < nn; ++j)
+            for (int i = 0; i < mm; ++i) { tot[j][i] += acc[j][i]; acc[j][i] = 0; }
       }
       for (int j = 0; j < nn; ++j)
-        for (int i = 0; i < mm; ++i) C[(size_t)(n0 + j) * ldc + m0 + i] = (float)acc[j][i];
+        for (int i = 0; i < mm; ++i) C[(size_t)(n0 + j) * ldc + m0 + i] = (float)(order == 2 ? tot[j][i] : acc[j][i]);
     }
   }
 }
@@ -79,7 +98,17 @@ void gemm_tn(int M, int N, int K, const float* A, int lda, const float* B, int l
       const float* b = B + (size_t)n * ldb;
       if (g_acc_float) {
         float s = 0;
-        for (int k = 0; k < K; ++k) s += a[k] * b[k];
+        if (g_acc_order == 1) {
+          for (int k = K - 1; k >= 0; --k) s += a[k] * b[k];
+        } else if (g_acc_order == 2) {
+          float blk = 0;
+          for (int k = 0; k < K; ++k) {
+            blk += a[k] * b[k];
+            if ((k & 31) == 31 || k == K - 1) { s += blk; blk = 0; }
+          }
+        } else {
+          for (int k = 0; k < K; ++k) s += a[k] * b[k];
+        }
         C[(size_t)n * ldc + m] = s;
       } else {
         double s = 0;
@@ -237,6 +266,7 @@ void attention(int type, int H, int B, int D, const AttW& w, const float* h_t, c
       sig[b] = (float)(1.0 / (1.0 + std::exp(-1.0 * (double)sig[b])));  // sigmoid_kernel ck:1581-1587
       p_t[b] = len[b] * sig[b];                                           // alignment_pos_kernel ck:1596-1603
       const int ip = (int)p_t[b];                                         // lower_upper_kernel ck:1606-1613
+      if (g_pt_log_on) g_pt_log.push_back(mask[b] == 1 ? p_t[b] : NAN);
       const int lo = (0 > ip - D) ? 0 : (ip - D);
       const int hi = ((len[b] - 1) < ip + D) ? (len[b] - 1) : (ip + D);
       int cur = lo;  // create_indicies_kernel ck:1649-1673
@@ -722,7 +752,15 @@ void beam_decode_one(const std::vector<const Model*>& models, const std::vector<
 // ---------------------------------------------------------------------------------
 extern "C" {
 
-void orc_set_acc_float(int on) { g_acc_float = on != 0; }
+// on: 0 = double accumulation, 1 / 2 / 3 = float accumulation with k ascending / descending / in blocks of 32
+void orc_set_acc_float(int on) { g_acc_float = on != 0; g_acc_order = on > 1 ? on - 1 : 0; }
+// window-position log of the local-p attention: start (clears), then read up to cap values; returns the count logged
+void orc_pt_log_start(int on) { g_pt_log_on = on != 0; g_pt_log.clear(); }
+int orc_pt_log_read(float* out, int cap) {
+  const int n = (int)g_pt_log.size();
+  for (int i = 0; i < n && i < cap; ++i) out[i] = g_pt_log[i];
+  return n;
+}
 // n <= 0: leave the OpenMP default (OMP_NUM_THREADS or the core count)
 void orc_set_num_threads(int n) {
 #ifdef _OPENMP

@@ -91,6 +91,32 @@ def test_config3_full_size_logprobs(api, oracle):
     assert abs(ppl(lp, tout) - ppl(want, tout)) / ppl(want, tout) < 5e-3
 
 
+def test_config3_near_integer_window_position(api, oracle):
+    """The first 8 sentences of the benchmark's own configuration-3 batch.  At step 30 of sentence 0 the oracle's
+    window position is p_t = 47.00012: 32 fp32 ulps above the integer at which (int)p_t cuts the window, closer than
+    the 1e-5 relative tolerance the path is held to.  An implementation that sums its GEMMs in another order may land
+    below 47 and attend positions 36..56 instead of 37..57; feed-input carries the difference to the end of that
+    sentence.  Every token that is not downstream of such a step must still agree to 1e-5 + the noise floor, and the
+    tokens downstream of it stay close (the window moved by one position, nothing else)."""
+    cfg = synth.make_cfg(2, 1000, 40000, 40000, attention=1, feed_input=1, D=10)
+    w = synth.make_weights(cfg, seed=1234, scale=0.1)
+    src, tin, tout = synth.make_s2s_batch(40000, 40000, 64, 10, 80, 60, 60, seed=1234, zipf_s=1.1)
+    src, tin, tout = src[:, :8], np.ascontiguousarray(tin[:, :8]), np.ascontiguousarray(tout[:, :8])
+    src = np.ascontiguousarray(src[(src != -1).any(axis=1)])
+    om = oracle.OracleModel(cfg, w)
+    msk = tout != -1
+    floor, want_m = oracle.fp32_noise_floor(lambda: om.score_batch(src, tin, tout)[msk])
+    want = om.score_batch(src, tin, tout)
+    clear, margin = oracle.localp_clear_tokens(om, src, tin, tout)
+    assert margin < 2e-4 and not clear[30, 0] and clear[29, 0] and clear[:, 1:].all()
+    assert 1e-6 < floor < 3e-5
+    for dtype in (F32_SIMT, F32_F16X2, F32_3XTF32):
+        lp, _ = build_model(api, cfg, w, dtype).get_error(src, tin, tout)
+        err = np.abs(lp - want) / np.abs(np.where(want == 0, 1, want))
+        assert err[msk & clear].max() <= helpers.LOGP_RTOL + floor, f"dtype {dtype}: {err[msk & clear].max():.3e}"
+        assert err[msk & ~clear].max() < 1e-2, f"dtype {dtype}: downstream of the shifted window {err[msk & ~clear].max():.3e}"
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # configuration 4: beam 12 decode, 2 x 1000, V = 50k, global attention
 # ---------------------------------------------------------------------------------------------------------------

@@ -92,3 +92,66 @@ def test_vocab_sharded_scoring_matches_single_process(tmp_path, world):
     for r in range(world):
         got = np.load(tmp_path / f"lp{r}.npy")
         np.testing.assert_allclose(got, want, rtol=2e-5, atol=2e-5)
+
+
+def _shard_topk(z, lo, k):
+    """What zrnn_softmax_topk_shard reports for the rows z [N, rows] of one shard (NumPy)."""
+    N, rows = z.shape
+    m = z.max(axis=1)
+    lse = m + np.log(np.exp(z - m[:, None]).sum(axis=1))
+    order = np.argsort(-z, axis=1, kind="stable")[:, :k]          # stable: ties to the lower row
+    val = np.take_along_axis(z, order, axis=1) - lse[:, None]
+    idx = order.astype(np.int32)
+    if rows < k:
+        val = np.concatenate([val, np.full((N, k - rows), -np.inf)], axis=1)
+        idx = np.concatenate([idx, np.full((N, k - rows), -1, np.int32)], axis=1)
+    eos = z[:, 1 - lo] - lse if lo <= 1 < lo + rows else np.full(N, -np.inf)
+    return val.astype(np.float32), idx, lse.astype(np.float32), eos.astype(np.float32)
+
+
+def _topk_worker(rank, world, port, V, H, N, k, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(3)
+        D = rng.standard_normal((V, H))
+        b = rng.standard_normal(V) * 0.1
+        h = rng.standard_normal((N, H))
+        bounds = sharded.shard_bounds(V, world)
+        lo, hi = bounds[rank]
+        val, idx, lse, eos = _shard_topk(h @ D[lo:hi].T + b[lo:hi], lo, k)
+        # the library's wire format: one buffer of [N*k val | N*k idx | N lse | N eos] 4-byte words per rank
+        mine = torch.as_tensor(np.concatenate([val.reshape(-1).view(np.int32), idx.reshape(-1), lse.view(np.int32),
+                                               eos.view(np.int32)]))
+        got = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(got, mine)
+        words = np.stack([g.numpy() for g in got])
+        vals = words[:, :N * k].view(np.float32).reshape(world, N, k)
+        idxs = words[:, N * k:2 * N * k].reshape(world, N, k)
+        lses = words[:, 2 * N * k:2 * N * k + N].view(np.float32)
+        eoss = words[:, 2 * N * k + N:].view(np.float32)
+        v, i, e = sharded.merge_topk_host(vals, idxs, lses, eoss, [a for a, _ in bounds], k)
+        np.savez(os.path.join(out_dir, f"topk{rank}.npz"), v=v, i=i, e=e)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,V,k", [(2, 301, 13), (3, 40, 16)])
+def test_sharded_topk_merge_matches_the_whole_vocabulary(tmp_path, world, V, k):
+    """Per-shard top-k + all-gather + merge over gloo ranks equals the top-k of the whole softmax; with V = 40 over 3
+    ranks every shard holds fewer rows than k."""
+    H, N = 16, 9
+    mp.spawn(_topk_worker, args=(world, _free_port(), V, H, N, k, str(tmp_path)), nprocs=world, join=True)
+    rng = np.random.default_rng(3)
+    D = rng.standard_normal((V, H))
+    b = rng.standard_normal(V) * 0.1
+    h = rng.standard_normal((N, H))
+    z = h @ D.T + b
+    logp = z - (z.max(axis=1, keepdims=True) + np.log(np.exp(z - z.max(axis=1, keepdims=True)).sum(axis=1, keepdims=True)))
+    order = np.argsort(-logp, axis=1, kind="stable")[:, :k]
+    for r in range(world):
+        got = np.load(tmp_path / f"topk{r}.npz")
+        np.testing.assert_array_equal(got["i"], order)
+        np.testing.assert_allclose(got["v"], np.take_along_axis(logp, order, axis=1), rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(got["e"], logp[:, 1], rtol=1e-5, atol=1e-5)

@@ -80,7 +80,22 @@ SIGNATURES = {
     "zrnn_softmax_topk": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, c_void_p, c_void_p, c_void_p,
                                          c_void_p]),
     "zrnn_softmax_destroy": (ctypes.c_int, [c_void_p]),
+    "zrnn_comm_unique_id": (ctypes.c_int, [ctypes.c_char_p]),
+    "zrnn_comm_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_void_p)]),
+    "zrnn_comm_rank": (ctypes.c_int, [c_void_p, c_int_p, c_int_p]),
+    "zrnn_comm_all_gather": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
+    "zrnn_comm_last_stage_ms": (ctypes.c_int, [c_void_p, c_float_p]),
+    "zrnn_comm_destroy": (ctypes.c_int, [c_void_p]),
+    "zrnn_shard_range": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, c_int_p, c_int_p]),
+    "zrnn_softmax_topk_shard": (ctypes.c_int, [c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_void_p]),
+    "zrnn_topk_merge": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zrnn_softmax_topk_sharded": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int, c_void_p,
+                                                 c_void_p, c_void_p, c_void_p]),
     "zrnn_model_create": (ctypes.c_int, [ctypes.POINTER(ModelConfig), ctypes.POINTER(c_void_p)]),
+    "zrnn_model_create_sharded": (ctypes.c_int, [ctypes.POINTER(ModelConfig), ctypes.c_int, ctypes.c_int,
+                                                 ctypes.POINTER(c_void_p)]),
     "zrnn_model_num_tensors": (ctypes.c_int, [c_void_p]),
     "zrnn_model_tensor_info": (ctypes.c_int, [c_void_p, ctypes.c_int, ctypes.c_char_p, c_int_p, c_int_p]),
     "zrnn_model_set_tensor": (ctypes.c_int, [c_void_p, ctypes.c_int, c_float_p]),
@@ -122,6 +137,11 @@ SIGNATURES = {
                                                        ctypes.POINTER(c_void_p), ctypes.c_int, ctypes.c_int,
                                                        ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                                                        ctypes.c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "zrnn_score_batch_sharded": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_int, c_void_p, c_void_p,
+                                                ctypes.c_int, ctypes.c_int, c_void_p, ctypes.POINTER(ctypes.c_double)]),
+    "zrnn_beam_decode_batch_sharded": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_int, ctypes.c_int,
+                                                      ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                                      ctypes.c_int, c_void_p, c_void_p, c_void_p]),
     "zrnn_model_destroy": (ctypes.c_int, [c_void_p]),
 }
 

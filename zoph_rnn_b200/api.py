@@ -215,6 +215,40 @@ class softmax_layer:
         check(lib().zrnn_softmax_topk(self._h, _ptr(h), N, k, _ptr(val), _ptr(idx), _ptr(eos), _stream()))
         return val.view(N, k), idx.view(N, k), eos
 
+    def topk_shard(self, h, k):
+        """This layer's rows only: (logp [N,k] under the layer's own normaliser, local row ids [N,k], lse [N],
+        <EOF> value [N] or -inf)."""
+        N = h.numel() // self.H
+        val = torch.empty(N * k, dtype=torch.float32, device="cuda")
+        idx = torch.empty(N * k, dtype=torch.int32, device="cuda")
+        lse = torch.empty(N, dtype=torch.float32, device="cuda")
+        eos = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_softmax_topk_shard(self._h, _ptr(h), N, k, _ptr(val), _ptr(idx), _ptr(lse), _ptr(eos), _stream()))
+        return val.view(N, k), idx.view(N, k), lse, eos
+
+    @staticmethod
+    def merge_topk(val, idx, lse, eos, shard_lo):
+        """val / idx [G,N,k], lse / eos [G,N] CUDA tensors and the shards' first word ids -> what topk() of the whole
+        vocabulary returns."""
+        G, N, k = val.shape
+        lo = torch.as_tensor(np.asarray(shard_lo, dtype=np.int32), device="cuda")
+        oval = torch.empty(N * k, dtype=torch.float32, device="cuda")
+        oidx = torch.empty(N * k, dtype=torch.int32, device="cuda")
+        oeos = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_topk_merge(_ptr(val.contiguous()), _ptr(idx.contiguous()), _ptr(lse.contiguous()),
+                                    _ptr(eos.contiguous()), _ptr(lo), G, N, k, _ptr(oval), _ptr(oidx), _ptr(oeos),
+                                    _stream()))
+        return oval.view(N, k), oidx.view(N, k), oeos
+
+    def topk_sharded(self, comm, h, k):
+        """topk() of the whole vocabulary over the ranks of `comm` (a Communicator); this layer holds the rank's rows."""
+        N = h.numel() // self.H
+        val = torch.empty(N * k, dtype=torch.float32, device="cuda")
+        idx = torch.empty(N * k, dtype=torch.int32, device="cuda")
+        eos = torch.empty(N, dtype=torch.float32, device="cuda")
+        check(lib().zrnn_softmax_topk_sharded(self._h, comm._h, _ptr(h), N, k, _ptr(val), _ptr(idx), _ptr(eos), _stream()))
+        return val.view(N, k), idx.view(N, k), eos
+
     def __del__(self):
         try:
             if getattr(self, "_h", None) and self._owned:
@@ -224,12 +258,70 @@ class softmax_layer:
             pass
 
 
+def shard_range(V, world, rank):
+    """Rows of the output vocabulary that rank `rank` of `world` holds."""
+    lo, hi = ctypes.c_int(), ctypes.c_int()
+    check(lib().zrnn_shard_range(V, world, rank, ctypes.byref(lo), ctypes.byref(hi)))
+    return lo.value, hi.value
+
+
+class Communicator:
+    """The library's collective layer (NCCL behind the C ABI).  `Communicator.unique_id()` on rank 0, the 128 bytes
+    to every rank by any host channel, then `Communicator(id, rank, world)` on every rank; world == 1 needs no id."""
+
+    def __init__(self, unique_id, rank, world):
+        self._h = ctypes.c_void_p()
+        self.rank, self.world = rank, world
+        check(lib().zrnn_comm_create(unique_id, rank, world, ctypes.byref(self._h)))
+
+    @staticmethod
+    def unique_id():
+        buf = ctypes.create_string_buffer(128)
+        check(lib().zrnn_comm_unique_id(buf))
+        return buf.raw
+
+    @classmethod
+    def from_torch_distributed(cls, group=None):
+        """One communicator per rank of an initialised torch.distributed group (the id travels through it)."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [cls.unique_id() if rank == 0 and world > 1 else None]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0, group=group)
+        return cls(box[0], rank, world)
+
+    def all_gather(self, send, recv):
+        check(lib().zrnn_comm_all_gather(self._h, _ptr(send), _ptr(recv), send.numel() * send.element_size(), _stream()))
+        return recv
+
+    STAGES = ("stack", "gather_states", "vocab_rows", "gather_partials_combine", "d2h")
+
+    def last_stage_ms(self):
+        """Device time of the stages of this rank's last sharded scoring call."""
+        ms = (ctypes.c_float * 5)()
+        check(lib().zrnn_comm_last_stage_ms(self._h, ms))
+        return dict(zip(self.STAGES, [float(x) for x in ms]))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().zrnn_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except TypeError:
+            pass
+
+
 class neuralMT_model:
     """src/model.h: the whole model.  cfg is a dict with keys num_layers, H, V_src, V_tgt, lm, attention,
     feed_input, D (zoph_rnn_b200.synth.make_cfg builds one)."""
 
-    def __init__(self, cfg=None, dtype=F32, _handle=None):
+    def __init__(self, cfg=None, dtype=F32, _handle=None, shard=None):
+        """shard = (lo, hi): keep only those rows of the softmax on this GPU (see shard_range, Communicator)."""
         self._h = ctypes.c_void_p()
+        self.shard = shard
         if _handle is not None:
             self._h = _handle
             c = ModelConfig()
@@ -238,7 +330,10 @@ class neuralMT_model:
         else:
             c = ModelConfig(cfg["num_layers"], cfg["H"], cfg["V_src"], cfg["V_tgt"], cfg["lm"], cfg["attention"],
                             cfg["feed_input"], cfg["D"], dtype)
-            check(lib().zrnn_model_create(ctypes.byref(c), ctypes.byref(self._h)))
+            if shard is None:
+                check(lib().zrnn_model_create(ctypes.byref(c), ctypes.byref(self._h)))
+            else:
+                check(lib().zrnn_model_create_sharded(ctypes.byref(c), shard[0], shard[1], ctypes.byref(self._h)))
             self.cfg = dict(cfg, dtype=dtype)
 
     @classmethod
@@ -282,6 +377,39 @@ class neuralMT_model:
         tot = ctypes.c_double()
         check(lib().zrnn_score_batch(self._h, ps, S, pi, po, T, B, ctypes.c_void_p(out.ctypes.data), ctypes.byref(tot)))
         return out, tot.value
+
+    def get_error_sharded(self, comm, src_ids, tgt_in, tgt_out):
+        """get_error over the ranks of `comm` for a model created with shard=...; every rank passes the same batch
+        and receives the whole (logp [T,B], total)."""
+        ks = None if src_ids is None else np.ascontiguousarray(src_ids, dtype=np.int32)
+        ki = np.ascontiguousarray(tgt_in, dtype=np.int32)
+        ko = np.ascontiguousarray(tgt_out, dtype=np.int32)
+        T, B = ki.shape
+        S = ks.shape[0] if ks is not None else 0
+        out = np.empty((T, B), dtype=np.float32)
+        tot = ctypes.c_double()
+        check(lib().zrnn_score_batch_sharded(self._h, comm._h, None if ks is None else ctypes.c_void_p(ks.ctypes.data), S,
+                                             ctypes.c_void_p(ki.ctypes.data), ctypes.c_void_p(ko.ctypes.data), T, B,
+                                             ctypes.c_void_p(out.ctypes.data), ctypes.byref(tot)))
+        return out, tot.value
+
+    def decode_sharded(self, comm, sources, beam=12, k_best=1, min_ratio=0.5, max_ratio=1.5, penalty=0.0,
+                       longest_sent=100):
+        """decode() with the softmax's pre-selection sharded over the ranks of `comm`; every rank gets the result."""
+        n = len(sources)
+        Lmax = longest_sent + 4
+        ids = np.empty((n, k_best, Lmax), dtype=np.int32)
+        ln = np.empty((n, k_best), dtype=np.int32)
+        sc = np.empty((n, k_best), dtype=np.float32)
+        if n == 0:
+            return ids, ln, sc
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(s, dtype=np.int32) for s in sources]), dtype=np.int32)
+        lens = np.ascontiguousarray([len(s) for s in sources], dtype=np.int32)
+        check(lib().zrnn_beam_decode_batch_sharded(self._h, comm._h, ctypes.c_void_p(flat.ctypes.data),
+                                                   ctypes.c_void_p(lens.ctypes.data), n, beam, k_best, min_ratio,
+                                                   max_ratio, penalty, longest_sent, ctypes.c_void_p(ids.ctypes.data),
+                                                   ctypes.c_void_p(ln.ctypes.data), ctypes.c_void_p(sc.ctypes.data)))
+        return ids, ln, sc
 
     def get_error_device(self, d_src, S, d_tin, d_tout, T, B, d_logp):
         """Device-resident variant: int32 CUDA tensors in, float32 CUDA tensor out, asynchronous."""

@@ -471,8 +471,9 @@ cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, c
 // exp in float, accumulation and the final log in double.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, const float* __restrict__ ps,
-                                                  int n_parts, int N, int n, bool active, float* s_m /*[8][32]*/,
+                                                  int n_parts, size_t N, int n, bool active, float* s_m /*[8][32]*/,
                                                   double* s_s /*[8][32]*/, float* mx_out, double* sum_out) {
+  // N: distance (in floats) between two parts' rows
   const int cx = threadIdx.x, py = threadIdx.y;
   float mx = -INFINITY;
   if (active)
@@ -499,7 +500,8 @@ __device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, 
 }
 __global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
                                                            const float* __restrict__ tgt, int n_parts, int n_tgt, int N,
-                                                           const int* __restrict__ mask, float* __restrict__ logp) {
+                                                           size_t part_stride, const int* __restrict__ mask,
+                                                           float* __restrict__ logp) {
   __shared__ float s_m[8 * 32];
   __shared__ double s_s[8 * 32];
   const int n = blockIdx.x * 32 + threadIdx.x;
@@ -507,11 +509,11 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restric
   const bool active = in && !(mask && mask[n] != 1);
   float mx;
   double sum;
-  lse_column_reduce(pm, ps, n_parts, N, n, active, s_m, s_s, &mx, &sum);
+  lse_column_reduce(pm, ps, n_parts, part_stride, n, active, s_m, s_s, &mx, &sum);
   if (threadIdx.y != 0 || !in) return;
   if (!active) { logp[n] = 0.f; return; }
   double tg = 0.0;
-  for (int i = 0; i < n_tgt; ++i) tg += (double)tgt[(size_t)i * N + n];
+  for (int i = 0; i < n_tgt; ++i) tg += (double)tgt[(size_t)i * part_stride + n];
   logp[n] = (float)((tg - (double)mx) - log(sum));
 }
 __global__ void __launch_bounds__(256) lse_reduce_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
@@ -536,16 +538,17 @@ cudaError_t launch_lse_reduce(const float* pm, const float* ps, int n_parts, int
   return cudaGetLastError();
 }
 cudaError_t launch_lse_combine_shards(const float* pm, const float* ps, const float* tgt, int G, int N, const int* mask,
-                                      float* logp, cudaStream_t st) {
+                                      float* logp, cudaStream_t st, size_t shard_stride) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, G, G, N, mask, logp);
+  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, G, G, N, shard_stride ? shard_stride : (size_t)N, mask,
+                                                            logp);
   count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tgt, int n_parts, int N, const int* mask,
                                float* logp, cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, n_parts, 1, N, mask, logp);
+  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, n_parts, 1, N, (size_t)N, mask, logp);
   count_launch();
   return cudaGetLastError();
 }
@@ -569,7 +572,8 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
                                                          const float* __restrict__ part_max,
                                                          const float* __restrict__ part_sum, int n_parts,
                                                          int part_width, float* __restrict__ val_out,
-                                                         int* __restrict__ idx_out, float* __restrict__ logp_eos) {
+                                                         int* __restrict__ idx_out, float* __restrict__ logp_eos,
+                                                         int eos_row, float* __restrict__ lse_out) {
   __shared__ int sel[ZR_TOPK_TILES];
   __shared__ int s_nsel;
   __shared__ float tmax[256];
@@ -583,7 +587,8 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
   float m = -INFINITY, s = 0.f;
   const bool sum_in_pass2 = part_max && !part_sum;  // only tile maxima are known: sum exp(v - M) during the scan
   // the value the <EOF> probability needs, requested early by the thread that will use it
-  const float z_eos = (logp_eos && tid == 32 && V > 1) ? zc[1] : 0.f;
+  const bool has_eos = eos_row >= 0 && eos_row < V;  // the <EOF> row lies among these rows (false on other shards)
+  const float z_eos = (logp_eos && tid == 32 && has_eos) ? zc[eos_row] : 0.f;
   float pmv[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // this thread's tile maxima (n_parts <= 1024)
   if (part_max && n_parts <= ZR_TOPK_TILES) {
     float psv[4] = {0.f, 0.f, 0.f, 0.f};
@@ -634,7 +639,8 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
     if (lane == 0) {
       s_M = M;
       s_logS = (float)log(S);
-      if (logp_eos) logp_eos[col] = (V > 1) ? (z_eos - M) - s_logS : -INFINITY;
+      if (logp_eos) logp_eos[col] = has_eos ? (z_eos - M) - s_logS : -INFINITY;
+      if (lse_out) lse_out[col] = M + s_logS;
     }
   }
   // the k-th largest of the 256 thread maxima (duplicates count): k rounds of a warp-wide argmax over 8 values per
@@ -777,7 +783,8 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
       double S = 0.0;
       for (int i = 0; i < 8; ++i) S += (double)red_s[i];
       s_logS = (float)log(S);
-      if (logp_eos) logp_eos[col] = (V > 1) ? (zc[1] - s_M) - s_logS : -INFINITY;
+      if (logp_eos) logp_eos[col] = has_eos ? (zc[eos_row] - s_M) - s_logS : -INFINITY;
+      if (lse_out) lse_out[col] = s_M + s_logS;
     }
     __syncthreads();
   }
@@ -832,11 +839,94 @@ __global__ void __launch_bounds__(256) topk_logp_kernel(const float* __restrict_
 }
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
                              cudaStream_t st, const float* part_max, const float* part_sum, int n_parts,
-                             int part_width) {
+                             int part_width, int eos_row, float* lse_out) {
   if (N <= 0) return cudaSuccess;
   if (k < 1 || k > ZR_TOPK_MAX) return cudaErrorInvalidValue;
   topk_logp_kernel<<<N, 256, 0, st>>>(logits, V, N, k, part_max, part_sum, n_parts, part_width, val_out, idx_out,
-                                      logp_eos);
+                                      logp_eos, eos_row, lse_out);
+  count_launch();
+  return cudaGetLastError();
+}
+
+// Merge of G vocabulary shards' candidates.  Shard g reports, per column, its k best rows as log-probabilities under
+// its OWN normaliser (val, sorted), their row numbers inside the shard (idx), the log of its normaliser (lse) and the
+// <EOF> log-probability under that normaliser (-inf where the shard does not hold the row).  The global normaliser is
+// log sum_g exp(lse_g); a candidate's global log-probability is val + lse_g - that.  One warp per column picks the
+// k largest of the G * k candidates (ties: lower word id), sorted.
+__global__ void __launch_bounds__(128) topk_merge_kernel(const float* __restrict__ val, const int* __restrict__ idx,
+                                                          const float* __restrict__ lse, const float* __restrict__ eos,
+                                                          const int* __restrict__ shard_lo, int G, int N, int k,
+                                                          size_t cand_stride, size_t col_stride,
+                                                          float* __restrict__ val_out, int* __restrict__ idx_out,
+                                                          float* __restrict__ eos_out) {
+  // cand_stride: words between two shards' val (idx) blocks; col_stride: words between two shards' lse (eos) blocks
+  const int col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (col >= N) return;
+  float M = -INFINITY;
+  for (int g = 0; g < G; ++g) M = fmaxf(M, lse[g * col_stride + col]);
+  double S = 0.0;
+  for (int g = 0; g < G; ++g) S += exp((double)lse[g * col_stride + col] - (double)M);
+  const float LSE = M + (float)log(S);
+  if (eos_out && lane == 0) {
+    float e = -INFINITY;
+    for (int g = 0; g < G; ++g) {
+      const float eg = eos[g * col_stride + col];
+      if (eg != -INFINITY) e = eg + lse[g * col_stride + col] - LSE;
+    }
+    eos_out[col] = e;
+  }
+  // candidate c = g * k + r lives in lane c % 32, register c / 32 (G * k <= 8 * 16 = 128)
+  float cv[4];
+  int ci[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int c = lane + 32 * q;
+    cv[q] = -INFINITY;
+    ci[q] = 0x7fffffff;
+    if (c < G * k) {
+      const int g = c / k, r = c - g * k;
+      const size_t at = g * cand_stride + (size_t)col * k + r;
+      const int id = idx[at];
+      if (id >= 0) {
+        cv[q] = val[at] + lse[g * col_stride + col] - LSE;
+        ci[q] = id + shard_lo[g];
+      }
+    }
+  }
+  for (int r = 0; r < k; ++r) {
+    float bv = cv[0];
+    int bi = ci[0], bq = 0;
+#pragma unroll
+    for (int q = 1; q < 4; ++q)
+      if (cv[q] > bv || (cv[q] == bv && ci[q] < bi)) { bv = cv[q]; bi = ci[q]; bq = q; }
+    float wv = bv;
+    int wi = bi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+      if (ov > wv || (ov == wv && oi < wi)) { wv = ov; wi = oi; }
+    }
+    if (lane == 0) {
+      val_out[(size_t)col * k + r] = wv;
+      idx_out[(size_t)col * k + r] = wv == -INFINITY ? -1 : wi;
+    }
+    if (bv == wv && bi == wi) {  // the winner's owner drops it (word ids are unique, so exactly one lane)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (q == bq) { cv[q] = -INFINITY; ci[q] = 0x7fffffff; }
+    }
+  }
+}
+cudaError_t launch_topk_merge(const float* val, const int* idx, const float* lse, const float* eos, const int* shard_lo,
+                              int G, int N, int k, float* val_out, int* idx_out, float* eos_out, cudaStream_t st,
+                              size_t cand_stride, size_t col_stride) {
+  if (N <= 0) return cudaSuccess;
+  if (k < 1 || k > ZR_TOPK_MAX || G < 1 || G * k > 128) return cudaErrorInvalidValue;
+  if (!cand_stride) cand_stride = (size_t)N * k;
+  if (!col_stride) col_stride = (size_t)N;
+  topk_merge_kernel<<<(N + 3) / 4, 128, 0, st>>>(val, idx, lse, eos, shard_lo, G, N, k, cand_stride, col_stride, val_out,
+                                                 idx_out, eos_out);
   count_launch();
   return cudaGetLastError();
 }

@@ -116,9 +116,10 @@ cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st);
 // ---- softmax partial combine: logp[n] = (tgt - M) - log(sum_i s_i exp(m_i - M)); 0 where mask==0
 cudaError_t launch_lse_combine(const float* part_max, const float* part_sum, const float* tgt_logit, int n_parts,
                                int N, const int* mask, float* logp, cudaStream_t st);
-// same with the target logit summed over G shard rows of tgt_logit[G x N] (exactly one shard holds it, the others 0)
+// same with the target logit summed over G shard rows of tgt_logit[G x N] (exactly one shard holds it, the others 0);
+// shard_stride (floats, 0 = N) is the distance between two shards' rows in each of the three arrays
 cudaError_t launch_lse_combine_shards(const float* part_max, const float* part_sum, const float* tgt_logit, int G,
-                                      int N, const int* mask, float* logp, cudaStream_t st);
+                                      int N, const int* mask, float* logp, cudaStream_t st, size_t shard_stride = 0);
 // reduce n_parts row-tile partials to one (max, sum exp(z-max)) per column
 cudaError_t launch_lse_reduce(const float* part_max, const float* part_sum, int n_parts, int N, float* out_max,
                               float* out_sum, cudaStream_t st);
@@ -127,9 +128,18 @@ cudaError_t launch_lse_reduce(const float* part_max, const float* part_sum, int 
 // part_max / part_sum (optional): n_parts row-tile partials per column [part][N] produced by the logits GEMM, which
 // save the kernel its first pass over the column; with both and part_width (rows of z per tile) the second pass
 // reads only the tiles whose maximum reaches the selection bound
+// eos_row: the row of `logits` that holds <EOF> (1 for a whole vocabulary; -1 for a shard that does not hold it, whose
+// logp_eos is then -inf); lse_out (optional): log of the column's normaliser, for merging vocabulary shards
 cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* val_out, int* idx_out, float* logp_eos,
                              cudaStream_t st, const float* part_max = nullptr, const float* part_sum = nullptr,
-                             int n_parts = 0, int part_width = 0);
+                             int n_parts = 0, int part_width = 0, int eos_row = 1, float* lse_out = nullptr);
+// Merge of G vocabulary shards' top-k lists (each [G][N][k], lse / eos [G][N], shard_lo[G] on the device) into the k
+// best of the whole vocabulary per column, as log-probabilities under the global normaliser; G * k <= 128.
+// cand_stride / col_stride (4-byte words, 0 = dense) are the distances between two shards' val / idx and lse / eos
+// blocks, so the lists can be read straight out of an all-gather's receive buffer.
+cudaError_t launch_topk_merge(const float* val, const int* idx, const float* lse, const float* eos, const int* shard_lo,
+                              int G, int N, int k, float* val_out, int* idx_out, float* eos_out, cudaStream_t st,
+                              size_t cand_stride = 0, size_t col_stride = 0);
 
 // ---- attention
 struct AttArgs {
@@ -171,6 +181,7 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);
 // distribution of ensemble_factory::ensembles_models (src/ensemble_factory.hpp:768-795).  The renormalisation the
 // reference applies after averaging is the log-softmax the top-k kernel performs on `out`.
 #define ZR_ENSEMBLE_MAX 8
+#define ZR_SHARD_MAX 8  // vocabulary shards (ranks) a top-k merge takes
 struct EnsembleArgs {
   const float* logits[ZR_ENSEMBLE_MAX];  // each V x N, column-major
   int K, V, N;

@@ -2,6 +2,8 @@
 // Input_To_Hidden_Layer / Hidden_To_Hidden_Layer / attention_layer / softmax_layer, and the
 // neuralMT_model drivers for teacher-forced scoring and batched beam decoding.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <cmath>
 #include <cstdio>
@@ -605,17 +607,18 @@ int softmax_score_act(zrnn_softmax* S, const Act& h, const int* targets, const i
 // when ps_out is given, each tile's sum of exp(x - maximum)
 int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, const float** pm_out, int* np_out,
                        const float** ps_out = nullptr) {
-  ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)S->V * N));
+  const int Vs = S->hi - S->lo;  // rows this layer holds (the whole vocabulary unless it is a shard)
+  ZR_CUDA(S->logits.reserve(sizeof(float) * (size_t)Vs * N));
   const float *pm = nullptr;
   int np = 0;
   if (S->eng == ENG_SIMT) {
     zrnn::GemmArgs g;
     std::memset(&g, 0, sizeof(g));
     g.nsrc = 1;
-    g.src[0].A[0] = S->D; g.src[0].lda = S->V; g.src[0].B = h.f32; g.src[0].ldb = S->H; g.src[0].K = S->H;
-    g.M = S->V; g.N = N; g.C = S->logits.as<float>(); g.ldc = S->V; g.bias[0] = S->b;
+    g.src[0].A[0] = S->D; g.src[0].lda = Vs; g.src[0].B = h.f32; g.src[0].ldb = S->H; g.src[0].K = S->H;
+    g.M = Vs; g.N = N; g.C = S->logits.as<float>(); g.ldc = Vs; g.bias[0] = S->b;
     KScope ks(KC_SOFTMAX_GEMM, st);
-    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && S->V >= 512) ? 1 : 0, st));
+    ZR_CUDA(zrnn::launch_fused_gemm(g, 1, zrnn::EPI_STORE, (N >= 96 && Vs >= 512) ? 1 : 0, st));
   } else {
     const int eng = S->eng;
     np = S->n_tiles * zrnn::kPersistentParts;
@@ -625,7 +628,7 @@ int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, co
     ZR_TRY(act_maps(h, eng, S->H, S->Kpad, N, &tp.a[0], &tp.a_lo[0]));
     tp.nsrc = 1; tp.kblocks[0] = (S->H + 128 / eng_eb(eng) - 1) / (128 / eng_eb(eng)); tp.b_koff[0] = 0;
     tp.b = S->dmap; tp.b_lo = S->dmap_lo;
-    tp.M = N; tp.N = S->V; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = S->V;
+    tp.M = N; tp.N = Vs; tp.bias = S->b; tp.C = S->logits.as<float>(); tp.ldc = Vs;
     // the epilogue also leaves each tile's maximum and exp-sum: the top-k kernel derives the normaliser and its
     // selection bound from them and then reads only the few tiles that reach the bound
     tp.part_max = S->parts.as<float>(); tp.part_sum = ps_out ? tp.part_max + (size_t)np * N : nullptr;
@@ -640,13 +643,18 @@ int softmax_logits_act(zrnn_softmax* S, const Act& h, int N, cudaStream_t st, co
   if (ps_out && !pm) *ps_out = nullptr;
   return ZRNN_OK;
 }
-int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st) {
+// the k best rows of this layer's part of the vocabulary per column, as log-probabilities under the layer's own
+// normaliser; row numbers are local to the layer; lse (optional) receives the log of that normaliser
+int softmax_topk_act(zrnn_softmax* S, const Act& h, int N, int k, float* logp, int* idx, float* eos, cudaStream_t st,
+                     float* lse = nullptr) {
   const float *pm = nullptr, *ps = nullptr;
   int np = 0;
   ZR_TRY(softmax_logits_act(S, h, N, st, &pm, &np, &ps));
   KScope ks(KC_SOFTMAX_REDUCE, st);
-  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), S->V, N, k, logp, idx, eos, st, pm, ps, np,
-                                 S->BN / zrnn::kPersistentParts));
+  const int Vs = S->hi - S->lo;
+  const int eos_row = (1 >= S->lo && 1 < S->hi) ? 1 - S->lo : -1;  // <EOF> is word 1
+  ZR_CUDA(zrnn::launch_topk_logp(S->logits.as<float>(), Vs, N, k, logp, idx, eos, st, pm, ps, np,
+                                 S->BN / zrnn::kPersistentParts, eos_row, lse));
   return ZRNN_OK;
 }
 
@@ -702,6 +710,8 @@ struct zrnn_model {
   zrnn::TcMulti enc_multi;  // parameter block of the encoder's multi-cell launches (host scratch)
   const float* last_top = nullptr;
   int last_top_cols = 0;
+  Act last_top_act;  // the same vectors with their operand-form copies
+  bool sharded = false;  // the softmax layer holds a slice of the vocabulary: scoring / decoding need a zrnn_comm
   std::vector<int> h_tmp;
   // CUDA graph of one scoring pass, replayed while the shapes, buffers and stream stay the same
   struct ScoreGraph {
@@ -1223,7 +1233,17 @@ static void add_lstm_slots(zrnn_model* m, const std::string& pre, int owner, int
   if (feed) for (int g = 0; g < 4; ++g) add(std::string("Q_") + g2[g], H, H);
 }
 
+static int model_create_impl(const zrnn_model_config* c, int shard_lo, int shard_hi, zrnn_model** out);
 int zrnn_model_create(const zrnn_model_config* c, zrnn_model** out) {
+  ZR_CHECK(c && out, "model_create: null argument");
+  return model_create_impl(c, 0, c->V_tgt, out);
+}
+int zrnn_model_create_sharded(const zrnn_model_config* c, int shard_lo, int shard_hi, zrnn_model** out) {
+  ZR_CHECK(c && out, "model_create_sharded: null argument");
+  ZR_CHECK(0 <= shard_lo && shard_lo < shard_hi && shard_hi <= c->V_tgt, "model_create_sharded: bad vocabulary range");
+  return model_create_impl(c, shard_lo, shard_hi, out);
+}
+static int model_create_impl(const zrnn_model_config* c, int shard_lo, int shard_hi, zrnn_model** out) {
   ZR_CHECK(c && out, "model_create: null argument");
   ZR_CHECK(c->num_layers >= 1 && c->num_layers <= 8, "model_create: num_layers must be in [1,8]");
   ZR_CHECK(c->H > 0 && c->V_tgt > 1, "model_create: H and V_tgt must be positive");
@@ -1261,7 +1281,8 @@ int zrnn_model_create(const zrnn_model_config* c, zrnn_model** out) {
       for (int i = 0; i < 6; ++i) m->slots.push_back({names[i], rows[i], cols[i], 2, 0, i});
     }
   }
-  if (st == ZRNN_OK) st = zrnn_softmax_create(c->V_tgt, H, c->dtype, 0, c->V_tgt, &m->sm);
+  if (st == ZRNN_OK) st = zrnn_softmax_create(c->V_tgt, H, c->dtype, shard_lo, shard_hi, &m->sm);
+  m->sharded = !(shard_lo == 0 && shard_hi == c->V_tgt);
   if (st == ZRNN_OK) {
     m->slots.push_back({"softmax.D", c->V_tgt, H, 3, 0, 0});
     m->slots.push_back({"softmax.b_d", c->V_tgt, 1, 3, 0, 1});
@@ -1661,6 +1682,7 @@ int zrnn_score_batch_device(zrnn_model* m, const int* d_src_ids, int S_max, cons
                             const int* d_tgt_out, int T, int B, float* d_logp_out, void* stream) {
   ZR_CHECK(m && d_tgt_in && d_tgt_out && d_logp_out, "score_batch: null argument");
   if (!m->finalized) return fail(ZRNN_E_STATE, "score_batch: model weights not finalized");
+  ZR_CHECK(!m->sharded, "score_batch: the model's softmax is vocabulary-sharded; use zrnn_score_batch_sharded");
   ZR_CHECK(T >= 0 && B >= 0, "score_batch: negative size");
   ZR_CHECK(m->cfg.lm || (d_src_ids && S_max > 0), "score_batch: a sequence-to-sequence model needs source ids");
   if (T == 0 || B == 0) return ZRNN_OK;
@@ -1788,6 +1810,7 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
   }
   const Act& top = c.attention ? hts : tseq[L - 1];
   m->last_top = top.f32;
+  m->last_top_act = top;
   m->last_top_cols = (int)nT;
   if (!d_logp_out) return ZRNN_OK;
   return softmax_score_act(m->sm, top, tout_id, tout_mk, (int)nT, d_logp_out, s);
@@ -1851,6 +1874,119 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// collective layer: NCCL, loaded at first use (the library has no link-time dependency on it)
+// ------------------------------------------------------------------------------------------
+struct zrnn_comm {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+  DevBuf send, recv, aux, lo_buf;  // staging for the all-gathers; first vocabulary row of every rank
+  int lo_V = -1;                   // vocabulary size lo_buf was computed for
+  cudaEvent_t ev[6] = {};          // stage boundaries of the last sharded scoring call
+  float stage_ms[5] = {};
+  ~zrnn_comm() {
+    send.release(); recv.release(); aux.release(); lo_buf.release();
+    for (auto& e : ev) if (e) cudaEventDestroy(e);
+  }
+};
+
+namespace {
+struct NcclApi {
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  bool ok = false;
+};
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (h) {
+      api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+      api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
+      api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
+      api.AllGather = (decltype(api.AllGather))dlsym(h, "ncclAllGather");
+      api.GroupStart = (decltype(api.GroupStart))dlsym(h, "ncclGroupStart");
+      api.GroupEnd = (decltype(api.GroupEnd))dlsym(h, "ncclGroupEnd");
+      api.GetErrorString = (decltype(api.GetErrorString))dlsym(h, "ncclGetErrorString");
+      api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.GroupStart && api.GroupEnd &&
+               api.GetErrorString;
+    }
+  }
+  return &api;
+}
+#define ZR_NCCL(expr)                                                                                    \
+  do {                                                                                                   \
+    ncclResult_t _r = (expr);                                                                            \
+    if (_r != ncclSuccess) return fail(ZRNN_E_NCCL, std::string(#expr) + ": " + nccl_api()->GetErrorString(_r)); \
+  } while (0)
+
+// all-gather of `bytes` bytes per rank (device buffers; recv holds world * bytes, rank-major)
+int comm_all_gather(zrnn_comm* c, const void* send, void* recv, size_t bytes, cudaStream_t s) {
+  if (c->world == 1) {
+    if (send != recv) ZR_CUDA(cudaMemcpyAsync(recv, send, bytes, cudaMemcpyDeviceToDevice, s));
+    return ZRNN_OK;
+  }
+  ZR_NCCL(nccl_api()->AllGather(send, recv, bytes, ncclChar, c->comm, s));
+  return ZRNN_OK;
+}
+
+// near-equal contiguous ranges of n items over `world` ranks: [n*r/world, n*(r+1)/world)
+void shard_range(long long n, int world, int r, int* lo, int* hi) {
+  *lo = (int)(n * r / world);
+  *hi = (int)(n * (r + 1) / world);
+}
+
+// first vocabulary row of every rank's shard, on the device (cached per vocabulary size)
+int comm_shard_lo(zrnn_comm* c, int V, const int** d_lo) {
+  if (c->lo_V != V) {
+    std::vector<int> lo(c->world);
+    int hi_unused;
+    for (int g = 0; g < c->world; ++g) shard_range(V, c->world, g, &lo[g], &hi_unused);
+    ZR_CUDA(c->lo_buf.reserve(sizeof(int) * c->world));
+    ZR_CUDA(cudaMemcpy(c->lo_buf.p, lo.data(), sizeof(int) * c->world, cudaMemcpyHostToDevice));
+    c->lo_V = V;
+  }
+  *d_lo = c->lo_buf.as<int>();
+  return ZRNN_OK;
+}
+
+// Vocabulary-sharded pre-selection: this rank's k best rows and normaliser, ONE all-gather of k (value, row) pairs and
+// two floats per column, and the merge under the global normaliser, which reads the receive buffer in place.  Every
+// rank ends up with the same k candidates.
+int softmax_topk_sharded_act(zrnn_softmax* S, zrnn_comm* c, const Act& h, int N, int k, float* logp, int* idx, float* eos,
+                             cudaStream_t st) {
+  const int G = c->world;
+  int lo, hi;
+  shard_range(S->V, G, c->rank, &lo, &hi);
+  ZR_CHECK(S->lo == lo && S->hi == hi, "softmax_topk_sharded: the layer's vocabulary range is not this rank's share");
+  // per rank: [N*k val][N*k idx][N lse][N eos] as 4-byte words
+  const size_t words = (size_t)N * (2 * k + 2);
+  ZR_CUDA(c->send.reserve(words * 4));
+  ZR_CUDA(c->recv.reserve(words * 4 * G));
+  const int* d_lo = nullptr;
+  ZR_TRY(comm_shard_lo(c, S->V, &d_lo));
+  float* sv = c->send.as<float>();
+  int* si = (int*)(sv + (size_t)N * k);
+  float* sl = sv + 2 * (size_t)N * k;
+  float* se = sl + N;
+  ZR_TRY(softmax_topk_act(S, h, N, k, sv, si, se, st, sl));
+  ZR_TRY(comm_all_gather(c, c->send.p, c->recv.p, words * 4, st));
+  const float* rv = c->recv.as<float>();
+  KScope ks(KC_SOFTMAX_REDUCE, st);
+  ZR_CUDA(zrnn::launch_topk_merge(rv, (const int*)(rv + (size_t)N * k), rv + 2 * (size_t)N * k, rv + 2 * (size_t)N * k + N, d_lo,
+                                  G, N, k, logp, idx, eos, st, words, words));
+  return ZRNN_OK;
+}
+}  // namespace
 
 namespace {
 // Per-model state of a (possibly ensembled) beam search: encoder outputs and the decoder's recurrent state for
@@ -1989,14 +2125,16 @@ struct BeamModel {
 int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, const int* h_src_len,
                      const int* S_max, int n_sent, int beam, int k_best, float min_ratio, float max_ratio, float penalty,
                      int longest_sent, int* d_out_ids, int* d_out_len, float* d_out_score, int* d_out_align,
-                     cudaStream_t s) {
+                     cudaStream_t s, zrnn_comm* comm = nullptr) {
   ZR_CHECK(K >= 1 && K <= ZR_ENSEMBLE_MAX, "beam_decode: between 1 and 8 models");
+  ZR_CHECK(!comm || K == 1, "beam_decode: vocabulary sharding is not combined with ensembles");
   const int V = models[0]->cfg.V_tgt;
   for (int k = 0; k < K; ++k) {
     zrnn_model* m = models[k];
     ZR_CHECK(m, "beam_decode: null model");
     if (!m->finalized) return fail(ZRNN_E_STATE, "beam_decode: model weights not finalized");
     ZR_CHECK(!m->cfg.lm, "beam_decode: needs a sequence-to-sequence model");
+    ZR_CHECK(!m->sharded || comm, "beam_decode: the model's softmax is vocabulary-sharded; use zrnn_beam_decode_batch_sharded");
     ZR_CHECK(m->cfg.V_tgt == V, "beam_decode: ensembled models must share the target vocabulary");
     ZR_CHECK(S_max[k] > 0, "beam_decode: bad sizes");
   }
@@ -2078,7 +2216,8 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
     if (K == 1) {
       Act top;
       ZR_TRY(bm[0].forward(t, cur_ids, &top, s));
-      ZR_TRY(softmax_topk_act(m0->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
+      if (comm) ZR_TRY(softmax_topk_sharded_act(m0->sm, comm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
+      else ZR_TRY(softmax_topk_act(m0->sm, top, NB, kc, cand_val, cand_idx, logp_eos, s));
     } else {
       zrnn::EnsembleArgs ea;
       std::memset(&ea, 0, sizeof(ea));
@@ -2135,9 +2274,9 @@ int zrnn_beam_decode_batch(zrnn_model* m, const int* src_ids, const int* src_len
                                       longest_sent, out_ids, out_len, out_score, nullptr);
 }
 
-int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam,
-                                 int k_best, float min_ratio, float max_ratio, float penalty, int longest_sent,
-                                 int* out_ids, int* out_len, float* out_score, int* out_align) {
+static int beam_decode_host(zrnn_model* m, zrnn_comm* comm, const int* src_ids, const int* src_len, int n_sent, int beam,
+                            int k_best, float min_ratio, float max_ratio, float penalty, int longest_sent,
+                            int* out_ids, int* out_len, float* out_score, int* out_align) {
   ZR_CHECK(m && src_ids && src_len && out_ids && out_len && out_score, "beam_decode: null argument");
   ZR_CHECK(n_sent >= 0 && k_best >= 1 && longest_sent >= 1, "beam_decode: bad sizes");
   if (n_sent == 0) return ZRNN_OK;
@@ -2168,14 +2307,231 @@ int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* s
   int* d_al = out_align ? cv.take<int>(nO * Lmax) : nullptr;
   cudaStream_t s = m->stream;
   ZR_CUDA(cudaMemcpyAsync(d_src, padded.data(), sizeof(int) * padded.size(), cudaMemcpyHostToDevice, s));
-  ZR_TRY(zrnn_beam_decode_batch_align_device(m, d_src, src_len, S_max, n_sent, beam, k_best, min_ratio, max_ratio,
-                                             penalty, longest_sent, d_ids, d_len, d_sc, d_al, s));
+  const int* d_src_c = d_src;
+  ZR_TRY(beam_decode_core(&m, 1, &d_src_c, src_len, &S_max, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
+                          longest_sent, d_ids, d_len, d_sc, d_al, s, comm));
   if (out_align) ZR_CUDA(cudaMemcpyAsync(out_align, d_al, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_ids, d_ids, sizeof(int) * nO * Lmax, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_len, d_len, sizeof(int) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaMemcpyAsync(out_score, d_sc, sizeof(float) * nO, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaStreamSynchronize(s));
   ZR_TRY(device_error_status("beam_decode"));
+  return ZRNN_OK;
+}
+
+int zrnn_beam_decode_batch_align(zrnn_model* m, const int* src_ids, const int* src_len, int n_sent, int beam,
+                                 int k_best, float min_ratio, float max_ratio, float penalty, int longest_sent,
+                                 int* out_ids, int* out_len, float* out_score, int* out_align) {
+  return beam_decode_host(m, nullptr, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio, penalty,
+                          longest_sent, out_ids, out_len, out_score, out_align);
+}
+
+// ---------------------------------------------------------------- collective layer (vocabulary-sharded softmax)
+int zrnn_comm_unique_id(char* id128) {
+  ZR_CHECK(id128, "comm_unique_id: null argument");
+  static_assert(sizeof(ncclUniqueId) == ZRNN_COMM_ID_BYTES, "the id buffer of the C ABI is the size of NCCL's unique id");
+  if (!nccl_api()->ok) return fail(ZRNN_E_NCCL, "the NCCL library (libnccl.so.2) could not be loaded");
+  ncclUniqueId id;
+  ZR_NCCL(nccl_api()->GetUniqueId(&id));
+  std::memcpy(id128, &id, sizeof(id));
+  return ZRNN_OK;
+}
+int zrnn_comm_create(const char* id128, int rank, int world, zrnn_comm** out) {
+  ZR_CHECK(out && world >= 1 && rank >= 0 && rank < world, "comm_create: bad arguments");
+  ZR_CHECK(world <= ZR_SHARD_MAX, "comm_create: at most 8 ranks");
+  ZR_TRY(check_device());
+  auto* c = new zrnn_comm();
+  c->rank = rank;
+  c->world = world;
+  if (world > 1) {
+    if (!id128) { delete c; return fail(ZRNN_E_ARG, "comm_create: a group of more than one rank needs the unique id"); }
+    if (!nccl_api()->ok) { delete c; return fail(ZRNN_E_NCCL, "the NCCL library (libnccl.so.2) could not be loaded"); }
+    ncclUniqueId id;
+    std::memcpy(&id, id128, sizeof(id));
+    const ncclResult_t r = nccl_api()->CommInitRank(&c->comm, world, id, rank);
+    if (r != ncclSuccess) {
+      delete c;
+      return fail(ZRNN_E_NCCL, std::string("ncclCommInitRank: ") + nccl_api()->GetErrorString(r));
+    }
+  }
+  *out = c;
+  return ZRNN_OK;
+}
+int zrnn_comm_rank(const zrnn_comm* c, int* rank, int* world) {
+  ZR_CHECK(c, "comm_rank: null argument");
+  if (rank) *rank = c->rank;
+  if (world) *world = c->world;
+  return ZRNN_OK;
+}
+int zrnn_comm_all_gather(zrnn_comm* c, const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream) {
+  ZR_CHECK(c && d_send && d_recv, "comm_all_gather: null argument");
+  if (!bytes_per_rank) return ZRNN_OK;
+  return comm_all_gather(c, d_send, d_recv, bytes_per_rank, (cudaStream_t)stream);
+}
+int zrnn_comm_last_stage_ms(const zrnn_comm* c, float* ms5) {
+  ZR_CHECK(c && ms5, "comm_last_stage_ms: null argument");
+  for (int i = 0; i < 5; ++i) ms5[i] = c->stage_ms[i];
+  return ZRNN_OK;
+}
+int zrnn_comm_destroy(zrnn_comm* c) {
+  if (!c) return ZRNN_OK;
+  if (c->comm) nccl_api()->CommDestroy(c->comm);
+  delete c;
+  return ZRNN_OK;
+}
+int zrnn_shard_range(int V, int world, int rank, int* lo, int* hi) {
+  ZR_CHECK(V >= 0 && world >= 1 && rank >= 0 && rank < world && lo && hi, "shard_range: bad arguments");
+  shard_range(V, world, rank, lo, hi);
+  return ZRNN_OK;
+}
+
+int zrnn_softmax_topk_shard(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
+                            float* d_lse_out, float* d_logp_eos, void* stream) {
+  ZR_CHECK(S && d_h && d_logp_out && d_idx_out && d_lse_out && N >= 0, "softmax_topk_shard: bad arguments");
+  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk_shard: k must be in [1,16]");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_shard: weights not loaded");
+  if (N == 0) return ZRNN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  Act h;
+  ZR_TRY(softmax_input(S, d_h, N, &h, st));
+  return softmax_topk_act(S, h, N, k, d_logp_out, d_idx_out, d_logp_eos, st, d_lse_out);
+}
+int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, const float* d_eos, const int* d_shard_lo,
+                    int G, int N, int k, float* d_val_out, int* d_idx_out, float* d_eos_out, void* stream) {
+  ZR_CHECK(d_val && d_idx && d_lse && d_shard_lo && d_val_out && d_idx_out && N >= 0, "topk_merge: bad arguments");
+  ZR_CHECK(!d_eos_out || d_eos, "topk_merge: an <EOF> output needs the shards' <EOF> values");
+  ZR_CHECK(G >= 1 && G <= ZR_SHARD_MAX && k >= 1 && k <= 16, "topk_merge: 1..8 shards of 1..16 candidates");
+  if (N == 0) return ZRNN_OK;
+  ZR_CUDA(zrnn::launch_topk_merge(d_val, d_idx, d_lse, d_eos, d_shard_lo, G, N, k, d_val_out, d_idx_out, d_eos_out,
+                                  (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+int zrnn_softmax_topk_sharded(zrnn_softmax* S, zrnn_comm* c, const float* d_h, int N, int k, float* d_logp_out,
+                              int* d_idx_out, float* d_logp_eos, void* stream) {
+  ZR_CHECK(S && c && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk_sharded: bad arguments");
+  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk_sharded: k must be in [1,16]");
+  if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_sharded: weights not loaded");
+  if (N == 0) return ZRNN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  Act h;
+  ZR_TRY(softmax_input(S, d_h, N, &h, st));
+  return softmax_topk_sharded_act(S, c, h, N, k, d_logp_out, d_idx_out, d_logp_eos, st);
+}
+
+int zrnn_beam_decode_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, const int* src_len, int n_sent,
+                                   int beam, int k_best, float min_ratio, float max_ratio, float penalty,
+                                   int longest_sent, int* out_ids, int* out_len, float* out_score) {
+  ZR_CHECK(c, "beam_decode_sharded: null communicator");
+  return beam_decode_host(m, c, src_ids, src_len, n_sent, beam, k_best, min_ratio, max_ratio, penalty, longest_sent,
+                          out_ids, out_len, out_score, nullptr);
+}
+
+// Teacher-forced scoring over `world` ranks.  Every rank passes the SAME host batch.  The recurrent stack and the
+// attention run data-parallel (rank r takes the columns [B r / world, B (r+1) / world), padded to the widest share);
+// the top hidden states are all-gathered; every rank scores all columns against its slice of the vocabulary; one more
+// all-gather of (max, sum, target logit) per column and the combine give every rank the whole log-probability matrix.
+int zrnn_score_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, int S_max, const int* tgt_in,
+                             const int* tgt_out, int T, int B, float* logp_out, double* total_logp) {
+  ZR_CHECK(m && c && tgt_in && tgt_out && logp_out, "score_batch_sharded: null argument");
+  ZR_CHECK(T >= 0 && B >= 0 && S_max >= 0, "score_batch_sharded: negative size");
+  if (!m->finalized) return fail(ZRNN_E_STATE, "score_batch_sharded: model weights not finalized");
+  {
+    int lo, hi;
+    shard_range(m->cfg.V_tgt, c->world, c->rank, &lo, &hi);
+    ZR_CHECK(m->sm->lo == lo && m->sm->hi == hi, "score_batch_sharded: the model's vocabulary range is not this rank's share");
+  }
+  if (total_logp) *total_logp = 0.0;
+  if (T == 0 || B == 0) return ZRNN_OK;
+  const bool lm = m->cfg.lm != 0;
+  const int G = c->world, H = m->cfg.H;
+  const int S = lm ? 0 : S_max;
+  ZR_CHECK(lm || src_ids, "score_batch_sharded: a sequence-to-sequence model needs source ids");
+  if (S) ZR_TRY(check_ids(src_ids, (size_t)S * B, m->cfg.V_src, "score_batch_sharded (source)"));
+  ZR_TRY(check_ids(tgt_in, (size_t)T * B, m->cfg.V_tgt, "score_batch_sharded (target input)"));
+  ZR_TRY(check_ids(tgt_out, (size_t)T * B, m->cfg.V_tgt, "score_batch_sharded (target output)"));
+  const int Bp = (B + G - 1) / G;  // columns per rank (the last shares are padded with masked columns)
+  int b_lo, b_hi;
+  shard_range(B, G, c->rank, &b_lo, &b_hi);
+  const size_t nS = (size_t)S * Bp, nT = (size_t)T * Bp, nAll = nT * G;
+  // this rank's columns, and the target words of ALL columns in gathered order (rank, step, local column)
+  std::vector<int> h_ids(nS + nT + nAll, -1);
+  int* l_src = h_ids.data();
+  int* l_tin = l_src + nS;
+  int* a_tout = l_tin + nT;
+  for (int b = b_lo; b < b_hi; ++b) {
+    for (int t = 0; t < S; ++t) l_src[(size_t)t * Bp + (b - b_lo)] = src_ids[(size_t)t * B + b];
+    for (int t = 0; t < T; ++t) l_tin[(size_t)t * Bp + (b - b_lo)] = tgt_in[(size_t)t * B + b];
+  }
+  for (int g = 0; g < G; ++g) {
+    int lo, hi;
+    shard_range(B, G, g, &lo, &hi);
+    for (int t = 0; t < T; ++t)
+      for (int b = lo; b < hi; ++b) a_tout[(size_t)g * nT + (size_t)t * Bp + (b - lo)] = tgt_out[(size_t)t * B + b];
+  }
+  const Geom geo{H, round64(H), m->eng};
+  const bool op_gather = m->eng == ENG_BF16;  // the bf16 engine's operand form is half the bytes of the fp32 states
+  const size_t col_bytes = op_gather ? (size_t)geo.Kpad * 2 : sizeof(float) * (size_t)H;
+  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * h_ids.size()) + 2 * aligned(sizeof(int) * nAll) + aligned(sizeof(float) * nAll)));
+  ZR_CUDA(c->recv.reserve(col_bytes * nAll));
+  ZR_CUDA(c->send.reserve(3 * sizeof(float) * nAll));
+  ZR_CUDA(c->aux.reserve(3 * sizeof(float) * nAll * G));
+  Carver cv(m->io.p);
+  int* d_ids = cv.take<int>(h_ids.size());
+  int* d_tout = cv.take<int>(nAll);
+  int* d_mask = cv.take<int>(nAll);
+  float* d_lp = cv.take<float>(nAll);
+  cudaStream_t s = m->stream;
+  for (auto& e : c->ev) if (!e) ZR_CUDA(cudaEventCreate(&e));
+  ZR_CUDA(cudaEventRecord(c->ev[0], s));
+  ZR_CUDA(cudaMemcpyAsync(d_ids, h_ids.data(), sizeof(int) * h_ids.size(), cudaMemcpyHostToDevice, s));
+  m->drop_graph();
+  ZR_TRY(score_batch_body(m, S ? d_ids : nullptr, S, d_ids + nS, d_ids + nS, T, Bp, nullptr, s));
+  const Act top = m->last_top_act;
+  Act all;
+  ZR_CUDA(cudaEventRecord(c->ev[1], s));
+  if (op_gather) {
+    ZR_TRY(comm_all_gather(c, top.hi, c->recv.p, col_bytes * nT, s));
+    all.hi = c->recv.p;
+  } else {
+    ZR_TRY(comm_all_gather(c, top.f32, c->recv.p, col_bytes * nT, s));
+    ZR_TRY(softmax_input(m->sm, c->recv.as<float>(), (int)nAll, &all, s));
+  }
+  ZR_CUDA(cudaEventRecord(c->ev[2], s));
+  ZR_CUDA(zrnn::launch_prep_ids(d_ids + nS + nT, (int)nAll, d_tout, d_mask, s));
+  float* mx = c->send.as<float>();
+  float* sm = mx + nAll;
+  float* tg = sm + nAll;
+  {
+    int np = 0;
+    float *pm, *ps;
+    ZR_TRY(softmax_partials_launch(m->sm, all, d_tout, (int)nAll, &np, &pm, &ps, tg, s));
+    KScope ks(KC_SOFTMAX_REDUCE, s);
+    ZR_CUDA(zrnn::launch_lse_reduce(pm, ps, np, (int)nAll, mx, sm, s));
+  }
+  ZR_CUDA(cudaEventRecord(c->ev[3], s));
+  // one all-gather of [max | sum | target logit]; the combine reads the three [G][N] arrays with the block stride
+  ZR_TRY(comm_all_gather(c, c->send.p, c->aux.p, 3 * sizeof(float) * nAll, s));
+  const float* r = c->aux.as<float>();
+  ZR_CUDA(zrnn::launch_lse_combine_shards(r, r + nAll, r + 2 * nAll, G, (int)nAll, d_mask, d_lp, s, 3 * nAll));
+  ZR_CUDA(cudaEventRecord(c->ev[4], s));
+  std::vector<float> h_lp(nAll);
+  ZR_CUDA(cudaMemcpyAsync(h_lp.data(), d_lp, sizeof(float) * nAll, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaEventRecord(c->ev[5], s));
+  ZR_CUDA(cudaStreamSynchronize(s));
+  for (int i = 0; i < 5; ++i) ZR_CUDA(cudaEventElapsedTime(&c->stage_ms[i], c->ev[i], c->ev[i + 1]));
+  ZR_TRY(device_error_status("score_batch_sharded"));
+  double tot = 0;
+  for (int g = 0; g < G; ++g) {
+    int lo, hi;
+    shard_range(B, G, g, &lo, &hi);
+    for (int t = 0; t < T; ++t)
+      for (int b = lo; b < hi; ++b) {
+        const float v = h_lp[(size_t)g * nT + (size_t)t * Bp + (b - lo)];
+        logp_out[(size_t)t * B + b] = v;
+        tot += v;
+      }
+  }
+  if (total_logp) *total_logp = tot;
   return ZRNN_OK;
 }
 

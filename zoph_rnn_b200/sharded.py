@@ -1,4 +1,9 @@
-"""Multi-GPU host logic: sentence sharding (no collective) and vocabulary-sharded scoring.
+"""Multi-GPU host logic: sentence sharding (no collective) and vocabulary-sharded scoring / decoding.
+
+The production path is ShardedModel below: the collective layer lives behind the C ABI (zrnn_comm_*,
+zrnn_score_batch_sharded, zrnn_beam_decode_batch_sharded) and a host in any language drives it the same way.
+VocabShardedScorer and merge_topk_host restate the same ordering and combination rules over torch.distributed, so
+that they can be checked with gloo ranks on a machine without GPUs.
 
 One process per GPU (torch.distributed).  Sentences are independent, so configs that fit one GPU shard the
 minibatch by rank and never communicate.  A large-vocabulary model additionally shards the softmax matrix D by
@@ -14,8 +19,8 @@ import torch.distributed as dist
 
 def shard_bounds(n, world):
     """Contiguous, near-equal [lo, hi) ranges of n items over `world` ranks."""
-    edges = np.linspace(0, n, world + 1).astype(np.int64)
-    return [(int(edges[r]), int(edges[r + 1])) for r in range(world)]
+    # the same integer rule as zrnn_shard_range in the C ABI
+    return [(n * r // world, n * (r + 1) // world) for r in range(world)]
 
 
 def shard_columns(arr, rank, world):
@@ -102,3 +107,47 @@ class VocabShardedScorer:
             out[:, a:b] = logp[pos:pos + n].reshape(T, b - a)
             pos += n
         return out
+
+
+def merge_topk_host(vals, idxs, lses, eoss, shard_lo, k):
+    """NumPy statement of zrnn_topk_merge.  vals / idxs [G,N,k] (log-probabilities under each shard's own normaliser,
+    row numbers inside the shard, -1 = no row), lses / eoss [G,N].  Returns (logp [N,k], word ids [N,k], eos [N])
+    under the global normaliser; ties go to the lower word id."""
+    vals = np.asarray(vals, dtype=np.float64)
+    idxs = np.asarray(idxs)
+    lses = np.asarray(lses, dtype=np.float64)
+    eoss = np.asarray(eoss, dtype=np.float64)
+    G, N, kk = vals.shape
+    m = lses.max(axis=0)
+    lse = m + np.log(np.exp(lses - m).sum(axis=0))
+    glob = np.where(idxs >= 0, vals + lses[:, :, None] - lse[None, :, None], -np.inf)
+    ids = np.where(idxs >= 0, idxs + np.asarray(shard_lo).reshape(G, 1, 1), np.iinfo(np.int32).max)
+    glob = glob.transpose(1, 0, 2).reshape(N, G * kk)
+    ids = ids.transpose(1, 0, 2).reshape(N, G * kk)
+    out_v = np.empty((N, k), dtype=np.float32)
+    out_i = np.empty((N, k), dtype=np.int32)
+    for n in range(N):
+        order = np.lexsort((ids[n], -glob[n]))[:k]
+        out_v[n] = glob[n, order]
+        out_i[n] = np.where(np.isfinite(glob[n, order]), ids[n, order], -1)
+    with np.errstate(invalid="ignore"):
+        e = np.where(np.isfinite(eoss), eoss + lses - lse[None, :], -np.inf).max(axis=0)
+    return out_v, out_i, e.astype(np.float32)
+
+
+class ShardedModel:
+    """One rank of a vocabulary-sharded model: the recurrent stack and attention whole, rows
+    [V r / world, V (r + 1) / world) of the softmax, and the library's communicator.  Every rank calls score() /
+    decode() with the same arguments and gets the whole result."""
+
+    def __init__(self, cfg, weights, comm, dtype=0):
+        from . import api
+        self.comm = comm
+        self.model = api.neuralMT_model(cfg, dtype=dtype, shard=api.shard_range(cfg["V_tgt"], comm.world, comm.rank))
+        self.model.load_weights(weights)
+
+    def score(self, src, tin, tout):
+        return self.model.get_error_sharded(self.comm, src, tin, tout)
+
+    def decode(self, sources, **kw):
+        return self.model.decode_sharded(self.comm, sources, **kw)
