@@ -148,7 +148,7 @@ def reference_sample(w):
     return src, tin, tout, sample
 
 
-def run_reference(args, w, rank):
+def run_reference(args, w, rank, emit):
     """CPU arm: the oracle (a port of the reference's kernel math; the reference itself cannot be built
     for this machine) on a bounded sample of the workload, all host threads."""
     if rank != 0:
@@ -190,7 +190,7 @@ def run_reference(args, w, rank):
                 config=dict(workload=args.workload + ": " + w["desc"], sample=sample),
                 cpu_baseline=dict(value=val, unit=unit, cores=cores, kind="port", sample=sample),
                 e2e=dict(value=val, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
-    print(json.dumps(line))
+    emit(line)
 
 
 def metric_name(w):
@@ -538,8 +538,17 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    # stdout carries the ONE JSON line and nothing else: whatever a library prints to file descriptor 1 meanwhile (NCCL's
+    # version banner, for one) goes to stderr
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     if args.impl == "reference":
-        run_reference(args, w, rank)
+        run_reference(args, w, rank, emit)
         return
 
     import torch
@@ -549,7 +558,7 @@ def main():
     torch.cuda.set_device(local_rank)
     if args.cell_phases:
         if rank == 0:
-            print(json.dumps(cell_phases(w, args.dtype)))
+            emit(cell_phases(w, args.dtype))
         return
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -593,7 +602,7 @@ def main():
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w)
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

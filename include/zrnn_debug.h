@@ -25,6 +25,12 @@ int zrnn_debug_tc_timeline(long long* d_buf, int slots);
  * T * (L + 2 or 3) phases; NULL switches it off.  cta < 0: every CTA writes, CTA c to d_buf[(c * phases + phase) * 8 ..]. */
 int zrnn_debug_decoder_timeline(long long* d_buf, int cta);
 
+/* Exercise of the bounded device waits: launches one warp that waits on a barrier nothing will ever complete, with a
+ * limit of limit_cycles SM cycles (2e6 is about a millisecond).  The wait gives up, the kernel returns, and the device
+ * error word holds role 77: zrnn_tc_error() returns it, and the next model-level call that ends with a host
+ * synchronisation returns ZRNN_E_TIMEOUT once; the context stays usable. */
+int zrnn_debug_bounded_wait(long long limit_cycles, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,6 +38,7 @@ SIGNATURES = {
     "zrnn_debug_tc_profile": (ctypes.c_int, [c_void_p]),
     "zrnn_debug_tc_timeline": (ctypes.c_int, [c_void_p, ctypes.c_int]),
     "zrnn_debug_decoder_timeline": (ctypes.c_int, [c_void_p, ctypes.c_int]),
+    "zrnn_debug_bounded_wait": (ctypes.c_int, [ctypes.c_longlong, c_void_p]),
     "zrnn_device_count": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "zrnn_set_device": (ctypes.c_int, [ctypes.c_int]),
     "zrnn_launch_count": (ctypes.c_longlong, []),

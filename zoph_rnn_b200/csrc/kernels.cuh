@@ -181,6 +181,7 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);
 // distribution of ensemble_factory::ensembles_models (src/ensemble_factory.hpp:768-795).  The renormalisation the
 // reference applies after averaging is the log-softmax the top-k kernel performs on `out`.
 #define ZR_ENSEMBLE_MAX 8
+#define ZR_BEAM_MAX 31  // beam width (every hypothesis proposes beam + 1 <= 32 candidates per step)
 #define ZR_SHARD_MAX 8  // vocabulary shards (ranks) a top-k merge takes
 struct EnsembleArgs {
   const float* logits[ZR_ENSEMBLE_MAX];  // each V x N, column-major

@@ -33,15 +33,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Gives up after ~2e9 SM cycles or as soon as another role has given up (*abort_flag != 0).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+// Bounded wait.  Gives up after `limit` SM cycles (about a second by default) or as soon as another role has given up
+// (*abort_flag != 0); the first role to give up leaves `code` in the device error word.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                          long long limit = 2000000000LL) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > 2000000000LL) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         if (err) atomicExch(err, code);
         return false;

@@ -1029,4 +1029,25 @@ bool make_kmajor_map(CUtensorMap* out, const void* base, int elem_bytes, long lo
   return r == CUDA_SUCCESS;
 }
 
+// ------------------------------------------------------------------------------------------
+// Exercise of the bounded wait: one warp waits on a barrier that nothing ever completes, with a short limit, and
+// must come back with the error word set and the context intact.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) wait_probe_kernel(int* err, long long limit_cycles, int code) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_s;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_s, err, code, limit_cycles);
+}
+cudaError_t launch_wait_probe(int* err, long long limit_cycles, int code, cudaStream_t st) {
+  wait_probe_kernel<<<1, 32, 0, st>>>(err, limit_cycles, code);
+  count_launch();
+  return cudaGetLastError();
+}
+
 }  // namespace zrnn

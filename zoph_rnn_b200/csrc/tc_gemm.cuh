@@ -77,6 +77,8 @@ cudaError_t launch_tc_lstm_multi(const TcMulti& pm, int n, int mode, cudaStream_
 // [(n_tile * kPersistentParts + half) x M] and each covers tile width / kPersistentParts consecutive columns.
 constexpr int kPersistentParts = 2;
 cudaError_t launch_tc_gemm_persistent(const TcParams& p, int mode, int epi, cudaStream_t st);
+// One warp waits (bounded by limit_cycles SM cycles) on a barrier that never completes and reports `code` in *err.
+cudaError_t launch_wait_probe(int* err, long long limit_cycles, int code, cudaStream_t st);
 
 // Host helpers -------------------------------------------------------------------------------------------
 // 2-D K-major tensor map: `rows` rows of `k` elements, row stride ld (elements); box = (128-byte k-block) x box_rows

@@ -813,6 +813,13 @@ int zrnn_debug_decoder_timeline(long long* d_buf, int cta) {
   return ZRNN_OK;
 }
 
+int zrnn_debug_bounded_wait(long long limit_cycles, void* stream) {
+  ZR_CHECK(limit_cycles > 0 && limit_cycles <= 2000000000LL, "debug_bounded_wait: limit must be in (0, 2e9] cycles");
+  ZR_TRY(check_device());
+  ZR_CUDA(zrnn::launch_wait_probe(tc_error_word(), limit_cycles, 77, (cudaStream_t)stream));
+  return ZRNN_OK;
+}
+
 int zrnn_tc_error(void) {
   int* d = tc_error_word();
   int v = 0;
@@ -1207,7 +1214,7 @@ int zrnn_softmax_score(zrnn_softmax* S, const float* d_h, const int* d_targets, 
 int zrnn_softmax_topk(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                       float* d_logp_eos, void* stream) {
   ZR_CHECK(S && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk: bad arguments");
-  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk: k must be in [1,16]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk: k must be in [1,32]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk: weights not loaded");
   ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_topk: layer is vocabulary-sharded");
   if (N == 0) return ZRNN_OK;
@@ -2142,7 +2149,7 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
   if (n_sent == 0) return ZRNN_OK;
   const int cap = (int)std::sqrt((double)V);  // src/ensemble_factory.hpp:19-21
   if (beam > cap) beam = cap;
-  ZR_CHECK(beam >= 1 && beam <= 15, "beam_decode: beam must be in [1,15] after the sqrt(V) cap");
+  ZR_CHECK(beam >= 1 && beam <= ZR_BEAM_MAX, "beam_decode: beam must be in [1,31] after the sqrt(V) cap");
   const int kc = beam + 1;
   ZR_CHECK(kc <= V, "beam_decode: vocabulary smaller than beam+1");
   const int Lmax = longest_sent + 4;  // src/main.cu:408
@@ -2388,7 +2395,7 @@ int zrnn_shard_range(int V, int world, int rank, int* lo, int* hi) {
 int zrnn_softmax_topk_shard(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                             float* d_lse_out, float* d_logp_eos, void* stream) {
   ZR_CHECK(S && d_h && d_logp_out && d_idx_out && d_lse_out && N >= 0, "softmax_topk_shard: bad arguments");
-  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk_shard: k must be in [1,16]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_shard: k must be in [1,32]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_shard: weights not loaded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -2400,7 +2407,7 @@ int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, co
                     int G, int N, int k, float* d_val_out, int* d_idx_out, float* d_eos_out, void* stream) {
   ZR_CHECK(d_val && d_idx && d_lse && d_shard_lo && d_val_out && d_idx_out && N >= 0, "topk_merge: bad arguments");
   ZR_CHECK(!d_eos_out || d_eos, "topk_merge: an <EOF> output needs the shards' <EOF> values");
-  ZR_CHECK(G >= 1 && G <= ZR_SHARD_MAX && k >= 1 && k <= 16, "topk_merge: 1..8 shards of 1..16 candidates");
+  ZR_CHECK(G >= 1 && G <= ZR_SHARD_MAX && k >= 1 && k <= ZR_BEAM_MAX + 1, "topk_merge: 1..8 shards of 1..32 candidates");
   if (N == 0) return ZRNN_OK;
   ZR_CUDA(zrnn::launch_topk_merge(d_val, d_idx, d_lse, d_eos, d_shard_lo, G, N, k, d_val_out, d_idx_out, d_eos_out,
                                   (cudaStream_t)stream));
@@ -2409,7 +2416,7 @@ int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, co
 int zrnn_softmax_topk_sharded(zrnn_softmax* S, zrnn_comm* c, const float* d_h, int N, int k, float* d_logp_out,
                               int* d_idx_out, float* d_logp_eos, void* stream) {
   ZR_CHECK(S && c && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk_sharded: bad arguments");
-  ZR_CHECK(k >= 1 && k <= 16, "softmax_topk_sharded: k must be in [1,16]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_sharded: k must be in [1,32]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_sharded: weights not loaded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
