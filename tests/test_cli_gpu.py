@@ -136,3 +136,45 @@ def test_decode_ensemble_of_two_models(tmp_path, oracle):
                                                [np.array(s, dtype=np.int32) for s in xb]], beam=5, k_best=1, longest_sent=40)
     hyps = [[(list(ids[s, 0, :ln[s, 0]]), float(sc[s, 0]))] if ln[s, 0] > 0 else [] for s in range(len(xa))]
     assert open(os.path.join(str(tmp_path), "kbest.txt")).read() == textprep.unint(ma, textprep.format_kbest_ints(hyps, False))
+
+
+def _two_gpus():
+    import torch
+    return torch.cuda.device_count() >= 2
+
+
+@pytest.mark.parametrize("devices", [["0", "0", "0"], ["0", "1", "1"]])
+def test_multi_gpu_flag_shards_sentences(tmp_path, devices):
+    """-M g0 g1 ... : repeated indices are one device (the reference's `-M 0 0 0`), every distinct device gets a worker
+    process with a share of the device batches; the output files are byte-identical to the single-device run."""
+    if len(set(devices)) > 1 and not _two_gpus():
+        pytest.skip("needs two GPUs")
+    cfg = synth.make_cfg(2, 64, 200, 300, attention=1, feed_input=1, D=3)
+    model, sp, tp, w = make_text_fixture(str(tmp_path), cfg, 40, seed=21, max_len=12, scale=0.25)
+    score_args = ["-f", sp, tp, model, None, "-L", "14", "--attention-width", "3", "--device-batch", "8"]
+    dec_args = ["-k", "2", model, None, "--decode-main-data-files", sp, "-b", "5", "-L", "30", "--attention-width", "3",
+                "--dec-ratio", "0.5", "2.0", "--print-score", "1", "--device-batch", "6", "--UNK-decode", None]
+    outs = {}
+    for tag, extra in (("one", []), ("many", ["-M"] + devices)):
+        a = [f"scores_{tag}.txt" if x is None else x for x in score_args] + extra
+        rc, out = run_cli(a, tmp_path)
+        assert rc == 0, out
+        if tag == "many" and len(set(devices)) > 1:
+            assert "Sharding the sentences over 2 devices" in out
+        ppl = out.split("Perplexity dev set: ")[1].split()[0]
+        b = list(dec_args)
+        b[3], b[-1] = f"kbest_{tag}.txt", f"unk_{tag}.txt"
+        rc, out = run_cli(b + extra, tmp_path)
+        assert rc == 0, out
+        outs[tag] = (open(tmp_path / f"scores_{tag}.txt").read(), ppl, open(tmp_path / f"kbest_{tag}.txt").read(),
+                     open(tmp_path / f"unk_{tag}.txt").read())
+    assert outs["one"] == outs["many"]
+    assert len(outs["one"][0].split()) == 40 or len(outs["one"][0].split()) > 20
+    assert not [d for d in os.listdir(str(tmp_path)) if d.startswith("zoph_tmp_")]
+
+
+def test_multi_gpu_flag_rejects_missing_devices(tmp_path):
+    cfg = synth.make_cfg(1, 64, 50, 60, attention=0, feed_input=0)
+    model, sp, tp, w = make_text_fixture(str(tmp_path), cfg, 5, seed=22, max_len=8)
+    rc, out = run_cli(["-f", sp, tp, model, "s.txt", "-M", "0", "63"], tmp_path)
+    assert rc != 0 and "only" in out and "visible" in out

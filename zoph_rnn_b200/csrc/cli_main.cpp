@@ -5,14 +5,17 @@
 // way input_file_prep does, runs every minibatch through the C-ABI library and writes the reference's outputs.
 // Training flags are recognised and refused.  The binary contains no device code: all work goes through zrnn.h.
 #include <sys/stat.h>
+#include <sys/wait.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <fstream>
 #include <iomanip>
 #include <iostream>
 #include <map>
@@ -268,6 +271,7 @@ void remove_tmp_dir(const Params& p) {
   static const char* names[] = {"validation.txt", "decoder_output.txt"};
   for (const char* n : names) unlink((p.unique_dir + "/" + n).c_str());
   for (int k = 0; k < 8; ++k) unlink((p.unique_dir + "/kbest_tmp_" + std::to_string(k)).c_str());
+  for (int k = 0; k < 64; ++k) unlink((p.unique_dir + "/part_" + std::to_string(k) + ".bin").c_str());
   rmdir(p.unique_dir.c_str());
 }
 
@@ -305,12 +309,79 @@ void select_device(const Params& p) {
   if (n <= 0) die("no CUDA device is visible; this program has no CPU path");
   for (int g : p.gpus)
     if (g < 0 || g >= n) die("--multi-gpu names device " + std::to_string(g) + " but only " + std::to_string(n) + " are visible");
-  if (!p.gpus.empty()) {
-    // the reference pipelines layers over these devices; here one device holds the whole model and the rest are
-    // left to other processes (sentences shard across processes, not layers across devices)
-    check_status(zrnn_set_device(p.gpus[0]), "selecting the device");
-    if (p.gpus.size() > 1) logger << "Note: --multi-gpu layer placement is not used; running on device " << p.gpus[0] << "\n";
+  if (!p.gpus.empty()) check_status(zrnn_set_device(p.gpus[0]), "selecting the device");
+}
+
+// ------------------------------------------------------------------------------------------------ sentence sharding
+// The reference's -M g0 g1 ... gsoftmax places the layers and the softmax on those devices (src/main.cu:154,
+// src/model.hpp:34-51) and still runs one minibatch at a time.  Sentences are independent in the forward path, so
+// here every DISTINCT device named by -M gets a worker process that holds the whole model and takes every W-th device
+// batch; there is no exchange between the workers, and the parent merges their results in file order.  The workers
+// are forked before the first CUDA call of the process (a CUDA runtime does not survive a fork) and hand their
+// results back through files in the tmp directory.
+std::vector<int> distinct_devices(const Params& p) {
+  std::vector<int> d;
+  for (int g : p.gpus)
+    if (std::find(d.begin(), d.end(), g) == d.end()) d.push_back(g);
+  return d;
+}
+struct Workers {
+  int W = 1;    // worker processes
+  int me = -1;  // -1: no sharding, this process does everything; >= 0: this process is worker `me`
+  bool mine(int batch_index) const { return me < 0 || batch_index % W == me; }
+};
+std::string part_file(const Params& p, int w) { return p.unique_dir + "/part_" + std::to_string(w) + ".bin"; }
+// Forks one worker per distinct device.  Returns in every worker (me >= 0, its device made the only one of p) and,
+// after all workers have exited successfully, in the parent (me = -1, W = number of workers whose part files wait).
+Workers fork_workers(Params* p, bool* is_parent_of_workers) {
+  Workers wk;
+  *is_parent_of_workers = false;
+  const std::vector<int> dev = distinct_devices(*p);
+  if (dev.size() < 2) return wk;
+  wk.W = (int)dev.size();
+  logger << "Sharding the sentences over " << wk.W << " devices:";
+  for (int g : dev) logger << " " << g;
+  logger << "\n";
+  logger.flush();
+  std::vector<pid_t> pids;
+  for (int w = 0; w < wk.W; ++w) {
+    const pid_t pid = fork();
+    if (pid < 0) die("cannot fork a worker process");
+    if (pid == 0) {
+      wk.me = w;
+      p->gpus.assign(1, dev[w]);
+      return wk;
+    }
+    pids.push_back(pid);
   }
+  bool ok = true;
+  for (size_t w = 0; w < pids.size(); ++w) {
+    int st = 0;
+    if (waitpid(pids[w], &st, 0) < 0 || !WIFEXITED(st) || WEXITSTATUS(st) != 0) {
+      logger << "ERROR: the worker on device " << dev[w] << " failed\n";
+      ok = false;
+    }
+  }
+  if (!ok) { remove_tmp_dir(*p); die("sentence sharding: a worker failed"); }
+  *is_parent_of_workers = true;
+  return wk;
+}
+[[noreturn]] void worker_done() {
+  logger.flush();
+  _exit(0);
+}
+template <class T>
+void put_vec(std::ofstream& os, const std::vector<T>& v) {
+  const long long n = (long long)v.size();
+  os.write((const char*)&n, sizeof(n));
+  if (n) os.write((const char*)v.data(), sizeof(T) * v.size());
+}
+template <class T>
+bool get_vec(std::ifstream& is, std::vector<T>* v) {
+  long long n = 0;
+  if (!is.read((char*)&n, sizeof(n)) || n < 0) return false;
+  v->resize((size_t)n);
+  return n == 0 || (bool)is.read((char*)v->data(), sizeof(T) * v->size());
 }
 
 void print_prep_stats(const PrepStats& st, bool have_source, const char* what) {
@@ -378,9 +449,6 @@ int run_force_decode(const Options& opt, Params& p) {
     logger << "Integer minibatch file: " << int_file << "\n";
     return 0;
   }
-  select_device(p);
-  zrnn_model* model = load_model(p, model_file);
-
   // units = the reference's minibatches; order them by length so a device batch carries little padding
   const int n_units = (int)((recs.size() + p.minibatch - 1) / p.minibatch);
   std::vector<int> unit_len(n_units, 0), order(n_units);
@@ -392,27 +460,62 @@ int run_force_decode(const Options& opt, Params& p) {
   const int cap = p.device_batch > 0 ? p.device_batch : 256;
   std::vector<double> unit_sum(n_units, 0.0);
   long long total_target_words = 0;
-  std::vector<float> logp;
   const auto t0 = std::chrono::steady_clock::now();
-  for (int u0 = 0; u0 < n_units;) {
-    std::vector<int> rows;
-    int u1 = u0;
-    while (u1 < n_units && (rows.empty() || (int)rows.size() + p.minibatch <= cap)) {
-      const int u = order[u1++];
-      for (int r = u * p.minibatch; r < std::min((int)recs.size(), (u + 1) * p.minibatch); ++r) rows.push_back(r);
+  bool merge = false;
+  const Workers wk = fork_workers(&p, &merge);
+  if (merge) {
+    for (int w = 0; w < wk.W; ++w) {
+      std::ifstream is(part_file(p, w).c_str(), std::ios::binary);
+      std::vector<long long> words;
+      std::vector<int> units;
+      std::vector<double> sums;
+      if (!is || !get_vec(is, &words) || !get_vec(is, &units) || !get_vec(is, &sums) || words.size() != 1 ||
+          units.size() != sums.size())
+        die("sentence sharding: cannot read " + part_file(p, w));
+      total_target_words += words[0];
+      for (size_t i = 0; i < units.size(); ++i) unit_sum[units[i]] += sums[i];
     }
-    const Minibatch mb = zrnn::text::make_minibatch(recs, rows);
-    total_target_words += mb.target_words;
-    logp.assign((size_t)mb.T * mb.B, 0.f);
-    double total = 0;
-    check_status(zrnn_score_batch(model, p.sequence ? nullptr : mb.src.data(), mb.S_max, mb.tgt_in.data(),
-                                  mb.tgt_out.data(), mb.T, mb.B, logp.data(), &total), "scoring");
-    for (int b = 0; b < mb.B; ++b) {
-      double s = 0;
-      for (int t = 0; t < mb.T; ++t) s += logp[(size_t)b + (size_t)t * mb.B];
-      unit_sum[rows[b] / p.minibatch] += s;
+  } else {
+    select_device(p);
+    zrnn_model* model = load_model(p, model_file);
+    std::vector<float> logp;
+    std::vector<int> my_units;
+    int batch_index = 0;
+    for (int u0 = 0; u0 < n_units; ++batch_index) {
+      std::vector<int> rows;
+      int u1 = u0;
+      const int first = u1;
+      while (u1 < n_units && (rows.empty() || (int)rows.size() + p.minibatch <= cap)) {
+        const int u = order[u1++];
+        for (int r = u * p.minibatch; r < std::min((int)recs.size(), (u + 1) * p.minibatch); ++r) rows.push_back(r);
+      }
+      u0 = u1;
+      if (!wk.mine(batch_index)) continue;
+      for (int i = first; i < u1; ++i) my_units.push_back(order[i]);
+      const Minibatch mb = zrnn::text::make_minibatch(recs, rows);
+      total_target_words += mb.target_words;
+      logp.assign((size_t)mb.T * mb.B, 0.f);
+      double total = 0;
+      check_status(zrnn_score_batch(model, p.sequence ? nullptr : mb.src.data(), mb.S_max, mb.tgt_in.data(),
+                                    mb.tgt_out.data(), mb.T, mb.B, logp.data(), &total), "scoring");
+      for (int b = 0; b < mb.B; ++b) {
+        double s = 0;
+        for (int t = 0; t < mb.T; ++t) s += logp[(size_t)b + (size_t)t * mb.B];
+        unit_sum[rows[b] / p.minibatch] += s;
+      }
     }
-    u0 = u1;
+    zrnn_model_destroy(model);
+    if (wk.me >= 0) {
+      std::ofstream os(part_file(p, wk.me).c_str(), std::ios::binary);
+      std::vector<double> sums;
+      for (int u : my_units) sums.push_back(unit_sum[u]);
+      put_vec(os, std::vector<long long>(1, total_target_words));
+      put_vec(os, my_units);
+      put_vec(os, sums);
+      os.close();
+      if (!os) die("sentence sharding: cannot write " + part_file(p, wk.me));
+      worker_done();
+    }
   }
   const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
   std::ofstream fd(out_file.c_str());
@@ -430,7 +533,6 @@ int run_force_decode(const Options& opt, Params& p) {
   logger << std::setprecision(15) << "P_data dev set: " << p_data << "\n";
   logger << std::setprecision(6) << "Scored " << (int)recs.size() << " sentences in " << sec << " seconds ("
          << (double)total_target_words / sec << " target words per second)\n";
-  zrnn_model_destroy(model);
   return 0;
 }
 
@@ -487,15 +589,6 @@ int run_decode(const Options& opt, Params& p) {
   }
   if (p.prep_only) return 0;
   const std::vector<std::vector<int>>& sents = sents_k[0];
-  select_device(p);
-  std::vector<zrnn_model*> models(K);
-  for (int k = 0; k < K; ++k) models[k] = load_model(p, model_names[k]);
-  zrnn_model* model = models[0];
-  zrnn_model_config cfg;
-  zrnn_model_get_config(model, &cfg);
-  const int cap_beam = (int)std::floor(std::sqrt((double)cfg.V_tgt));
-  if (p.beam > cap_beam) logger << "Note: beam size " << p.beam << " is capped at floor(sqrt(target vocab)) = " << cap_beam << "\n";
-
   const int n = (int)sents.size();
   const int Lmax = p.longest_sent + 4;
   std::vector<int> all_len((size_t)n * num_hypotheses, 0);
@@ -510,44 +603,92 @@ int run_decode(const Options& opt, Params& p) {
   const int group = p.device_batch > 0 ? p.device_batch : 32;
   const auto t0 = std::chrono::steady_clock::now();
   long long out_words = 0;
-  for (int g0 = 0; g0 < n; g0 += group) {
-    const int g1 = std::min(n, g0 + group), ng = g1 - g0;
-    std::vector<std::vector<int>> flat_k(K), lens_k(K);
-    for (int k = 0; k < K; ++k)
-      for (int i = g0; i < g1; ++i) {
-        const auto& s = sents_k[k][order[i]];
-        if (s.empty()) die("source line with no words cannot be decoded");
-        flat_k[k].insert(flat_k[k].end(), s.begin(), s.end());
-        lens_k[k].push_back((int)s.size());
-      }
-    const std::vector<int>&flat = flat_k[0], &lens = lens_k[0];
-    std::vector<int> ids((size_t)ng * num_hypotheses * Lmax), len((size_t)ng * num_hypotheses);
-    std::vector<float> score((size_t)ng * num_hypotheses);
-    std::vector<int> align(unk ? ids.size() : 0);
-    if (K == 1) {
-      check_status(zrnn_beam_decode_batch_align(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses,
-                                                (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
-                                                ids.data(), len.data(), score.data(), unk ? align.data() : nullptr),
-                   "decoding");
-    } else {
-      std::vector<const int*> fp(K), lp(K);
-      for (int k = 0; k < K; ++k) { fp[k] = flat_k[k].data(); lp[k] = lens_k[k].data(); }
-      check_status(zrnn_beam_decode_ensemble_align(models.data(), K, fp.data(), lp.data(), ng, p.beam, num_hypotheses,
-                                                   (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty,
-                                                   p.longest_sent, ids.data(), len.data(), score.data(),
-                                                   unk ? align.data() : nullptr), "ensemble decoding");
+  bool merge = false;
+  const Workers wk = fork_workers(&p, &merge);
+  // copies the hypotheses of sentence `s` from a group's arrays (position i) into the file-order arrays
+  auto keep = [&](int s, size_t i, const std::vector<int>& ids, const std::vector<int>& len, const std::vector<float>& score,
+                  const std::vector<int>& align) {
+    const size_t dst = (size_t)s * num_hypotheses;
+    for (int h = 0; h < num_hypotheses; ++h) {
+      all_len[dst + h] = len[i * num_hypotheses + h];
+      all_score[dst + h] = score[i * num_hypotheses + h];
+      std::memcpy(&all_ids[(dst + h) * Lmax], &ids[(i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
+      if (unk) std::memcpy(&all_align[(dst + h) * Lmax], &align[(i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
+      out_words += all_len[dst + h];
     }
-    for (int i = 0; i < ng; ++i) {
-      const size_t dst = (size_t)order[g0 + i] * num_hypotheses;
-      for (int h = 0; h < num_hypotheses; ++h) {
-        all_len[dst + h] = len[(size_t)i * num_hypotheses + h];
-        all_score[dst + h] = score[(size_t)i * num_hypotheses + h];
-        std::memcpy(&all_ids[(dst + h) * Lmax], &ids[((size_t)i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
-        if (unk) std::memcpy(&all_align[(dst + h) * Lmax], &align[((size_t)i * num_hypotheses + h) * Lmax], sizeof(int) * Lmax);
-        out_words += all_len[dst + h];
-      }
+  };
+  if (merge) {
+    for (int w = 0; w < wk.W; ++w) {
+      std::ifstream is(part_file(p, w).c_str(), std::ios::binary);
+      std::vector<int> which, ids, len, align;
+      std::vector<float> score;
+      if (!is || !get_vec(is, &which) || !get_vec(is, &ids) || !get_vec(is, &len) || !get_vec(is, &score) ||
+          !get_vec(is, &align) || len.size() != which.size() * (size_t)num_hypotheses || score.size() != len.size() ||
+          ids.size() != len.size() * (size_t)Lmax || (unk && align.size() != ids.size()))
+        die("sentence sharding: cannot read " + part_file(p, w));
+      for (size_t i = 0; i < which.size(); ++i) keep(which[i], i, ids, len, score, align);
     }
-    logger << "Decoded " << g1 << " of " << n << " sentences\n";
+  } else {
+    select_device(p);
+    std::vector<zrnn_model*> models(K);
+    for (int k = 0; k < K; ++k) models[k] = load_model(p, model_names[k]);
+    zrnn_model* model = models[0];
+    zrnn_model_config cfg;
+    zrnn_model_get_config(model, &cfg);
+    const int cap_beam = (int)std::floor(std::sqrt((double)cfg.V_tgt));
+    if (p.beam > cap_beam) logger << "Note: beam size " << p.beam << " is capped at floor(sqrt(target vocab)) = " << cap_beam << "\n";
+    std::vector<int> my_which, my_ids, my_len, my_align;
+    std::vector<float> my_score;
+    for (int g0 = 0, batch_index = 0; g0 < n; g0 += group, ++batch_index) {
+      if (!wk.mine(batch_index)) continue;
+      const int g1 = std::min(n, g0 + group), ng = g1 - g0;
+      std::vector<std::vector<int>> flat_k(K), lens_k(K);
+      for (int k = 0; k < K; ++k)
+        for (int i = g0; i < g1; ++i) {
+          const auto& s = sents_k[k][order[i]];
+          if (s.empty()) die("source line with no words cannot be decoded");
+          flat_k[k].insert(flat_k[k].end(), s.begin(), s.end());
+          lens_k[k].push_back((int)s.size());
+        }
+      const std::vector<int>&flat = flat_k[0], &lens = lens_k[0];
+      std::vector<int> ids((size_t)ng * num_hypotheses * Lmax), len((size_t)ng * num_hypotheses);
+      std::vector<float> score((size_t)ng * num_hypotheses);
+      std::vector<int> align(unk ? ids.size() : 0);
+      if (K == 1) {
+        check_status(zrnn_beam_decode_batch_align(model, flat.data(), lens.data(), ng, p.beam, num_hypotheses,
+                                                  (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty, p.longest_sent,
+                                                  ids.data(), len.data(), score.data(), unk ? align.data() : nullptr),
+                     "decoding");
+      } else {
+        std::vector<const int*> fp(K), lp(K);
+        for (int k = 0; k < K; ++k) { fp[k] = flat_k[k].data(); lp[k] = lens_k[k].data(); }
+        check_status(zrnn_beam_decode_ensemble_align(models.data(), K, fp.data(), lp.data(), ng, p.beam, num_hypotheses,
+                                                     (float)p.min_ratio, (float)p.max_ratio, (float)p.penalty,
+                                                     p.longest_sent, ids.data(), len.data(), score.data(),
+                                                     unk ? align.data() : nullptr), "ensemble decoding");
+      }
+      for (int i = 0; i < ng; ++i) keep(order[g0 + i], (size_t)i, ids, len, score, align);
+      if (wk.me >= 0) {
+        for (int i = 0; i < ng; ++i) my_which.push_back(order[g0 + i]);
+        my_ids.insert(my_ids.end(), ids.begin(), ids.end());
+        my_len.insert(my_len.end(), len.begin(), len.end());
+        my_score.insert(my_score.end(), score.begin(), score.end());
+        my_align.insert(my_align.end(), align.begin(), align.end());
+      }
+      logger << "Decoded " << g1 << " of " << n << " sentences" << (wk.me >= 0 ? " (device " + std::to_string(p.gpus[0]) + ")" : "") << "\n";
+    }
+    for (zrnn_model* m : models) zrnn_model_destroy(m);
+    if (wk.me >= 0) {
+      std::ofstream os(part_file(p, wk.me).c_str(), std::ios::binary);
+      put_vec(os, my_which);
+      put_vec(os, my_ids);
+      put_vec(os, my_len);
+      put_vec(os, my_score);
+      put_vec(os, my_align);
+      os.close();
+      if (!os) die("sentence sharding: cannot write " + part_file(p, wk.me));
+      worker_done();
+    }
   }
   const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
   {
@@ -580,7 +721,6 @@ int run_decode(const Options& opt, Params& p) {
   if (!zrnn::text::unint_file(vocab, int_out, final_file, true, &err)) die(err);
   logger << std::setprecision(6) << "Decoded " << n << " sentences in " << sec << " seconds (" << (double)out_words / sec
          << " output words per second)\n";
-  for (zrnn_model* m : models) zrnn_model_destroy(m);
   return 0;
 }
 
@@ -598,7 +738,8 @@ void print_help() {
       "      --dec-ratio MIN MAX decoding length ratios (default 0.5 1.5)\n"
       "  -L, --longest-sent N    maximum sentence length (default 100)\n"
       "  -m, --minibatch-size N  minibatch size of the sequence force-decode (default 8)\n"
-      "  -M, --multi-gpu I ...   device indices; the first is used\n"
+      "  -M, --multi-gpu I ...   device indices; every distinct device gets a worker process with the whole model and\n"
+      "                          a share of the sentences (the reference places layers on them instead)\n"
       "      --attention-width D local attention half window (default 10)\n"
       "      --tmp-dir-location DIR, --logfile FILE, --legacy-model B\n"
       "  options of this program: --attention-type local-p|global-dot, --dtype f32|bf16|tf32|f32-simt|f32-3xtf32|f32-f16x2,\n"
