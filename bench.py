@@ -44,6 +44,10 @@ WORKLOADS = {
     "c3": dict(desc="seq2seq 2x1000 V=40k/40k B=64 S~U[10,80] T=60 local-p D=10 + feed-input fp32", kind="s2s",
                L=2, H=1000, Vs=40000, Vt=40000, B=64, S=(10, 80), T=(60, 60), att=1, feed=1, scale=0.1,
                dist="uniform", zipf=1.1),
+    # small stand-in with config 3's layer shapes (H=1000, B=64, local-p D=10, feed-input, ragged sources)
+    "c3s": dict(desc="profiling stand-in: 1x1000 V=8k/8k B=64 S~U[10,24] T=4 local-p D=10 + feed-input fp32", kind="s2s",
+                L=1, H=1000, Vs=8000, Vt=8000, B=64, S=(10, 24), T=(4, 4), att=1, feed=1, scale=0.1,
+                dist="uniform", zipf=1.1),
     "c4": dict(desc="beam decode 2x1000 V=50k global-dot attention beam 12, 64 sentences S~U[10,50]", kind="decode",
                L=2, H=1000, Vs=50000, Vt=50000, B=64, S=(10, 50), T=None, att=2, feed=1, scale=0.1,
                dist="uniform", zipf=1.1, beam=12, max_ratio=2.0, min_ratio=0.5, longest_sent=100),
