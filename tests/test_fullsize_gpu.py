@@ -87,8 +87,15 @@ def test_config3_full_size_logprobs(api, oracle):
         helpers.assert_logp_close(lp, want, rtol=helpers.LOGP_RTOL + floor)
         err = np.abs(lp - want) / np.abs(np.where(want == 0, 1, want))
         assert err[tout != -1].mean() < 2e-6
-    lp, _ = build_model(api, cfg, w, BF16).get_error(src, tin, tout)
-    assert abs(ppl(lp, tout) - ppl(want, tout)) / ppl(want, tout) < 5e-3
+    # Perplexity is a corpus statistic.  bf16 moves single tokens by ~0.1 nat (zero-mean; a quarter of the tokens by
+    # more than 0.05 nat, because a rounded p_t shifts whole windows), so on these 480 tokens its sampling noise
+    # (0.1 / sqrt(480) = 0.46 %) is as large as the 0.5 % gate.  32 sentences (1920 tokens) measure it.
+    src, tin, tout = synth.make_s2s_batch(40000, 40000, 32, 10, 80, 60, 60, seed=1234, zipf_s=1.1)
+    want = om.score_batch(src, tin, tout)
+    for dtype in (BF16, TF32):
+        lp, _ = build_model(api, cfg, w, dtype).get_error(src, tin, tout)
+        assert abs(ppl(lp, tout) - ppl(want, tout)) / ppl(want, tout) < 5e-3, f"dtype {dtype}"
+        assert np.abs(lp - want)[tout != -1].mean() < 0.08
 
 
 def test_config3_near_integer_window_position(api, oracle):

@@ -39,7 +39,8 @@ struct SyncCta {  // the team is a whole CTA
   __device__ __forceinline__ void operator()() const { __syncthreads(); }
 };
 constexpr int kAttTeam = 256;                                         // threads per column team
-constexpr int kAttLocalScratchBytes = (32 + ZR_ATT_MAXW) * 4 + ZR_ATT_MAXW * 4 + 16;
+constexpr int kAttLocalSmall = (32 + ZR_ATT_MAXW) * 4 + ZR_ATT_MAXW * 4 + 16;      // sums, weights, slots, p_t, window
+constexpr int kAttLocalScratchBytes = 8 * 256 * 16 + ((kAttLocalSmall + 15) / 16) * 16;  // + 8 partial contexts
 constexpr int kAttGlobalScratchBytes = 8 * 256 * 16 + 4 * 8 * 4;
 
 // sum over the team; result valid in every thread.  `red` holds 32 floats.
@@ -63,16 +64,17 @@ __device__ __forceinline__ float team_sum(float v, float* red, int tid, Sync syn
 // kernels of src/custom_kernels.h:1581-1813): p_t from tanh(W_p h) and v_p, the window [p_t - D, p_t + D] cut at the
 // sentence, scores h_s . (W_a^T h), softmax over the valid window positions with the maximum started at 0, the
 // un-renormalised Gaussian, the context.  16-byte loads, and no data-dependent branch inside the loops over the
-// window, so the loads of all window slots are in flight together.  An empty slot gets weight 0 and reads row 0 of
-// the source memory.
+// window.  An empty slot gets weight 0 and reads row 0 of the source memory.
+// Windows of up to 24 slots (D <= 11; the reference's default D is 10) take the register path: warp w owns slots w,
+// w + 8, w + 16, requests their rows in one go, keeps them in registers for the score AND the context (the source
+// memory is read once), and the eight partial contexts meet in shared memory.  Wider windows walk the slots twice.
 template <class Sync>
 __device__ __forceinline__ void att_local_fast_body(const AttArgs& a, const int b, const int tid, unsigned char* scratch,
                                                     Sync sync) {
-  float* red = reinterpret_cast<float*>(scratch);
+  float4(*s_ctx)[256] = reinterpret_cast<float4(*)[256]>(scratch);
+  float* red = reinterpret_cast<float*>(scratch + 8 * 256 * 16);
   float* s_al = red + 32;
   int* s_slot = reinterpret_cast<int*>(s_al + ZR_ATT_MAXW);
-  float* s_p = reinterpret_cast<float*>(s_slot + ZR_ATT_MAXW);
-  int* s_lohi = reinterpret_cast<int*>(s_p + 1);
   const int lane = tid & 31, w = tid >> 5;
   const int H = a.H, H4 = H >> 2, Wn = 2 * a.D + 1, sb = b / a.cols_per_sent;
   float* c = a.c_t + (size_t)b * H;
@@ -91,18 +93,7 @@ __device__ __forceinline__ void att_local_fast_body(const AttArgs& a, const int 
     const float4 t = reinterpret_cast<const float4*>(a.tanh1 + (size_t)b * a.ld_tq)[tid];
     part = v.x * t.x + v.y * t.y + v.z * t.z + v.w * t.w;
   }
-  const float tot = team_sum(part, red, tid, sync);
-  const int len = a.len[sb], off = a.offset[sb];
-  if (tid == 0) {
-    const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)tot)));
-    const float pt = len * sg;
-    const int ip = (int)pt;
-    *s_p = pt;
-    s_lohi[0] = (0 > ip - a.D) ? 0 : (ip - a.D);
-    s_lohi[1] = ((len - 1) < ip + a.D) ? (len - 1) : (ip + a.D);
-  }
-  sync();
-  const int lo = s_lohi[0], hi = s_lohi[1];
+  // q = W_a^T h does not depend on the window: request it before the reduction
   const float4* q4 = reinterpret_cast<const float4*>(a.q + (size_t)b * a.ld_tq);
   float4 qv[8];
 #pragma unroll
@@ -110,49 +101,100 @@ __device__ __forceinline__ void att_local_fast_body(const AttArgs& a, const int 
     const int j4 = lane + 32 * i;
     qv[i] = j4 < H4 ? q4[j4] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (int j = w; j < Wn; j += 8) {
-    const int pos = lo + j;
-    const bool valid = pos <= hi;
-    const int slot = valid ? len - 1 - pos + off : 0;  // an empty slot reads row 0 and is discarded
-    const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)slot * a.B_src + sb) * H);
-    float sc = 0.f;
+  const float tot = team_sum(part, red, tid, sync);
+  const int len = a.len[sb], off = a.offset[sb];
+  // every thread derives the window itself (the same arithmetic on the same value: no barrier needed for it)
+  const float sg = (float)(1.0 / (1.0 + exp(-1.0 * (double)tot)));
+  const float pt = len * sg;
+  const int ip = (int)pt;
+  const int lo = (0 > ip - a.D) ? 0 : (ip - a.D);
+  const int hi = ((len - 1) < ip + a.D) ? (len - 1) : (ip + a.D);
+  const bool reg_path = Wn <= 24;
+  float4 rows[3][8];
+  if (reg_path) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int j4 = lane + 32 * i;
-      if (j4 < H4) {
-        const float4 r = __ldg(r4 + j4);
-        sc += r.x * qv[i].x + r.y * qv[i].y + r.z * qv[i].z + r.w * qv[i].w;
+    for (int u = 0; u < 3; ++u) {
+      const int j = w + 8 * u, pos = lo + j;
+      const bool valid = j < Wn && pos <= hi;
+      const int slot = valid ? len - 1 - pos + off : 0;
+      const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)slot * a.B_src + sb) * H);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j4 = lane + 32 * i;
+        rows[u][i] = j4 < H4 ? __ldg(r4 + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    sc = warp_sum(sc);
-    if (lane == 0) { s_al[j] = valid ? sc : 0.f; s_slot[j] = valid ? slot : -1; }
+#pragma unroll
+    for (int u = 0; u < 3; ++u) {
+      const int j = w + 8 * u, pos = lo + j;
+      const bool valid = j < Wn && pos <= hi;
+      float sc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        sc += rows[u][i].x * qv[i].x + rows[u][i].y * qv[i].y + rows[u][i].z * qv[i].z + rows[u][i].w * qv[i].w;
+      sc = warp_sum(sc);
+      if (lane == 0 && j < Wn) { s_al[j] = valid ? sc : 0.f; s_slot[j] = valid ? len - 1 - pos + off : -1; }
+    }
+  } else {
+    for (int j = w; j < Wn; j += 8) {
+      const int pos = lo + j;
+      const bool valid = pos <= hi;
+      const int slot = valid ? len - 1 - pos + off : 0;  // an empty slot reads row 0 and is discarded
+      const float4* r4 = reinterpret_cast<const float4*>(a.hs + ((size_t)slot * a.B_src + sb) * H);
+      float sc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j4 = lane + 32 * i;
+        if (j4 < H4) {
+          const float4 r = __ldg(r4 + j4);
+          sc += r.x * qv[i].x + r.y * qv[i].y + r.z * qv[i].z + r.w * qv[i].w;
+        }
+      }
+      sc = warp_sum(sc);
+      if (lane == 0) { s_al[j] = valid ? sc : 0.f; s_slot[j] = valid ? slot : -1; }
+    }
   }
   sync();
-  if (tid == 0) {
-    float sum = 0.f, mx = 0.f;  // the reference starts the max at 0
-    for (int j = 0; j < Wn; ++j)
-      if (s_slot[j] != -1 && s_al[j] > mx) mx = s_al[j];
-    for (int j = 0; j < Wn; ++j) {
-      if (s_slot[j] != -1) { s_al[j] = expf(s_al[j] - mx); sum += s_al[j]; }
-      else s_al[j] = 0.f;
-    }
-    const float sigma_sq = (float)((a.D * a.D) / 4.0);
-    for (int j = 0; j < Wn; ++j) {
-      if (s_slot[j] != -1) {
-        const float d = *s_p - (float)(lo + j);
-        const float gs = expf((-1.f * d * d) / (2.f * sigma_sq));
-        if (sum != 0.f) s_al[j] = (s_al[j] / sum) * gs;
+  // softmax over the window by the first warps, one slot per lane (the sums are warp reductions)
+  {
+    if (w == 0) {
+      float mx = 0.f;  // the reference starts the max at 0
+      for (int j = lane; j < Wn; j += 32)
+        if (s_slot[j] != -1) mx = fmaxf(mx, s_al[j]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float e[2] = {0.f, 0.f};
+      float sum = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int j = lane + 32 * u;
+        if (j < Wn && s_slot[j] != -1) e[u] = expf(s_al[j] - mx);
+        sum += e[u];
+      }
+      sum = warp_sum(sum);
+      const float sigma_sq = (float)((a.D * a.D) / 4.0);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int j = lane + 32 * u;
+        if (j < Wn) {
+          float v = e[u];
+          if (s_slot[j] != -1) {
+            const float d = pt - (float)(lo + j);
+            const float gs = expf((-1.f * d * d) / (2.f * sigma_sq));
+            if (sum != 0.f) v = (v / sum) * gs;
+          }
+          s_al[j] = v;
+        }
+      }
+      __syncwarp();
+      if (a.viterbi_out && lane == 0) {
+        float best = a.viterbi_init;
+        int best_pos = -1;
+        for (int j = 0; j < Wn; ++j)
+          if (best < s_al[j]) { best = s_al[j]; best_pos = (s_slot[j] != -1) ? lo + j : -1; }
+        a.viterbi_out[b] = best_pos;
       }
     }
-    if (a.viterbi_out) {
-      float best = a.viterbi_init;
-      int best_pos = -1;
-      for (int j = 0; j < Wn; ++j)
-        if (best < s_al[j]) { best = s_al[j]; best_pos = (s_slot[j] != -1) ? lo + j : -1; }
-      a.viterbi_out[b] = best_pos;
-    }
-    for (int j = 0; j < Wn; ++j)
-      if (s_slot[j] == -1) s_slot[j] = 0;  // weight 0, any readable row
   }
   sync();
   if (a.align_out) {
@@ -165,13 +207,41 @@ __device__ __forceinline__ void att_local_fast_body(const AttArgs& a, const int 
       for (int j = tid; j < Wn; j += kAttTeam) a.align_out[(size_t)j * a.B + b] = s_al[j];
     }
   }
-  if (tid < H4) {
+  if (reg_path) {
+    // each warp's share of the context from the rows it still holds, then the eight shares in a fixed order
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const int j = w + 8 * u;
+        const float wj = (j < Wn) ? s_al[j] : 0.f;
+        acc.x += wj * rows[u][i].x; acc.y += wj * rows[u][i].y; acc.z += wj * rows[u][i].z; acc.w += wj * rows[u][i].w;
+      }
+      s_ctx[w][lane + 32 * i] = acc;
+    }
+    sync();
+    if (tid < H4) {
+      float4 acc = s_ctx[0][tid];
+#pragma unroll
+      for (int q = 1; q < 8; ++q) {
+        const float4 r = s_ctx[q][tid];
+        acc.x += r.x; acc.y += r.y; acc.z += r.z; acc.w += r.w;
+      }
+      reinterpret_cast<float4*>(c)[tid] = acc;
+      att_store_op(a, b, 4 * tid + 0, acc.x);
+      att_store_op(a, b, 4 * tid + 1, acc.y);
+      att_store_op(a, b, 4 * tid + 2, acc.z);
+      att_store_op(a, b, 4 * tid + 3, acc.w);
+    }
+  } else if (tid < H4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const size_t colb = (size_t)sb * H;
 #pragma unroll 7
     for (int j = 0; j < Wn; ++j) {
       const float wj = s_al[j];
-      const float4 r = __ldg(reinterpret_cast<const float4*>(a.hs + (size_t)s_slot[j] * a.B_src * H + colb) + tid);
+      const int slot = s_slot[j] == -1 ? 0 : s_slot[j];  // weight 0, any readable row
+      const float4 r = __ldg(reinterpret_cast<const float4*>(a.hs + (size_t)slot * a.B_src * H + colb) + tid);
       acc.x += wj * r.x; acc.y += wj * r.y; acc.z += wj * r.z; acc.w += wj * r.w;
     }
     reinterpret_cast<float4*>(c)[tid] = acc;
