@@ -1892,9 +1892,21 @@ struct zrnn_comm {
   int lo_V = -1;                   // vocabulary size lo_buf was computed for
   cudaEvent_t ev[6] = {};          // stage boundaries of the last sharded scoring call
   float stage_ms[5] = {};
+  void* pin = nullptr;             // page-locked host staging for the ids going in and the log-probabilities coming out
+  size_t pin_cap = 0;
+  cudaError_t pin_reserve(size_t bytes) {
+    if (bytes <= pin_cap) return cudaSuccess;
+    if (pin) cudaFreeHost(pin);
+    pin = nullptr;
+    pin_cap = 0;
+    cudaError_t e = cudaHostAlloc(&pin, bytes, cudaHostAllocDefault);
+    if (e == cudaSuccess) pin_cap = bytes;
+    return e;
+  }
   ~zrnn_comm() {
     send.release(); recv.release(); aux.release(); lo_buf.release();
     for (auto& e : ev) if (e) cudaEventDestroy(e);
+    if (pin) cudaFreeHost(pin);
   }
 };
 
@@ -2461,8 +2473,12 @@ int zrnn_score_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, in
   shard_range(B, G, c->rank, &b_lo, &b_hi);
   const size_t nS = (size_t)S * Bp, nT = (size_t)T * Bp, nAll = nT * G;
   // this rank's columns, and the target words of ALL columns in gathered order (rank, step, local column)
-  std::vector<int> h_ids(nS + nT + nAll, -1);
-  int* l_src = h_ids.data();
+  const size_t n_ids = nS + nT + nAll;
+  ZR_CUDA(c->pin_reserve(aligned(sizeof(int) * n_ids) + sizeof(float) * nAll));
+  int* h_ids = (int*)c->pin;
+  float* h_lp = (float*)((char*)c->pin + aligned(sizeof(int) * n_ids));
+  std::fill(h_ids, h_ids + n_ids, -1);
+  int* l_src = h_ids;
   int* l_tin = l_src + nS;
   int* a_tout = l_tin + nT;
   for (int b = b_lo; b < b_hi; ++b) {
@@ -2478,19 +2494,19 @@ int zrnn_score_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, in
   const Geom geo{H, round64(H), m->eng};
   const bool op_gather = m->eng == ENG_BF16;  // the bf16 engine's operand form is half the bytes of the fp32 states
   const size_t col_bytes = op_gather ? (size_t)geo.Kpad * 2 : sizeof(float) * (size_t)H;
-  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * h_ids.size()) + 2 * aligned(sizeof(int) * nAll) + aligned(sizeof(float) * nAll)));
+  ZR_CUDA(m->io.reserve(aligned(sizeof(int) * n_ids) + 2 * aligned(sizeof(int) * nAll) + aligned(sizeof(float) * nAll)));
   ZR_CUDA(c->recv.reserve(col_bytes * nAll));
   ZR_CUDA(c->send.reserve(3 * sizeof(float) * nAll));
   ZR_CUDA(c->aux.reserve(3 * sizeof(float) * nAll * G));
   Carver cv(m->io.p);
-  int* d_ids = cv.take<int>(h_ids.size());
+  int* d_ids = cv.take<int>(n_ids);
   int* d_tout = cv.take<int>(nAll);
   int* d_mask = cv.take<int>(nAll);
   float* d_lp = cv.take<float>(nAll);
   cudaStream_t s = m->stream;
   for (auto& e : c->ev) if (!e) ZR_CUDA(cudaEventCreate(&e));
   ZR_CUDA(cudaEventRecord(c->ev[0], s));
-  ZR_CUDA(cudaMemcpyAsync(d_ids, h_ids.data(), sizeof(int) * h_ids.size(), cudaMemcpyHostToDevice, s));
+  ZR_CUDA(cudaMemcpyAsync(d_ids, h_ids, sizeof(int) * n_ids, cudaMemcpyHostToDevice, s));
   m->drop_graph();
   ZR_TRY(score_batch_body(m, S ? d_ids : nullptr, S, d_ids + nS, d_ids + nS, T, Bp, nullptr, s));
   const Act top = m->last_top_act;
@@ -2521,8 +2537,7 @@ int zrnn_score_batch_sharded(zrnn_model* m, zrnn_comm* c, const int* src_ids, in
   const float* r = c->aux.as<float>();
   ZR_CUDA(zrnn::launch_lse_combine_shards(r, r + nAll, r + 2 * nAll, G, (int)nAll, d_mask, d_lp, s, 3 * nAll));
   ZR_CUDA(cudaEventRecord(c->ev[4], s));
-  std::vector<float> h_lp(nAll);
-  ZR_CUDA(cudaMemcpyAsync(h_lp.data(), d_lp, sizeof(float) * nAll, cudaMemcpyDeviceToHost, s));
+  ZR_CUDA(cudaMemcpyAsync(h_lp, d_lp, sizeof(float) * nAll, cudaMemcpyDeviceToHost, s));
   ZR_CUDA(cudaEventRecord(c->ev[5], s));
   ZR_CUDA(cudaStreamSynchronize(s));
   for (int i = 0; i < 5; ++i) ZR_CUDA(cudaEventElapsedTime(&c->stage_ms[i], c->ev[i], c->ev[i + 1]));
