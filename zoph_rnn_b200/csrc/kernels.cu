@@ -473,27 +473,50 @@ cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, c
 __device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, const float* __restrict__ ps,
                                                   int n_parts, size_t N, int n, bool active, float* s_m /*[8][32]*/,
                                                   double* s_s /*[8][32]*/, float* mx_out, double* sum_out) {
-  // N: distance (in floats) between two parts' rows
+  // N: distance (in floats) between two parts' rows.  One pass: every thread keeps a running (max, sum) over its
+  // parts, rescaling the sum when the maximum moves, and requests four parts' values before it uses any of them (the
+  // loop is a chain of L2 round trips otherwise); the eight (max, sum) pairs of a column meet in shared memory.
   const int cx = threadIdx.x, py = threadIdx.y;
   float mx = -INFINITY;
-  if (active)
-    for (int i = py; i < n_parts; i += 8) mx = fmaxf(mx, pm[(size_t)i * N + n]);
-  s_m[py * 32 + cx] = mx;
-  __syncthreads();
-#pragma unroll
-  for (int q = 0; q < 8; ++q) mx = fmaxf(mx, s_m[q * 32 + cx]);
   double sum = 0.0;
-  if (active)
-    for (int i = py; i < n_parts; i += 8) {
-      const float m = pm[(size_t)i * N + n];
-      if (m != -INFINITY) sum += (double)(ps[(size_t)i * N + n] * expf(m - mx));
+  if (active) {
+    for (int i0 = py; i0 < n_parts; i0 += 32) {
+      float m4[4], s4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + 8 * u;
+        const bool in = i < n_parts;
+        m4[u] = in ? pm[(size_t)i * N + n] : -INFINITY;
+        s4[u] = in ? ps[(size_t)i * N + n] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float m = m4[u];
+        if (m == -INFINITY) continue;
+        if (m > mx) {
+          sum = sum * (double)expf(mx - m) + (double)s4[u];  // expf(-inf) = 0 on the first part
+          mx = m;
+        } else {
+          sum += (double)(s4[u] * expf(m - mx));
+        }
+      }
     }
+  }
+  s_m[py * 32 + cx] = mx;
   s_s[py * 32 + cx] = sum;
   __syncthreads();
   if (py == 0) {
-    sum = 0.0;
+    float M = mx;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) sum += s_s[q * 32 + cx];
+    for (int q = 1; q < 8; ++q) M = fmaxf(M, s_m[q * 32 + cx]);
+    double S = 0.0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float mq = s_m[q * 32 + cx];
+      if (mq != -INFINITY) S += s_s[q * 32 + cx] * (double)expf(mq - M);
+    }
+    mx = M;
+    sum = S;
   }
   *mx_out = mx;
   *sum_out = sum;
@@ -1184,6 +1207,8 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
   const int H = a.H, B = a.B, Bp = CG * CPT;
   float4* Wt = reinterpret_cast<float4*>(seq_smem);                       // [H][Hc]
   float* hb = reinterpret_cast<float*>(seq_smem + (size_t)H * Hc * 16);   // [2][H][Bp]
+  // one transaction barrier per copy of h: the bytes of a step's exchange complete it (no cluster barrier per step)
+  uint64_t* hbar = reinterpret_cast<uint64_t*>(seq_smem + (size_t)H * Hc * 16 + ((2 * (size_t)H * Bp * 4 + 15) / 16) * 16);
   unsigned rank, csize;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
@@ -1205,6 +1230,12 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
     hb[e] = c < B ? a.h0[(size_t)c * H + k] : 0.f;
     hb[(size_t)H * Bp + e] = 0.f;
   }
+  if (tid == 0) {
+    const uint32_t b0 = (uint32_t)__cvta_generic_to_shared(hbar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b0));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b0 + 8));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   const int jl = tid % Hc, cg = tid / Hc;
   const bool active = cg < CG && jl < nj;
   const int j = j0 + jl, cb = cg * CPT;  // unit and first column of this thread
@@ -1215,18 +1246,33 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
   if (active) { bi = a.bias[j]; bf = a.bias[H + j]; bg = a.bias[2 * H + j]; bo = a.bias[3 * H + j]; }
   // every copy of h_0 is in place before anybody reads or overwrites one
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  uint32_t hb_remote[8];
+  uint32_t hb_remote[8], bar_remote[8];
+  const uint32_t bar_local = (uint32_t)__cvta_generic_to_shared(hbar);
   {
     const uint32_t local = (uint32_t)__cvta_generic_to_shared(hb);
     for (unsigned q = 0; q < 8; ++q) {
-      uint32_t r = local;
-      if (q < csize) asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(q));
+      uint32_t r = local, rb = bar_local;
+      if (q < csize) {
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(q));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(bar_local), "r"(q));
+      }
       hb_remote[q] = r;
+      bar_remote[q] = rb;
     }
   }
-  for (int t = 0; t < a.S; ++t) {
+  // Exchange protocol.  Step t reads h_t from copy t & 1 and sends h_(t+1) into copy (t + 1) & 1 of EVERY CTA of the
+  // cluster (its own included) with st.async, whose bytes count on the receiver's barrier of that copy; a step
+  // starts when the barrier of its copy has all H * B values.  Two copies suffice: a CTA sends h_(t+2) into the copy
+  // that held h_t only after it has received every h_(t+1), and each of those was sent after its sender's last read
+  // of h_t.  The wait is bounded; a thread that gives up sets the error word and leaves (so do all others, in turn).
+  const uint32_t step_bytes = (uint32_t)H * (uint32_t)B * 4u;
+  bool alive = true;
+  for (int t = 0; t < a.S && alive; ++t) {
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
+    if (tid == 0 && t + 1 < a.S)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_local + 8u * ((t + 1) & 1)), "r"(step_bytes)
+                   : "memory");
     float4 xp[CPT];
     float mk[CPT];
     if (active) {  // the inputs of the epilogue do not depend on the recurrence: request them before the k loop
@@ -1240,7 +1286,27 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
     float ai[CPT], af[CPT], ag[CPT], ao[CPT], hnew[CPT];
 #pragma unroll
     for (int c = 0; c < CPT; ++c) ai[c] = af[c] = ag[c] = ao[c] = hnew[c] = 0.f;
-    if (active) {
+    if (active && t > 0) {  // h_t complete in this CTA's copy?
+      const uint32_t bar = bar_local + 8u * (t & 1), parity = (uint32_t)((t - 1) >> 1) & 1u;
+      const long long t0 = clock64();
+      for (int spins = 0;; ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+        if ((spins & 63) == 63 && clock64() - t0 > 400000000LL) {
+          if (a.err) atomicExch(a.err, 88);
+          alive = false;
+          break;
+        }
+      }
+    }
+    if (active && alive) {
       const float4* wp = Wt + jl;
       const float* hp = hcur + cb;
 #pragma unroll 4
@@ -1266,17 +1332,18 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
           const float hn = go * tanhf(cn) * mk[c];
           cst[c] = cn * mk[c];
           hnew[c] = hn;
-          // the new h into every CTA's copy of the other buffer
-          const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + cb + c) * 4);
-          for (unsigned q = 0; q < csize; ++q)
-            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(hb_remote[q] + off), "f"(hn) : "memory");
+          // the new h into every CTA's copy of the other buffer (nobody reads the last step's)
+          if (t + 1 < a.S) {
+            const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + cb + c) * 4);
+            const uint32_t boff = 8u * ((t + 1) & 1);
+            for (unsigned q = 0; q < csize; ++q)
+              asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(hb_remote[q] + off),
+                           "r"(__float_as_uint(hn)), "r"(bar_remote[q] + boff)
+                           : "memory");
+          }
         }
       }
-    }
-    // the arrival publishes the exchange; the copies for the consumers outside the kernel go out while the barrier
-    // completes (they need not be visible to the cluster, so they stay off the step's critical path)
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    if (active) {
+      // the copies for the consumers outside the kernel, off the step's critical path
 #pragma unroll
       for (int c = 0; c < CPT; ++c) {
         if (cb + c < B) {
@@ -1286,12 +1353,183 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
         }
       }
     }
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
+  // no CTA leaves while a peer may still write into its shared memory or wait for its bytes
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   if (active)
 #pragma unroll
     for (int c = 0; c < CPT; ++c)
       if (cb + c < B) a.c_out[(size_t)(cb + c) * H + j] = cst[c];
+}
+
+// The same time loop for the narrowest case (at most 8 columns, 64 <= H <= 128: configuration 1), with the recurrent
+// weights in REGISTERS and a warp per hidden unit.  In the kernel above a step is one long dependent instruction
+// stream per thread (a thousand instructions at one warp per scheduler: every stall is exposed), and every thread
+// re-reads its unit's weights from shared memory at every k.  Here lane s of a unit's warp keeps the unit's 4 x 4
+// weights of k = s, s + 32, s + 64, s + 96 in registers for the whole sequence, reads h_t[k][0..7] (32 bytes) and
+// accumulates all 8 columns: 128 FMAs per lane and step.  A 31-shuffle butterfly leaves lane s with gate s / 8 of
+// column s % 8; lanes 0..7 fetch their column's other three gates, do the gate math, keep c, and send h.  Thirteen
+// to sixteen warps per CTA hide each other's latencies.  Cluster of 8 CTAs, exchange and barriers as above.
+__global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, int Hc) {
+  extern __shared__ __align__(16) unsigned char seq_smem[];
+  constexpr int KI = 4, Bp = 8;
+  const int H = a.H, B = a.B;
+  float* hb = reinterpret_cast<float*>(seq_smem);                               // [2][H][8]
+  uint64_t* hbar = reinterpret_cast<uint64_t*>(seq_smem + 2 * (size_t)H * Bp * 4);
+  unsigned rank, csize;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+  const int tid = threadIdx.x, s = tid & 31, jl = tid >> 5;
+  const int j0 = (int)rank * Hc;
+  const int nj = H - j0 < Hc ? (H - j0 > 0 ? H - j0 : 0) : Hc;
+  const bool active = jl < nj;  // per warp
+  const int j = j0 + jl;
+  for (int e = tid; e < H * Bp; e += blockDim.x) {
+    const int k = e >> 3, c = e & 7;
+    hb[e] = c < B ? a.h0[(size_t)c * H + k] : 0.f;
+    hb[(size_t)H * Bp + e] = 0.f;
+  }
+  if (tid == 0) {
+    const uint32_t b0 = (uint32_t)__cvta_generic_to_shared(hbar);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b0));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b0 + 8));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  float w[4][KI];
+  const size_t HH = (size_t)H * H;
+#pragma unroll
+  for (int i = 0; i < KI; ++i) {
+    const int k = i * 32 + s;
+    const bool in = active && k < H;
+    const size_t at = in ? (size_t)k * H + j : 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) w[g][i] = in ? __ldg(a.Wh + g * HH + at) : 0.f;
+  }
+  const bool col = active && s < B;  // this lane finishes column s of unit j
+  float cst = col ? a.c0[(size_t)s * H + j] : 0.f;
+  float bi = 0.f, bf = 0.f, bg = 0.f, bo = 0.f;
+  if (col) { bi = a.bias[j]; bf = a.bias[H + j]; bg = a.bias[2 * H + j]; bo = a.bias[3 * H + j]; }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  const uint32_t bar_local = (uint32_t)__cvta_generic_to_shared(hbar);
+  const uint32_t hb_local = (uint32_t)__cvta_generic_to_shared(hb);
+  const uint32_t step_bytes = (uint32_t)H * (uint32_t)B * 4u;
+  bool alive = true;
+  for (int t = 0; t < a.S && alive; ++t) {
+    const float* hcur = hb + (size_t)(t & 1) * H * Bp;
+    const size_t nb = (size_t)t * B;
+    if (tid == 0 && t + 1 < a.S)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_local + 8u * ((t + 1) & 1)), "r"(step_bytes)
+                   : "memory");
+    float4 xp = make_float4(0.f, 0.f, 0.f, 0.f);
+    float mk = 0.f;
+    if (col) {
+      xp = reinterpret_cast<const float4*>(a.xp)[(nb + s) * H + j];
+      mk = (float)a.mask[nb + s];
+    }
+    if (active && t > 0) {
+      const uint32_t bar = bar_local + 8u * (t & 1), parity = (uint32_t)((t - 1) >> 1) & 1u;
+      const long long t0 = clock64();
+      for (int spins = 0;; ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) break;
+        if ((spins & 63) == 63 && clock64() - t0 > 400000000LL) {
+          if (a.err) atomicExch(a.err, 88);
+          alive = false;
+          break;
+        }
+      }
+      alive = __all_sync(0xffffffffu, alive);  // a warp gives up as a whole
+    }
+    if (active && alive) {
+      float acc[4][8];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[g][c] = 0.f;
+#pragma unroll
+      for (int i = 0; i < KI; ++i) {
+        const int k = i * 32 + s;
+        if (k < H) {
+          const float4* h4 = reinterpret_cast<const float4*>(hcur + (size_t)k * Bp);
+          const float4 ha = h4[0], hc = h4[1];
+          const float hv[8] = {ha.x, ha.y, ha.z, ha.w, hc.x, hc.y, hc.z, hc.w};
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[g][c] = fmaf(w[g][i], hv[c], acc[g][c]);
+        }
+      }
+      // butterfly over the warp: value index g * 8 + c; every round a lane keeps the half selected by one bit of its id
+      float v16[16], v8[8], v4[4], v2[2], v1;
+      {
+        const bool up = (s & 16) != 0;
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const float lo = acc[x >> 3][x & 7], hi = acc[2 + (x >> 3)][x & 7];
+          v16[x] = (up ? hi : lo) + __shfl_xor_sync(0xffffffffu, up ? lo : hi, 16);
+        }
+      }
+      {
+        const bool up = (s & 8) != 0;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) v8[x] = (up ? v16[8 + x] : v16[x]) + __shfl_xor_sync(0xffffffffu, up ? v16[x] : v16[8 + x], 8);
+      }
+      {
+        const bool up = (s & 4) != 0;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) v4[x] = (up ? v8[4 + x] : v8[x]) + __shfl_xor_sync(0xffffffffu, up ? v8[x] : v8[4 + x], 4);
+      }
+      {
+        const bool up = (s & 2) != 0;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) v2[x] = (up ? v4[2 + x] : v4[x]) + __shfl_xor_sync(0xffffffffu, up ? v4[x] : v4[2 + x], 2);
+      }
+      {
+        const bool up = (s & 1) != 0;
+        v1 = (up ? v2[1] : v2[0]) + __shfl_xor_sync(0xffffffffu, up ? v2[0] : v2[1], 1);
+      }
+      // lane s now holds gate s >> 3 of column s & 7; lanes 0..7 collect their column's four gates
+      const int c8 = s & 7;
+      const float si = __shfl_sync(0xffffffffu, v1, c8), sf = __shfl_sync(0xffffffffu, v1, 8 + c8);
+      const float sg = __shfl_sync(0xffffffffu, v1, 16 + c8), so = __shfl_sync(0xffffffffu, v1, 24 + c8);
+      if (col) {
+        const float gi = sigmoidf_acc(si + xp.x + bi);
+        const float gf = sigmoidf_acc(sf + xp.y + bf);
+        const float gg = tanhf(sg + xp.z + bg);
+        const float go = sigmoidf_acc(so + xp.w + bo);
+        const float cn = gf * cst + gi * gg;
+        const float hn = go * tanhf(cn) * mk;
+        cst = cn * mk;
+        if (t + 1 < a.S) {
+          const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + s) * 4);
+          const uint32_t boff = 8u * ((t + 1) & 1);
+#pragma unroll
+          for (unsigned q = 0; q < 8; ++q) {
+            if (q < csize) {
+              uint32_t ra, rb;
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(hb_local + off), "r"(q));
+              asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(bar_local + boff), "r"(q));
+              asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(ra),
+                           "r"(__float_as_uint(hn)), "r"(rb)
+                           : "memory");
+            }
+          }
+        }
+        const size_t n = nb + s;
+        a.h_seq[n * H + j] = hn;
+        seq_store_op(a, n, j, hn);
+      }
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (col) a.c_out[(size_t)s * H + j] = cst;
 }
 
 namespace {
@@ -1313,7 +1551,7 @@ bool seq_plan(int H, int B, SeqPlan* p) {
       if (force_cpt && CPT != force_cpt) continue;
       const int CG = (B + CPT - 1) / CPT;
       const int threads = (Hc * CG + 31) / 32 * 32;
-      const size_t smem = (size_t)H * Hc * 16 + 2 * (size_t)H * CG * CPT * 4;
+      const size_t smem = (size_t)H * Hc * 16 + (2 * (size_t)H * CG * CPT * 4 + 15) / 16 * 16 + 16;
       if (threads <= (CPT >= 4 ? 256 : 1024) && smem <= 200 * 1024) {
         *p = SeqPlan{C, Hc, CG, CPT, threads, smem};
         return true;
@@ -1352,6 +1590,11 @@ cudaError_t launch_seq_t(const SeqArgs& a, const SeqPlan& pl, cudaStream_t st) {
 }
 }  // namespace
 
+// the register-weight variant: 8 columns at most, 8 CTAs of at most 16 units (one warp each), 4 k values per lane
+static bool seq_reg_fits(int H, int B) {
+  static const bool off = std::getenv("ZRNN_SEQ_NO_REG") != nullptr;
+  return !off && B <= 8 && H >= 64 && H <= 128;
+}
 bool lstm_seq_resident_supported(int H, int B) {
   SeqPlan pl;
   return seq_plan(H, B, &pl);
@@ -1365,6 +1608,24 @@ cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st) {
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  if (seq_reg_fits(a.H, a.B)) {
+    const int Hc = (a.H + 7) / 8;
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(8);
+    cfg.blockDim = dim3(32 * Hc);
+    cfg.dynamicSmemBytes = 2 * (size_t)a.H * 8 * 4 + 16;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 8;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, lstm_seq_reg_kernel, a, Hc);
+  }
   switch (pl.CPT) {
     case 1: return launch_seq_t<1>(a, pl, st);
     case 2: return launch_seq_t<2>(a, pl, st);

@@ -1506,7 +1506,8 @@ static int run_stack(zrnn_model* m, const std::vector<zrnn_lstm_layer*>& layers,
       std::memset(&a, 0, sizeof(a));
       a.H = g.H; a.B = B; a.S = S;
       a.Mx = Ly->Mx; a.Wh = Ly->Wh; a.bias = Ly->b;
-      if (l == 0) { a.emb = Ly->W; a.ids = ids0; a.V = Ly->V; a.err = tc_error_word(); }
+      a.err = tc_error_word();
+      if (l == 0) { a.emb = Ly->W; a.ids = ids0; a.V = Ly->V; }
       else a.x_seq = seq[l - 1].f32;
       a.mask = mask;
       a.h0 = h0[l].f32;
