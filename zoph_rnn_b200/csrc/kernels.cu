@@ -1147,34 +1147,78 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
 // resident-weight LSTM sequence kernel (small layers)
 // ------------------------------------------------------------------------------------------
 // xp[(n*H + j)*4 + g] = sum_k Mx[g][j,k] * x[k, n] for every column n = t*B + b of the sequence
-__global__ void __launch_bounds__(128) lstm_seq_xpart_kernel(const SeqArgs a) {
+// Input-side products of ALL steps: xp[n][j] = (M_i, M_f, M_g, M_o)[:, j] . x_n for every column n = (step, sentence).
+// A CTA takes 8 columns at a time (their x vectors staged in shared memory) and 128 hidden units; its 256 threads are
+// two halves of the k range, each thread accumulating 4 gates x 8 columns, so that a weight value fetched from L2 is
+// used 8 times and the loads of ten k values are in flight together (one column per CTA and one load per FMA made this
+// launch as long as the whole recurrent loop it prepares).
+constexpr int kSeqXpartMaxH = 320;
+__global__ void __launch_bounds__(256) lstm_seq_xpart_kernel(const SeqArgs a) {
+  __shared__ __align__(16) float xs[kSeqXpartMaxH * 8];
+  __shared__ __align__(16) float red[32 * 128];
   const int H = a.H, N = a.S * a.B;
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int tid = threadIdx.x, jt = tid & 127, half = tid >> 7;
+  const int j = blockIdx.x * 128 + jt;
   const size_t HH = (size_t)H * H;
-  for (int n = blockIdx.y; n < N; n += gridDim.y) {
-    const float* x;
-    if (a.x_seq) {
-      x = a.x_seq + (size_t)n * H;
-    } else {
-      int id = a.ids[n];
-      if (id < 0) id = 0;
-      if (a.V > 0 && id >= a.V) {
-        id = 0;
-        if (a.err && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(a.err, kErrBadTokenId);
+  const int k_lo = half ? H / 2 : 0, k_hi = half ? H : H / 2;
+  for (int n0 = blockIdx.y * 8; n0 < N; n0 += gridDim.y * 8) {
+    __syncthreads();  // the previous group's xs and red are free
+    for (int c = 0; c < 8; ++c) {
+      const int n = n0 + c;
+      const float* x = nullptr;
+      if (n < N) {
+        if (a.x_seq) {
+          x = a.x_seq + (size_t)n * H;
+        } else {
+          int id = a.ids[n];
+          if (id < 0) id = 0;
+          if (a.V > 0 && id >= a.V) {
+            id = 0;
+            if (a.err && tid == 0 && blockIdx.x == 0) atomicExch(a.err, kErrBadTokenId);
+          }
+          x = a.emb + (size_t)id * H;
+        }
       }
-      x = a.emb + (size_t)id * H;
+      for (int k = tid; k < H; k += 256) xs[k * 8 + c] = x ? __ldg(x + k) : 0.f;
     }
+    __syncthreads();
+    float acc[4][8];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[g][c] = 0.f;
     if (j < H) {
-      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
-      for (int k = 0; k < H; ++k) {
-        const float xv = __ldg(x + k);
+#pragma unroll 10
+      for (int k = k_lo; k < k_hi; ++k) {
         const size_t at = (size_t)k * H + j;
-        acc0 = fmaf(__ldg(a.Mx + at), xv, acc0);
-        acc1 = fmaf(__ldg(a.Mx + HH + at), xv, acc1);
-        acc2 = fmaf(__ldg(a.Mx + 2 * HH + at), xv, acc2);
-        acc3 = fmaf(__ldg(a.Mx + 3 * HH + at), xv, acc3);
+        const float w0 = __ldg(a.Mx + at), w1 = __ldg(a.Mx + HH + at), w2 = __ldg(a.Mx + 2 * HH + at), w3 = __ldg(a.Mx + 3 * HH + at);
+        const float4 xa = *reinterpret_cast<const float4*>(xs + k * 8), xb = *reinterpret_cast<const float4*>(xs + k * 8 + 4);
+        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          acc[0][c] = fmaf(w0, xv[c], acc[0][c]);
+          acc[1][c] = fmaf(w1, xv[c], acc[1][c]);
+          acc[2][c] = fmaf(w2, xv[c], acc[2][c]);
+          acc[3][c] = fmaf(w3, xv[c], acc[3][c]);
+        }
       }
-      reinterpret_cast<float4*>(a.xp)[(size_t)n * H + j] = make_float4(acc0, acc1, acc2, acc3);
+    }
+    if (half == 1) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) red[(g * 8 + c) * 128 + jt] = acc[g][c];
+    }
+    __syncthreads();
+    if (half == 0 && j < H) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int n = n0 + c;
+        if (n < N)
+          reinterpret_cast<float4*>(a.xp)[(size_t)n * H + j] =
+              make_float4(acc[0][c] + red[(0 * 8 + c) * 128 + jt], acc[1][c] + red[(1 * 8 + c) * 128 + jt],
+                          acc[2][c] + red[(2 * 8 + c) * 128 + jt], acc[3][c] + red[(3 * 8 + c) * 128 + jt]);
+      }
     }
   }
 }
@@ -1535,7 +1579,7 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
 namespace {
 struct SeqPlan { int C, Hc, CG, CPT, threads; size_t smem; };
 bool seq_plan(int H, int B, SeqPlan* p) {
-  if (H < 1 || B < 1 || B > 32) return false;
+  if (H < 1 || H > kSeqXpartMaxH || B < 1 || B > 32) return false;
   // A step is a chain of short dependent stages (matrix-vector product, gate math, exchange), so what pays is
   // parallelism: the largest cluster that leaves every CTA a few hidden units, and one column per thread as long as
   // the block holds that many threads (measured at H = 100, B = 8: 8 CTAs x 1 column per thread 3.7 us per step,
@@ -1602,9 +1646,10 @@ bool lstm_seq_resident_supported(int H, int B) {
 cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st) {
   SeqPlan pl;
   if (!seq_plan(a.H, a.B, &pl) || a.S < 1) return cudaErrorInvalidValue;
-  const int N = a.S * a.B;
-  dim3 grid((a.H + 127) / 128, N > 2048 ? 2048 : N);
-  lstm_seq_xpart_kernel<<<grid, 128, 0, st>>>(a);
+  const int N = a.S * a.B, groups = (N + 7) / 8;
+  if (a.H > kSeqXpartMaxH) return cudaErrorInvalidValue;
+  dim3 grid((a.H + 127) / 128, groups > 1024 ? 1024 : groups);
+  lstm_seq_xpart_kernel<<<grid, 256, 0, st>>>(a);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
