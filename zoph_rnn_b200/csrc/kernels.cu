@@ -81,6 +81,42 @@ cudaError_t launch_prep_ids(const int* raw, int n, int* nonm1, int* mask01, cuda
   return cudaGetLastError();
 }
 
+// The first launch of a scoring pass: the id preparation of up to three id arrays (-1 -> 0 and a 0/1 mask,
+// src/custom_kernels.h:9-50) and the zero fills of the start states, which were one graph node each.
+__global__ void __launch_bounds__(256) score_prologue_kernel(const PrologueArgs a) {
+  const size_t gtid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, gsz = (size_t)gridDim.x * blockDim.x;
+  for (int q = 0; q < 3; ++q) {
+    const int* raw = a.raw[q];
+    if (!raw) continue;
+    for (size_t i = gtid; i < (size_t)a.n[q]; i += gsz) {
+      const int v = raw[i];
+      a.ids[q][i] = v == -1 ? 0 : v;
+      a.mask[q][i] = v == -1 ? 0 : 1;
+    }
+  }
+  for (int z = 0; z < a.n_zero; ++z) {
+    uint4* p = reinterpret_cast<uint4*>(a.zero_ptr[z]);
+    const size_t n16 = a.zero_bytes[z] >> 4;
+    for (size_t i = gtid; i < n16; i += gsz) p[i] = make_uint4(0u, 0u, 0u, 0u);
+    // tails shorter than 16 bytes (sizes are multiples of 4)
+    const size_t done = n16 << 4, rest = (a.zero_bytes[z] - done) >> 2;
+    if (gtid < rest) reinterpret_cast<unsigned*>(reinterpret_cast<char*>(a.zero_ptr[z]) + done)[gtid] = 0u;
+  }
+}
+cudaError_t launch_score_prologue(const PrologueArgs& a, cudaStream_t st) {
+  size_t work = 0;
+  for (int q = 0; q < 3; ++q) work = a.raw[q] && (size_t)a.n[q] > work ? (size_t)a.n[q] : work;
+  for (int z = 0; z < a.n_zero; ++z) {
+    if ((reinterpret_cast<uintptr_t>(a.zero_ptr[z]) & 15) || (a.zero_bytes[z] & 3)) return cudaErrorInvalidValue;
+    work = (a.zero_bytes[z] >> 4) > work ? (a.zero_bytes[z] >> 4) : work;
+  }
+  if (work == 0) return cudaSuccess;
+  const size_t blocks = (work + 255) / 256;
+  score_prologue_kernel<<<(unsigned)(blocks > 1184 ? 1184 : blocks), 256, 0, st>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
 __global__ void fill_int_kernel(int* p, int v, size_t n) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
 }

@@ -84,6 +84,19 @@ int gemm_rows_per_tile(int gates, int tile);
 // Exact fp32 FMA arithmetic.  Replaces the per-step loop of src/model.hpp:1581-1600 / :1765-1795 over
 // LSTM_IH_Node / LSTM_HH_Node::forward_prop_GPU (src/LSTM.hpp:76-421, src/LSTM_HH.hpp:103-333) for layers without
 // feed-input.
+// one launch for the start of a scoring pass: id preparation of up to three arrays + zero fills (16-byte aligned
+// regions whose sizes are multiples of 4 bytes)
+struct PrologueArgs {
+  const int* raw[3];
+  int n[3];
+  int* ids[3];
+  int* mask[3];
+  void* zero_ptr[12];
+  size_t zero_bytes[12];
+  int n_zero;
+};
+cudaError_t launch_score_prologue(const PrologueArgs& a, cudaStream_t st);
+
 struct SeqArgs {
   int H, B, S;           // hidden size, columns, steps
   const float* Mx;       // 4 x (H x H) input matrices, gate order i,f,g,o, each column-major

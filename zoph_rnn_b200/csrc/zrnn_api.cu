@@ -1774,12 +1774,23 @@ static int score_batch_body(zrnn_model* m, const int* d_src_ids, int S_max, cons
   std::vector<float*> cst[2];
   for (int k = 0; k < 2; ++k) { cst[k].resize(L); for (int l = 0; l < L; ++l) cst[k][l] = cv.take<float>(HB); }
   std::vector<int> cur(L, 0);
-  ZR_TRY(act_zero(zero, g, B, s));
-  for (int l = 0; l < L; ++l) ZR_CUDA(cudaMemsetAsync(cst[0][l], 0, sizeof(float) * HB, s));
-  ZR_CUDA(zrnn::launch_prep_ids(d_tgt_in, (int)nT, tin_id, tin_mk, s));
-  ZR_CUDA(zrnn::launch_prep_ids(d_tgt_out, (int)nT, tout_id, tout_mk, s));
+  {
+    // one launch: the three id preparations and the zero fills of the start states
+    zrnn::PrologueArgs pa;
+    std::memset(&pa, 0, sizeof(pa));
+    pa.raw[0] = d_tgt_in; pa.n[0] = (int)nT; pa.ids[0] = tin_id; pa.mask[0] = tin_mk;
+    pa.raw[1] = d_tgt_out; pa.n[1] = (int)nT; pa.ids[1] = tout_id; pa.mask[1] = tout_mk;
+    if (!c.lm) { pa.raw[2] = d_src_ids; pa.n[2] = (int)nS; pa.ids[2] = src_id; pa.mask[2] = src_mk; }
+    auto zero_fill = [&](void* p, size_t bytes) {
+      if (p && bytes) { pa.zero_ptr[pa.n_zero] = p; pa.zero_bytes[pa.n_zero] = bytes; ++pa.n_zero; }
+    };
+    zero_fill(zero.f32, sizeof(float) * B * g.H);
+    zero_fill(zero.hi, (size_t)B * g.Kpad * eng_eb(g.eng));
+    zero_fill(zero.lo, (size_t)B * g.Kpad * eng_eb(g.eng));
+    for (int l = 0; l < L; ++l) zero_fill(cst[0][l], sizeof(float) * HB);
+    ZR_CUDA(zrnn::launch_score_prologue(pa, s));
+  }
   if (!c.lm) {
-    ZR_CUDA(zrnn::launch_prep_ids(d_src_ids, (int)nS, src_id, src_mk, s));
     ZR_CUDA(zrnn::launch_src_len(src_mk, S, B, len, off, s));
     ZR_TRY(run_encoder(m, g, src_id, src_mk, S, B, X0, zero, sseq, cst, cur, s));
     if (c.attention) ZR_TRY(zrnn_att_set_source(m->att, sseq[L - 1].f32, S, B, len, off, 1));
