@@ -1182,7 +1182,6 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st) {
 // ------------------------------------------------------------------------------------------
 // resident-weight LSTM sequence kernel (small layers)
 // ------------------------------------------------------------------------------------------
-// xp[(n*H + j)*4 + g] = sum_k Mx[g][j,k] * x[k, n] for every column n = t*B + b of the sequence
 // Input-side products of ALL steps: xp[n][j] = (M_i, M_f, M_g, M_o)[:, j] . x_n for every column n = (step, sentence).
 // A CTA takes 8 columns at a time (their x vectors staged in shared memory) and 128 hidden units; its 256 threads are
 // two halves of the k range, each thread accumulating 4 gates x 8 columns, so that a weight value fetched from L2 is
@@ -1277,10 +1276,12 @@ __device__ __forceinline__ void seq_store_op(const SeqArgs& a, size_t n, int i, 
 
 // One cluster of C CTAs per launch.  CTA r keeps Wt[k][jl] = (Wh_i, Wh_f, Wh_g, Wh_o)[j0 + jl, k] for its Hc hidden
 // units in shared memory; thread (jl, cg) owns the cell of unit j0 + jl for CPT consecutive columns.  h_{t-1} lives in
-// every CTA's shared memory (hb[buf][k][column], double-buffered); after a step each thread writes its new h values
-// into all C copies and a cluster barrier closes the step.
-// Shared memory is the bound: a thread reads its unit's four weights once per k for all of its columns, so the more
-// columns a thread owns the fewer times the weight slice is read per step (CPT = 8: once for 8 columns).
+// every CTA's shared memory (hb[buf][k][column], double-buffered); after a step each thread sends its new h values
+// into all C copies with st.async, and the bytes arriving complete the receiving copy's transaction barrier (see the
+// exchange protocol inside).
+// A thread reads its unit's four weights once per k for all of its columns, so the more columns a thread owns the
+// fewer times the weight slice is read per step (CPT = 8: once for 8 columns) - and the longer its instruction
+// stream; with few columns more threads win.
 template <int CPT>
 __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_kernel(const SeqArgs a, int Hc, int CG) {
   extern __shared__ __align__(16) unsigned char seq_smem[];
