@@ -271,6 +271,10 @@ int zrnn_model_finalize(zrnn_model* m);
  * (src/add_model_info.h:7-9); att_type_override picks local-p or global-dot when the header says the model
  * has attention (the reference has no flag for the type), D is --attention-width. */
 int zrnn_model_load_file(const char* path, int att_type_override, int D, int dtype, zrnn_model** out);
+/* The same for rank `rank` of `world` of a vocabulary-sharded group: only rows [V rank / world, V (rank+1) / world) of
+ * D and b_d stay on this GPU (every rank parses the whole file). */
+int zrnn_model_load_file_sharded(const char* path, int att_type_override, int D, int dtype, int world, int rank,
+                                 zrnn_model** out);
 int zrnn_model_get_config(zrnn_model* m, zrnn_model_config* cfg);
 /* Host-only pieces of the same loader (no device is touched).  zrnn_model_file_header reads line 1 of a model.nn
  * (header[9], zero-filled beyond the *n_header_ints integers the file carries; src/add_model_info.h:7-9) and counts

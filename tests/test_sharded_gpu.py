@@ -155,6 +155,24 @@ def test_one_rank_communicator_equals_the_plain_calls(api, oracle, dtype):
     np.testing.assert_allclose(gs, ws, rtol=1e-5, atol=1e-5)
 
 
+def test_sharded_model_from_a_weight_file(api, tmp_path):
+    """zrnn_model_load_file_sharded keeps the rank's rows of D; with one rank that is the whole model."""
+    from zoph_rnn_b200.model_file import write_model_nn
+    cfg = synth.make_cfg(2, 64, 40, 50, attention=1, feed_input=1, D=3)
+    w = synth.make_weights(cfg, seed=2, scale=0.3)
+    p = tmp_path / "model.nn"
+    write_model_nn(p, cfg, w)
+    comm = api.Communicator(None, 0, 1)
+    m = api.neuralMT_model.from_file_sharded(p, comm, att_type=1, D=3, dtype=3)
+    assert m.shard == (0, 50)
+    src, tin, tout = synth.make_s2s_batch(40, 50, 5, 3, 9, 3, 8, seed=1)
+    got, _ = m.get_error_sharded(comm, src, tin, tout)
+    want, _ = build_model(api, cfg, w, 3).get_error(src, tin, tout)
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+    with pytest.raises(api.ZrnnError):
+        api.check(api.lib().zrnn_model_load_file_sharded(str(p).encode(), 1, 3, 3, 2, 5, None))
+
+
 TWO_RANK_SCRIPT = r"""
 import os, sys, time
 import numpy as np

@@ -103,6 +103,8 @@ SIGNATURES = {
     "zrnn_model_finalize": (ctypes.c_int, [c_void_p]),
     "zrnn_model_load_file": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                             ctypes.POINTER(c_void_p)]),
+    "zrnn_model_load_file_sharded": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                    ctypes.c_int, ctypes.POINTER(c_void_p)]),
     "zrnn_model_file_header": (ctypes.c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
                                               ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "zrnn_model_file_read": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int),

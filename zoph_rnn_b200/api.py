@@ -343,6 +343,16 @@ class neuralMT_model:
         check(lib().zrnn_model_load_file(str(path).encode(), att_type, D, dtype, ctypes.byref(h)))
         return cls(_handle=h)
 
+    @classmethod
+    def from_file_sharded(cls, path, comm, att_type=ATT_LOCAL_P, D=10, dtype=F32):
+        """from_file for one rank of a vocabulary-sharded group (comm: a Communicator)."""
+        h = ctypes.c_void_p()
+        check(lib().zrnn_model_load_file_sharded(str(path).encode(), att_type, D, dtype, comm.world, comm.rank,
+                                                 ctypes.byref(h)))
+        m = cls(_handle=h)
+        m.shard = shard_range(m.cfg["V_tgt"], comm.world, comm.rank)
+        return m
+
     def tensor_spec(self):
         out = []
         for i in range(lib().zrnn_model_num_tensors(self._h)):

@@ -80,6 +80,11 @@ struct Carver {
   }
 };
 size_t aligned(size_t bytes) { return (bytes + 255) / 256 * 256; }
+// near-equal contiguous ranges of n items over `world` ranks: [n*r/world, n*(r+1)/world)
+void shard_range(long long n, int world, int r, int* lo, int* hi) {
+  *lo = (int)(n * r / world);
+  *hi = (int)(n * (r + 1) / world);
+}
 
 cudaError_t upload(float** dst, const float* src, size_t n) {
   cudaError_t e = cudaMalloc((void**)dst, n * sizeof(float));
@@ -1374,7 +1379,18 @@ int zrnn_model_finalize(zrnn_model* m) {
   return ZRNN_OK;
 }
 
+static int model_load_file_impl(const char* path, int att_type_override, int D, int dtype, int world, int rank,
+                                zrnn_model** out);
 int zrnn_model_load_file(const char* path, int att_type_override, int D, int dtype, zrnn_model** out) {
+  return model_load_file_impl(path, att_type_override, D, dtype, 1, 0, out);
+}
+int zrnn_model_load_file_sharded(const char* path, int att_type_override, int D, int dtype, int world, int rank,
+                                 zrnn_model** out) {
+  ZR_CHECK(world >= 1 && world <= ZR_SHARD_MAX && rank >= 0 && rank < world, "load_file_sharded: bad rank / world");
+  return model_load_file_impl(path, att_type_override, D, dtype, world, rank, out);
+}
+static int model_load_file_impl(const char* path, int att_type_override, int D, int dtype, int world, int rank,
+                                zrnn_model** out) {
   ZR_CHECK(path && out, "load_file: null argument");
   zrnn::ModelFileReader rd;
   zrnn::ModelFileHeader h;
@@ -1389,7 +1405,9 @@ int zrnn_model_load_file(const char* path, int att_type_override, int D, int dty
   c.D = D > 0 ? D : 10;
   c.dtype = dtype;
   zrnn_model* m = nullptr;
-  ZR_TRY(zrnn_model_create(&c, &m));
+  int lo = 0, hi = c.V_tgt;
+  if (world > 1) shard_range(c.V_tgt, world, rank, &lo, &hi);
+  ZR_TRY(model_create_impl(&c, lo, hi, &m));
   for (size_t i = 0; i < m->slots.size(); ++i) {
     m->staged[i].resize((size_t)m->slots[i].rows * m->slots[i].cols);
     m->have_host[i] = 1;
@@ -1970,11 +1988,6 @@ int comm_all_gather(zrnn_comm* c, const void* send, void* recv, size_t bytes, cu
   return ZRNN_OK;
 }
 
-// near-equal contiguous ranges of n items over `world` ranks: [n*r/world, n*(r+1)/world)
-void shard_range(long long n, int world, int r, int* lo, int* hi) {
-  *lo = (int)(n * r / world);
-  *hi = (int)(n * (r + 1) / world);
-}
 
 // first vocabulary row of every rank's shard, on the device (cached per vocabulary size)
 int comm_shard_lo(zrnn_comm* c, int V, const int** d_lo) {
