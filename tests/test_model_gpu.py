@@ -264,7 +264,8 @@ def test_f16_split_refuses_weights_outside_the_fp16_range(api):
 
 @pytest.mark.parametrize("dtype", [3, 0, 1])
 @pytest.mark.parametrize("L,H,B,T", [(1, 100, 8, 35), (2, 64, 1, 9), (2, 200, 32, 12), (3, 300, 5, 7), (1, 8, 3, 40),
-                                     (2, 36, 17, 2), (1, 100, 8, 1), (2, 128, 7, 20), (1, 121, 8, 3), (2, 100, 9, 6)])
+                                     (2, 36, 17, 2), (1, 100, 8, 1), (2, 128, 7, 20), (1, 121, 8, 3), (2, 100, 9, 6), (1, 65, 4, 6),
+                                     (1, 72, 8, 50)])
 def test_small_layers_one_launch_per_layer(api, oracle, L, H, B, T, dtype):
     """Language models whose layers fit the shared memory of a cluster run each layer's whole time loop in one launch
     (recurrent weights resident, h exchanged between the CTAs of the cluster with asynchronous stores that complete a

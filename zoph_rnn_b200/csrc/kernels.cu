@@ -1351,7 +1351,7 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
   for (int t = 0; t < a.S && alive; ++t) {
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
-    if (tid == 0 && t + 1 < a.S)
+    if (tid == 0 && nj > 0 && t + 1 < a.S)  // (a CTA without units neither waits nor is sent to: it must not arm)
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_local + 8u * ((t + 1) & 1)), "r"(step_bytes)
                    : "memory");
     float4 xp[CPT];
@@ -1417,7 +1417,7 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
           if (t + 1 < a.S) {
             const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + cb + c) * 4);
             const uint32_t boff = 8u * ((t + 1) & 1);
-            for (unsigned q = 0; q < csize; ++q)
+            for (unsigned q = 0; q < csize && (int)q * Hc < H; ++q)
               asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(hb_remote[q] + off),
                            "r"(__float_as_uint(hn)), "r"(bar_remote[q] + boff)
                            : "memory");
@@ -1465,6 +1465,10 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
   const int nj = H - j0 < Hc ? (H - j0 > 0 ? H - j0 : 0) : Hc;
   const bool active = jl < nj;  // per warp
   const int j = j0 + jl;
+  // CTAs of the cluster that own hidden units.  The others (a cluster larger than H / Hc) take no part in the
+  // exchange: nobody sends to them, and they must not arm their barriers (a thread that arrives step after step on a
+  // barrier nobody completes overflows its arrival count).
+  const unsigned n_recv = (unsigned)((H + Hc - 1) / Hc);
   for (int e = tid; e < H * Bp; e += blockDim.x) {
     const int k = e >> 3, c = e & 7;
     hb[e] = c < B ? a.h0[(size_t)c * H + k] : 0.f;
@@ -1498,7 +1502,7 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
   for (int t = 0; t < a.S && alive; ++t) {
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
-    if (tid == 0 && t + 1 < a.S)
+    if (tid == 0 && nj > 0 && t + 1 < a.S)
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_local + 8u * ((t + 1) & 1)), "r"(step_bytes)
                    : "memory");
     float4 xp = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1592,8 +1596,8 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
           const uint32_t off = (uint32_t)((((size_t)((t + 1) & 1) * H + j) * Bp + s) * 4);
           const uint32_t boff = 8u * ((t + 1) & 1);
 #pragma unroll
-          for (unsigned q = 0; q < 8; ++q) {
-            if (q < csize) {
+          for (unsigned q = 0; q < 16; ++q) {
+            if (q < n_recv) {
               uint32_t ra, rb;
               asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(hb_local + off), "r"(q));
               asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(bar_local + boff), "r"(q));
@@ -1691,20 +1695,37 @@ cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (seq_reg_fits(a.H, a.B)) {
-    const int Hc = (a.H + 7) / 8;
+    // a cluster of 16 CTAs (non-portable size) where the device schedules one, else 8: half the warps per SM
+    static int cluster_size[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = dim3(8);
-    cfg.blockDim = dim3(32 * Hc);
-    cfg.dynamicSmemBytes = 2 * (size_t)a.H * 8 * 4 + 16;
-    cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 8;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    cfg.dynamicSmemBytes = 2 * (size_t)a.H * 8 * 4 + 16;
+    cfg.stream = st;
+    if (cluster_size[dev] == 0) {
+      cluster_size[dev] = 8;
+      static const bool no16 = std::getenv("ZRNN_SEQ_NO_C16") != nullptr;
+      if (!no16 && cudaFuncSetAttribute(lstm_seq_reg_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+        const int Hc16 = (a.H + 15) / 16;
+        cfg.gridDim = dim3(16);
+        cfg.blockDim = dim3(32 * Hc16);
+        attr[0].val.clusterDim.x = 16;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, lstm_seq_reg_kernel, &cfg) == cudaSuccess && n >= 1) cluster_size[dev] = 16;
+      }
+      (void)cudaGetLastError();
+    }
+    const int C = cluster_size[dev], Hc = (a.H + C - 1) / C;
+    cfg.gridDim = dim3(C);
+    cfg.blockDim = dim3(32 * Hc);
+    attr[0].val.clusterDim.x = C;
     count_launch();
     return cudaLaunchKernelEx(&cfg, lstm_seq_reg_kernel, a, Hc);
   }
