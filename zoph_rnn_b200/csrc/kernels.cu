@@ -1191,6 +1191,9 @@ constexpr int kSeqXpartMaxH = 320;
 __global__ void __launch_bounds__(256) lstm_seq_xpart_kernel(const SeqArgs a) {
   __shared__ __align__(16) float xs[kSeqXpartMaxH * 8];
   __shared__ __align__(16) float red[32 * 128];
+  // the sequence kernel that follows may start now: its set-up (weights into registers or shared memory, barriers)
+  // needs nothing from this launch, and it waits (griddepcontrol.wait) before it reads the first product
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int H = a.H, N = a.S * a.B;
   const int tid = threadIdx.x, jt = tid & 127, half = tid >> 7;
   const int j = blockIdx.x * 128 + jt;
@@ -1348,6 +1351,7 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
   // of h_t.  The wait is bounded; a thread that gives up sets the error word and leaves (so do all others, in turn).
   const uint32_t step_bytes = (uint32_t)H * (uint32_t)B * 4u;
   bool alive = true;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the input-side products (the launch before this one) are complete
   for (int t = 0; t < a.S && alive; ++t) {
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
@@ -1457,9 +1461,8 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
   const int H = a.H, B = a.B;
   float* hb = reinterpret_cast<float*>(seq_smem);                               // [2][H][8]
   uint64_t* hbar = reinterpret_cast<uint64_t*>(seq_smem + 2 * (size_t)H * Bp * 4);
-  unsigned rank, csize;
+  unsigned rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
   const int tid = threadIdx.x, s = tid & 31, jl = tid >> 5;
   const int j0 = (int)rank * Hc;
   const int nj = H - j0 < Hc ? (H - j0 > 0 ? H - j0 : 0) : Hc;
@@ -1499,6 +1502,7 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
   const uint32_t hb_local = (uint32_t)__cvta_generic_to_shared(hb);
   const uint32_t step_bytes = (uint32_t)H * (uint32_t)B * 4u;
   bool alive = true;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the input-side products (the launch before this one) are complete
   for (int t = 0; t < a.S && alive; ++t) {
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
@@ -1663,13 +1667,15 @@ cudaError_t launch_seq_t(const SeqArgs& a, const SeqPlan& pl, cudaStream_t st) {
   cfg.blockDim = dim3(pl.threads);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = pl.C;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_pdl ? 2 : 1;
   count_launch();
   return cudaLaunchKernelEx(&cfg, lstm_seq_resident_kernel<CPT>, a, pl.Hc, pl.CG);
 }
@@ -1701,12 +1707,14 @@ cudaError_t launch_lstm_seq_resident(const SeqArgs& a, cudaStream_t st) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl ? 2 : 1;
     cfg.dynamicSmemBytes = 2 * (size_t)a.H * 8 * 4 + 16;
     cfg.stream = st;
     if (cluster_size[dev] == 0) {
