@@ -1353,6 +1353,9 @@ __global__ void __launch_bounds__(CPT >= 4 ? 256 : 1024, 1) lstm_seq_resident_ke
   bool alive = true;
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the input-side products (the launch before this one) are complete
   for (int t = 0; t < a.S && alive; ++t) {
+    // with the last step under way the next launch may be scheduled: it sets itself up beside this kernel's few CTAs
+    // and waits for this grid to complete before it touches its results
+    if (t == a.S - 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
     if (tid == 0 && nj > 0 && t + 1 < a.S)  // (a CTA without units neither waits nor is sent to: it must not arm)
@@ -1504,6 +1507,9 @@ __global__ void __launch_bounds__(512, 1) lstm_seq_reg_kernel(const SeqArgs a, i
   bool alive = true;
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the input-side products (the launch before this one) are complete
   for (int t = 0; t < a.S && alive; ++t) {
+    // with the last step under way the next launch may be scheduled: it sets itself up beside this kernel's few CTAs
+    // and waits for this grid to complete before it touches its results
+    if (t == a.S - 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const float* hcur = hb + (size_t)(t & 1) * H * Bp;
     const size_t nb = (size_t)t * B;
     if (tid == 0 && nj > 0 && t + 1 < a.S)
