@@ -502,25 +502,28 @@ cudaError_t launch_fused_gemm(const GemmArgs& a, int gates, int epi, int tile, c
 }
 
 // ------------------------------------------------------------------------------------------
-// combine per-tile softmax partials.  A CTA of 32 x 8 threads handles 32 consecutive columns: thread (cx, py) walks
-// over parts py, py + 8, ... of column cx (coalesced over cx), the 8 partial results per column meet in shared memory.
+// combine per-tile softmax partials.  A CTA of kLseCx x kLsePy = 8 x 32 threads handles 8 consecutive columns: thread
+// (cx, py) walks over parts py, py + 32, ... of column cx (a 32-byte sector per part row), the 32 partial results per
+// column meet in shared memory.  Few columns per CTA: the job is a chain of L2 round trips per thread, so what pays is
+// many threads per column and many CTAs (280 columns of configuration 1: 35 CTAs of two load batches each).
 // exp in float, accumulation and the final log in double.
 // ------------------------------------------------------------------------------------------
+constexpr int kLseCx = 8, kLsePy = 32;
 __device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, const float* __restrict__ ps,
-                                                  int n_parts, size_t N, int n, bool active, float* s_m /*[8][32]*/,
-                                                  double* s_s /*[8][32]*/, float* mx_out, double* sum_out) {
+                                                  int n_parts, size_t N, int n, bool active, float* s_m /*[kLsePy][kLseCx]*/,
+                                                  double* s_s /*[kLsePy][kLseCx]*/, float* mx_out, double* sum_out) {
   // N: distance (in floats) between two parts' rows.  One pass: every thread keeps a running (max, sum) over its
   // parts, rescaling the sum when the maximum moves, and requests four parts' values before it uses any of them (the
-  // loop is a chain of L2 round trips otherwise); the eight (max, sum) pairs of a column meet in shared memory.
-  const int cx = threadIdx.x, py = threadIdx.y;
+  // loop is a chain of L2 round trips otherwise); the kLsePy (max, sum) pairs of a column meet in shared memory.
+  const int cx = threadIdx.x, py = threadIdx.y;  // cx < kLseCx, py < kLsePy
   float mx = -INFINITY;
   double sum = 0.0;
   if (active) {
-    for (int i0 = py; i0 < n_parts; i0 += 32) {
+    for (int i0 = py; i0 < n_parts; i0 += 4 * kLsePy) {
       float m4[4], s4[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int i = i0 + 8 * u;
+        const int i = i0 + kLsePy * u;
         const bool in = i < n_parts;
         m4[u] = in ? pm[(size_t)i * N + n] : -INFINITY;
         s4[u] = in ? ps[(size_t)i * N + n] : 0.f;
@@ -538,18 +541,18 @@ __device__ __forceinline__ void lse_column_reduce(const float* __restrict__ pm, 
       }
     }
   }
-  s_m[py * 32 + cx] = mx;
-  s_s[py * 32 + cx] = sum;
+  s_m[py * kLseCx + cx] = mx;
+  s_s[py * kLseCx + cx] = sum;
   __syncthreads();
   if (py == 0) {
     float M = mx;
 #pragma unroll
-    for (int q = 1; q < 8; ++q) M = fmaxf(M, s_m[q * 32 + cx]);
+    for (int q = 1; q < kLsePy; ++q) M = fmaxf(M, s_m[q * kLseCx + cx]);
     double S = 0.0;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const float mq = s_m[q * 32 + cx];
-      if (mq != -INFINITY) S += s_s[q * 32 + cx] * (double)expf(mq - M);
+    for (int q = 0; q < kLsePy; ++q) {
+      const float mq = s_m[q * kLseCx + cx];
+      if (mq != -INFINITY) S += s_s[q * kLseCx + cx] * (double)expf(mq - M);
     }
     mx = M;
     sum = S;
@@ -561,9 +564,9 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restric
                                                            const float* __restrict__ tgt, int n_parts, int n_tgt, int N,
                                                            size_t part_stride, const int* __restrict__ mask,
                                                            float* __restrict__ logp) {
-  __shared__ float s_m[8 * 32];
-  __shared__ double s_s[8 * 32];
-  const int n = blockIdx.x * 32 + threadIdx.x;
+  __shared__ float s_m[kLsePy * kLseCx];
+  __shared__ double s_s[kLsePy * kLseCx];
+  const int n = blockIdx.x * kLseCx + threadIdx.x;
   const bool in = n < N;
   const bool active = in && !(mask && mask[n] != 1);
   float mx;
@@ -578,9 +581,9 @@ __global__ void __launch_bounds__(256) lse_combine_kernel(const float* __restric
 __global__ void __launch_bounds__(256) lse_reduce_kernel(const float* __restrict__ pm, const float* __restrict__ ps,
                                                           int n_parts, int N, float* __restrict__ out_max,
                                                           float* __restrict__ out_sum) {
-  __shared__ float s_m[8 * 32];
-  __shared__ double s_s[8 * 32];
-  const int n = blockIdx.x * 32 + threadIdx.x;
+  __shared__ float s_m[kLsePy * kLseCx];
+  __shared__ double s_s[kLsePy * kLseCx];
+  const int n = blockIdx.x * kLseCx + threadIdx.x;
   const bool in = n < N;
   float mx;
   double sum;
@@ -592,14 +595,14 @@ __global__ void __launch_bounds__(256) lse_reduce_kernel(const float* __restrict
 cudaError_t launch_lse_reduce(const float* pm, const float* ps, int n_parts, int N, float* out_max, float* out_sum,
                               cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_reduce_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, n_parts, N, out_max, out_sum);
+  lse_reduce_kernel<<<(N + kLseCx - 1) / kLseCx, dim3(kLseCx, kLsePy), 0, st>>>(pm, ps, n_parts, N, out_max, out_sum);
   count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_lse_combine_shards(const float* pm, const float* ps, const float* tgt, int G, int N, const int* mask,
                                       float* logp, cudaStream_t st, size_t shard_stride) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, G, G, N, shard_stride ? shard_stride : (size_t)N, mask,
+  lse_combine_kernel<<<(N + kLseCx - 1) / kLseCx, dim3(kLseCx, kLsePy), 0, st>>>(pm, ps, tgt, G, G, N, shard_stride ? shard_stride : (size_t)N, mask,
                                                             logp);
   count_launch();
   return cudaGetLastError();
@@ -607,7 +610,7 @@ cudaError_t launch_lse_combine_shards(const float* pm, const float* ps, const fl
 cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tgt, int n_parts, int N, const int* mask,
                                float* logp, cudaStream_t st) {
   if (N <= 0) return cudaSuccess;
-  lse_combine_kernel<<<(N + 31) / 32, dim3(32, 8), 0, st>>>(pm, ps, tgt, n_parts, 1, N, (size_t)N, mask, logp);
+  lse_combine_kernel<<<(N + kLseCx - 1) / kLseCx, dim3(kLseCx, kLsePy), 0, st>>>(pm, ps, tgt, n_parts, 1, N, (size_t)N, mask, logp);
   count_launch();
   return cudaGetLastError();
 }
