@@ -189,7 +189,7 @@ int zrnn_softmax_combine(const float* d_max, const float* d_sum, const float* d_
                          const int* d_mask01, float* d_logp_out, void* stream);
 /* get_distribution_GPU (src/softmax.hpp:514-632) fused with the per-column pre-selection of
  * decoder::expand_hypothesis_without_fsa (src/decoder.h:1197-1219): the k largest log-probabilities of
- * each of N columns, sorted descending (k <= 32), their word ids, and the log-probability of <EOF> (id 1). */
+ * each of N columns, sorted descending (k <= 33), their word ids, and the log-probability of <EOF> (id 1). */
 int zrnn_softmax_topk(zrnn_softmax* sm, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                       float* d_logp_eos, void* stream);
 int zrnn_softmax_destroy(zrnn_softmax* sm);
@@ -211,6 +211,9 @@ int zrnn_comm_unique_id(char* id128);
 /* Collective call: blocks until all `world` ranks have joined.  The calling thread's current device is the
  * rank's GPU.  world == 1 needs no id (NULL) and no NCCL: its collectives are local copies. */
 int zrnn_comm_create(const char* id128, int rank, int world, zrnn_comm** out);
+/* The same around a communicator the host already owns (an ncclComm_t passed as void*; it must come from the NCCL
+ * library this process has loaded as libnccl.so.2).  zrnn_comm_destroy leaves that communicator alone. */
+int zrnn_comm_from_nccl(void* nccl_comm, int rank, int world, zrnn_comm** out);
 int zrnn_comm_rank(const zrnn_comm* c, int* rank, int* world);
 /* d_recv receives world * bytes_per_rank bytes, rank-major. */
 int zrnn_comm_all_gather(zrnn_comm* c, const void* d_send, void* d_recv, size_t bytes_per_rank, void* stream);
@@ -230,7 +233,7 @@ int zrnn_softmax_topk_shard(zrnn_softmax* sm, const float* d_h, int N, int k, fl
                             float* d_lse_out, float* d_logp_eos, void* stream);
 /* Sharded decoding, step 2: the k best of G shards' lists (d_val / d_idx [G][N][k], d_lse / d_eos [G][N],
  * d_shard_lo[G] = first word id of every shard) under the global normaliser log sum_g exp(lse_g); word ids are
- * global, ties go to the lower id, as in zrnn_softmax_topk.  G <= 8, k <= 32. */
+ * global, ties go to the lower id, as in zrnn_softmax_topk.  G <= 8, k <= 33. */
 int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, const float* d_eos, const int* d_shard_lo,
                     int G, int N, int k, float* d_val_out, int* d_idx_out, float* d_eos_out, void* stream);
 /* Both steps with the all-gather between them (k (value, id) pairs and two floats per column and rank): what
@@ -311,7 +314,7 @@ zrnn_softmax* zrnn_model_softmax(zrnn_model* m);
  * finish_current_hypotheses, output_k_best_hypotheses (src/decoder.h:1157-1315, 672-688, 1386-1463).
  * The reference decodes one sentence at a time; results equal n_sent independent decodes.
  * src_ids: concatenated reversed source ids; src_len[n_sent]; beam (-b) is capped at floor(sqrt(V_tgt)) as in the
- * reference and must then be at most 31 (ZRNN_E_ARG beyond);
+ * reference and must then be at most 32 (ZRNN_E_ARG beyond);
  * k_best (-k n-best count); min_ratio/max_ratio (--dec-ratio); penalty (--penalty); longest_sent (-L).
  * Outputs (host): out_ids [n_sent*k_best*(longest_sent+4)] padded with -1, out_len [n_sent*k_best]
  * (0 = fewer than k hypotheses passed the length filter), out_score [n_sent*k_best]. */

@@ -33,7 +33,8 @@ def build_model(api, cfg, w, dtype, shard=None):
 
 @pytest.mark.parametrize("dtype", [3, 0, 1])
 @pytest.mark.parametrize("G", [2, 3, 8])
-@pytest.mark.parametrize("V,H,N,k", [(1003, 64, 37, 13), (20011, 128, 130, 16), (50, 64, 5, 12)])
+@pytest.mark.parametrize("V,H,N,k", [(1003, 64, 37, 13), (20011, 128, 130, 16), (50, 64, 5, 12),
+                                     (5003, 64, 20, 33)])
 def test_topk_shards_merge_to_the_unsharded_topk(api, oracle, G, dtype, V, H, N, k):
     """G shards on one GPU: zrnn_softmax_topk_shard per shard + zrnn_topk_merge against zrnn_softmax_topk of the whole
     layer (same word ids wherever the neighbours are no near-tie; values to fp32 rounding of the normaliser) and the
@@ -126,6 +127,9 @@ def test_sharded_calls_check_their_arguments(api):
     assert e.value.status == 1
     with pytest.raises(api.ZrnnError):
         api.Communicator(None, 0, 9)
+    import ctypes
+    h = ctypes.c_void_p()
+    assert api.lib().zrnn_comm_from_nccl(None, 0, 2, ctypes.byref(h)) == 1  # no communicator given
 
 
 @pytest.mark.parametrize("dtype", [3, 5, 1])

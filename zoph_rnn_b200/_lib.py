@@ -83,6 +83,7 @@ SIGNATURES = {
     "zrnn_softmax_destroy": (ctypes.c_int, [c_void_p]),
     "zrnn_comm_unique_id": (ctypes.c_int, [ctypes.c_char_p]),
     "zrnn_comm_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_void_p)]),
+    "zrnn_comm_from_nccl": (ctypes.c_int, [c_void_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(c_void_p)]),
     "zrnn_comm_rank": (ctypes.c_int, [c_void_p, c_int_p, c_int_p]),
     "zrnn_comm_all_gather": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "zrnn_comm_last_stage_ms": (ctypes.c_int, [c_void_p, c_float_p]),

@@ -618,7 +618,7 @@ cudaError_t launch_lse_combine(const float* pm, const float* ps, const float* tg
 // ------------------------------------------------------------------------------------------
 // per-column top-k of log-softmax(z): one CTA per column
 // ------------------------------------------------------------------------------------------
-#define ZR_TOPK_MAX 32
+#define ZR_TOPK_MAX 33
 #define ZR_TOPK_CAND 512
 // Two passes over the column.  Pass 1: per-thread online (max, sum exp) and per-thread maximum; the k-th largest of
 // the 256 thread maxima is a lower bound of the column's k-th largest value.  Pass 2: every element >= that bound
@@ -937,11 +937,11 @@ __global__ void __launch_bounds__(128) topk_merge_kernel(const float* __restrict
     }
     eos_out[col] = e;
   }
-  // candidate c = g * k + r lives in lane c % 32, register c / 32 (G * k <= 8 * 32 = 256)
-  float cv[8];
-  int ci[8];
+  // candidate c = g * k + r lives in lane c % 32, register c / 32 (G * k <= 8 * 33 = 264)
+  float cv[9];
+  int ci[9];
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
+  for (int q = 0; q < 9; ++q) {
     const int c = lane + 32 * q;
     cv[q] = -INFINITY;
     ci[q] = 0x7fffffff;
@@ -959,7 +959,7 @@ __global__ void __launch_bounds__(128) topk_merge_kernel(const float* __restrict
     float bv = cv[0];
     int bi = ci[0], bq = 0;
 #pragma unroll
-    for (int q = 1; q < 8; ++q)
+    for (int q = 1; q < 9; ++q)
       if (cv[q] > bv || (cv[q] == bv && ci[q] < bi)) { bv = cv[q]; bi = ci[q]; bq = q; }
     float wv = bv;
     int wi = bi;
@@ -975,7 +975,7 @@ __global__ void __launch_bounds__(128) topk_merge_kernel(const float* __restrict
     }
     if (bv == wv && bi == wi) {  // the winner's owner drops it (word ids are unique, so exactly one lane)
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
+      for (int q = 0; q < 9; ++q)
         if (q == bq) { cv[q] = -INFINITY; ci[q] = 0x7fffffff; }
     }
   }
@@ -984,7 +984,7 @@ cudaError_t launch_topk_merge(const float* val, const int* idx, const float* lse
                               int G, int N, int k, float* val_out, int* idx_out, float* eos_out, cudaStream_t st,
                               size_t cand_stride, size_t col_stride) {
   if (N <= 0) return cudaSuccess;
-  if (k < 1 || k > ZR_TOPK_MAX || G < 1 || G * k > 256) return cudaErrorInvalidValue;
+  if (k < 1 || k > ZR_TOPK_MAX || G < 1 || G * k > 288) return cudaErrorInvalidValue;
   if (!cand_stride) cand_stride = (size_t)N * k;
   if (!col_stride) col_stride = (size_t)N;
   topk_merge_kernel<<<(N + 3) / 4, 128, 0, st>>>(val, idx, lse, eos, shard_lo, G, N, k, cand_stride, col_stride, val_out,
@@ -1872,13 +1872,13 @@ __device__ void beam_insert_hyp(const BeamArgs& a, int s, const int* row, int la
   sc[pos] = score;
 }
 
-// NL: candidates per lane of the selecting warp: 8 covers beam * (beam + 1) <= 256 (beam <= 15), 32 covers beam <= 31
+// NL: candidates per lane of the selecting warp: 8 covers beam * (beam + 1) <= 256 (beam <= 15), 33 covers beam <= 32
 template <int NL>
 __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
   __shared__ float cv[32 * NL];
   __shared__ int ci[32 * NL];
-  __shared__ int n_chg[32], n_cur[32];
-  __shared__ float n_sc[32];
+  __shared__ int n_chg[ZR_BEAM_MAX], n_cur[ZR_BEAM_MAX];
+  __shared__ float n_sc[ZR_BEAM_MAX];
   const int s = blockIdx.x, tid = threadIdx.x, beam = a.beam, kc = a.k_cand, t = a.step;
   const int base = s * beam;
   const int max_steps = a.max_steps[s];
@@ -1989,9 +1989,9 @@ __global__ void __launch_bounds__(256) beam_step_kernel(const BeamArgs a) {
 }
 cudaError_t launch_beam_step(const BeamArgs& a, cudaStream_t st) {
   if (a.n_sent <= 0) return cudaSuccess;
-  if (a.beam < 1 || a.beam > ZR_BEAM_MAX || a.k_cand > ZR_BEAM_MAX + 1 || a.beam * a.k_cand > 1024) return cudaErrorInvalidValue;
+  if (a.beam < 1 || a.beam > ZR_BEAM_MAX || a.k_cand > ZR_BEAM_MAX + 1 || a.beam * a.k_cand > 32 * 33) return cudaErrorInvalidValue;
   if (a.beam * a.k_cand <= 256) beam_step_kernel<8><<<a.n_sent, 256, 0, st>>>(a);
-  else beam_step_kernel<32><<<a.n_sent, 256, 0, st>>>(a);
+  else beam_step_kernel<33><<<a.n_sent, 256, 0, st>>>(a);
   count_launch();
   return cudaGetLastError();
 }

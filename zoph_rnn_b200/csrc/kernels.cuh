@@ -147,7 +147,7 @@ cudaError_t launch_topk_logp(const float* logits, int V, int N, int k, float* va
                              cudaStream_t st, const float* part_max = nullptr, const float* part_sum = nullptr,
                              int n_parts = 0, int part_width = 0, int eos_row = 1, float* lse_out = nullptr);
 // Merge of G vocabulary shards' top-k lists (each [G][N][k], lse / eos [G][N], shard_lo[G] on the device) into the k
-// best of the whole vocabulary per column, as log-probabilities under the global normaliser; G * k <= 128.
+// best of the whole vocabulary per column, as log-probabilities under the global normaliser; G * k <= 288.
 // cand_stride / col_stride (4-byte words, 0 = dense) are the distances between two shards' val / idx and lse / eos
 // blocks, so the lists can be read straight out of an all-gather's receive buffer.
 cudaError_t launch_topk_merge(const float* val, const int* idx, const float* lse, const float* eos, const int* shard_lo,
@@ -194,7 +194,7 @@ cudaError_t launch_att_global(const AttArgs& a, cudaStream_t st);
 // distribution of ensemble_factory::ensembles_models (src/ensemble_factory.hpp:768-795).  The renormalisation the
 // reference applies after averaging is the log-softmax the top-k kernel performs on `out`.
 #define ZR_ENSEMBLE_MAX 8
-#define ZR_BEAM_MAX 31  // beam width (every hypothesis proposes beam + 1 <= 32 candidates per step)
+#define ZR_BEAM_MAX 32  // beam width (every hypothesis proposes beam + 1 <= 33 candidates per step)
 #define ZR_SHARD_MAX 8  // vocabulary shards (ranks) a top-k merge takes
 struct EnsembleArgs {
   const float* logits[ZR_ENSEMBLE_MAX];  // each V x N, column-major

@@ -1219,7 +1219,7 @@ int zrnn_softmax_score(zrnn_softmax* S, const float* d_h, const int* d_targets, 
 int zrnn_softmax_topk(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                       float* d_logp_eos, void* stream) {
   ZR_CHECK(S && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk: bad arguments");
-  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk: k must be in [1,32]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk: k must be in [1,33]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk: weights not loaded");
   ZR_CHECK(S->lo == 0 && S->hi == S->V, "softmax_topk: layer is vocabulary-sharded");
   if (N == 0) return ZRNN_OK;
@@ -1917,6 +1917,7 @@ int zrnn_beam_decode_batch_device(zrnn_model* m, const int* d_src, const int* h_
 // ------------------------------------------------------------------------------------------
 struct zrnn_comm {
   ncclComm_t comm = nullptr;
+  bool owned = true;  // false: the communicator belongs to the host (zrnn_comm_from_nccl)
   int rank = 0, world = 1;
   DevBuf send, recv, aux, lo_buf;  // staging for the all-gathers; first vocabulary row of every rank
   int lo_V = -1;                   // vocabulary size lo_buf was computed for
@@ -2186,7 +2187,7 @@ int beam_decode_core(zrnn_model* const* models, int K, const int* const* d_src, 
   if (n_sent == 0) return ZRNN_OK;
   const int cap = (int)std::sqrt((double)V);  // src/ensemble_factory.hpp:19-21
   if (beam > cap) beam = cap;
-  ZR_CHECK(beam >= 1 && beam <= ZR_BEAM_MAX, "beam_decode: beam must be in [1,31] after the sqrt(V) cap");
+  ZR_CHECK(beam >= 1 && beam <= ZR_BEAM_MAX, "beam_decode: beam must be in [1,32] after the sqrt(V) cap");
   const int kc = beam + 1;
   ZR_CHECK(kc <= V, "beam_decode: vocabulary smaller than beam+1");
   const int Lmax = longest_sent + 4;  // src/main.cu:408
@@ -2401,6 +2402,19 @@ int zrnn_comm_create(const char* id128, int rank, int world, zrnn_comm** out) {
   *out = c;
   return ZRNN_OK;
 }
+int zrnn_comm_from_nccl(void* nccl_comm, int rank, int world, zrnn_comm** out) {
+  ZR_CHECK(out && nccl_comm && world >= 2 && rank >= 0 && rank < world, "comm_from_nccl: bad arguments");
+  ZR_CHECK(world <= ZR_SHARD_MAX, "comm_from_nccl: at most 8 ranks");
+  ZR_TRY(check_device());
+  if (!nccl_api()->ok) return fail(ZRNN_E_NCCL, "the NCCL library (libnccl.so.2) could not be loaded");
+  auto* c = new zrnn_comm();
+  c->comm = (ncclComm_t)nccl_comm;
+  c->owned = false;
+  c->rank = rank;
+  c->world = world;
+  *out = c;
+  return ZRNN_OK;
+}
 int zrnn_comm_rank(const zrnn_comm* c, int* rank, int* world) {
   ZR_CHECK(c, "comm_rank: null argument");
   if (rank) *rank = c->rank;
@@ -2419,7 +2433,7 @@ int zrnn_comm_last_stage_ms(const zrnn_comm* c, float* ms5) {
 }
 int zrnn_comm_destroy(zrnn_comm* c) {
   if (!c) return ZRNN_OK;
-  if (c->comm) nccl_api()->CommDestroy(c->comm);
+  if (c->comm && c->owned) nccl_api()->CommDestroy(c->comm);
   delete c;
   return ZRNN_OK;
 }
@@ -2432,7 +2446,7 @@ int zrnn_shard_range(int V, int world, int rank, int* lo, int* hi) {
 int zrnn_softmax_topk_shard(zrnn_softmax* S, const float* d_h, int N, int k, float* d_logp_out, int* d_idx_out,
                             float* d_lse_out, float* d_logp_eos, void* stream) {
   ZR_CHECK(S && d_h && d_logp_out && d_idx_out && d_lse_out && N >= 0, "softmax_topk_shard: bad arguments");
-  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_shard: k must be in [1,32]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_shard: k must be in [1,33]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_shard: weights not loaded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -2444,7 +2458,7 @@ int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, co
                     int G, int N, int k, float* d_val_out, int* d_idx_out, float* d_eos_out, void* stream) {
   ZR_CHECK(d_val && d_idx && d_lse && d_shard_lo && d_val_out && d_idx_out && N >= 0, "topk_merge: bad arguments");
   ZR_CHECK(!d_eos_out || d_eos, "topk_merge: an <EOF> output needs the shards' <EOF> values");
-  ZR_CHECK(G >= 1 && G <= ZR_SHARD_MAX && k >= 1 && k <= ZR_BEAM_MAX + 1, "topk_merge: 1..8 shards of 1..32 candidates");
+  ZR_CHECK(G >= 1 && G <= ZR_SHARD_MAX && k >= 1 && k <= ZR_BEAM_MAX + 1, "topk_merge: 1..8 shards of 1..33 candidates");
   if (N == 0) return ZRNN_OK;
   ZR_CUDA(zrnn::launch_topk_merge(d_val, d_idx, d_lse, d_eos, d_shard_lo, G, N, k, d_val_out, d_idx_out, d_eos_out,
                                   (cudaStream_t)stream));
@@ -2453,7 +2467,7 @@ int zrnn_topk_merge(const float* d_val, const int* d_idx, const float* d_lse, co
 int zrnn_softmax_topk_sharded(zrnn_softmax* S, zrnn_comm* c, const float* d_h, int N, int k, float* d_logp_out,
                               int* d_idx_out, float* d_logp_eos, void* stream) {
   ZR_CHECK(S && c && d_h && d_logp_out && d_idx_out && N >= 0, "softmax_topk_sharded: bad arguments");
-  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_sharded: k must be in [1,32]");
+  ZR_CHECK(k >= 1 && k <= ZR_BEAM_MAX + 1, "softmax_topk_sharded: k must be in [1,33]");
   if (!S->loaded) return fail(ZRNN_E_STATE, "softmax_topk_sharded: weights not loaded");
   if (N == 0) return ZRNN_OK;
   cudaStream_t st = (cudaStream_t)stream;
